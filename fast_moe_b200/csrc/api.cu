@@ -1,0 +1,230 @@
+// C ABI glue: error reporting, the device status word, and the operator-level entry points that
+// map the reference's operator arguments onto the grouped GEMM / combine / SiLU launchers.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace fmoe {
+
+long long g_misc_launches = 0;
+int launch_silu(const void* in, int dtype, long long ldi, void* out, long long ldo, long long rows, int cols,
+                cudaStream_t st);
+
+namespace {
+thread_local char g_err[512] = "";
+// First problem a kernel met on this device since the last reset (FMOE_DEV_*).
+__device__ int g_dev_status = 0;
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(FMOE_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+}
+
+int* device_status_ptr(int* err) {
+  // One address per device; a process drives one device in practice, but look it up per device
+  // to stay correct when it does not.
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = cuda_fail(e, "cudaGetDevice");
+    return nullptr;
+  }
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_dev_status);
+    if (e != cudaSuccess) {
+      *err = cuda_fail(e, "cudaGetSymbolAddress(status word)");
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+namespace {
+
+// Fills the weight part of a GemmDesc; rejects layouts the tensor-core path cannot read.
+int set_weight(GemmDesc& g, const char* op, int64_t w_se, int64_t w_sk, int64_t w_sn) {
+  if (g.K > 1 && w_sk != 1) {
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "%s: weight must have K contiguous (stride_k == 1, got %lld); pass the [E, N, K]-stored view",
+                op, (long long)w_sk);
+  }
+  g.b_se = w_se;
+  g.b_sn = w_sn;
+  return FMOE_OK;
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_version(void) { return 100; }
+
+extern "C" const char* fmoe_last_error(void) { return g_err; }
+
+extern "C" long long fmoe_kernel_launch_count(void) { return g_misc_launches + grouped_gemm_launch_count(); }
+
+extern "C" int fmoe_device_status(int* status_out, int reset, void* stream) {
+  FMOE_REQUIRE(status_out != nullptr, "device_status: status_out is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int err = 0;
+  int* p = device_status_ptr(&err);
+  if (!p) return err;
+  FMOE_CUDA_OK(cudaMemcpyAsync(status_out, p, sizeof(int), cudaMemcpyDeviceToHost, st));
+  if (reset) FMOE_CUDA_OK(cudaMemsetAsync(p, 0, sizeof(int), st));
+  FMOE_CUDA_OK(cudaStreamSynchronize(st));
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_index_select_jagged_bmm(const int64_t* offsets, const int64_t* index, int index_div,
+                                            int64_t total_rows, const void* jagged, int dtype, int64_t L,
+                                            int64_t ldj, const void* weight, int64_t w_se, int64_t w_sk,
+                                            int64_t w_sn, const void* bias, int64_t bias_se, int E, int K, int N,
+                                            int epilogue, void* out, int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "index_select_jagged_bmm: dtype must be bf16 or f32");
+  FMOE_REQUIRE(epilogue == FMOE_EPI_NONE || epilogue == FMOE_EPI_SILU, "index_select_jagged_bmm: bad epilogue %d",
+               epilogue);
+  FMOE_REQUIRE(index != nullptr && index_div >= 1, "index_select_jagged_bmm: index is required");
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = dtype;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = jagged; g.a_rows = L; g.lda = ldj;
+  g.index = index; g.index_div = index_div;
+  g.b0 = weight;
+  int rc = set_weight(g, "index_select_jagged_bmm", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.bias0 = bias; g.bias_se = bias_se;
+  g.epilogue = epilogue;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fmoe_index_select_jagged_bmm_swiglu(const int64_t* offsets, const int64_t* index, int index_div,
+                                                   int64_t total_rows, const void* jagged, int dtype, int64_t L,
+                                                   int64_t ldj, const void* weight, const void* weight_p,
+                                                   int64_t w_se, int64_t w_sk, int64_t w_sn, const void* bias,
+                                                   const void* bias_p, int64_t bias_se, int E, int K, int N,
+                                                   void* out, int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "index_select_jagged_bmm_swiglu: dtype must be bf16 or f32");
+  FMOE_REQUIRE(index != nullptr && index_div >= 1, "index_select_jagged_bmm_swiglu: index is required");
+  FMOE_REQUIRE(weight_p != nullptr, "index_select_jagged_bmm_swiglu: weight_p is NULL");
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = dtype;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = jagged; g.a_rows = L; g.lda = ldj;
+  g.index = index; g.index_div = index_div;
+  g.b0 = weight; g.b1 = weight_p;
+  int rc = set_weight(g, "index_select_jagged_bmm_swiglu", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.bias0 = bias; g.bias1 = bias_p; g.bias_se = bias_se;
+  g.epilogue = FMOE_EPI_SWIGLU;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fmoe_index_select_jagged_bmm_fp8(const int64_t* offsets, const int64_t* index, int index_div,
+                                                int64_t total_rows, const void* jagged_q, const float* jagged_scale,
+                                                int64_t L, int64_t ldj, const void* weight_q,
+                                                const float* weight_scale, const void* weight_p_q,
+                                                const float* weight_p_scale, int64_t w_se, int64_t w_sk,
+                                                int64_t w_sn, int64_t ws_se, const void* bias, const void* bias_p,
+                                                int64_t bias_se, int E, int K, int N, int epilogue, void* out,
+                                                int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(index != nullptr && index_div >= 1, "index_select_jagged_bmm_fp8: index is required");
+  FMOE_REQUIRE(jagged_scale && weight_scale, "index_select_jagged_bmm_fp8: scales are required");
+  FMOE_REQUIRE((weight_p_q == nullptr) == (weight_p_scale == nullptr),
+               "index_select_jagged_bmm_fp8: weight_p_q and weight_p_scale go together");
+  FMOE_REQUIRE((epilogue == FMOE_EPI_SWIGLU) == (weight_p_q != nullptr),
+               "index_select_jagged_bmm_fp8: SwiGLU epilogue if and only if weight_p_q is given");
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = FMOE_E4M3;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = jagged_q; g.a_rows = L; g.lda = ldj;
+  g.index = index; g.index_div = index_div;
+  g.b0 = weight_q; g.b1 = weight_p_q;
+  int rc = set_weight(g, "index_select_jagged_bmm_fp8", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.bias0 = bias; g.bias1 = bias_p; g.bias_se = bias_se;
+  g.a_scale = jagged_scale; g.b0_scale = weight_scale; g.b1_scale = weight_p_scale; g.bscale_se = ws_se;
+  g.epilogue = epilogue;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype,
+                                    int64_t ldj, const float* jagged_scale, const void* weight,
+                                    const float* weight_scale, int64_t w_se, int64_t w_sk, int64_t w_sn,
+                                    int64_t ws_se, const void* bias, int64_t bias_se, int E, int K, int N,
+                                    int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo,
+                                    void* stream) {
+  const bool fp8 = dtype == FMOE_E4M3;
+  FMOE_REQUIRE(fp8 || dtype == FMOE_BF16 || dtype == FMOE_F32, "silu_jagged_bmm: bad dtype %d", dtype);
+  FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm: FP8 operands need their scales");
+  FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm: has_silu is not available on FP8 input (quantise silu(x) instead)");
+  FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm: has_silu needs act_scratch");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const void* a = jagged;
+  int64_t lda = ldj;
+  if (has_silu && total_rows > 0) {
+    int rc = launch_silu(jagged, dtype, ldj, act_scratch, K, total_rows, K, st);
+    if (rc != FMOE_OK) return rc;
+    a = act_scratch;
+    lda = K;
+  }
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = dtype;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = a; g.a_rows = total_rows; g.lda = lda;
+  g.b0 = weight;
+  int rc = set_weight(g, "silu_jagged_bmm", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.bias0 = bias; g.bias_se = bias_se;
+  g.a_scale = jagged_scale; g.b0_scale = weight_scale; g.bscale_se = ws_se;
+  g.epilogue = FMOE_EPI_NONE;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, st);
+}
+
+extern "C" int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t total_rows, const void* jagged,
+                                            int dtype, int64_t ldj, const void* weight, int64_t w_se, int64_t w_sk,
+                                            int64_t w_sn, const void* bias, int64_t bias_se,
+                                            const int64_t* reverse_index, const void* gating_scores, int g_dtype,
+                                            const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
+                                            int has_silu, void* act_scratch, void* bmm_scratch, void* out,
+                                            int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(bmm_scratch != nullptr, "silu_jagged_bmm_combine: bmm_scratch is NULL");
+  FMOE_REQUIRE(total_rows == L * k, "silu_jagged_bmm_combine: rows %lld != L*k = %lld", (long long)total_rows,
+               (long long)(L * k));
+  // the GEMM result has the activation type, as F.linear returns it
+  const int bmm_dtype = dtype;
+  int rc = fmoe_silu_jagged_bmm(offsets, total_rows, jagged, dtype, ldj, nullptr, weight, nullptr, w_se, w_sk, w_sn,
+                                0, bias, bias_se, E, K, N, has_silu, act_scratch, bmm_scratch, bmm_dtype, N, stream);
+  if (rc != FMOE_OK) return rc;
+  return fmoe_mul_merge_k_add(reverse_index, bmm_scratch, bmm_dtype, N, gating_scores, g_dtype, gates_index, L, k, N,
+                              out, out_dtype, ldo, stream);
+}

@@ -1,0 +1,190 @@
+// Gate-weighted k-way combine (mul_merge_k_add) and the elementwise SiLU pass.
+//
+// out[t, :] = sum_j value[p_j, :] * weight[weight_index[p_j]],  p_j = reverse_index[t, j]
+//
+// Replaces pytorch_mul_merge_k_add (kernels/pytorch/moe.py:14-37: gather of the gate weights,
+// mul, fp32 upcast, index_add, cast = about five passes over [L*k, D]) and the Triton gather form
+// _mul_merge_k_add_fwd (kernels/triton/triton_moe.py:864-914) with one pass: HBM-bound, reads
+// L*k*D values once and writes L*D. The sum runs in fp32 in ascending row order, which is the
+// order index_add visits the rows of one token, so the result is reproducible bit for bit.
+#include "common.cuh"
+
+namespace fmoe {
+
+extern long long g_misc_launches;
+
+namespace {
+
+constexpr int kCombineThreads = 256;
+
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <typename VT, typename WT, typename OT, int VEC>
+__global__ void __launch_bounds__(kCombineThreads)
+combine_kernel(const long long* __restrict__ reverse_index, const VT* __restrict__ value, long long ldv,
+               const WT* __restrict__ weight, const long long* __restrict__ weight_index, long long L, int k, int D,
+               OT* __restrict__ out, long long ldo, long long n_rows, int* status) {
+  // both bf16: Tensor.mul rounds the product to bf16 before the fp32 accumulation
+  constexpr bool kRoundProduct = (sizeof(VT) == 2 && sizeof(WT) == 2);
+  const int vec_per_row = (D + VEC - 1) / VEC;
+  const long long total = L * vec_per_row;
+  for (long long w = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; w < total;
+       w += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = w / vec_per_row;
+    const int c0 = static_cast<int>(w - t * vec_per_row) * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const long long p = reverse_index[t * k + j];
+      if (p < 0 || p >= n_rows) {
+        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+        continue;
+      }
+      float g = 1.f;
+      if (weight != nullptr) {
+        long long wi = weight_index ? weight_index[p] : p;
+        if (wi < 0 || wi >= n_rows) {
+          atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+          continue;
+        }
+        g = ldf(weight + wi);
+      }
+      const VT* src = value + p * ldv + c0;
+      float v[VEC];
+      if (c0 + VEC <= D) {
+        if constexpr (sizeof(VT) * VEC == 16) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(src);
+          const VT* e = reinterpret_cast<const VT*>(&raw);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[i] = ldf(e + i);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[i] = ldf(src + i);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = (c0 + i < D) ? ldf(src + i) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float prod = weight != nullptr ? __fmul_rn(v[i], g) : v[i];
+        if (kRoundProduct && weight != nullptr) prod = __bfloat162float(__float2bfloat16_rn(prod));
+        acc[i] = __fadd_rn(acc[i], prod);
+      }
+    }
+    OT* dst = out + t * ldo + c0;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      if (c0 + i < D) {
+        if constexpr (sizeof(OT) == 2) {
+          dst[i] = __float2bfloat16_rn(acc[i]);
+        } else {
+          dst[i] = acc[i];
+        }
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_kernel(const T* __restrict__ in, long long ldi, T* __restrict__ out, long long ldo, long long rows, int cols) {
+  const long long total = rows * cols;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols;
+    const int c = static_cast<int>(i - r * cols);
+    const float x = ldf(in + r * ldi + c);
+    const float y = x / (1.0f + expf(-x));
+    if constexpr (sizeof(T) == 2) {
+      out[r * ldo + c] = __float2bfloat16_rn(y);
+    } else {
+      out[r * ldo + c] = y;
+    }
+  }
+}
+
+template <typename VT, typename WT, typename OT>
+int launch_combine(const long long* rev, const void* value, long long ldv, const void* weight, const long long* widx,
+                   long long L, int k, int D, void* out, long long ldo, int* status, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(VT);
+  // vector loads need every row start 16-byte aligned
+  const bool aligned = ((ldv * sizeof(VT)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(value) & 15) == 0);
+  const long long n_rows = L * k;
+  const long long work = L * ((D + VEC - 1) / VEC);
+  long long blocks = (work + kCombineThreads - 1) / kCombineThreads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  if (aligned) {
+    combine_kernel<VT, WT, OT, VEC><<<static_cast<unsigned>(blocks), kCombineThreads, 0, st>>>(
+        rev, static_cast<const VT*>(value), ldv, static_cast<const WT*>(weight), widx, L, k, D,
+        static_cast<OT*>(out), ldo, n_rows, status);
+  } else {
+    const long long work1 = L * static_cast<long long>(D);
+    long long b1 = (work1 + kCombineThreads - 1) / kCombineThreads;
+    if (b1 > 148 * 16) b1 = 148 * 16;
+    if (b1 < 1) b1 = 1;
+    combine_kernel<VT, WT, OT, 1><<<static_cast<unsigned>(b1), kCombineThreads, 0, st>>>(
+        rev, static_cast<const VT*>(value), ldv, static_cast<const WT*>(weight), widx, L, k, D,
+        static_cast<OT*>(out), ldo, n_rows, status);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+}  // namespace
+
+int launch_silu(const void* in, int dtype, long long ldi, void* out, long long ldo, long long rows, int cols,
+                cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return FMOE_OK;
+  long long blocks = (rows * cols + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == FMOE_BF16) {
+    silu_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(in), ldi, static_cast<__nv_bfloat16*>(out), ldo, rows, cols);
+  } else if (dtype == FMOE_F32) {
+    silu_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const float*>(in), ldi,
+                                                                       static_cast<float*>(out), ldo, rows, cols);
+  } else {
+    return fail(FMOE_ERR_BAD_ARG, "silu: dtype %d not supported", dtype);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_mul_merge_k_add(const int64_t* reverse_index, const void* value, int v_dtype, int64_t ldv,
+                                    const void* weight, int w_dtype, const int64_t* weight_index, int64_t L, int k,
+                                    int D, void* out, int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(L >= 0 && k >= 1 && D >= 1, "mul_merge_k_add: L=%lld k=%d D=%d", (long long)L, k, D);
+  FMOE_REQUIRE(reverse_index && value && out, "mul_merge_k_add: NULL pointer argument");
+  FMOE_REQUIRE(v_dtype == FMOE_BF16 || v_dtype == FMOE_F32, "mul_merge_k_add: value must be bf16 or f32");
+  FMOE_REQUIRE(weight == nullptr || w_dtype == FMOE_BF16 || w_dtype == FMOE_F32,
+               "mul_merge_k_add: weight must be bf16 or f32");
+  // Tensor.mul promotes bf16 x f32 to f32; with no weight the value type is kept.
+  const int expect_out = (weight != nullptr && (v_dtype == FMOE_F32 || w_dtype == FMOE_F32)) ? FMOE_F32 : v_dtype;
+  FMOE_REQUIRE(out_dtype == expect_out, "mul_merge_k_add: out dtype %d, expected %d (type promotion of value*weight)",
+               out_dtype, expect_out);
+  if (L == 0) return FMOE_OK;
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long* rev = reinterpret_cast<const long long*>(reverse_index);
+  const long long* widx = reinterpret_cast<const long long*>(weight_index);
+  const bool wf32 = (weight == nullptr) ? (v_dtype == FMOE_F32) : (w_dtype == FMOE_F32);
+  if (v_dtype == FMOE_BF16 && !wf32)
+    return launch_combine<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(rev, value, ldv, weight, widx, L, k, D, out, ldo, status, st);
+  if (v_dtype == FMOE_BF16 && wf32)
+    return launch_combine<__nv_bfloat16, float, float>(rev, value, ldv, weight, widx, L, k, D, out, ldo, status, st);
+  if (v_dtype == FMOE_F32 && wf32)
+    return launch_combine<float, float, float>(rev, value, ldv, weight, widx, L, k, D, out, ldo, status, st);
+  return launch_combine<float, __nv_bfloat16, float>(rev, value, ldv, weight, widx, L, k, D, out, ldo, status, st);
+}

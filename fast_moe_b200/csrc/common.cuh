@@ -1,0 +1,77 @@
+// Shared declarations of the library's translation units: status codes, the error
+// string, the device-side status word and the internal launchers behind the C ABI.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fmoe_b200.h"
+
+namespace fmoe {
+
+// Records a message for fmoe_last_error() (thread-local) and returns `code`.
+int fail(int code, const char* fmt, ...);
+// Wraps a CUDA runtime return code.
+int cuda_fail(cudaError_t e, const char* what);
+
+#define FMOE_CUDA_OK(expr)                                   \
+  do {                                                       \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) return ::fmoe::cuda_fail(_e, #expr); \
+  } while (0)
+
+#define FMOE_REQUIRE(cond, ...)                                          \
+  do {                                                                   \
+    if (!(cond)) return ::fmoe::fail(FMOE_ERR_BAD_ARG, __VA_ARGS__);     \
+  } while (0)
+
+// Device-side status word of the current device (0 = clean). Kernels record the first
+// problem they meet (a wait that ran out, an index out of range) and return; they never
+// trap. Defined in api.cu; the address is resolved once per device.
+int* device_status_ptr(int* err);
+
+static inline int dtype_size(int dt) {
+  switch (dt) {
+    case FMOE_F32: return 4;
+    case FMOE_BF16: return 2;
+    case FMOE_E4M3: return 1;
+    default: return 0;
+  }
+}
+
+// ------------------------------------------------------------------ grouped GEMM
+// out[r, :] = epilogue( A[src(r), :] @ B[e(r)] ), r in [offsets[e], offsets[e+1]).
+struct GemmDesc {
+  int dtype;                 // operand type of A and B: FMOE_BF16, FMOE_F32 (tf32 math), FMOE_E4M3
+  int E, N, K;
+  const int64_t* offsets;    // device [E+1]
+  int64_t total_rows;        // upper bound on offsets[E] (= rows of `out`)
+  // A operand
+  const void* a;
+  int64_t a_rows;            // rows of the A source
+  int64_t lda;               // elements
+  const int64_t* index;      // device [total_rows] or null; source row = index[r] / index_div
+  int index_div;
+  // B operands, logical [E, K, N], element (e,k,n) at b + e*b_se + n*b_sn + k (K contiguous)
+  const void* b0;
+  const void* b1;            // second operand of the gated (SwiGLU) form, else null
+  int64_t b_se, b_sn;        // elements
+  // bias [E, N] in the output type (nullable)
+  const void* bias0;
+  const void* bias1;
+  int64_t bias_se;
+  // FP8 row scales (the multipliers used at quantisation; the epilogue divides by them)
+  const float* a_scale;      // per A-source row, or null
+  const float* b0_scale;     // [E, N]
+  const float* b1_scale;
+  int64_t bscale_se;
+  int epilogue;              // FMOE_EPI_*
+  void* out;
+  int out_dtype;             // FMOE_BF16 or FMOE_F32
+  int64_t ldo;               // elements
+};
+int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream);
+int grouped_gemm_launch_count();
+
+}  // namespace fmoe

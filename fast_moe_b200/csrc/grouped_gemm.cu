@@ -1,0 +1,595 @@
+// Grouped ("jagged") GEMM for sm_100a: every expert e multiplies its own row segment
+// [offsets[e], offsets[e+1]) of the activations by its own weight matrix.
+//
+//   out[r, n] = epilogue( sum_k A[src(r), k] * B[e(r)][k, n] )
+//
+// Replaces, forward only, the reference's per-expert loops
+//   pytorch_index_select_jagged_bmm          kernels/pytorch/moe.py:40-84
+//   pytorch_index_select_jagged_bmm_swiglu   kernels/pytorch/moe.py:87-146
+//   pytorch_silu_jagged_bmm                  kernels/pytorch/moe.py:255-275
+//   pytorch_index_select_jagged_bmm_fp8      kernels/pytorch/moe_fp8.py:98-139
+// and the Triton kernels that sit behind the same operators
+// (kernels/triton/triton_moe.py:184-282, :2526-2671, :3167-3347; triton_moe_fp8.py:770-884).
+//
+// Shape of the kernel (one persistent CTA per SM, 192 threads):
+//   warp 0   producer: TMA loads into a ring of shared-memory stages. The activation rows of a
+//            tile are scattered in memory, so they are fetched with TMA tile::gather4 (each lane
+//            gathers four token rows, 32 lanes = one 128-row tile); weights come as ordinary
+//            3-D tiles of the [E, N, K] tensor. Both land in the 128-byte-swizzled K-major
+//            layout the tensor core reads.
+//   warp 1   one elected thread issues tcgen05.mma (M=128, N up to 256, fp32 accumulators in
+//            tensor memory, double buffered so the epilogue of tile i overlaps the MMAs of i+1).
+//   warps 2-5 epilogue: tcgen05.ld the accumulator, apply rowwise FP8 descale / bias / SiLU /
+//            SwiGLU, convert and store only the rows and columns that exist.
+// Tiles are enumerated on the device from `offsets` (variable rows per expert, empty experts
+// contribute nothing), so no host synchronisation is needed and no CTA is launched for work
+// that does not exist.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace fmoe {
+namespace {
+
+constexpr int kBM = 128;            // rows per tile (= TMEM lanes)
+constexpr int kRowBytes = 128;      // bytes of K per stage row: one swizzle atom
+constexpr int kThreads = 192;
+constexpr int kMaxExperts = 2048;
+constexpr int kABytes = kBM * kRowBytes;
+
+struct GemmParams {
+  const long long* offsets;
+  const long long* index;
+  int index_div;
+  int E, N, K;
+  int num_kb;
+  int n_tiles;
+  long long a_rows;
+  void* out;
+  long long ldo;
+  const void* bias0;
+  const void* bias1;
+  long long bias_se;
+  const float* a_scale;
+  const float* b0_scale;
+  const float* b1_scale;
+  long long bscale_se;
+  int epilogue;
+  int vec_ok;        // output rows are 16-byte aligned: vector stores allowed
+  int* status;
+};
+
+template <int MMA_N>
+struct SmemPlan {
+  static constexpr int kBBytes = MMA_N * kRowBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (MMA_N == 256) ? 4 : 6;
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kPmBytes = (kMaxExperts + 1) * 4 + 12;
+  static constexpr int kTotal = 1024 + kTileBytes + kBarBytes + kPmBytes;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+template <typename OutT>
+__device__ __forceinline__ float load_as_float(const void* p, long long i) {
+  if constexpr (sizeof(OutT) == 4) {
+    return reinterpret_cast<const float*>(p)[i];
+  } else {
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  }
+}
+
+// Stores v[0..31] to dst[0..31] (columns col0..col0+31 of one output row), masking columns
+// that lie beyond N.
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int ncols, bool vec_ok) {
+  if constexpr (sizeof(OutT) == 2) {
+    if (vec_ok && ncols == 32) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+  } else {
+    if (vec_ok && ncols == 32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(dst + 4 * j) =
+            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) dst[i] = v[i];
+    }
+  }
+}
+
+// Walks the tile list. Tiles are ordered expert-major, then column block, then row block, so
+// CTAs that run at the same time share the weight tile of one expert through L2.
+struct TileWalker {
+  const int* pm;   // prefix of row-tile counts per expert, pm[E] = total row tiles
+  int n_tiles;
+  int E;
+  int e;
+  __device__ TileWalker(const int* pm_, int n_tiles_, int E_) : pm(pm_), n_tiles(n_tiles_), E(E_), e(0) {}
+  // Decodes tile t (monotonically increasing across calls).
+  __device__ __forceinline__ void decode(int t, int& expert, int& mb, int& nb) {
+    while (e < E - 1 && t >= pm[e + 1] * n_tiles) ++e;
+    const int local = t - pm[e] * n_tiles;
+    const int mt = pm[e + 1] - pm[e];
+    nb = local / mt;
+    mb = local - nb * mt;
+    expert = e;
+  }
+};
+
+template <int ESIZE, int MMA_N, bool DUAL, bool GATHER, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+                    const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
+  using Plan = SmemPlan<MMA_N>;
+  constexpr int kStages = Plan::kStages;
+  constexpr int kTileN = DUAL ? MMA_N / 2 : MMA_N;       // output columns per tile
+  constexpr int kKElems = kRowBytes / ESIZE;             // K elements per stage
+  constexpr int kUmmaKBytes = 32;                        // bytes of K per tcgen05.mma
+  constexpr int kKind = ESIZE == 2 ? ptx::KIND_F16 : (ESIZE == 4 ? ptx::KIND_TF32 : ptx::KIND_F8);
+  constexpr uint32_t kFmt = ESIZE == 2 ? 1u : (ESIZE == 4 ? 2u : 0u);
+  constexpr uint32_t kIdesc = ptx::umma_idesc(kFmt, kBM, MMA_N);
+  constexpr uint32_t kTmemCols = 2 * MMA_N;              // two accumulator buffers
+  constexpr uint32_t kStageTx = kABytes + Plan::kBBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
+  const uint32_t bar_addr = tiles_addr + Plan::kTileBytes;
+  uint8_t* bar_ptr = tiles_ptr + Plan::kTileBytes;
+  // barrier map (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_addr + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_addr + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 200);
+  int* pm = reinterpret_cast<int*>(bar_ptr + Plan::kBarBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- set-up: barriers, tile prefix, tensor memory
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    pm[0] = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB0);
+    if (DUAL) ptx::prefetch_tmap(&tmB1);
+  }
+  for (int e = threadIdx.x; e < p.E; e += kThreads) {
+    long long len = p.offsets[e + 1] - p.offsets[e];
+    if (len < 0) len = 0;
+    pm[e + 1] = static_cast<int>((len + kBM - 1) / kBM);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // inclusive scan of pm[1..E], 32 entries at a time
+    int carry = 0;
+    for (int base = 1; base <= p.E; base += 32) {
+      const int i = base + lane;
+      int v = (i <= p.E) ? pm[i] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      v += carry;
+      if (i <= p.E) pm[i] = v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = pm[p.E] * p.n_tiles;
+  const int num_kb = p.num_kb;
+
+  if (warp == 0) {
+    // =========================================================== producer
+    TileWalker walk(pm, p.n_tiles, p.E);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int e, mb, nb;
+      walk.decode(t, e, mb, nb);
+      const long long seg0 = p.offsets[e];
+      const long long seg1 = p.offsets[e + 1];
+      const long long row0 = seg0 + static_cast<long long>(mb) * kBM;
+      int r[4] = {0, 0, 0, 0};
+      if constexpr (GATHER) {
+        // Rows past the end of the segment re-read the tile's first row; their results are
+        // never stored.
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          long long rr = row0 + 4 * lane + j;
+          if (rr >= seg1) rr = row0;
+          long long src = p.index ? p.index[rr] / p.index_div : rr;
+          if (src < 0 || src >= p.a_rows) {
+            atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
+            src = 0;
+          }
+          r[j] = static_cast<int>(src);
+        }
+      }
+      const int n0 = nb * kTileN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                    FMOE_DEV_WAIT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
+        const uint32_t b_dst = a_dst + kABytes;
+        const uint32_t bar = full_bar(stage);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, kStageTx);
+        __syncwarp();
+        const int k0 = kb * kKElems;
+        if constexpr (GATHER) {
+          ptx::tma_gather4_2d(a_dst + lane * 512u, &tmA, bar, k0, r[0], r[1], r[2], r[3]);
+        } else {
+          if (lane == 0) ptx::tma_load_2d(a_dst, &tmA, bar, k0, static_cast<int>(row0));
+        }
+        if (lane == 0) {
+          ptx::tma_load_3d(b_dst, &tmB0, bar, k0, n0, e);
+          if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================================================== MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
+                                  FMOE_DEV_WAIT_MMA)) {
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * MMA_N;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_src = tiles_addr + stage * Plan::kStageBytes;
+          const uint64_t da = ptx::umma_desc_k_sw128(a_src);
+          const uint64_t db = ptx::umma_desc_k_sw128(a_src + kABytes);
+#pragma unroll
+          for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
+            ptx::umma_ss<kKind>(d_tmem, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(stage));      // stage reusable once these MMAs have read it
+          if (kb == num_kb - 1) ptx::umma_commit(tfull_bar(acc));
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // =========================================================== epilogue (4 warps)
+    TileWalker walk(pm, p.n_tiles, p.E);
+    const int q = warp & 3;                    // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    const bool fp8 = (ESIZE == 1);
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      int e, mb, nb;
+      walk.decode(t, e, mb, nb);
+      const long long seg1 = p.offsets[e + 1];
+      const long long row = p.offsets[e] + static_cast<long long>(mb) * kBM + row_in_tile;
+      const bool row_ok = row < seg1;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (!ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, p.status, FMOE_DEV_WAIT_EPILOGUE)) {
+        break;
+      }
+      ptx::tc_fence_after();
+      float inv_a = 1.0f;
+      if (fp8 && p.a_scale != nullptr && row_ok) {
+        long long src = row;
+        if (GATHER && p.index) src = p.index[row] / p.index_div;
+        if (src < 0 || src >= p.a_rows) src = 0;
+        inv_a = p.a_scale[src];
+      }
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MMA_N;
+      OutT* out_row = reinterpret_cast<OutT*>(p.out) + row * p.ldo;
+      const int n0 = nb * kTileN;
+#pragma unroll 1
+      for (int c = 0; c < kTileN; c += 32) {
+        uint32_t r0[32];
+        float v[32];
+        ptx::tmem_ld_32x32b_x32(t_row + c, r0);
+        if constexpr (DUAL) {
+          uint32_t r1[32];
+          ptx::tmem_ld_32x32b_x32(t_row + kTileN + c, r1);
+          ptx::tmem_ld_wait();
+          const int col0 = n0 + c;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            float g = __uint_as_float(r0[i]);
+            float u = __uint_as_float(r1[i]);
+            if (col < p.N) {
+              if (fp8 && p.a_scale != nullptr) {
+                const long long so = static_cast<long long>(e) * p.bscale_se + col;
+                g = __bfloat162float(__float2bfloat16_rn(g)) / (inv_a * p.b0_scale[so]);
+                u = __bfloat162float(__float2bfloat16_rn(u)) / (inv_a * p.b1_scale[so]);
+              }
+              if (p.bias0) g += load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col);
+              if (p.bias1) u += load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col);
+            }
+            v[i] = silu_f(g) * u;
+          }
+        } else {
+          ptx::tmem_ld_wait();
+          const int col0 = n0 + c;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            float g = __uint_as_float(r0[i]);
+            if (col < p.N) {
+              if (fp8 && p.a_scale != nullptr) {
+                const long long so = static_cast<long long>(e) * p.bscale_se + col;
+                g = __bfloat162float(__float2bfloat16_rn(g)) / (inv_a * p.b0_scale[so]);
+              }
+              if (p.bias0) g += load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col);
+            }
+            v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
+          }
+        }
+        const int ncols = min(32, p.N - (n0 + c));
+        if (row_ok && ncols > 0) store_chunk<OutT>(out_row + n0 + c, v, ncols, p.vec_ok != 0);
+      }
+      // accumulator buffer free again
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ---- tear-down
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // A wait ran out. Give copies still in flight time to land before shared memory and
+    // tensor memory are handed back.
+    __nanosleep(2000000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn(int* err) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || sym == nullptr) {
+    *err = fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available (%s)",
+                e != cudaSuccess ? cudaGetErrorString(e) : "driver query failed");
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+CUtensorMapDataType tmap_dtype(int dt) {
+  switch (dt) {
+    case FMOE_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case FMOE_F32: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+
+int make_tmap(CUtensorMap* m, int dt, int rank, const void* base, const cuuint64_t* dims,
+              const cuuint64_t* strides_bytes, const cuuint32_t* box, const char* what) {
+  int err = 0;
+  EncodeTiledFn fn = encode_fn(&err);
+  if (!fn) return err;
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, tmap_dtype(dt), rank, const_cast<void*>(base), dims, strides_bytes, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "tensor map for %s rejected (CUresult %d): base %p, dims %llu x %llu, row stride %llu B", what,
+                static_cast<int>(r), base, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                (unsigned long long)strides_bytes[0]);
+  }
+  return FMOE_OK;
+}
+
+int g_launches = 0;
+int g_num_sms = 0;
+
+template <int ESIZE, int MMA_N, bool DUAL, bool GATHER, typename OutT>
+int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const GemmParams& p,
+             int grid, cudaStream_t stream) {
+  using Plan = SmemPlan<MMA_N>;
+  auto kern = grouped_gemm_kernel<ESIZE, MMA_N, DUAL, GATHER, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal));
+    attr_set = true;
+  }
+  kern<<<grid, kThreads, Plan::kTotal, stream>>>(tmA, tmB0, tmB1, p);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_launches;
+  return FMOE_OK;
+}
+
+template <int ESIZE, typename OutT>
+int dispatch_shape(bool dual, bool gather, const CUtensorMap& tmA, const CUtensorMap& tmB0,
+                   const CUtensorMap& tmB1, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (dual) {
+    return gather ? launch_t<ESIZE, 256, true, true, OutT>(tmA, tmB0, tmB1, p, grid, stream)
+                  : launch_t<ESIZE, 256, true, false, OutT>(tmA, tmB0, tmB1, p, grid, stream);
+  }
+  return gather ? launch_t<ESIZE, 256, false, true, OutT>(tmA, tmB0, tmB1, p, grid, stream)
+                : launch_t<ESIZE, 256, false, false, OutT>(tmA, tmB0, tmB1, p, grid, stream);
+}
+
+}  // namespace
+
+int grouped_gemm_launch_count() { return g_launches; }
+
+int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
+  const int esize = dtype_size(d.dtype);
+  FMOE_REQUIRE(esize != 0, "grouped_gemm: unknown operand dtype %d", d.dtype);
+  FMOE_REQUIRE(d.E >= 1 && d.E <= kMaxExperts, "grouped_gemm: E=%d outside [1, %d]", d.E, kMaxExperts);
+  FMOE_REQUIRE(d.N >= 1 && d.K >= 1, "grouped_gemm: N=%d K=%d must be positive", d.N, d.K);
+  FMOE_REQUIRE(d.offsets && d.a && d.b0 && d.out, "grouped_gemm: null pointer argument");
+  FMOE_REQUIRE(d.out_dtype == FMOE_BF16 || d.out_dtype == FMOE_F32, "grouped_gemm: output must be bf16 or f32");
+  FMOE_REQUIRE(d.dtype != FMOE_F32 || d.out_dtype == FMOE_F32, "grouped_gemm: f32 operands need an f32 output");
+  FMOE_REQUIRE(d.epilogue != FMOE_EPI_SWIGLU || d.b1 != nullptr, "grouped_gemm: SwiGLU needs a second weight");
+  FMOE_REQUIRE(d.index == nullptr || d.index_div >= 1, "grouped_gemm: index_div must be >= 1");
+  if ((d.lda * esize) % 16 != 0 || (d.b_sn * esize) % 16 != 0 || (d.b_se * esize) % 16 != 0 ||
+      (reinterpret_cast<uintptr_t>(d.a) & 15) || (reinterpret_cast<uintptr_t>(d.b0) & 15) ||
+      (d.b1 && (reinterpret_cast<uintptr_t>(d.b1) & 15))) {
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "grouped_gemm: TMA needs 16-byte aligned bases and row strides (lda=%lld, b_sn=%lld, b_se=%lld "
+                "elements of %d bytes)", (long long)d.lda, (long long)d.b_sn, (long long)d.b_se, esize);
+  }
+  if (d.total_rows <= 0) return FMOE_OK;
+  FMOE_REQUIRE(d.a_rows >= 1, "grouped_gemm: empty A source with %lld output rows", (long long)d.total_rows);
+  FMOE_REQUIRE(d.a_rows < (1ll << 31) && d.total_rows < (1ll << 31), "grouped_gemm: more than 2^31 rows");
+
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    FMOE_CUDA_OK(cudaGetDevice(&dev));
+    FMOE_CUDA_OK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+
+  const bool dual = d.epilogue == FMOE_EPI_SWIGLU;
+  const bool gather = d.index != nullptr;
+  const int tile_n = dual ? 128 : 256;
+  const int k_elems = kRowBytes / esize;
+
+  CUtensorMap tmA, tmB0, tmB1;
+  {
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.a_rows)};
+    cuuint64_t str[1] = {static_cast<cuuint64_t>(d.lda) * esize};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(k_elems), gather ? 1u : static_cast<cuuint32_t>(kBM)};
+    int rc = make_tmap(&tmA, d.dtype, 2, d.a, dims, str, box, "activations");
+    if (rc != FMOE_OK) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.N), static_cast<cuuint64_t>(d.E)};
+    cuuint64_t str[2] = {static_cast<cuuint64_t>(d.b_sn) * esize, static_cast<cuuint64_t>(d.b_se) * esize};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(tile_n), 1u};
+    int rc = make_tmap(&tmB0, d.dtype, 3, d.b0, dims, str, box, "weights");
+    if (rc != FMOE_OK) return rc;
+    if (dual) {
+      rc = make_tmap(&tmB1, d.dtype, 3, d.b1, dims, str, box, "second weights");
+      if (rc != FMOE_OK) return rc;
+    } else {
+      tmB1 = tmB0;
+    }
+  }
+
+  GemmParams p;
+  p.offsets = reinterpret_cast<const long long*>(d.offsets);
+  p.index = reinterpret_cast<const long long*>(d.index);
+  p.index_div = d.index_div > 0 ? d.index_div : 1;
+  p.E = d.E;
+  p.N = d.N;
+  p.K = d.K;
+  p.num_kb = (d.K + k_elems - 1) / k_elems;
+  p.n_tiles = (d.N + tile_n - 1) / tile_n;
+  p.a_rows = d.a_rows;
+  p.out = d.out;
+  p.ldo = d.ldo;
+  p.bias0 = d.bias0;
+  p.bias1 = d.bias1;
+  p.bias_se = d.bias_se;
+  p.a_scale = d.a_scale;
+  p.b0_scale = d.b0_scale;
+  p.b1_scale = d.b1_scale;
+  p.bscale_se = d.bscale_se;
+  p.epilogue = d.epilogue;
+  const int osize = dtype_size(d.out_dtype);
+  p.vec_ok = ((d.ldo * osize) % 16 == 0) && ((reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
+  p.status = status;
+
+  // Persistent grid: one CTA per SM, never more CTAs than the largest possible tile count.
+  const long long max_m_tiles = (d.total_rows + kBM - 1) / kBM + d.E;
+  long long max_tiles = max_m_tiles * p.n_tiles;
+  int grid = static_cast<int>(max_tiles < g_num_sms ? max_tiles : g_num_sms);
+  if (grid < 1) grid = 1;
+
+  if (d.dtype == FMOE_BF16) {
+    if (d.out_dtype == FMOE_BF16) return dispatch_shape<2, __nv_bfloat16>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    return dispatch_shape<2, float>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+  } else if (d.dtype == FMOE_F32) {
+    return dispatch_shape<4, float>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+  } else {
+    if (d.out_dtype == FMOE_BF16) return dispatch_shape<1, __nv_bfloat16>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    return dispatch_shape<1, float>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+  }
+}
+
+}  // namespace fmoe

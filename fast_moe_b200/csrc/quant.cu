@@ -1,0 +1,215 @@
+// Rowwise FP8 (e4m3fn) quantisation with a power-of-two scale per row.
+//
+//   amax  = max |row|
+//   scale = 2^floor(log2(448 / amax)), replaced by 2^127 when that is inf or NaN
+//   q     = e4m3fn(row * scale)
+//
+// Follows calculate_scale / pytorch_rowwise_quant_fp8 (kernels/pytorch/quant_fp8.py:13-34),
+// pytorch_silu_jagged_fp8 and pytorch_bmm_weight_rowwise_quant_fp8
+// (kernels/pytorch/moe_fp8.py:17-43); replaces the two-pass Triton kernels
+// (kernels/triton/triton_quant_fp8.py:130-302, triton_moe_fp8.py:142-219, :292-348).
+// HBM-bound: each row is read once from DRAM (the second pass hits L1/L2) and written once at
+// one byte per element.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace fmoe {
+
+extern long long g_misc_launches;
+
+namespace {
+
+// 448 / amax is evaluated in the type of amax (the reference divides a Python scalar by a
+// tensor, which keeps the tensor's type), then widened to fp32 for log2/floor/exp2.
+__device__ __forceinline__ float calc_scale(float amax, bool amax_is_bf16) {
+  float x = __fdiv_rn(448.0f, amax);
+  if (amax_is_bf16) x = __bfloat162float(__float2bfloat16_rn(x));
+  // fp32 log2 rounded correctly (computed in double, then rounded once). floor() of it decides
+  // the exponent, so values of x a hair below a power of two behave as they do in fp32 log2.
+  const float y = static_cast<float>(log2(static_cast<double>(x)));
+  const float two127 = 1.7014118346046923e38f;
+  if (isnan(y) || y == INFINITY) return two127;
+  if (y == -INFINITY) return 0.0f;          // amax = inf: exp2(-inf) = 0 is finite and is kept
+  const int f = static_cast<int>(floorf(y));
+  if (f >= 128) return two127;              // exp2 overflows to inf -> fallback
+  return ldexpf(1.0f, f);
+}
+
+// Two floats -> two e4m3fn bytes (low byte = a). Hardware conversion rounds to nearest even
+// and saturates; the reference cast does not saturate: anything that rounds beyond 448
+// (|v| > 464) and NaN become 0x7F with the sign kept.
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float a, float b) {
+  uint16_t pk;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(pk) : "f"(a), "f"(b));
+  uint32_t r = pk;
+  if (!(fabsf(a) <= 464.0f)) r = (r & 0xFF00u) | 0x7Fu | ((__float_as_uint(a) >> 24) & 0x80u);
+  if (!(fabsf(b) <= 464.0f)) r = (r & 0x00FFu) | ((0x7Fu | ((__float_as_uint(b) >> 24) & 0x80u)) << 8);
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ float ld_act(const T* p, bool apply_silu) {
+  float v;
+  if constexpr (sizeof(T) == 2) {
+    v = __bfloat162float(*p);
+    if (apply_silu) v = __bfloat162float(__float2bfloat16_rn(v / (1.0f + expf(-v))));
+  } else {
+    v = *p;
+    if (apply_silu) v = v / (1.0f + expf(-v));
+  }
+  return v;
+}
+
+// TPR threads cooperate on one row; a block holds 256 / TPR rows.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(256)
+rowwise_quant_kernel(const T* __restrict__ in, long long ldi, long long rows, int cols, int apply_silu,
+                     int store_reciprocal, uint8_t* __restrict__ q, long long ldq, float* __restrict__ scale_out) {
+  constexpr int kRowsPerBlock = 256 / TPR;
+  __shared__ float s_red[256 / 32];
+  __shared__ int s_nan[256 / 32];
+  const int sub = threadIdx.x / TPR;
+  const int lane_in_row = threadIdx.x % TPR;
+  const long long row = static_cast<long long>(blockIdx.x) * kRowsPerBlock + sub;
+  const bool active = row < rows;
+  const T* src = in + (active ? row : 0) * ldi;
+  const bool silu = apply_silu != 0;
+
+  float amax = 0.f;
+  int has_nan = 0;
+  if (active) {
+    for (int c = lane_in_row; c < cols; c += TPR) {
+      const float v = fabsf(ld_act<T>(src + c, silu));
+      has_nan |= isnan(v) ? 1 : 0;
+      amax = fmaxf(amax, v);
+    }
+  }
+  // reduce over the TPR threads of the row
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    if (o < TPR) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      has_nan |= __shfl_xor_sync(0xffffffffu, has_nan, o);
+    }
+  }
+  if constexpr (TPR > 32) {
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) {
+      s_red[warp] = amax;
+      s_nan[warp] = has_nan;
+    }
+    __syncthreads();
+    amax = 0.f;
+    has_nan = 0;
+#pragma unroll
+    for (int w = 0; w < 256 / 32; ++w) {
+      amax = fmaxf(amax, s_red[w]);
+      has_nan |= s_nan[w];
+    }
+  }
+  if (has_nan) amax = NAN;   // torch.max propagates NaN
+  // after SiLU the reference holds fp32 values, so the division is fp32 there
+  const float scale = calc_scale(amax, sizeof(T) == 2 && !silu);
+  if (active && lane_in_row == 0 && scale_out != nullptr) {
+    scale_out[row] = store_reciprocal ? __fdiv_rn(1.0f, scale) : scale;
+  }
+  if (!active) return;
+  uint8_t* dst = q + row * ldq;
+  const int pairs = cols >> 1;
+  const bool dst_even = (reinterpret_cast<uintptr_t>(dst) & 1) == 0;
+  if (dst_even) {
+    for (int pidx = lane_in_row; pidx < pairs; pidx += TPR) {
+      const float a = ld_act<T>(src + 2 * pidx, silu) * scale;
+      const float b = ld_act<T>(src + 2 * pidx + 1, silu) * scale;
+      *reinterpret_cast<uint16_t*>(dst + 2 * pidx) = static_cast<uint16_t>(f32x2_to_e4m3x2(a, b));
+    }
+    if ((cols & 1) && lane_in_row == 0) {
+      const float a = ld_act<T>(src + cols - 1, silu) * scale;
+      dst[cols - 1] = static_cast<uint8_t>(f32x2_to_e4m3x2(a, 0.f) & 0xFF);
+    }
+  } else {
+    for (int c = lane_in_row; c < cols; c += TPR) {
+      const float a = ld_act<T>(src + c, silu) * scale;
+      dst[c] = static_cast<uint8_t>(f32x2_to_e4m3x2(a, 0.f) & 0xFF);
+    }
+  }
+}
+
+// weight [E, K, D]: one thread per (e, d) column, reduction over K.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colwise_quant_kernel(const T* __restrict__ w, int E, int K, int D, uint8_t* __restrict__ q,
+                     float* __restrict__ scale_out) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(E) * D) return;
+  const int e = static_cast<int>(i / D);
+  const int d = static_cast<int>(i - static_cast<long long>(e) * D);
+  const T* src = w + static_cast<long long>(e) * K * D + d;
+  float amax = 0.f;
+  int has_nan = 0;
+  for (int kk = 0; kk < K; ++kk) {
+    const float v = fabsf(ld_act<T>(src + static_cast<long long>(kk) * D, false));
+    has_nan |= isnan(v) ? 1 : 0;
+    amax = fmaxf(amax, v);
+  }
+  if (has_nan) amax = NAN;
+  const float scale = calc_scale(amax, sizeof(T) == 2);
+  if (scale_out) scale_out[i] = scale;
+  uint8_t* dst = q + static_cast<long long>(e) * K * D + d;
+  for (int kk = 0; kk < K; ++kk) {
+    const float a = ld_act<T>(src + static_cast<long long>(kk) * D, false) * scale;
+    dst[static_cast<long long>(kk) * D] = static_cast<uint8_t>(f32x2_to_e4m3x2(a, 0.f) & 0xFF);
+  }
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_rowwise_quant_fp8(const void* in, int in_dtype, int64_t rows, int cols, int64_t ldi,
+                                      int apply_silu, int store_reciprocal, void* q, int64_t ldq, float* scale_out,
+                                      void* stream) {
+  FMOE_REQUIRE(rows >= 0 && cols >= 1, "rowwise_quant_fp8: rows=%lld cols=%d", (long long)rows, cols);
+  FMOE_REQUIRE(in_dtype == FMOE_BF16 || in_dtype == FMOE_F32, "rowwise_quant_fp8: input must be bf16 or f32");
+  FMOE_REQUIRE(rows == 0 || (in && q), "rowwise_quant_fp8: NULL pointer argument");
+  if (rows == 0) return FMOE_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* qq = static_cast<uint8_t*>(q);
+  const bool wide = cols > 1024;
+  const long long blocks = wide ? rows : (rows + 7) / 8;
+  FMOE_REQUIRE(blocks < (1ll << 31), "rowwise_quant_fp8: too many rows");
+  const unsigned g = static_cast<unsigned>(blocks);
+  if (in_dtype == FMOE_BF16) {
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(in);
+    if (wide) rowwise_quant_kernel<__nv_bfloat16, 256><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq, scale_out);
+    else rowwise_quant_kernel<__nv_bfloat16, 32><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq, scale_out);
+  } else {
+    const float* p = static_cast<const float*>(in);
+    if (wide) rowwise_quant_kernel<float, 256><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq, scale_out);
+    else rowwise_quant_kernel<float, 32><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq, scale_out);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_bmm_weight_quant_fp8(const void* weight, int dtype, int E, int K, int D, void* q,
+                                         float* scale_out, void* stream) {
+  FMOE_REQUIRE(E >= 1 && K >= 1 && D >= 1, "bmm_weight_quant_fp8: E=%d K=%d D=%d", E, K, D);
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "bmm_weight_quant_fp8: weight must be bf16 or f32");
+  FMOE_REQUIRE(weight && q, "bmm_weight_quant_fp8: NULL pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long n = static_cast<long long>(E) * D;
+  const unsigned g = static_cast<unsigned>((n + 255) / 256);
+  if (dtype == FMOE_BF16)
+    colwise_quant_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(weight), E, K, D,
+                                                           static_cast<uint8_t*>(q), scale_out);
+  else
+    colwise_quant_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(weight), E, K, D,
+                                                   static_cast<uint8_t*>(q), scale_out);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}

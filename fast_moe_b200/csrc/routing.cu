@@ -1,0 +1,320 @@
+// Routing kernels: gate logits -> softmax -> top-k -> renormalised scores, and the stable
+// counting sort that turns the [L, k] expert choices into per-expert jagged offsets and the
+// permutation tensors the expert GEMMs and the combine consume.
+//
+// Replaces the eager ATen sequence of the reference (modules/fast_moe_module.py:93-144:
+// softmax, topk, scatter_, mul, normalize, two stable sorts, floor-divide, sum, gather, cumsum,
+// max + device-to-host sync). All of this is integer / HBM-bound work: one pass over x for the
+// logits, one pass over the [L, k] indices for the histogram and one for the placement.
+#include "common.cuh"
+
+namespace fmoe {
+
+extern long long g_misc_launches;
+
+namespace {
+
+constexpr int kGateWarps = 8;
+constexpr int kMaxGateExperts = 256;
+constexpr int kRouteBlock = 256;   // tokens per block in the counting sort
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// One warp per token. Logits are accumulated in fp32 with the reduction order fixed by the
+// lane layout, so the same input always routes the same way.
+template <typename XT>
+__global__ void __launch_bounds__(kGateWarps * 32)
+gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ gw,
+                 const float* __restrict__ gb, const float* __restrict__ logits_in, long long L, int d, int E,
+                 int k, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
+                 float* __restrict__ topk_score) {
+  __shared__ float s_logit[kGateWarps][kMaxGateExperts];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long t = static_cast<long long>(blockIdx.x) * kGateWarps + warp;
+  if (t >= L) return;
+  float* lg = s_logit[warp];
+
+  if (logits_in != nullptr) {
+    for (int e = lane; e < E; e += 32) lg[e] = logits_in[t * E + e];
+  } else {
+    const XT* xr = x + t * ldx;
+    constexpr int EC = 8;   // experts per pass over the row
+    for (int e0 = 0; e0 < E; e0 += EC) {
+      float acc[EC];
+#pragma unroll
+      for (int i = 0; i < EC; ++i) acc[i] = 0.f;
+      for (int c = lane; c < d; c += 32) {
+        const float xv = to_f<XT>(xr[c]);
+#pragma unroll
+        for (int i = 0; i < EC; ++i) {
+          if (e0 + i < E) acc[i] = fmaf(xv, gw[static_cast<long long>(e0 + i) * d + c], acc[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < EC; ++i) {
+        float v = acc[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && e0 + i < E) lg[e0 + i] = v + (gb ? gb[e0 + i] : 0.f);
+      }
+    }
+  }
+  __syncwarp();
+  if (logits_out != nullptr) {
+    for (int e = lane; e < E; e += 32) logits_out[t * E + e] = lg[e];
+  }
+  // softmax over E
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(lg[e] - mx);
+    lg[e] = p;
+    sum += p;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncwarp();
+  // top-k by repeated arg-max; a taken entry is marked with -1 (scores are >= 0)
+  float norm = 0.f;
+  for (int j = 0; j < k; ++j) {
+    float best = -2.f;
+    int best_e = E;
+    for (int e = lane; e < E; e += 32) {
+      const float v = lg[e];
+      if (v > best) {   // ascending e within the lane: first maximum wins
+        best = v;
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ov > best || (ov == best && oe < best_e)) {
+        best = ov;
+        best_e = oe;
+      }
+    }
+    const float sc = best / sum;
+    norm += sc;
+    if (lane == 0) {
+      topk_idx[t * k + j] = best_e;
+      topk_score[t * k + j] = sc;
+      lg[best_e] = -1.f;
+    }
+    __syncwarp();
+  }
+  // F.normalize(p=1, eps=1e-12) over the k kept scores
+  const float denom = fmaxf(norm, 1e-12f);
+  if (lane == 0) {
+    for (int j = 0; j < k; ++j) topk_score[t * k + j] = topk_score[t * k + j] / denom;
+  }
+}
+
+// ---- counting sort -------------------------------------------------------------------------
+// Pass 1: per block of kRouteBlock tokens, how many of its rows go to each expert.
+// A token never picks the same expert twice, so the stable order inside one expert is simply
+// ascending token id; per-warp bit masks of "which lanes picked e" give every row its rank.
+__device__ __forceinline__ void build_masks(const long long* __restrict__ topk_idx, long long L, int E, int k,
+                                            unsigned* masks /*[8][E]*/, int* status) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < (kRouteBlock / 32) * E; i += kRouteBlock) masks[i] = 0u;
+  __syncthreads();
+  const long long t = static_cast<long long>(blockIdx.x) * kRouteBlock + threadIdx.x;
+  if (t < L) {
+    for (int s = 0; s < k; ++s) {
+      const long long e = topk_idx[t * k + s];
+      if (e < 0 || e >= E) {
+        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+        continue;
+      }
+      atomicOr(&masks[warp * E + static_cast<int>(e)], 1u << lane);
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kRouteBlock)
+route_count_kernel(const long long* __restrict__ topk_idx, long long L, int E, int k, int* __restrict__ block_cnt,
+                   int* status) {
+  extern __shared__ unsigned masks[];
+  build_masks(topk_idx, L, E, k, masks, status);
+  for (int e = threadIdx.x; e < E; e += kRouteBlock) {
+    int c = 0;
+#pragma unroll
+    for (int w = 0; w < kRouteBlock / 32; ++w) c += __popc(masks[w * E + e]);
+    block_cnt[static_cast<long long>(blockIdx.x) * E + e] = c;
+  }
+}
+
+// Pass 2 (one block): turn block_cnt[b][e] into the exclusive prefix over b, and produce
+// lengths, offsets and max_len.
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int* __restrict__ block_cnt, int nb, int E, long long* __restrict__ lengths,
+                  long long* __restrict__ offsets, long long* __restrict__ max_len) {
+  __shared__ long long s_part[1024];
+  __shared__ long long s_carry;
+  __shared__ long long s_max;
+  if (threadIdx.x == 0) {
+    s_carry = 0;
+    s_max = 0;
+  }
+  for (int base = 0; base < E; base += 1024) {
+    const int e = base + threadIdx.x;
+    long long total = 0;
+    if (e < E) {
+      for (int b = 0; b < nb; ++b) {
+        const long long i = static_cast<long long>(b) * E + e;
+        const int c = block_cnt[i];
+        block_cnt[i] = static_cast<int>(total);
+        total += c;
+      }
+      if (lengths) lengths[e] = total;
+    }
+    s_part[threadIdx.x] = total;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      long long run = s_carry;
+      long long mx = s_max;
+      const int n = min(1024, E - base);
+      for (int i = 0; i < n; ++i) {
+        const long long v = s_part[i];
+        offsets[base + i] = run;
+        run += v;
+        mx = v > mx ? v : mx;
+      }
+      s_carry = run;
+      s_max = mx;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    offsets[E] = s_carry;
+    if (max_len) *max_len = s_max;
+  }
+}
+
+// Pass 3: placement.
+__global__ void __launch_bounds__(kRouteBlock)
+route_place_kernel(const long long* __restrict__ topk_idx, long long L, int E, int k,
+                   const int* __restrict__ block_base, const long long* __restrict__ offsets,
+                   long long* __restrict__ gate_index, long long* __restrict__ token_index,
+                   long long* __restrict__ reverse_index, int* status) {
+  extern __shared__ unsigned masks[];
+  build_masks(topk_idx, L, E, k, masks, status);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long t = static_cast<long long>(blockIdx.x) * kRouteBlock + threadIdx.x;
+  if (t >= L) return;
+  const unsigned lt = (1u << lane) - 1u;
+  for (int s = 0; s < k; ++s) {
+    const long long e64 = topk_idx[t * k + s];
+    if (e64 < 0 || e64 >= E) continue;
+    const int e = static_cast<int>(e64);
+    int rank = block_base[static_cast<long long>(blockIdx.x) * E + e];
+    for (int w = 0; w < warp; ++w) rank += __popc(masks[w * E + e]);
+    rank += __popc(masks[warp * E + e] & lt);
+    const long long pos = offsets[e] + rank;
+    if (gate_index) gate_index[pos] = t * k + s;
+    if (token_index) token_index[pos] = t;
+    if (reverse_index) {
+      // position among this token's rows = number of its picks with a smaller expert id
+      int j = 0;
+      for (int s2 = 0; s2 < k; ++s2) {
+        const long long e2 = topk_idx[t * k + s2];
+        j += (e2 < e64) ? 1 : 0;
+      }
+      reverse_index[t * k + j] = pos;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
+                              const float* logits_in, int64_t L, int d, int E, int k, float* logits_out,
+                              int64_t* topk_idx, float* topk_score, void* stream) {
+  FMOE_REQUIRE(L >= 0 && E >= 1 && E <= kMaxGateExperts, "gate_topk: E=%d outside [1, %d]", E, kMaxGateExperts);
+  FMOE_REQUIRE(k >= 1 && k <= E, "gate_topk: k=%d must be in [1, E=%d]", k, E);
+  FMOE_REQUIRE(topk_idx && topk_score, "gate_topk: output pointers must not be NULL");
+  FMOE_REQUIRE(logits_in || (x && gate_w && d >= 1), "gate_topk: need either logits_in or x and gate_w");
+  FMOE_REQUIRE(logits_in || x_dtype == FMOE_BF16 || x_dtype == FMOE_F32, "gate_topk: x must be bf16 or f32");
+  if (L == 0) return FMOE_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>((L + kGateWarps - 1) / kGateWarps);
+  long long* idx = reinterpret_cast<long long*>(topk_idx);
+  if (logits_in || x_dtype == FMOE_F32) {
+    gate_topk_kernel<float><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const float*>(x), ldx, gate_w, gate_b,
+                                                               logits_in, L, d, E, k, logits_out, idx, topk_score);
+  } else {
+    gate_topk_kernel<__nv_bfloat16><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx,
+                                                                       gate_w, gate_b, logits_in, L, d, E, k,
+                                                                       logits_out, idx, topk_score);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" size_t fmoe_route_workspace_bytes(int64_t L, int E, int k) {
+  (void)k;
+  if (L < 0 || E < 1) return 0;
+  const int64_t nb = (L + kRouteBlock - 1) / kRouteBlock;
+  return static_cast<size_t>((nb > 0 ? nb : 1) * E) * sizeof(int);
+}
+
+extern "C" int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, int k, int64_t* lengths,
+                                   int64_t* offsets, int64_t* gate_index, int64_t* token_index,
+                                   int64_t* reverse_index, int64_t* max_len, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  FMOE_REQUIRE(E >= 1 && E <= 4096, "route_metadata: E=%d outside [1, 4096]", E);
+  FMOE_REQUIRE(k >= 1 && k <= E, "route_metadata: k=%d must be in [1, E=%d]", k, E);
+  FMOE_REQUIRE(L >= 0 && L * k < (1ll << 31), "route_metadata: L*k must be below 2^31");
+  FMOE_REQUIRE(offsets != nullptr && (L == 0 || topk_idx != nullptr), "route_metadata: NULL offsets or topk_idx");
+  FMOE_REQUIRE(workspace != nullptr && workspace_bytes >= fmoe_route_workspace_bytes(L, E, k),
+               "route_metadata: workspace of %zu bytes is smaller than the %zu needed", workspace_bytes,
+               fmoe_route_workspace_bytes(L, E, k));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  const int nb = static_cast<int>((L + kRouteBlock - 1) / kRouteBlock);
+  int* block_cnt = static_cast<int*>(workspace);
+  const size_t smem = static_cast<size_t>(kRouteBlock / 32) * E * sizeof(unsigned);
+  const long long* idx = reinterpret_cast<const long long*>(topk_idx);
+  if (smem > 48 * 1024) {
+    FMOE_CUDA_OK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FMOE_CUDA_OK(cudaFuncSetAttribute(route_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  if (nb > 0) {
+    route_count_kernel<<<nb, kRouteBlock, smem, st>>>(idx, L, E, k, block_cnt, status);
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+  }
+  route_scan_kernel<<<1, 1024, 0, st>>>(block_cnt, nb, E, reinterpret_cast<long long*>(lengths),
+                                        reinterpret_cast<long long*>(offsets), reinterpret_cast<long long*>(max_len));
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  if (nb > 0 && (gate_index || token_index || reverse_index)) {
+    route_place_kernel<<<nb, kRouteBlock, smem, st>>>(idx, L, E, k, block_cnt, reinterpret_cast<long long*>(offsets),
+                                                      reinterpret_cast<long long*>(gate_index),
+                                                      reinterpret_cast<long long*>(token_index),
+                                                      reinterpret_cast<long long*>(reverse_index), status);
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+  }
+  return FMOE_OK;
+}

@@ -1,0 +1,362 @@
+"""Operators of the MoE forward path with the reference's signatures (kernels/moe.py:39-292),
+backed by libfmoe_b200 (hand-written sm_100a kernels). Forward only.
+
+``kernel=`` / ``triton_option=`` are accepted and ignored: there is one implementation here.
+Tensors must live on a CUDA device; outputs are freshly allocated on the same device.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+from .utils import KernelType
+
+
+@dataclass
+class IndexSelectJaggedBmmOption:
+    """Backward-pass tuning knobs of the reference (kernels/triton/triton_moe.py:36-43);
+    accepted for signature compatibility, unused by the forward kernels."""
+
+    d_weight_optimization: bool = False
+    d_weight_split_k_kernel: bool = False
+    d_weight_split_k_kernel_tma: bool = False
+    gemm_out_bf16: bool = False
+
+
+@dataclass
+class SiluJaggedBmmCombineOption:
+    """See kernels/triton/triton_moe.py:3562-3567; unused by the forward kernels."""
+
+    activation_checkpointing: bool = False
+    d_weight_optimization: bool = False
+    d_weight_split_k_kernel: bool = False
+    d_weight_split_k_kernel_tma: bool = False
+
+
+def _elem_align(dt: torch.dtype) -> int:
+    """Elements per 16 bytes: TMA needs 16-byte aligned bases and row strides."""
+    return 16 // torch.empty((), dtype=dt).element_size()
+
+
+def _check_float(t: torch.Tensor, name: str) -> None:
+    if t.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError(f"{name}: float32 or bfloat16 expected, got {t.dtype}")
+
+
+def prep_activation(jagged: torch.Tensor, k_pad: int) -> torch.Tensor:
+    """Returns a [rows, >=K] view/copy whose last dim is contiguous, whose row stride and base
+    are 16-byte aligned, zero-padded to k_pad columns when K itself is not aligned."""
+    K = jagged.shape[1]
+    a = _elem_align(jagged.dtype)
+    if k_pad != K:
+        return torch.nn.functional.pad(jagged, (0, k_pad - K))
+    if jagged.stride(1) != 1 or jagged.stride(0) % a != 0 or jagged.data_ptr() % 16 != 0:
+        return jagged.contiguous()
+    return jagged
+
+
+def prep_weight(weight: torch.Tensor, k_pad: int) -> Tuple[torch.Tensor, int, int]:
+    """weight is logical [E, K, N]. Returns (storage [E, N, k_pad] with K contiguous, expert
+    stride, row stride) in elements. The permuted view FastMoELayer passes
+    (modules/fast_moe_module.py:167,177) is used in place; a plain contiguous [E, K, N] tensor is
+    transposed once (a copy)."""
+    E, K, N = weight.shape
+    a = _elem_align(weight.dtype)
+    wt = weight.permute(0, 2, 1)  # [E, N, K]
+    ok = (
+        wt.stride(2) == 1
+        and wt.stride(1) % a == 0
+        and wt.stride(0) % a == 0
+        and wt.data_ptr() % 16 == 0
+        and k_pad == K
+    )
+    if not ok:
+        wt = wt.contiguous()
+        if k_pad != K:
+            wt = torch.nn.functional.pad(wt, (0, k_pad - K))
+    return wt, wt.stride(0), wt.stride(1)
+
+
+def _pad_k(K: int, dt: torch.dtype) -> int:
+    a = _elem_align(dt)
+    return (K + a - 1) // a * a
+
+
+def _prep_bias(bias: Optional[torch.Tensor], out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    if bias is None:
+        return None
+    b = bias.to(out_dtype)
+    return b if b.is_contiguous() else b.contiguous()
+
+
+def _index_i64(t: torch.Tensor) -> torch.Tensor:
+    t = t if t.dtype == torch.int64 else t.to(torch.int64)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def index_select_jagged_bmm(
+    max_seq_len: int,
+    offsets: torch.Tensor,
+    index: torch.Tensor,
+    jagged: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    kernel: KernelType = KernelType.PYTORCH,
+    triton_option: Optional[IndexSelectJaggedBmmOption] = None,
+    *,
+    _epilogue: int = _lib.EPI_NONE,
+) -> torch.Tensor:
+    """out[r] = jagged[index.view(-1)[r] // A] @ weight[e] + bias[e] for the rows r of expert e.
+
+    Same contract as the reference operator (kernels/moe.py:39-68): offsets [E+1], index [L, A],
+    jagged [L, K], weight [E, K, N] (any strides), bias [E, N] or None -> [L*A, N].
+    ``max_seq_len`` is accepted and not needed: the tile list is built on the device.
+    """
+    assert index.ndim == 2 and index.shape[0] == jagged.shape[0]
+    _check_float(jagged, "jagged")
+    assert weight.dtype == jagged.dtype, f"{weight.dtype=} {jagged.dtype=}"
+    dev = _lib.require_cuda(offsets, index, jagged, weight, bias)
+    lib = _lib.load()
+    L, K = jagged.shape
+    E, Kw, N = weight.shape
+    assert Kw == K, f"weight {tuple(weight.shape)} does not match jagged {tuple(jagged.shape)}"
+    rows = index.numel()
+    kp = _pad_k(K, jagged.dtype)
+    a = prep_activation(jagged, kp)
+    w, w_se, w_sn = prep_weight(weight, kp)
+    b = _prep_bias(bias, jagged.dtype)
+    off = _index_i64(offsets)
+    idx = _index_i64(index)
+    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    dt = _lib.dtype_code(jagged.dtype)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_index_select_jagged_bmm(
+                off.data_ptr(), idx.data_ptr(), index.shape[1], rows, a.data_ptr(), dt, L, a.stride(0),
+                w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, _epilogue, out.data_ptr(), dt, out.stride(0),
+                _lib.stream_ptr(dev),
+            )
+        )
+    return out
+
+
+def index_select_jagged_bmm_swiglu(
+    max_seq_len: int,
+    offsets: torch.Tensor,
+    index: torch.Tensor,
+    jagged: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    weight_p: torch.Tensor,
+    bias_p: Optional[torch.Tensor],
+    kernel: KernelType = KernelType.PYTORCH,
+) -> torch.Tensor:
+    """silu(x @ weight[e] + bias[e]) * (x @ weight_p[e] + bias_p[e]) on the gathered rows, one
+    kernel, the activation row tile shared by both products (kernels/moe.py:156-189)."""
+    assert index.ndim == 2 and index.shape[0] == jagged.shape[0]
+    _check_float(jagged, "jagged")
+    assert weight.dtype == jagged.dtype and weight_p.dtype == jagged.dtype
+    assert weight.shape == weight_p.shape
+    dev = _lib.require_cuda(offsets, index, jagged, weight, weight_p, bias, bias_p)
+    lib = _lib.load()
+    L, K = jagged.shape
+    E, Kw, N = weight.shape
+    assert Kw == K
+    rows = index.numel()
+    kp = _pad_k(K, jagged.dtype)
+    a = prep_activation(jagged, kp)
+    w, w_se, w_sn = prep_weight(weight, kp)
+    wp, wp_se, wp_sn = prep_weight(weight_p, kp)
+    if (wp_se, wp_sn) != (w_se, w_sn):
+        # the kernel walks both weights with one set of strides
+        w = w.contiguous()
+        wp = wp.contiguous()
+        w_se, w_sn = w.stride(0), w.stride(1)
+    b = _prep_bias(bias, jagged.dtype)
+    bp = _prep_bias(bias_p, jagged.dtype)
+    off = _index_i64(offsets)
+    idx = _index_i64(index)
+    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    dt = _lib.dtype_code(jagged.dtype)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_index_select_jagged_bmm_swiglu(
+                off.data_ptr(), idx.data_ptr(), index.shape[1], rows, a.data_ptr(), dt, L, a.stride(0),
+                w.data_ptr(), wp.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), _lib.ptr(bp), N, E, kp, N,
+                out.data_ptr(), dt, out.stride(0), _lib.stream_ptr(dev),
+            )
+        )
+    return out
+
+
+def index_select_jagged_gating_bmm(
+    max_seq_len: int,
+    offsets: torch.Tensor,
+    index: torch.Tensor,
+    jagged_a: torch.Tensor,
+    jagged_b: torch.Tensor,
+    weight_a: torch.Tensor,
+    bias_a: Optional[torch.Tensor],
+    weight_b: torch.Tensor,
+    bias_b: Optional[torch.Tensor],
+    kernel: KernelType = KernelType.PYTORCH,
+) -> torch.Tensor:
+    """silu(A_g @ Wa + ba) * (B_g @ Wb + bb) (kernels/moe.py:192-233). With ``jagged_a is
+    jagged_b`` this is the SwiGLU operator and runs as one kernel; two distinct inputs run as two
+    grouped GEMMs (the first with the SiLU epilogue) and one multiply."""
+    assert (
+        index.ndim == 2
+        and index.shape[0] == jagged_a.shape[0] == jagged_b.shape[0]
+        and jagged_a.shape == jagged_b.shape
+        and weight_a.shape == weight_b.shape
+    )
+    if jagged_a is jagged_b:
+        return index_select_jagged_bmm_swiglu(max_seq_len, offsets, index, jagged_a, weight_a, bias_a, weight_b, bias_b)
+    alpha_silu = index_select_jagged_bmm(max_seq_len, offsets, index, jagged_a, weight_a, bias_a, _epilogue=_lib.EPI_SILU)
+    beta = index_select_jagged_bmm(max_seq_len, offsets, index, jagged_b, weight_b, bias_b)
+    return alpha_silu.mul_(beta)
+
+
+def mul_merge_k_add(
+    index: torch.Tensor,
+    reverse_index: torch.Tensor,
+    value: torch.Tensor,
+    stable_sorting: bool = False,
+    weight: Optional[torch.Tensor] = None,
+    weight_index: Optional[torch.Tensor] = None,
+    kernel: KernelType = KernelType.PYTORCH,
+    triton_cc_version: str = "",
+) -> torch.Tensor:
+    """out[t] = sum over the k rows p of token t of value[p] * weight.view(-1)[weight_index[p]]
+    (kernels/moe.py:71-115). Uses the gather form (``reverse_index``), fp32 accumulation in
+    ascending row order; ``index`` only takes part in the shape checks."""
+    N = index.shape[0]
+    L, K = reverse_index.shape
+    _, D = value.shape
+    assert index.ndim == 1 and reverse_index.ndim == 2
+    assert N == L * K and N == value.shape[0]
+    _check_float(value, "value")
+    dev = _lib.require_cuda(reverse_index, value, weight, weight_index)
+    lib = _lib.load()
+    w = None
+    widx = None
+    out_dtype = value.dtype
+    if weight is not None:
+        assert weight_index is not None
+        assert weight.numel() == weight_index.numel() == value.shape[0], (
+            f"{weight.shape=}, {weight_index.shape=}, {value.shape=}"
+        )
+        _check_float(weight, "weight")
+        w = weight.contiguous().view(-1)
+        widx = _index_i64(weight_index)
+        out_dtype = torch.promote_types(value.dtype, weight.dtype)
+    v = value if value.stride(1) == 1 else value.contiguous()
+    rev = _index_i64(reverse_index)
+    out = torch.empty((L, D), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_mul_merge_k_add(
+                rev.data_ptr(), v.data_ptr(), _lib.dtype_code(v.dtype), v.stride(0), _lib.ptr(w),
+                _lib.dtype_code(w.dtype) if w is not None else 0, _lib.ptr(widx), L, K, D, out.data_ptr(),
+                _lib.dtype_code(out_dtype), out.stride(0), _lib.stream_ptr(dev),
+            )
+        )
+    return out
+
+
+def silu_jagged_bmm(
+    offsets: torch.Tensor,
+    jagged: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    has_silu: bool = True,
+) -> torch.Tensor:
+    """[silu](jagged) @ weight[e] + bias[e] per expert segment; weight is logical [E, K, N]
+    (the GEMM half of silu_jagged_bmm_combine, kernels/pytorch/moe.py:255-275)."""
+    _check_float(jagged, "jagged")
+    assert weight.dtype == jagged.dtype
+    dev = _lib.require_cuda(offsets, jagged, weight, bias)
+    lib = _lib.load()
+    rows, K = jagged.shape
+    E, Kw, N = weight.shape
+    assert Kw == K
+    kp = _pad_k(K, jagged.dtype)
+    a = prep_activation(jagged, kp)
+    w, w_se, w_sn = prep_weight(weight, kp)
+    b = _prep_bias(bias, jagged.dtype)
+    off = _index_i64(offsets)
+    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    scratch = torch.empty((rows, kp), dtype=jagged.dtype, device=dev) if has_silu else None
+    dt = _lib.dtype_code(jagged.dtype)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_silu_jagged_bmm(
+                off.data_ptr(), rows, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
+                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), out.data_ptr(), dt, out.stride(0),
+                _lib.stream_ptr(dev),
+            )
+        )
+    return out
+
+
+def silu_jagged_bmm_combine(
+    max_seq_len: int,
+    offsets: torch.Tensor,
+    jagged: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    index: torch.Tensor,
+    reverse_index: torch.Tensor,
+    gating_scores: Optional[torch.Tensor] = None,
+    gates_index: Optional[torch.Tensor] = None,
+    has_silu: bool = True,
+    kernel: KernelType = KernelType.PYTORCH,
+    triton_option: Optional[SiluJaggedBmmCombineOption] = None,
+) -> torch.Tensor:
+    """Down projection of every expert segment followed by the gate-weighted merge of each
+    token's k rows (kernels/moe.py:236-292): [L*k, D_in] -> [L, D_out]."""
+    N = index.shape[0]
+    L, K = reverse_index.shape
+    _, D_in = jagged.shape
+    E, _, D_out = weight.shape
+    assert index.ndim == 1 and reverse_index.ndim == 2
+    assert N == L * K and N == jagged.shape[0], f"{N=}, {L=}, {K=}, {jagged.shape=}"
+    if kernel == KernelType.TRITON_CC:
+        raise NotImplementedError("TRITON_CC is not supported for silu_jagged_bmm_combine")
+    _check_float(jagged, "jagged")
+    assert weight.dtype == jagged.dtype
+    dev = _lib.require_cuda(offsets, jagged, weight, bias, reverse_index, gating_scores, gates_index)
+    lib = _lib.load()
+    kp = _pad_k(D_in, jagged.dtype)
+    a = prep_activation(jagged, kp)
+    w, w_se, w_sn = prep_weight(weight, kp)
+    b = _prep_bias(bias, jagged.dtype)
+    off = _index_i64(offsets)
+    rev = _index_i64(reverse_index)
+    g = None
+    gidx = None
+    out_dtype = jagged.dtype
+    if gating_scores is not None:
+        assert gates_index is not None
+        assert gating_scores.numel() == gates_index.numel() == N
+        _check_float(gating_scores, "gating_scores")
+        g = gating_scores.contiguous().view(-1)
+        gidx = _index_i64(gates_index)
+        out_dtype = torch.promote_types(jagged.dtype, g.dtype)
+    act_scratch = torch.empty((N, kp), dtype=jagged.dtype, device=dev) if has_silu else None
+    bmm_scratch = torch.empty((N, D_out), dtype=jagged.dtype, device=dev)
+    out = torch.empty((L, D_out), dtype=out_dtype, device=dev)
+    dt = _lib.dtype_code(jagged.dtype)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_silu_jagged_bmm_combine(
+                off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), D_out,
+                rev.data_ptr(), _lib.ptr(g), _lib.dtype_code(g.dtype) if g is not None else 0, _lib.ptr(gidx), L, K,
+                E, kp, D_out, 1 if has_silu else 0, _lib.ptr(act_scratch), bmm_scratch.data_ptr(), out.data_ptr(),
+                _lib.dtype_code(out_dtype), out.stride(0), _lib.stream_ptr(dev),
+            )
+        )
+    return out

@@ -1,0 +1,201 @@
+/*
+ * fmoe_b200 -- C ABI of the sm_100a implementation of the FastMoE forward hot path.
+ *
+ * The reference (meta-recsys/fast_moe) is a pure-Python operator library; its "FFI" for this path
+ * is the set of Python callables in kernels/moe.py, kernels/moe_fp8.py and the routing code of
+ * modules/fast_moe_module.py. Each entry point below is what a binding of one of those callables
+ * needs from native code; the comment above it cites the reference interface it stands in for
+ * (paths are relative to the reference repository).
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers unless a comment says "host". The library never allocates,
+ *    frees or copies on the caller's behalf: outputs and scratch buffers are passed in.
+ *  - Every function enqueues work on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ *    default stream) and returns without synchronising. Return value: FMOE_OK or a negative
+ *    fmoe_status; fmoe_last_error() gives the message of the calling thread's last failure.
+ *  - Index tensors are int64 ("long"), as in the reference. Row strides (ld*) are in elements.
+ *  - Weights are logical [E, K, N] tensors described by element strides (se, sk, sn). The tensor
+ *    core path needs K contiguous (sk == 1), which is the layout FastMoELayer hands to the
+ *    operators (a permuted view of [E, N, K] storage, modules/fast_moe_module.py:167,177).
+ *  - Kernels never trap. A kernel that meets an out-of-range index or a wait that runs out
+ *    records a code in a per-device status word and returns; fmoe_device_status() reads it.
+ */
+#ifndef FMOE_B200_H_
+#define FMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FMOE_OK = 0,
+  FMOE_ERR_BAD_ARG = -1,     /* shape / pointer / dtype relation violated (the reference asserts) */
+  FMOE_ERR_UNSUPPORTED = -2, /* valid for the reference, not for this kernel (e.g. stride not 16-byte aligned) */
+  FMOE_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed */
+  FMOE_ERR_DEVICE = -4       /* the device status word is non-zero (see fmoe_device_status) */
+} fmoe_status;
+
+/* element types */
+enum { FMOE_F32 = 0, FMOE_BF16 = 1, FMOE_E4M3 = 3 };
+
+/* GEMM epilogues */
+enum { FMOE_EPI_NONE = 0, FMOE_EPI_SILU = 1, FMOE_EPI_SWIGLU = 2 };
+
+/* codes a kernel may leave in the device status word */
+enum {
+  FMOE_DEV_OK = 0,
+  FMOE_DEV_BAD_INDEX = 1,      /* an index / expert id outside its range was skipped */
+  FMOE_DEV_WAIT_PRODUCER = 2,  /* bounded waits that gave up, by pipeline role */
+  FMOE_DEV_WAIT_MMA = 3,
+  FMOE_DEV_WAIT_EPILOGUE = 4
+};
+
+int fmoe_version(void);
+/* Message of the last failure on the calling thread (host string, never NULL). */
+const char* fmoe_last_error(void);
+/* Copies the device status word of the current device to *status_out (host), after synchronising
+ * `stream`; clears it when reset != 0. */
+int fmoe_device_status(int* status_out, int reset, void* stream);
+/* Number of kernels this library has launched in this process (all entry points). */
+long long fmoe_kernel_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Routing.
+ * Replaces GatingNetwork.forward + FastMoELayer._select_top_k_experts
+ * (modules/fast_moe_module.py:21-27, :93-105): logits = x @ Wg^T + bg in fp32, softmax over the
+ * E experts, top-k (slots in descending score order, ties to the lower expert id), scores of the
+ * chosen experts renormalised to sum 1 (F.normalize p=1, eps 1e-12).
+ *   x         [L, d] bf16 or f32 (x_dtype), row stride ldx; may be NULL when logits_in is given
+ *   gate_w    [E, d] f32 row-major (nn.Linear weight), gate_b [E] f32 or NULL
+ *   logits_in [L, E] f32 or NULL: when non-NULL the matrix product is skipped
+ *   logits_out[L, E] f32 or NULL
+ *   topk_idx  [L, k] int64, topk_score [L, k] f32
+ * 1 <= k <= E <= 256.
+ */
+int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
+                   const float* logits_in, int64_t L, int d, int E, int k, float* logits_out,
+                   int64_t* topk_idx, float* topk_score, void* stream);
+
+/* Replaces FastMoELayer._compute_routing_metadata (modules/fast_moe_module.py:107-144) and the
+ * fbgemm op asynchronous_complete_cumsum it calls (:131): a stable counting sort of the L*k
+ * (token, slot) pairs by expert id.
+ *   topk_idx      [L, k] int64 in
+ *   lengths       [E]    rows per expert
+ *   offsets       [E+1]  exclusive prefix of lengths, offsets[E] = L*k
+ *   gate_index    [L*k]  stable argsort of topk_idx.view(-1): value = token*k + slot
+ *   token_index   [L*k]  gate_index / k
+ *   reverse_index [L, k] stable argsort of token_index, i.e. for each token the sorted positions
+ *                        of its k rows (ascending expert id)
+ *   max_len       [1]    max(lengths) (stays on the device: no kernel here needs it on the host)
+ *   workspace            fmoe_route_workspace_bytes(L, E, k) bytes of scratch
+ * Any output pointer except offsets may be NULL.
+ */
+size_t fmoe_route_workspace_bytes(int64_t L, int E, int k);
+int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, int k, int64_t* lengths, int64_t* offsets,
+                        int64_t* gate_index, int64_t* token_index, int64_t* reverse_index, int64_t* max_len,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Up projection.
+ * index_select_jagged_bmm (kernels/moe.py:39-68 -> kernels/pytorch/moe.py:40-84):
+ *   out[r, :] = jagged[index[r] / index_div, :] @ weight[e] + bias[e],  offsets[e] <= r < offsets[e+1]
+ *   offsets [E+1] int64; index [rows] int64 (the flattened [L, A] tensor, index_div = A)
+ *   jagged  [L, K] dtype (bf16, or f32 computed with tf32 tensor-core math), row stride ldj
+ *   weight  logical [E, K, N], element strides (w_se, w_sk, w_sn), same dtype
+ *   bias    [E, N] same dtype as out, expert stride bias_se, or NULL
+ *   out     [rows, N] out_dtype (bf16 or f32), row stride ldo; rows = offsets[E] (<= total_rows)
+ * `epilogue` = FMOE_EPI_NONE for the reference operator; FMOE_EPI_SILU additionally applies SiLU
+ * (used by the layer to fold the activation that silu_jagged_bmm_combine would otherwise apply to
+ * its input, kernels/pytorch/moe.py:262-263).
+ */
+int fmoe_index_select_jagged_bmm(const int64_t* offsets, const int64_t* index, int index_div, int64_t total_rows,
+                                 const void* jagged, int dtype, int64_t L, int64_t ldj, const void* weight,
+                                 int64_t w_se, int64_t w_sk, int64_t w_sn, const void* bias, int64_t bias_se,
+                                 int E, int K, int N, int epilogue, void* out, int out_dtype, int64_t ldo,
+                                 void* stream);
+
+/* index_select_jagged_bmm_swiglu (kernels/moe.py:156-189 -> kernels/pytorch/moe.py:87-146):
+ *   out[r, :] = silu(x_r @ weight[e] + bias[e]) * (x_r @ weight_p[e] + bias_p[e])
+ * weight and weight_p share shape and strides. */
+int fmoe_index_select_jagged_bmm_swiglu(const int64_t* offsets, const int64_t* index, int index_div,
+                                        int64_t total_rows, const void* jagged, int dtype, int64_t L, int64_t ldj,
+                                        const void* weight, const void* weight_p, int64_t w_se, int64_t w_sk,
+                                        int64_t w_sn, const void* bias, const void* bias_p, int64_t bias_se, int E,
+                                        int K, int N, void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* moe_fp8.index_select_jagged_bmm(fp8=True) (kernels/moe_fp8.py:185-248 ->
+ * kernels/pytorch/moe_fp8.py:98-139) on operands that are already quantised with
+ * fmoe_rowwise_quant_fp8: jagged_q [L, K] e4m3 with jagged_scale [L]; weight_q logical [E, K, N]
+ * e4m3, K contiguous, with weight_scale [E, N] (expert stride ws_se). Scales are the multipliers
+ * used at quantisation; the epilogue divides by their product, then adds bias.
+ * weight_p_q / weight_p_scale non-NULL selects the SwiGLU form of the same product. */
+int fmoe_index_select_jagged_bmm_fp8(const int64_t* offsets, const int64_t* index, int index_div,
+                                     int64_t total_rows, const void* jagged_q, const float* jagged_scale, int64_t L,
+                                     int64_t ldj, const void* weight_q, const float* weight_scale,
+                                     const void* weight_p_q, const float* weight_p_scale, int64_t w_se, int64_t w_sk,
+                                     int64_t w_sn, int64_t ws_se, const void* bias, const void* bias_p,
+                                     int64_t bias_se, int E, int K, int N, int epilogue, void* out, int out_dtype,
+                                     int64_t ldo, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Down projection.
+ * pytorch_silu_jagged_bmm (kernels/pytorch/moe.py:255-275), the GEMM half of
+ * silu_jagged_bmm_combine: out[r, :] = act(jagged[r, :]) @ weight[e] + bias[e] with act = SiLU
+ * when has_silu != 0. The activation cannot be applied between shared memory and the tensor core,
+ * so with has_silu the caller passes act_scratch ([rows, K], same dtype, row stride K) which
+ * receives silu(jagged) first. jagged_scale / weight_scale non-NULL select the FP8 form (jagged
+ * and weight are then e4m3 and has_silu must be 0).
+ */
+int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype, int64_t ldj,
+                         const float* jagged_scale, const void* weight, const float* weight_scale, int64_t w_se,
+                         int64_t w_sk, int64_t w_sn, int64_t ws_se, const void* bias, int64_t bias_se, int E, int K,
+                         int N, int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* mul_merge_k_add (kernels/moe.py:71-115 -> kernels/pytorch/moe.py:14-37):
+ *   out[t, :] = sum_j value[p_j, :] * weight[weight_index[p_j]],  p_j = reverse_index[t, j], j = 0..k-1
+ * accumulated in fp32 in that order (ascending row, the order index_add visits them), the product
+ * rounded to the value type first when value and weight are both bf16 (what Tensor.mul does).
+ *   value [L*k, D] v_dtype, row stride ldv; reverse_index [L, k] int64
+ *   weight: flat array of w_dtype (bf16/f32) or NULL; weight_index [L*k] int64 or NULL (identity)
+ *   out [L, D] out_dtype, row stride ldo
+ */
+int fmoe_mul_merge_k_add(const int64_t* reverse_index, const void* value, int v_dtype, int64_t ldv,
+                         const void* weight, int w_dtype, const int64_t* weight_index, int64_t L, int k, int D,
+                         void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* silu_jagged_bmm_combine (kernels/moe.py:236-292 -> kernels/pytorch/moe.py:278-303):
+ * fmoe_silu_jagged_bmm into bmm_scratch ([rows, N], out_dtype, row stride N) followed by
+ * fmoe_mul_merge_k_add with gating_scores / gates_index. */
+int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype,
+                                 int64_t ldj, const void* weight, int64_t w_se, int64_t w_sk, int64_t w_sn,
+                                 const void* bias, int64_t bias_se, const int64_t* reverse_index,
+                                 const void* gating_scores, int g_dtype, const int64_t* gates_index, int64_t L, int k,
+                                 int E, int K, int N, int has_silu, void* act_scratch, void* bmm_scratch, void* out,
+                                 int out_dtype, int64_t ldo, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * FP8 rowwise quantisation.
+ * pytorch_rowwise_quant_fp8 + calculate_scale (kernels/pytorch/quant_fp8.py:13-34), and with
+ * apply_silu != 0 pytorch_silu_jagged_fp8 (kernels/pytorch/moe_fp8.py:17-33):
+ *   amax = max|row|; scale = 2^floor(log2(448/amax)), 2^127 when that is not finite;
+ *   q = e4m3fn(row * scale) (round to nearest even, no saturation: |v| > 464 gives NaN as
+ *   Tensor.to(float8_e4m3fn) does)
+ *   in [rows, cols] in_dtype (bf16/f32) row stride ldi; q [rows, cols] bytes, row stride ldq;
+ *   scale_out [rows] f32 receives scale, or 1/scale when store_reciprocal != 0; may be NULL.
+ */
+int fmoe_rowwise_quant_fp8(const void* in, int in_dtype, int64_t rows, int cols, int64_t ldi, int apply_silu,
+                           int store_reciprocal, void* q, int64_t ldq, float* scale_out, void* stream);
+
+/* pytorch_bmm_weight_rowwise_quant_fp8 (kernels/pytorch/moe_fp8.py:36-43): weight [E, K, D]
+ * contiguous, absmax over K for every (e, d), q = e4m3fn(weight * scale[e, d]).
+ * scale_out [E, D] may be NULL (the reference returns only the quantised tensor). */
+int fmoe_bmm_weight_quant_fp8(const void* weight, int dtype, int E, int K, int D, void* q, float* scale_out,
+                              void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMOE_B200_H_ */
