@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""MoE-layer forward benchmark (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2]
+
+A step is one forward pass of the layer over one batch of synthetic tokens.
+  N = 1   "c2": 4096 tokens (8 x 512), d=1024, h=4096, 8 SwiGLU experts, top-2, bf16.
+  N > 1   "c5": expert parallel, 64 experts sharded over the ranks, d=4096, h=14336, top-2, bf16,
+          8192 tokens per rank (weak scaling); launched by torchrun, one rank per GPU.
+`value` is tokens/s of the whole job with inputs resident in HBM; `e2e` is the same metric with
+the step's tokens copied host->device and its output copied device->host inside the timed
+region. `--impl reference` times the CPU restatement of the reference's PYTORCH path
+(oracle/moe_oracle.py) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: tokens (per rank), d, h, o, E (total), k
+    "c2": dict(tokens=4096, batch=8, seq=512, d=1024, h=4096, o=1024, E=8, k=2, fp8=False),
+    "c3": dict(tokens=16384, batch=32, seq=512, d=4096, h=14336, o=4096, E=8, k=2, fp8=True),
+    "c4": dict(tokens=8192, batch=16, seq=512, d=2048, h=8192, o=2048, E=64, k=8, fp8=False, zipf=1.2),
+    "c5": dict(tokens=8192, batch=16, seq=512, d=4096, h=14336, o=4096, E=64, k=2, fp8=False),
+}
+
+
+def layer_flops(c, tokens):
+    A = tokens * c["k"]
+    return 2 * tokens * c["d"] * c["E"] + 4 * A * c["d"] * c["h"] + 2 * A * c["h"] * c["o"]
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Polls nvidia-smi during the timed region (clocks, power, throttle reasons)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [l for t, l in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines]
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def make_inputs(c, rank, device, dtype=torch.bfloat16):
+    """Seeded synthetic data: x ~ N(0,1) (per-rank seed), weights / gate ~ N(0, 0.02) (shared seed)."""
+    g = torch.Generator().manual_seed(1234 + rank)
+    x = torch.randn(c["batch"], c["seq"], c["d"], generator=g)
+    if c.get("fp8"):
+        rows = torch.randperm(c["tokens"], generator=g)[: c["tokens"] // 100]
+        x.view(-1, c["d"])[rows] *= 50.0
+    return x.to(dtype)
+
+
+def build_layer(c, device, e_local=None, e_first=0):
+    import fast_moe_b200 as fm
+
+    torch.manual_seed(0)
+    layer = fm.SwiGLUFastMoELayer(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, fp8=bool(c.get("fp8")))
+    with torch.no_grad():
+        layer.gate.gate.weight.normal_(0, 0.02)
+        layer.gate.gate.bias.zero_()
+        if c.get("zipf"):
+            # biased router: expert loads follow Zipf(s) over a seeded permutation of the experts
+            g = torch.Generator().manual_seed(7)
+            ranks = torch.randperm(c["E"], generator=g).float() + 1.0
+            p = ranks.pow(-c["zipf"])
+            layer.gate.gate.bias.copy_((p / p.sum()).log())
+    return layer.to(device)
+
+
+def cpu_oracle_step(c, x_cpu, params, k):
+    from oracle import moe_oracle as O
+
+    return O.moe_layer_swiglu(x_cpu, params["gate_w"], params["gate_b"], params["w_gate"], params["w_up"],
+                              params["w_down"], k)
+
+
+def cpu_params(c, tokens):
+    g = torch.Generator().manual_seed(0)
+    E, d, h, o = c["E"], c["d"], c["h"], c["o"]
+    return dict(
+        gate_w=torch.randn(E, d, generator=g) * 0.02, gate_b=torch.zeros(E),
+        w_gate=(torch.randn(E, h, d, generator=g) * 0.02).permute(0, 2, 1),
+        w_up=(torch.randn(E, h, d, generator=g) * 0.02).permute(0, 2, 1),
+        w_down=(torch.randn(E, o, h, generator=g) * 0.02).permute(0, 2, 1),
+    )
+
+
+def time_cpu_baseline(c, tokens, budget_s=20.0):
+    """The CPU restatement of the reference's PYTORCH path on a bounded sample of the workload:
+    the token count is scaled down until one forward takes a few seconds."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    flops_full = layer_flops(c, tokens)
+    # assume >= 0.2 TFLOP/s; keep the sample's estimated cost under ~budget/4 per run
+    sample = tokens
+    while layer_flops(c, sample) / 2e11 > budget_s / 4 and sample > 256:
+        sample //= 2
+    p = cpu_params(c, sample)
+    x = torch.randn(1, sample, c["d"], generator=torch.Generator().manual_seed(99))
+    with torch.no_grad():
+        cpu_oracle_step(c, x, p, c["k"])   # warm-up
+        times = []
+        t_all = time.perf_counter()
+        while len(times) < 3 and time.perf_counter() - t_all < budget_s:
+            t0 = time.perf_counter()
+            cpu_oracle_step(c, x, p, c["k"])
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return dict(value=sample / t, unit="tokens/s", cores=cores, kind="port",
+                sample=f"{sample} of {tokens} tokens, fp32, torch CPU ({cores} threads), median of {len(times)} runs",
+                seconds_per_run=t)
+
+
+def run_reference(args, c, name):
+    """Reference arm: the CPU restatement of the reference's PYTORCH path, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tokens = c["tokens"]
+    sample = tokens
+    while layer_flops(c, sample) / 2e11 > 4.0 and sample > 256:
+        sample //= 2
+    p = cpu_params(c, sample)
+    x = torch.randn(1, sample, c["d"], generator=torch.Generator().manual_seed(99))
+    with torch.no_grad():
+        for _ in range(max(1, min(args.warmup, 3))):
+            cpu_oracle_step(c, x, p, c["k"])
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            cpu_oracle_step(c, x, p, c["k"])
+        dt = (time.perf_counter() - t0) / args.steps
+    val = sample / dt
+    sample_desc = f"each step = {sample} of {tokens} tokens per rank, fp32, torch CPU, {cores} threads"
+    line = dict(
+        impl="reference", metric="moe_layer_fwd_tokens_per_s", value=val, unit="tokens/s", n_gpus=args.gpus,
+        steps=args.steps, warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak",
+        vs_baseline=None, dtype="f32", data="synthetic", config=workload_config(c, name, args.gpus),
+        cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port", sample=sample_desc),
+        e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+    )
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(c, name, n_gpus):
+    return dict(
+        workload=f"{name}: SwiGLU MoE layer forward, {c['tokens']} tokens/rank, d={c['d']}, h={c['h']}, "
+                 f"E={c['E']}, top-{c['k']}" + (", fp8 e4m3 rowwise" if c.get("fp8") else ", bf16"),
+        tokens_per_rank=c["tokens"], global_tokens=c["tokens"] * n_gpus, d=c["d"], h=c["h"], E=c["E"], k=c["k"],
+        parallelism="single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} ({c['E'] // n_gpus} experts/rank)",
+        l2="working set (weights + activations) is larger than the 126 MB L2; no explicit flush",
+    )
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    name = args.config or ("c2" if args.gpus == 1 else "c5")
+    c = CONFIGS[name]
+    if args.impl == "reference":
+        run_reference(args, c, name)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    from fast_moe_b200 import _lib
+
+    k = c["k"]
+    x_host = make_inputs(c, rank, device).pin_memory()
+    x_dev = x_host.to(device)
+    if world > 1:
+        from fast_moe_b200.modules.expert_parallel import ExpertParallelSwiGLUMoE
+
+        torch.manual_seed(0)
+        layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device)
+    else:
+        layer = build_layer(c, device)
+    if c.get("fp8"):
+        layer.quantize_weights()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        y = layer(x_dev, k)
+    barrier()
+    timer = _lib.StageTimer()
+    _lib.set_stage_timer(timer)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    launches0 = _lib.kernel_launch_count()
+    barrier()
+    t_wall0 = time.perf_counter()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        y = layer(x_dev, k)
+    ev1.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = _lib.kernel_launch_count() - launches0
+    _lib.set_stage_timer(None)
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    stage_ms = {n: (tot / cnt) for n, (tot, cnt) in timer.totals_ms().items()}
+    status = _lib.device_status(device)
+
+    # ---- end to end: host tokens in, host result out, every step
+    y_host = torch.empty((c["batch"], c["seq"], c["o"]), dtype=torch.bfloat16).pin_memory()
+    for _ in range(3):
+        xd = x_host.to(device, non_blocking=True)
+        y_host.copy_(layer(xd, k), non_blocking=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        xd = x_host.to(device, non_blocking=True)
+        y_host.copy_(layer(xd, k), non_blocking=True)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = t.tolist()
+
+    if rank == 0:
+        peaks = load_peaks()
+        ms_step = ms_total / args.steps
+        tokens_total = c["tokens"] * world
+        A = c["tokens"] * k
+        up_ms = stage_ms.get("up")
+        up_flops = 4 * A * c["d"] * c["h"]
+        # the up-projection kernel is timed alone between two events: burst peak is its yardstick
+        peak_tf = peaks["bf16_tflops"] * (2.0 if c.get("fp8") else 1.0)
+        roofline = None
+        if up_ms:
+            ach = up_flops / (up_ms * 1e-3) / 1e12
+            roofline = dict(bound="tensor", kernel="grouped_gemm_kernel (gather + gate/up GEMM + SwiGLU)",
+                            achieved=ach, peak=peak_tf, unit="TFLOP/s", frac=ach / peak_tf,
+                            traffic=None, peak_source=peaks["source"] + (" (2x bf16 burst for fp8)" if c.get("fp8") else " burst"),
+                            flops_per_launch=up_flops, avg_launch_ms=up_ms)
+        line = dict(
+            metric="moe_layer_fwd_tokens_per_s", value=tokens_total / (ms_step * 1e-3), unit="tokens/s",
+            n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,
+            scaling="weak", vs_baseline=None, dtype="e4m3" if c.get("fp8") else "bf16", data="synthetic",
+            config=workload_config(c, name, world),
+            layer_tflops_per_gpu=layer_flops(c, c["tokens"]) / (ms_step * 1e-3) / 1e12,
+            stage_ms=stage_ms, roofline=roofline, clocks=clocks, gpu_launches=int(launches),
+            device_status=status,
+            e2e=dict(value=tokens_total / (ms_e2e / args.steps * 1e-3), unit="tokens/s",
+                     h2d_bytes_per_step=x_host.numel() * x_host.element_size(),
+                     d2h_bytes_per_step=y_host.numel() * y_host.element_size(), ms_per_step=ms_e2e / args.steps),
+        )
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = time_cpu_baseline(c, c["tokens"])
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

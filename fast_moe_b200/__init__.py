@@ -1,0 +1,35 @@
+"""fast_moe_b200: the FastMoE mixture-of-experts forward path on hand-written sm_100a CUDA
+kernels (tcgen05 grouped GEMMs fed by TMA, routing / combine / FP8-quantisation kernels) behind
+the operator and module signatures of meta-recsys/fast_moe. The kernels live in
+``lib/libfmoe_b200.so`` (C ABI: include/fmoe_b200.h); there is no CPU or PyTorch fallback."""
+from .kernels.moe import (
+    IndexSelectJaggedBmmOption,
+    SiluJaggedBmmCombineOption,
+    index_select_jagged_bmm,
+    index_select_jagged_bmm_swiglu,
+    index_select_jagged_gating_bmm,
+    mul_merge_k_add,
+    silu_jagged_bmm,
+    silu_jagged_bmm_combine,
+)
+from .kernels.routing import RoutingMetadata, gate_topk, route_metadata
+from .kernels.utils import KernelType
+from .modules.fast_moe_module import FastMoELayer, GatingNetwork, SwiGLUFastMoELayer
+
+__all__ = [
+    "FastMoELayer",
+    "GatingNetwork",
+    "SwiGLUFastMoELayer",
+    "KernelType",
+    "IndexSelectJaggedBmmOption",
+    "SiluJaggedBmmCombineOption",
+    "index_select_jagged_bmm",
+    "index_select_jagged_bmm_swiglu",
+    "index_select_jagged_gating_bmm",
+    "mul_merge_k_add",
+    "silu_jagged_bmm",
+    "silu_jagged_bmm_combine",
+    "gate_topk",
+    "route_metadata",
+    "RoutingMetadata",
+]

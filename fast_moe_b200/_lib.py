@@ -68,8 +68,10 @@ SIGNATURES = {
     ),
     "fmoe_silu_jagged_bmm": (
         c_int,
-        [P, I64, P, c_int, I64, P, P, P, I64, I64, I64, I64, P, I64, c_int, c_int, c_int, c_int, P, P, c_int, I64, P],
+        [P, I64, P, c_int, I64, P, P, P, I64, I64, I64, I64, P, I64, c_int, c_int, c_int, c_int, P, P, P, P, c_int,
+         I64, P],
     ),
+    "fmoe_gather_rows": (c_int, [P, c_int, I64, I64, P, c_int, I64, c_int, P, I64, P]),
     "fmoe_mul_merge_k_add": (c_int, [P, P, c_int, I64, P, c_int, P, I64, c_int, c_int, P, c_int, I64, P]),
     "fmoe_silu_jagged_bmm_combine": (
         c_int,
@@ -165,3 +167,57 @@ def raise_on_device_status(device: Optional[torch.device] = None) -> None:
 
 def kernel_launch_count() -> int:
     return int(load().fmoe_kernel_launch_count())
+
+
+# ---------------------------------------------------------------------------- stage timing
+class StageTimer:
+    """Optional CUDA-event timing of the stages of a layer forward ("route", "up", "down",
+    "combine", ...). Disabled unless a caller installs one with ``set_stage_timer``; events are
+    recorded on the current stream, so they time exactly the kernels launched in between."""
+
+    def __init__(self) -> None:
+        self.pairs = {}
+
+    def stage(self, name: str):
+        return _Stage(self, name)
+
+    def totals_ms(self):
+        torch.cuda.synchronize()
+        return {k: (sum(a.elapsed_time(b) for a, b in v), len(v)) for k, v in self.pairs.items()}
+
+
+class _Stage:
+    def __init__(self, timer: "StageTimer", name: str) -> None:
+        self.timer, self.name = timer, name
+
+    def __enter__(self):
+        self.a = torch.cuda.Event(enable_timing=True)
+        self.b = torch.cuda.Event(enable_timing=True)
+        self.a.record()
+        return self
+
+    def __exit__(self, *exc):
+        self.b.record()
+        self.timer.pairs.setdefault(self.name, []).append((self.a, self.b))
+        return False
+
+
+class _NoStage:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_STAGE = _NoStage()
+_stage_timer: Optional[StageTimer] = None
+
+
+def set_stage_timer(t: Optional[StageTimer]) -> None:
+    global _stage_timer
+    _stage_timer = t
+
+
+def stage(name: str):
+    return _NO_STAGE if _stage_timer is None else _stage_timer.stage(name)

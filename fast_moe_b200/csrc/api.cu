@@ -177,13 +177,15 @@ extern "C" int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, 
                                     int64_t ldj, const float* jagged_scale, const void* weight,
                                     const float* weight_scale, int64_t w_se, int64_t w_sk, int64_t w_sn,
                                     int64_t ws_se, const void* bias, int64_t bias_se, int E, int K, int N,
-                                    int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo,
+                                    int has_silu, void* act_scratch, const int64_t* jagged_index,
+                                    const int64_t* out_row_index, void* out, int out_dtype, int64_t ldo,
                                     void* stream) {
   const bool fp8 = dtype == FMOE_E4M3;
   FMOE_REQUIRE(fp8 || dtype == FMOE_BF16 || dtype == FMOE_F32, "silu_jagged_bmm: bad dtype %d", dtype);
   FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm: FP8 operands need their scales");
   FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm: has_silu is not available on FP8 input (quantise silu(x) instead)");
   FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm: has_silu needs act_scratch");
+  FMOE_REQUIRE(!(has_silu && jagged_index), "silu_jagged_bmm: has_silu and jagged_index cannot be combined");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const void* a = jagged;
   int64_t lda = ldj;
@@ -200,6 +202,8 @@ extern "C" int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, 
   g.offsets = offsets;
   g.total_rows = total_rows;
   g.a = a; g.a_rows = total_rows; g.lda = lda;
+  g.index = jagged_index; g.index_div = 1;
+  g.out_index = out_row_index;
   g.b0 = weight;
   int rc = set_weight(g, "silu_jagged_bmm", w_se, w_sk, w_sn);
   if (rc != FMOE_OK) return rc;
@@ -223,7 +227,8 @@ extern "C" int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t tota
   // the GEMM result has the activation type, as F.linear returns it
   const int bmm_dtype = dtype;
   int rc = fmoe_silu_jagged_bmm(offsets, total_rows, jagged, dtype, ldj, nullptr, weight, nullptr, w_se, w_sk, w_sn,
-                                0, bias, bias_se, E, K, N, has_silu, act_scratch, bmm_scratch, bmm_dtype, N, stream);
+                                0, bias, bias_se, E, K, N, has_silu, act_scratch, nullptr, nullptr, bmm_scratch, bmm_dtype, N,
+                                stream);
   if (rc != FMOE_OK) return rc;
   return fmoe_mul_merge_k_add(reverse_index, bmm_scratch, bmm_dtype, N, gating_scores, g_dtype, gates_index, L, k, N,
                               out, out_dtype, ldo, stream);

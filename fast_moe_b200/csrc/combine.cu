@@ -106,6 +106,28 @@ silu_kernel(const T* __restrict__ in, long long ldi, T* __restrict__ out, long l
   }
 }
 
+// dst[r, :] = src[index[r] / div, :] in 16-byte pieces (or bytes when rows are not 16-byte
+// aligned). One warp-sized group of threads walks a row, so reads and writes are coalesced.
+template <typename V>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint8_t* __restrict__ src, long long src_rows, long long lds_bytes,
+                   const long long* __restrict__ index, int div, long long rows, int row_bytes,
+                   uint8_t* __restrict__ dst, long long ldd_bytes, int* status) {
+  const int vec_per_row = row_bytes / static_cast<int>(sizeof(V));
+  const long long total = rows * vec_per_row;
+  for (long long w = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; w < total;
+       w += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = w / vec_per_row;
+    const int c = static_cast<int>(w - r * vec_per_row);
+    long long s = index[r] / div;
+    if (s < 0 || s >= src_rows) {
+      atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+      continue;
+    }
+    reinterpret_cast<V*>(dst + r * ldd_bytes)[c] = reinterpret_cast<const V*>(src + s * lds_bytes)[c];
+  }
+}
+
 template <typename VT, typename WT, typename OT>
 int launch_combine(const long long* rev, const void* value, long long ldv, const void* weight, const long long* widx,
                    long long L, int k, int D, void* out, long long ldo, int* status, cudaStream_t st) {
@@ -159,6 +181,38 @@ int launch_silu(const void* in, int dtype, long long ldi, void* out, long long l
 }  // namespace fmoe
 
 using namespace fmoe;
+
+extern "C" int fmoe_gather_rows(const void* src, int dtype, int64_t src_rows, int64_t lds, const int64_t* index,
+                                int index_div, int64_t rows, int cols, void* dst, int64_t ldd, void* stream) {
+  const int es = dtype_size(dtype);
+  FMOE_REQUIRE(es != 0, "gather_rows: unknown dtype %d", dtype);
+  FMOE_REQUIRE(rows >= 0 && cols >= 1 && index_div >= 1, "gather_rows: rows=%lld cols=%d div=%d", (long long)rows, cols,
+               index_div);
+  FMOE_REQUIRE(rows == 0 || (src && index && dst), "gather_rows: NULL pointer argument");
+  if (rows == 0) return FMOE_OK;
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int row_bytes = cols * es;
+  const bool v16 = (row_bytes % 16 == 0) && ((lds * es) % 16 == 0) && ((ldd * es) % 16 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+  const long long work = rows * (v16 ? row_bytes / 16 : row_bytes);
+  long long blocks = (work + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const long long* idx = reinterpret_cast<const long long*>(index);
+  if (v16)
+    gather_rows_kernel<uint4><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint8_t*>(src), src_rows, lds * es, idx, index_div, rows, row_bytes,
+        static_cast<uint8_t*>(dst), ldd * es, status);
+  else
+    gather_rows_kernel<uint8_t><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint8_t*>(src), src_rows, lds * es, idx, index_div, rows, row_bytes,
+        static_cast<uint8_t*>(dst), ldd * es, status);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
 
 extern "C" int fmoe_mul_merge_k_add(const int64_t* reverse_index, const void* value, int v_dtype, int64_t ldv,
                                     const void* weight, int w_dtype, const int64_t* weight_index, int64_t L, int k,

@@ -67,6 +67,7 @@ struct GemmDesc {
   const float* b1_scale;
   int64_t bscale_se;
   int epilogue;              // FMOE_EPI_*
+  const int64_t* out_index;  // device [total_rows] or null: row r is stored at out[out_index[r]]
   void* out;
   int out_dtype;             // FMOE_BF16 or FMOE_F32
   int64_t ldo;               // elements

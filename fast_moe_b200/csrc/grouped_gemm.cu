@@ -42,11 +42,13 @@ constexpr int kABytes = kBM * kRowBytes;
 struct GemmParams {
   const long long* offsets;
   const long long* index;
+  const long long* out_index;
   int index_div;
   int E, N, K;
   int num_kb;
   int n_tiles;
   long long a_rows;
+  long long out_rows;
   void* out;
   long long ldo;
   const void* bias0;
@@ -343,7 +345,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         inv_a = p.a_scale[src];
       }
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MMA_N;
-      OutT* out_row = reinterpret_cast<OutT*>(p.out) + row * p.ldo;
+      long long dst_row = row;
+      if (p.out_index != nullptr && row_ok) {
+        dst_row = p.out_index[row];
+        if (dst_row < 0 || dst_row >= p.out_rows) {
+          atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
+          dst_row = row;
+        }
+      }
+      OutT* out_row = reinterpret_cast<OutT*>(p.out) + dst_row * p.ldo;
       const int n0 = nb * kTileN;
 #pragma unroll 1
       for (int c = 0; c < kTileN; c += 32) {
@@ -554,6 +564,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   GemmParams p;
   p.offsets = reinterpret_cast<const long long*>(d.offsets);
   p.index = reinterpret_cast<const long long*>(d.index);
+  p.out_index = reinterpret_cast<const long long*>(d.out_index);
+  p.out_rows = d.total_rows;
   p.index_div = d.index_div > 0 ? d.index_div : 1;
   p.E = d.E;
   p.N = d.N;

@@ -295,7 +295,8 @@ def silu_jagged_bmm(
         _lib.check(
             lib.fmoe_silu_jagged_bmm(
                 off.data_ptr(), rows, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
-                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), out.data_ptr(), dt, out.stride(0),
+                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), None, None, out.data_ptr(), dt,
+                out.stride(0),
                 _lib.stream_ptr(dev),
             )
         )

@@ -1,0 +1,98 @@
+"""Routing operators: gate -> softmax -> top-k, and the stable counting sort that produces the
+jagged offsets and permutation tensors. They stand in for the eager ATen sequence in the
+reference's FastMoELayer (modules/fast_moe_module.py:93-144)."""
+from __future__ import annotations
+
+from typing import NamedTuple, Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+
+class RoutingMetadata(NamedTuple):
+    gate_index: torch.Tensor      # [L*k] int64: stable argsort of topk_idx.view(-1); value = token*k + slot
+    token_index: torch.Tensor     # [L*k] int64: gate_index // k
+    offsets: torch.Tensor         # [E+1] int64
+    reverse_index: torch.Tensor   # [L, k] int64: stable argsort of token_index
+    lengths: torch.Tensor         # [E] int64
+    max_len: torch.Tensor         # [1] int64, on the device
+
+
+def gate_topk(
+    x: Optional[torch.Tensor],
+    gate_weight: Optional[torch.Tensor],
+    gate_bias: Optional[torch.Tensor],
+    k: int,
+    logits: Optional[torch.Tensor] = None,
+    return_logits: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """softmax(x @ Wg^T + bg) -> top-k -> scores of the chosen experts renormalised to sum 1.
+
+    x [L, d] (bf16 / f32), gate_weight [E, d], gate_bias [E] or None; the gate parameters are
+    used in fp32. Alternatively pass ``logits`` [L, E] f32 and no x. Returns
+    (topk_idx [L, k] int64 with slots in descending score order, ties to the lower expert id;
+    topk_score [L, k] f32; logits [L, E] f32 if requested).
+    """
+    lib = _lib.load()
+    if logits is not None:
+        dev = _lib.require_cuda(logits)
+        lg = logits.to(torch.float32).contiguous()
+        L, E = lg.shape
+        xx = gw = gb = None
+        d = 0
+        x_dt = _lib.F32
+        ldx = 0
+    else:
+        assert x is not None and gate_weight is not None
+        dev = _lib.require_cuda(x, gate_weight, gate_bias)
+        assert x.ndim == 2 and gate_weight.ndim == 2 and gate_weight.shape[1] == x.shape[1]
+        xx = x if x.stride(1) == 1 else x.contiguous()
+        gw = gate_weight.to(torch.float32).contiguous()
+        gb = None if gate_bias is None else gate_bias.to(torch.float32).contiguous()
+        L, d = xx.shape
+        E = gw.shape[0]
+        x_dt = _lib.dtype_code(xx.dtype)
+        ldx = xx.stride(0)
+        lg = None
+    idx = torch.empty((L, k), dtype=torch.int64, device=dev)
+    score = torch.empty((L, k), dtype=torch.float32, device=dev)
+    lout = torch.empty((L, E), dtype=torch.float32, device=dev) if return_logits else None
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_gate_topk(
+                _lib.ptr(xx), x_dt, ldx, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(lg), L, d, E, k, _lib.ptr(lout),
+                idx.data_ptr(), score.data_ptr(), _lib.stream_ptr(dev),
+            )
+        )
+    return idx, score, lout
+
+
+def route_metadata(topk_idx: torch.Tensor, num_experts: int) -> RoutingMetadata:
+    """Stable counting sort of the (token, slot) pairs by expert id, on the device, with no
+    host synchronisation."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(topk_idx)
+    assert topk_idx.ndim == 2
+    idx = topk_idx.to(torch.int64).contiguous()
+    L, k = idx.shape
+    E = num_experts
+    A = L * k
+    i64 = dict(dtype=torch.int64, device=dev)
+    lengths = torch.empty(E, **i64)
+    offsets = torch.empty(E + 1, **i64)
+    gate_index = torch.empty(A, **i64)
+    token_index = torch.empty(A, **i64)
+    reverse = torch.empty((L, k), **i64)
+    max_len = torch.empty(1, **i64)
+    ws_bytes = int(lib.fmoe_route_workspace_bytes(L, E, k))
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_route_metadata(
+                idx.data_ptr(), L, E, k, lengths.data_ptr(), offsets.data_ptr(), gate_index.data_ptr(),
+                token_index.data_ptr(), reverse.data_ptr(), max_len.data_ptr(), ws.data_ptr(), ws.numel(),
+                _lib.stream_ptr(dev),
+            )
+        )
+    return RoutingMetadata(gate_index, token_index, offsets, reverse, lengths, max_len)

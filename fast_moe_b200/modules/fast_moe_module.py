@@ -1,0 +1,208 @@
+"""MoE layers on the sm_100a kernels.
+
+``FastMoELayer`` keeps the constructor, parameter names and forward signature of the reference
+layer (modules/fast_moe_module.py:45-225): gate Linear + softmax, top-k, fc1 + bias -> SiLU ->
+fc2 + bias per expert, gate-weighted combine. ``SwiGLUFastMoELayer`` is the same routing around
+a SwiGLU expert (index_select_jagged_bmm_swiglu + silu_jagged_bmm_combine(has_silu=False),
+kernels/moe.py:156-189, :236-292), optionally with e4m3 operands and rowwise scales.
+Forward only; tensors must be on a CUDA device.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+from torch.autograd.profiler import record_function
+
+from .. import _lib
+from ..kernels import moe as ops
+from ..kernels import moe_fp8 as ops_fp8
+from ..kernels.routing import RoutingMetadata, gate_topk, route_metadata
+from ..kernels.utils import KernelType
+
+
+class GatingNetwork(nn.Module):
+    """Linear(d -> E); same parameter names as the reference (modules/fast_moe_module.py:21-27).
+    ``forward`` returns the dense softmax scores through PyTorch for callers that want them; the
+    layers below use the fused gate/top-k kernel instead."""
+
+    def __init__(self, input_dim: int, num_experts: int) -> None:
+        super().__init__()
+        self.gate = nn.Linear(input_dim, num_experts)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.softmax(self.gate(x), dim=2)
+
+
+def _xavier_stack(num: int, rows: int, cols: int) -> torch.Tensor:
+    """[num, rows, cols], each matrix Xavier-uniform (what utils/utils.py:38-42 produces)."""
+    bound = math.sqrt(6.0 / (rows + cols))
+    return torch.empty(num, rows, cols).uniform_(-bound, bound)
+
+
+class _CastCache:
+    """Per-dtype copies of parameters, refreshed when the parameter changes in place. The
+    reference re-casts every weight on every forward (modules/fast_moe_module.py:167-168,
+    :177-178); here the cast happens once per weight update."""
+
+    def __init__(self) -> None:
+        self._store: Dict[Tuple[str, torch.dtype], Tuple[int, int, torch.Tensor]] = {}
+
+    def get(self, name: str, p: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        if p.dtype == dtype:
+            return p.detach()
+        key = (name, dtype)
+        hit = self._store.get(key)
+        if hit is not None and hit[0] == p._version and hit[1] == p.data_ptr():
+            return hit[2]
+        t = p.detach().to(dtype)
+        self._store[key] = (p._version, p.data_ptr(), t)
+        return t
+
+
+class _MoEBase(nn.Module):
+    num_experts: int
+
+    def _route(self, x_flat: torch.Tensor, k: int) -> Tuple[torch.Tensor, RoutingMetadata]:
+        gate: nn.Linear = self.gate.gate  # type: ignore[attr-defined]
+        with _lib.stage("route"):
+            idx, score, _ = gate_topk(x_flat, gate.weight.detach(), None if gate.bias is None else gate.bias.detach(), k)
+            meta = route_metadata(idx, self.num_experts)
+        return score, meta
+
+
+class FastMoELayer(_MoEBase):
+    def __init__(
+        self,
+        input_dim: int,
+        hidden_dim: int,
+        output_dim: int,
+        num_experts: int,
+        kernel: KernelType = KernelType.PYTORCH,
+        dtype: torch.dtype = torch.bfloat16,
+    ) -> None:
+        super().__init__()
+        self.input_dim = input_dim
+        self.hidden_dim = hidden_dim
+        self.output_dim = output_dim
+        self.num_experts = num_experts
+        self.kernel = kernel   # kept for interface compatibility; one implementation exists
+        self.dtype = dtype
+        self.gate = GatingNetwork(input_dim, num_experts)
+        # stored [E, out, in]: the operators receive the permuted [E, in, out] view, whose
+        # reduction dimension is contiguous - the layout the tensor core reads directly
+        self._experts_hidden_w = nn.Parameter(_xavier_stack(num_experts, hidden_dim, input_dim).to(dtype))
+        self._experts_hidden_bias = nn.Parameter(torch.zeros(num_experts, hidden_dim, dtype=dtype))
+        self._experts_w = nn.Parameter(_xavier_stack(num_experts, output_dim, hidden_dim).to(dtype))
+        self._experts_bias = nn.Parameter(torch.zeros(num_experts, output_dim, dtype=dtype))
+        self._cast = _CastCache()
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
+        shape = x.shape
+        k = num_experts_per_tok
+        x_flat = x.reshape(-1, self.input_dim)
+        score, meta = self._route(x_flat, k)
+        with record_function("## expert_forward##"):
+            dt = x.dtype
+            w1 = self._cast.get("w1", self._experts_hidden_w, dt).permute(0, 2, 1)
+            b1 = self._cast.get("b1", self._experts_hidden_bias, dt)
+            w2 = self._cast.get("w2", self._experts_w, dt).permute(0, 2, 1)
+            b2 = self._cast.get("b2", self._experts_bias, dt)
+            # SiLU is applied in the first GEMM's epilogue rather than on the second GEMM's input
+            with _lib.stage("up"):
+                hidden = ops.index_select_jagged_bmm(
+                    0, meta.offsets, meta.gate_index.view(-1, k), x_flat, w1, b1, _epilogue=_lib.EPI_SILU
+                )
+            with _lib.stage("down_combine"):
+                y = ops.silu_jagged_bmm_combine(
+                    0, meta.offsets, hidden, w2, b2, meta.token_index, meta.reverse_index,
+                    gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
+                )
+        return y.view(*shape[:-1], self.output_dim)
+
+
+class SwiGLUFastMoELayer(_MoEBase):
+    """Top-k routed SwiGLU experts: y = sum_j g_j * W_down[e_j] (silu(x W_gate[e_j]) * (x W_up[e_j])).
+
+    Parameters are stored with the reduction dimension contiguous: w_gate / w_up [E, h, d],
+    w_down [E, o, h]. With ``fp8=True`` the weights are quantised once (per output row, rule of
+    kernels/pytorch/quant_fp8.py:13-34) by ``quantize_weights()`` and the forward quantises x
+    and the hidden activations per row before each e4m3 GEMM.
+    """
+
+    def __init__(
+        self,
+        input_dim: int,
+        hidden_dim: int,
+        output_dim: int,
+        num_experts: int,
+        dtype: torch.dtype = torch.bfloat16,
+        init_std: float = 0.02,
+        fp8: bool = False,
+    ) -> None:
+        super().__init__()
+        self.input_dim = input_dim
+        self.hidden_dim = hidden_dim
+        self.output_dim = output_dim
+        self.num_experts = num_experts
+        self.dtype = dtype
+        self.fp8 = fp8
+        self.gate = GatingNetwork(input_dim, num_experts)
+        self.w_gate = nn.Parameter((torch.randn(num_experts, hidden_dim, input_dim) * init_std).to(dtype))
+        self.w_up = nn.Parameter((torch.randn(num_experts, hidden_dim, input_dim) * init_std).to(dtype))
+        self.w_down = nn.Parameter((torch.randn(num_experts, output_dim, hidden_dim) * init_std).to(dtype))
+        self._cast = _CastCache()
+        self._q: Optional[Dict[str, Tuple[torch.Tensor, torch.Tensor]]] = None
+
+    @torch.no_grad()
+    def quantize_weights(self) -> None:
+        """(Re)builds the e4m3 copies of the three weight tensors and their [E, rows] scales."""
+        self._q = {
+            name: ops_fp8.rowwise_quant_fp8(getattr(self, name).detach())
+            for name in ("w_gate", "w_up", "w_down")
+        }
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
+        shape = x.shape
+        k = num_experts_per_tok
+        x_flat = x.reshape(-1, self.input_dim)
+        score, meta = self._route(x_flat, k)
+        dt = x.dtype
+        index = meta.gate_index.view(-1, k)
+        with record_function("## expert_forward##"):
+            if self.fp8:
+                if self._q is None:
+                    self.quantize_weights()
+                assert self._q is not None
+                (wg, sg), (wu, su), (wd, sd) = self._q["w_gate"], self._q["w_up"], self._q["w_down"]
+                with _lib.stage("quant_x"):
+                    xq, xs = ops_fp8.rowwise_quant_fp8(x_flat)
+                with _lib.stage("up"):
+                    hidden = ops_fp8.index_select_jagged_bmm_fp8_quantized(
+                        meta.offsets, index, xq, xs, wg, sg, None, out_dtype=dt, weight_p_q=wu, weight_p_scale=su
+                    )
+                with _lib.stage("quant_hidden"):
+                    hq, hs = ops_fp8.rowwise_quant_fp8(hidden)
+                with _lib.stage("down"):
+                    y_rows = ops_fp8.fp8_jagged_bmm_quantized(meta.offsets, hq, hs, wd, sd, None, out_dtype=dt)
+                with _lib.stage("combine"):
+                    y = ops.mul_merge_k_add(
+                        meta.token_index, meta.reverse_index, y_rows, weight=score.to(dt),
+                        weight_index=meta.gate_index,
+                    )
+            else:
+                wg = self._cast.get("wg", self.w_gate, dt).permute(0, 2, 1)
+                wu = self._cast.get("wu", self.w_up, dt).permute(0, 2, 1)
+                wd = self._cast.get("wd", self.w_down, dt).permute(0, 2, 1)
+                with _lib.stage("up"):
+                    hidden = ops.index_select_jagged_bmm_swiglu(0, meta.offsets, index, x_flat, wg, None, wu, None)
+                with _lib.stage("down_combine"):
+                    y = ops.silu_jagged_bmm_combine(
+                        0, meta.offsets, hidden, wd, None, meta.token_index, meta.reverse_index,
+                        gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
+                    )
+        return y.view(*shape[:-1], self.output_dim)

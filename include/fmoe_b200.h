@@ -148,11 +148,16 @@ int fmoe_index_select_jagged_bmm_fp8(const int64_t* offsets, const int64_t* inde
  * so with has_silu the caller passes act_scratch ([rows, K], same dtype, row stride K) which
  * receives silu(jagged) first. jagged_scale / weight_scale non-NULL select the FP8 form (jagged
  * and weight are then e4m3 and has_silu must be 0).
+ * jagged_index / out_row_index (both [total_rows] int64, nullable) are not part of the reference
+ * operator: when given, row r reads jagged[jagged_index[r]] and is stored at out[out_row_index[r]].
+ * The expert-parallel layer uses them to consume rows in the order the all-to-all delivered them
+ * and to hand results back in that order, without a separate permutation pass.
  */
 int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype, int64_t ldj,
                          const float* jagged_scale, const void* weight, const float* weight_scale, int64_t w_se,
                          int64_t w_sk, int64_t w_sn, int64_t ws_se, const void* bias, int64_t bias_se, int E, int K,
-                         int N, int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo, void* stream);
+                         int N, int has_silu, void* act_scratch, const int64_t* jagged_index,
+                         const int64_t* out_row_index, void* out, int out_dtype, int64_t ldo, void* stream);
 
 /* mul_merge_k_add (kernels/moe.py:71-115 -> kernels/pytorch/moe.py:14-37):
  *   out[t, :] = sum_j value[p_j, :] * weight[weight_index[p_j]],  p_j = reverse_index[t, j], j = 0..k-1
@@ -175,6 +180,14 @@ int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t total_rows, con
                                  const void* gating_scores, int g_dtype, const int64_t* gates_index, int64_t L, int k,
                                  int E, int K, int N, int has_silu, void* act_scratch, void* bmm_scratch, void* out,
                                  int out_dtype, int64_t ldo, void* stream);
+
+/* Row gather: dst[r, :] = src[index[r] / index_div, :], r < rows. The index_select step of
+ * pytorch_index_select_jagged_bmm (kernels/pytorch/moe.py:69-73: jagged[index]) as a standalone
+ * kernel; the expert-parallel layer uses it to pack the rows it sends, already in
+ * (destination rank, expert, token) order, which is the order of gate_index.
+ *   src [src_rows, cols] dtype (element size 1, 2 or 4 bytes), row stride lds; dst row stride ldd. */
+int fmoe_gather_rows(const void* src, int dtype, int64_t src_rows, int64_t lds, const int64_t* index,
+                     int index_div, int64_t rows, int cols, void* dst, int64_t ldd, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * FP8 rowwise quantisation.
