@@ -11,7 +11,7 @@
 // and the Triton kernels that sit behind the same operators
 // (kernels/triton/triton_moe.py:184-282, :2526-2671, :3167-3347; triton_moe_fp8.py:770-884).
 //
-// Shape of the kernel (one persistent CTA per SM, 192 threads):
+// Shape of the kernel (one persistent CTA per SM):
 //   warp 0   producer: TMA loads into a ring of shared-memory stages. The activation rows of a
 //            tile are scattered in memory, so they are fetched with TMA tile::gather4 (each lane
 //            gathers four token rows, 32 lanes = one 128-row tile); weights come as ordinary
@@ -35,8 +35,10 @@ namespace {
 
 constexpr int kBM = 128;            // rows per tile (= TMEM lanes)
 constexpr int kRowBytes = 128;      // bytes of K per stage row: one swizzle atom
-constexpr int kThreads = 192;
-constexpr int kMaxExperts = 2048;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // TMA warp + MMA warp + epilogue warps
+constexpr int kGatherThreads = 128;    // 4 extra warps that gather activation rows (GATHER kernels)
+constexpr int kMaxExperts = 1024;
 constexpr int kABytes = kBM * kRowBytes;
 
 struct GemmParams {
@@ -47,6 +49,8 @@ struct GemmParams {
   int E, N, K;
   int num_kb;
   int n_tiles;
+  const void* a;
+  long long lda;
   long long a_rows;
   long long out_rows;
   void* out;
@@ -69,9 +73,10 @@ struct SmemPlan {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (MMA_N == 256) ? 4 : 6;
   static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kStagingBytes = kEpilogueWarps * 2048;   // 32 rows x 64 bytes per epilogue warp
   static constexpr int kBarBytes = 256;
-  static constexpr int kPmBytes = (kMaxExperts + 1) * 4 + 12;
-  static constexpr int kTotal = 1024 + kTileBytes + kBarBytes + kPmBytes;
+  static constexpr int kPmBytes = 2 * ((kMaxExperts + 1) * 4 + 12);   // tile prefix + row offsets
+  static constexpr int kTotal = 1024 + kTileBytes + kStagingBytes + kBarBytes + kPmBytes;
 };
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
@@ -120,6 +125,63 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int
   }
 }
 
+
+// Writes one 32-column chunk (v) of 32 rows - one row per lane - to global memory with full-line
+// accesses: the chunk is first laid out in the warp's 2 KB staging area (64-byte rows, 16-byte
+// pieces XOR-swizzled so that neither phase has bank conflicts), then every group of 4 lanes
+// writes one row's 64 contiguous bytes, 8 rows per instruction. Rows that do not exist (tail of
+// a segment) are skipped; rows may go anywhere (st_row), which also serves the scattered store.
+// For 4-byte outputs the chunk goes out in two halves of 16 columns.
+template <typename OutT>
+__device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, const float (&v)[32],
+                                                OutT* const (&st_row)[4], const bool (&st_ok)[4], int col0) {
+  constexpr int kHalves = sizeof(OutT) == 2 ? 1 : 2;
+  const uint32_t my_row = stage_w + lane * 64;
+  const int wsw = (lane >> 1) & 3;
+#pragma unroll
+  for (int h = 0; h < kHalves; ++h) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w0, w1, w2, w3;
+      if constexpr (sizeof(OutT) == 2) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * c + 0], v[8 * c + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * c + 2], v[8 * c + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * c + 4], v[8 * c + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * c + 6], v[8 * c + 7]);
+        w0 = *reinterpret_cast<uint32_t*>(&h0);
+        w1 = *reinterpret_cast<uint32_t*>(&h1);
+        w2 = *reinterpret_cast<uint32_t*>(&h2);
+        w3 = *reinterpret_cast<uint32_t*>(&h3);
+      } else {
+        w0 = __float_as_uint(v[16 * h + 4 * c + 0]);
+        w1 = __float_as_uint(v[16 * h + 4 * c + 1]);
+        w2 = __float_as_uint(v[16 * h + 4 * c + 2]);
+        w3 = __float_as_uint(v[16 * h + 4 * c + 3]);
+      }
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((c ^ wsw) << 4)), "r"(w0), "r"(w1),
+                   "r"(w2), "r"(w3)
+                   : "memory");
+    }
+    __syncwarp();
+    const int piece = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = (lane >> 2) + 8 * i;
+      uint32_t w0, w1, w2, w3;
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                   : "r"(stage_w + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4))
+                   : "memory");
+      if (st_ok[i]) {
+        constexpr int kPieceElems = 16 / sizeof(OutT);
+        OutT* dst = st_row[i] + col0 + (kHalves == 2 ? 16 * h : 0) + piece * kPieceElems;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // Walks the tile list. Tiles are ordered expert-major, then column block, then row block, so
 // CTAs that run at the same time share the weight tile of one expert through L2.
 struct TileWalker {
@@ -140,7 +202,7 @@ struct TileWalker {
 };
 
 template <int ESIZE, int MMA_N, bool DUAL, bool GATHER, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(GATHER ? kThreads + kGatherThreads : kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
   using Plan = SmemPlan<MMA_N>;
@@ -152,14 +214,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr uint32_t kFmt = ESIZE == 2 ? 1u : (ESIZE == 4 ? 2u : 0u);
   constexpr uint32_t kIdesc = ptx::umma_idesc(kFmt, kBM, MMA_N);
   constexpr uint32_t kTmemCols = 2 * MMA_N;              // two accumulator buffers
-  constexpr uint32_t kStageTx = kABytes + Plan::kBBytes;
+  // bytes the TMA unit reports per stage: the gathered activation rows arrive through cp.async
+  // and are tracked by thread arrivals instead
+  constexpr uint32_t kStageTx = (GATHER ? 0 : kABytes) + Plan::kBBytes;
+  constexpr uint32_t kFullArrivals = GATHER ? 1 + kGatherThreads / 32 : 1;   // TMA thread + one per gather warp
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
-  const uint32_t bar_addr = tiles_addr + Plan::kTileBytes;
-  uint8_t* bar_ptr = tiles_ptr + Plan::kTileBytes;
+  const uint32_t staging_addr = tiles_addr + Plan::kTileBytes;
+  const uint32_t bar_addr = staging_addr + Plan::kStagingBytes;
+  uint8_t* bar_ptr = tiles_ptr + Plan::kTileBytes + Plan::kStagingBytes;
   // barrier map (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_addr + 8u * s; };
   auto empty_bar = [&](int s) { return bar_addr + 8u * (kStages + s); };
@@ -168,6 +234,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 192);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 200);
   int* pm = reinterpret_cast<int*>(bar_ptr + Plan::kBarBytes);
+  int* soff = pm + kMaxExperts + 2;   // offsets[] as 32-bit rows, read by every role at tile changes
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -175,12 +242,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // ---- set-up: barriers, tile prefix, tensor memory
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(full_bar(s), kFullArrivals);
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), 4);
+      ptx::mbar_init(tempty_bar(a), kEpilogueWarps);
     }
     *abort_flag = 0;
     pm[0] = 0;
@@ -189,10 +256,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     ptx::prefetch_tmap(&tmB0);
     if (DUAL) ptx::prefetch_tmap(&tmB1);
   }
-  for (int e = threadIdx.x; e < p.E; e += kThreads) {
-    long long len = p.offsets[e + 1] - p.offsets[e];
+  for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+    const long long o0 = p.offsets[e], o1 = p.offsets[e + 1];
+    long long len = o1 - o0;
     if (len < 0) len = 0;
     pm[e + 1] = static_cast<int>((len + kBM - 1) / kBM);
+    soff[e] = static_cast<int>(o0);
+    if (e == p.E - 1) soff[p.E] = static_cast<int>(o1 < o0 ? o0 : o1);
   }
   __syncthreads();
   if (warp == 0) {
@@ -224,83 +294,59 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int num_kb = p.num_kb;
 
   if (warp == 0) {
-    // =========================================================== producer
-    TileWalker walk(pm, p.n_tiles, p.E);
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      int e, mb, nb;
-      walk.decode(t, e, mb, nb);
-      const long long seg0 = p.offsets[e];
-      const long long seg1 = p.offsets[e + 1];
-      const long long row0 = seg0 + static_cast<long long>(mb) * kBM;
-      int r[4] = {0, 0, 0, 0};
-      if constexpr (GATHER) {
-        // Rows past the end of the segment re-read the tile's first row; their results are
-        // never stored.
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          long long rr = row0 + 4 * lane + j;
-          if (rr >= seg1) rr = row0;
-          long long src = p.index ? p.index[rr] / p.index_div : rr;
-          if (src < 0 || src >= p.a_rows) {
-            atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
-            src = 0;
+    // =========================================================== TMA producer (one thread)
+    if (lane == 0) {
+      TileWalker walk(pm, p.n_tiles, p.E);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int e, mb, nb;
+        walk.decode(t, e, mb, nb);
+        const int row0 = soff[e] + mb * kBM;
+        const int n0 = nb * kTileN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                      FMOE_DEV_WAIT_PRODUCER)) {
+            ok = false;
+            break;
           }
-          r[j] = static_cast<int>(src);
-        }
-      }
-      const int n0 = nb * kTileN;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                                    FMOE_DEV_WAIT_PRODUCER)) {
-          ok = false;
-          break;
-        }
-        const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
-        const uint32_t b_dst = a_dst + kABytes;
-        const uint32_t bar = full_bar(stage);
-        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, kStageTx);
-        __syncwarp();
-        const int k0 = kb * kKElems;
-        if constexpr (GATHER) {
-          ptx::tma_gather4_2d(a_dst + lane * 512u, &tmA, bar, k0, r[0], r[1], r[2], r[3]);
-        } else {
-          if (lane == 0) ptx::tma_load_2d(a_dst, &tmA, bar, k0, static_cast<int>(row0));
-        }
-        if (lane == 0) {
+          const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          const uint32_t bar = full_bar(stage);
+          ptx::mbar_arrive_expect_tx(bar, kStageTx);
+          const int k0 = kb * kKElems;
+          if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
           ptx::tma_load_3d(b_dst, &tmB0, bar, k0, n0, e);
           if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
-        }
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // =========================================================== MMA issuer
-    int stage = 0;
-    uint32_t phase = 0;
-    int it = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
-                                  FMOE_DEV_WAIT_MMA)) {
-        break;
-      }
-      ptx::tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * MMA_N;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
-          ok = false;
+    // =========================================================== MMA issuer (one thread)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
           break;
         }
         ptx::tc_fence_after();
-        if (lane == 0) {
+        const uint32_t d_tmem = tmem_base + acc * MMA_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
           const uint32_t a_src = tiles_addr + stage * Plan::kStageBytes;
           const uint64_t da = ptx::umma_desc_k_sw128(a_src);
           const uint64_t db = ptx::umma_desc_k_sw128(a_src + kABytes);
@@ -310,41 +356,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           ptx::umma_commit(empty_bar(stage));      // stage reusable once these MMAs have read it
           if (kb == num_kb - 1) ptx::umma_commit(tfull_bar(acc));
-        }
-        __syncwarp();
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
-  } else {
-    // =========================================================== epilogue (4 warps)
+  } else if (warp < 2 + kEpilogueWarps) {
+    // =========================================================== epilogue (8 warps)
+    // A warp may only read the TMEM lanes of its quarter (warp id mod 4); two warps share a
+    // quarter and split the tile's columns. Each warp pulls its whole share of the accumulator
+    // into registers with back-to-back tcgen05.ld, waits once, hands the buffer back to the MMA
+    // warp, and only then does the arithmetic and the stores.
     TileWalker walk(pm, p.n_tiles, p.E);
-    const int q = warp & 3;                    // TMEM lane quarter this warp may read
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row_in_tile = q * 32 + lane;
-    const bool fp8 = (ESIZE == 1);
+    constexpr bool fp8 = (ESIZE == 1);
+    constexpr int kChunks = kTileN / 64;              // 32-column chunks per warp: 4 plain, 2 gated
+    const uint32_t stage_w = staging_addr + (warp - 2) * 2048;
+    const int c_begin = half * kChunks * 32;
     int it = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
       int e, mb, nb;
       walk.decode(t, e, mb, nb);
-      const long long seg1 = p.offsets[e + 1];
-      const long long row = p.offsets[e] + static_cast<long long>(mb) * kBM + row_in_tile;
-      const bool row_ok = row < seg1;
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      if (!ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, p.status, FMOE_DEV_WAIT_EPILOGUE)) {
-        break;
-      }
-      ptx::tc_fence_after();
-      float inv_a = 1.0f;
+      const long long row = static_cast<long long>(soff[e]) + mb * kBM + row_in_tile;
+      const bool row_ok = row < soff[e + 1];
+      float scale_a = 1.0f;
       if (fp8 && p.a_scale != nullptr && row_ok) {
         long long src = row;
         if (GATHER && p.index) src = p.index[row] / p.index_div;
         if (src < 0 || src >= p.a_rows) src = 0;
-        inv_a = p.a_scale[src];
+        scale_a = p.a_scale[src];
       }
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MMA_N;
       long long dst_row = row;
       if (p.out_index != nullptr && row_ok) {
         dst_row = p.out_index[row];
@@ -354,57 +399,176 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       OutT* out_row = reinterpret_cast<OutT*>(p.out) + dst_row * p.ldo;
+      // Coalesced store phase: lane l writes the 16-byte piece (l & 3) of rows (l >> 2) + 8 i.
+      // It needs those rows' destinations, which live in the lanes that own them.
+      OutT* st_row[4];
+      bool st_ok[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int src_lane = (lane >> 2) + 8 * i;
+        const unsigned long long ptr_bits =
+            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out_row), src_lane);
+        st_row[i] = reinterpret_cast<OutT*>(ptr_bits);
+        st_ok[i] = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, src_lane) != 0;
+      }
       const int n0 = nb * kTileN;
-#pragma unroll 1
-      for (int c = 0; c < kTileN; c += 32) {
-        uint32_t r0[32];
-        float v[32];
-        ptx::tmem_ld_32x32b_x32(t_row + c, r0);
-        if constexpr (DUAL) {
-          uint32_t r1[32];
-          ptx::tmem_ld_32x32b_x32(t_row + kTileN + c, r1);
-          ptx::tmem_ld_wait();
-          const int col0 = n0 + c;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      if (!ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, p.status, FMOE_DEV_WAIT_EPILOGUE)) {
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MMA_N + c_begin;
+      // 64 accumulator registers in flight per round: two 32-column chunks (plain), or one chunk
+      // of each of the two accumulators (gated)
+      constexpr int kPerRound = DUAL ? 1 : 2;
+#pragma unroll
+      for (int j0 = 0; j0 < kChunks; j0 += kPerRound) {
+        uint32_t r0[kPerRound][32];
+        uint32_t r1[kPerRound][32];
+#pragma unroll
+        for (int j = 0; j < kPerRound; ++j) {
+          ptx::tmem_ld_32x32b_x32(t_row + 32 * (j0 + j), r0[j]);
+          if constexpr (DUAL) ptx::tmem_ld_32x32b_x32(t_row + kTileN + 32 * (j0 + j), r1[j]);
+        }
+        ptx::tmem_ld_wait();
+        if (j0 + kPerRound >= kChunks) {
+          // last read of this accumulator buffer: the next tile's MMAs may overwrite it
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        }
+#pragma unroll
+        for (int j = 0; j < kPerRound; ++j) {
+          const int col0 = n0 + c_begin + 32 * (j0 + j);
+          const int ncols = min(32, p.N - col0);
+          float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = col0 + i;
-            float g = __uint_as_float(r0[i]);
-            float u = __uint_as_float(r1[i]);
+            float g = __uint_as_float(r0[j][i]);
+            float u = DUAL ? __uint_as_float(r1[j][i]) : 0.f;
             if (col < p.N) {
               if (fp8 && p.a_scale != nullptr) {
                 const long long so = static_cast<long long>(e) * p.bscale_se + col;
-                g = __bfloat162float(__float2bfloat16_rn(g)) / (inv_a * p.b0_scale[so]);
-                u = __bfloat162float(__float2bfloat16_rn(u)) / (inv_a * p.b1_scale[so]);
+                g = __bfloat162float(__float2bfloat16_rn(g)) / (scale_a * p.b0_scale[so]);
+                if constexpr (DUAL) u = __bfloat162float(__float2bfloat16_rn(u)) / (scale_a * p.b1_scale[so]);
               }
               if (p.bias0) g += load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col);
-              if (p.bias1) u += load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col);
+              if constexpr (DUAL) {
+                if (p.bias1) u += load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col);
+              }
             }
-            v[i] = silu_f(g) * u;
+            if constexpr (DUAL) {
+              v[i] = silu_f(g) * u;
+            } else {
+              v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
+            }
           }
-        } else {
-          ptx::tmem_ld_wait();
-          const int col0 = n0 + c;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            float g = __uint_as_float(r0[i]);
-            if (col < p.N) {
-              if (fp8 && p.a_scale != nullptr) {
-                const long long so = static_cast<long long>(e) * p.bscale_se + col;
-                g = __bfloat162float(__float2bfloat16_rn(g)) / (inv_a * p.b0_scale[so]);
-              }
-              if (p.bias0) g += load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col);
-            }
-            v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
+          if (ncols == 32 && p.vec_ok) {
+            stage_and_store<OutT>(stage_w, lane, v, st_row, st_ok, col0);
+          } else if (row_ok && ncols > 0) {
+            store_chunk<OutT>(out_row + col0, v, ncols, false);
           }
         }
-        const int ncols = min(32, p.N - (n0 + c));
-        if (row_ok && ncols > 0) store_chunk<OutT>(out_row + n0 + c, v, ncols, p.vec_ok != 0);
       }
-      // accumulator buffer free again
-      ptx::tc_fence_before();
+    }
+  } else {
+    // =========================================================== activation-row gather (4 warps)
+    // Thread g copies the 16-byte piece (g & 7) of rows (g >> 3) + 16 i, i = 0..7: eight
+    // neighbouring threads read one full 128-byte line of a token row, and write it into the
+    // 128-byte-swizzled tile (piece c of row r lands at r * 128 + ((c ^ (r & 7)) << 4)).
+    if constexpr (GATHER) {
+      TileWalker walk(pm, p.n_tiles, p.E);
+      const int g = threadIdx.x - kThreads;
+      const int piece = g & 7;
+      const int rbase = g >> 3;
+      const uint32_t dst_off = rbase * kRowBytes + ((piece ^ (rbase & 7)) << 4);
+      const long long k_bytes = static_cast<long long>(p.K) * ESIZE;
+      const long long lda_bytes = p.lda * ESIZE;
+      const uint8_t* a_base = reinterpret_cast<const uint8_t*>(p.a);
+      // Row addresses of a tile: rows past the end of the segment re-read the tile's first row
+      // (their results are never stored).
+      auto tile_rows = [&](int t, const uint8_t* (&dst)[8]) {
+        int e, mb, nb;
+        walk.decode(t, e, mb, nb);
+        const int seg1 = soff[e + 1];
+        const int row0 = soff[e] + mb * kBM;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          int rr = row0 + rbase + 16 * i;
+          if (rr >= seg1) rr = row0;
+          long long srow = p.index[rr] / p.index_div;
+          if (srow < 0 || srow >= p.a_rows) {
+            atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
+            srow = 0;
+          }
+          dst[i] = a_base + srow * lda_bytes + piece * 16;
+        }
+      };
+      constexpr int kLag = 2;   // stages between issuing a copy and publishing it (< kStages)
+      int stage = 0;
+      int arr_stage = 0;
+      int issued = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint8_t* src[8];
+      const uint8_t* nsrc[8];
+      if (static_cast<int>(blockIdx.x) < total_tiles) tile_rows(blockIdx.x, src);
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        // the next tile's indices are fetched while this tile's K loop runs
+        const int t_next = t + gridDim.x;
+        if (t_next < total_tiles) {
+          tile_rows(t_next, nsrc);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) nsrc[i] = src[i];
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                      FMOE_DEV_WAIT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const long long koff = static_cast<long long>(kb) * kRowBytes;
+          // K is a multiple of 16 bytes: a piece is either whole or entirely past the end (zero-filled)
+          const uint32_t nbytes = (koff + piece * 16 < k_bytes) ? 16u : 0u;
+          const uint32_t dst = tiles_addr + stage * Plan::kStageBytes + dst_off;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            ptx::cp_async_16(dst + i * 16 * kRowBytes, src[i] + (nbytes ? koff : 0), nbytes);
+          }
+          ptx::cp_async_commit();
+          ++issued;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          // Publish the stage issued kLag iterations ago: by now its copies have normally landed,
+          // so the wait does not stall. One arrival per warp instead of one per thread keeps the
+          // mbarrier from becoming the bottleneck.
+          if (issued > kLag) {
+            ptx::cp_async_wait_group<kLag>();
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(full_bar(arr_stage));
+            if (++arr_stage == kStages) arr_stage = 0;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) src[i] = nsrc[i];
+      }
+      // drain: publish what is still in flight
+      ptx::cp_async_wait_all();
+      ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (ok) {
+        const int left = issued < kLag ? issued : kLag;
+        for (int r = 0; r < left; ++r) {
+          if (lane == 0) ptx::mbar_arrive(full_bar(arr_stage));
+          if (++arr_stage == kStages) arr_stage = 0;
+        }
+      }
     }
   }
 
@@ -483,7 +647,7 @@ int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap&
     FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal));
     attr_set = true;
   }
-  kern<<<grid, kThreads, Plan::kTotal, stream>>>(tmA, tmB0, tmB1, p);
+  kern<<<grid, GATHER ? kThreads + kGatherThreads : kThreads, Plan::kTotal, stream>>>(tmA, tmB0, tmB1, p);
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_launches;
   return FMOE_OK;
@@ -521,6 +685,10 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
                 "grouped_gemm: TMA needs 16-byte aligned bases and row strides (lda=%lld, b_sn=%lld, b_se=%lld "
                 "elements of %d bytes)", (long long)d.lda, (long long)d.b_sn, (long long)d.b_se, esize);
   }
+  if (d.index != nullptr && (static_cast<long long>(d.K) * esize) % 16 != 0) {
+    return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: gathered rows need K to be a multiple of 16 bytes (K=%d x %d B); pad K",
+                d.K, esize);
+  }
   if (d.total_rows <= 0) return FMOE_OK;
   FMOE_REQUIRE(d.a_rows >= 1, "grouped_gemm: empty A source with %lld output rows", (long long)d.total_rows);
   FMOE_REQUIRE(d.a_rows < (1ll << 31) && d.total_rows < (1ll << 31), "grouped_gemm: more than 2^31 rows");
@@ -543,7 +711,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.a_rows)};
     cuuint64_t str[1] = {static_cast<cuuint64_t>(d.lda) * esize};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(k_elems), gather ? 1u : static_cast<cuuint32_t>(kBM)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(kBM)};
     int rc = make_tmap(&tmA, d.dtype, 2, d.a, dims, str, box, "activations");
     if (rc != FMOE_OK) return rc;
   }
@@ -572,6 +740,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.K = d.K;
   p.num_kb = (d.K + k_elems - 1) / k_elems;
   p.n_tiles = (d.N + tile_n - 1) / tile_n;
+  p.a = d.a;
+  p.lda = d.lda;
   p.a_rows = d.a_rows;
   p.out = d.out;
   p.ldo = d.ldo;

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the grouped GEMM uses:
-// mbarrier, TMA (cp.async.bulk.tensor, tile and tile::gather4 modes), tensor memory
+// mbarrier, TMA (cp.async.bulk.tensor tile mode), cp.async with mbarrier completion, tensor memory
 // (tcgen05.alloc/ld/dealloc) and the 5th-generation tensor-core MMA (tcgen05.mma).
 // Every spin-wait in here is bounded; nothing traps.
 #pragma once
@@ -65,14 +65,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // than limit_ns, in which case it raises the flag itself and records `code` in *status
 // (first error wins). The caller must then leave its loop and fall through to the
 // common tear-down; nothing ever spins without a limit.
+//
+// The hot path is a bare try_wait loop: the first kFastSpins polls read no timer at all (reading
+// %globaltimer costs hundreds of cycles, which showed up as ~500 cycles per pipeline stage when
+// it sat in front of every wait that was not immediately ready). Only a wait that has already
+// spun for a long time starts looking at the clock, about once per 1024 polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag, int* status, int code,
                                                   uint64_t limit_ns = 2000000000ull) {
-  if (mbar_try_wait(bar, parity)) return true;
+  constexpr uint32_t kFastSpins = 1u << 14;
+#pragma unroll 1
+  for (uint32_t i = 0; i < kFastSpins; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (((++spins) & 63u) == 0u) {
+    if (((++spins) & 1023u) == 0u) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
@@ -116,17 +125,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
-// Gather of four independent rows (r0..r3) of a 2-D tensor, same column window c0; the
-// four rows land back to back at dst (4 x box bytes). The tensor map's box is {cols, 1}.
-__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar,
-                                               int c0, int r0, int r1, int r2, int r3) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(r0), "r"(r1),
-      "r"(r2), "r"(r3)
-      : "memory");
+// ---------------------------------------------------------------- cp.async (per-thread 16-byte copies)
+// Copies src_bytes (0 or 16) bytes from global memory and zero-fills the rest of the 16.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Blocks until at most N of this thread's most recent cp.async groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ---------------------------------------------------------------- tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {

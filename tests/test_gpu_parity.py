@@ -234,10 +234,14 @@ def test_fp8_up_projection_against_golden(name):
     assert out.dtype == torch.bfloat16
     # bound of the reference's fp8-vs-emulation test (kernels/tests/moe_fp8_test.py:337-370)
     torch.testing.assert_close(out.float().cpu(), g["out"].float(), rtol=1e-2, atol=1e-2)
-    # dequantised result within 6e-2 (relative to the row's largest magnitude) of the unquantised product
+    # against the unquantised product: the reference's own bound for these small-K, U(-1,1) shapes
+    # (kernels/tests/moe_fp8_test.py:302-335); the quantisation error must not exceed what the
+    # reference's emulation itself shows on the same data
     ref = g["out_unquantised"]
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=1e-1, atol=4e-1)
     rel = (out.float().cpu() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-6)
-    assert rel.max().item() < 6e-2
+    rel_golden = (g["out"].float() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-6)
+    assert rel.max().item() <= rel_golden.max().item() * 1.1 + 1e-3
     clean_status()
 
 
