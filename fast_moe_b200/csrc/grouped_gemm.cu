@@ -11,20 +11,28 @@
 // and the Triton kernels that sit behind the same operators
 // (kernels/triton/triton_moe.py:184-282, :2526-2671, :3167-3347; triton_moe_fp8.py:770-884).
 //
-// Shape of the kernel (one persistent CTA per SM):
-//   warp 0   producer: TMA loads into a ring of shared-memory stages. The activation rows of a
-//            tile are scattered in memory, so they are fetched with TMA tile::gather4 (each lane
-//            gathers four token rows, 32 lanes = one 128-row tile); weights come as ordinary
-//            3-D tiles of the [E, N, K] tensor. Both land in the 128-byte-swizzled K-major
-//            layout the tensor core reads.
-//   warp 1   one elected thread issues tcgen05.mma (M=128, N up to 256, fp32 accumulators in
-//            tensor memory, double buffered so the epilogue of tile i overlaps the MMAs of i+1).
-//   warps 2-5 epilogue: tcgen05.ld the accumulator, apply rowwise FP8 descale / bias / SiLU /
-//            SwiGLU, convert and store only the rows and columns that exist.
+// Shape of the kernel: persistent CTAs, one per SM, either alone (128-row tiles) or as CTA pairs
+// (clusters of two, tcgen05 cta_group::2, 256-row tiles: each CTA stages its own 128 activation
+// rows and its half of the 256 weight rows, which halves the shared-memory traffic per FLOP).
+//   warp 0     one thread issues the TMA loads (weights as 3-D tiles of [E, N, K]; activations
+//              as 2-D tiles when their rows are contiguous) into a ring of shared-memory stages.
+//   warp 1     one thread (of the pair's leader CTA) issues tcgen05.mma, M = 128 or 256, N = 256,
+//              fp32 accumulators in tensor memory, double buffered so that the epilogue of tile
+//              i overlaps the MMAs of tile i+1.
+//   warps 2-9  epilogue: tcgen05.ld the accumulator, rowwise FP8 descale / bias / SiLU / SwiGLU,
+//              convert, transpose through shared memory and store whole lines; only rows and
+//              columns that exist are written; rows may be scattered (out_index).
+//   warps 10-13 (kernels that gather): the rows of a tile are scattered over the token matrix, so
+//              these warps fetch them with 16-byte cp.async copies straight into the 128-byte-
+//              swizzled K-major layout the tensor core reads (TMA's 4-row gather mode was
+//              measured at half the throughput of this for 128-byte row pieces).
+//   warp 14    (pairs that gather) forwards "rows have landed" to the leader CTA's barrier.
 // Tiles are enumerated on the device from `offsets` (variable rows per expert, empty experts
-// contribute nothing), so no host synchronisation is needed and no CTA is launched for work
-// that does not exist.
+// contribute nothing), so no host synchronisation is needed and no CTA is launched for work that
+// does not exist. Every wait is bounded; a wait that gives up records a status code and the
+// kernel drains instead of hanging.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <stdio.h>
 
 #include "common.cuh"
@@ -33,11 +41,14 @@
 namespace fmoe {
 namespace {
 
-constexpr int kBM = 128;            // rows per tile (= TMEM lanes)
+constexpr int kBM = 128;            // rows per CTA and tile (= TMEM lanes)
+constexpr int kMmaN = 256;          // accumulator columns per tile
 constexpr int kRowBytes = 128;      // bytes of K per stage row: one swizzle atom
 constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // TMA warp + MMA warp + epilogue warps
-constexpr int kGatherThreads = 128;    // 4 extra warps that gather activation rows (GATHER kernels)
+constexpr int kGatherWarps = 4;
+constexpr int kGatherThreads = 32 * kGatherWarps;
+constexpr int kBaseThreads = 64 + 32 * kEpilogueWarps;           // TMA warp, MMA warp, epilogue warps
+constexpr int kGatherKernelThreads = kBaseThreads + kGatherThreads + 32;   // + gather warps + relay warp
 constexpr int kMaxExperts = 1024;
 constexpr int kABytes = kBM * kRowBytes;
 
@@ -67,13 +78,13 @@ struct GemmParams {
   int* status;
 };
 
-template <int MMA_N>
+template <int CTAS>
 struct SmemPlan {
-  static constexpr int kBBytes = MMA_N * kRowBytes;
+  static constexpr int kBBytes = (kMmaN / CTAS) * kRowBytes;     // weight rows this CTA stages
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (MMA_N == 256) ? 4 : 6;
+  static constexpr int kStages = (CTAS == 1) ? 4 : 6;
   static constexpr int kTileBytes = kStages * kStageBytes;
-  static constexpr int kStagingBytes = kEpilogueWarps * 2048;   // 32 rows x 64 bytes per epilogue warp
+  static constexpr int kStagingBytes = kEpilogueWarps * 2048;    // 32 rows x 64 bytes per epilogue warp
   static constexpr int kBarBytes = 256;
   static constexpr int kPmBytes = 2 * ((kMaxExperts + 1) * 4 + 12);   // tile prefix + row offsets
   static constexpr int kTotal = 1024 + kTileBytes + kStagingBytes + kBarBytes + kPmBytes;
@@ -201,23 +212,27 @@ struct TileWalker {
   }
 };
 
-template <int ESIZE, int MMA_N, bool DUAL, bool GATHER, typename OutT>
-__global__ void __launch_bounds__(GATHER ? kThreads + kGatherThreads : kThreads, 1)
+template <int ESIZE, int CTAS, bool DUAL, bool GATHER, typename OutT>
+__global__ void __launch_bounds__(GATHER ? kGatherKernelThreads : kBaseThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
-  using Plan = SmemPlan<MMA_N>;
+  using Plan = SmemPlan<CTAS>;
+  constexpr bool kPair = (CTAS == 2);
   constexpr int kStages = Plan::kStages;
-  constexpr int kTileN = DUAL ? MMA_N / 2 : MMA_N;       // output columns per tile
+  constexpr int kTileRows = kBM * CTAS;                  // rows per tile (both CTAs of a pair)
+  constexpr int kTileN = DUAL ? kMmaN / 2 : kMmaN;       // output columns per tile
   constexpr int kKElems = kRowBytes / ESIZE;             // K elements per stage
   constexpr int kUmmaKBytes = 32;                        // bytes of K per tcgen05.mma
   constexpr int kKind = ESIZE == 2 ? ptx::KIND_F16 : (ESIZE == 4 ? ptx::KIND_TF32 : ptx::KIND_F8);
   constexpr uint32_t kFmt = ESIZE == 2 ? 1u : (ESIZE == 4 ? 2u : 0u);
-  constexpr uint32_t kIdesc = ptx::umma_idesc(kFmt, kBM, MMA_N);
-  constexpr uint32_t kTmemCols = 2 * MMA_N;              // two accumulator buffers
-  // bytes the TMA unit reports per stage: the gathered activation rows arrive through cp.async
-  // and are tracked by thread arrivals instead
-  constexpr uint32_t kStageTx = (GATHER ? 0 : kABytes) + Plan::kBBytes;
-  constexpr uint32_t kFullArrivals = GATHER ? 1 + kGatherThreads / 32 : 1;   // TMA thread + one per gather warp
+  constexpr uint32_t kIdesc = ptx::umma_idesc(kFmt, kTileRows, kMmaN);
+  constexpr uint32_t kTmemCols = 2 * kMmaN;              // two accumulator buffers
+  // Bytes the TMA unit reports per stage to the (leader's) full barrier; gathered activation rows
+  // arrive through cp.async and are tracked by thread arrivals instead.
+  constexpr uint32_t kStageTx = CTAS * ((GATHER ? 0 : kABytes) + Plan::kBBytes);
+  // Arrivals on a full barrier: the leader's TMA thread, plus (gather) either every gather thread
+  // of a lone CTA or one relay thread per CTA of a pair.
+  constexpr uint32_t kFullArrivals = !GATHER ? 1 : (kPair ? 1 + CTAS : 1 + kGatherThreads);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -226,11 +241,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t staging_addr = tiles_addr + Plan::kTileBytes;
   const uint32_t bar_addr = staging_addr + Plan::kStagingBytes;
   uint8_t* bar_ptr = tiles_ptr + Plan::kTileBytes + Plan::kStagingBytes;
-  // barrier map (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  // barrier map (8 bytes each): full[S], empty[S], afull[S], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_addr + 8u * s; };
   auto empty_bar = [&](int s) { return bar_addr + 8u * (kStages + s); };
-  auto tfull_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + 2 + a); };
+  auto afull_bar = [&](int s) { return bar_addr + 8u * (2 * kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_addr + 8u * (3 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_addr + 8u * (3 * kStages + 2 + a); };
+  static_assert(8 * (3 * kStages + 4) <= 192, "barrier area too small");
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 192);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 200);
   int* pm = reinterpret_cast<int*>(bar_ptr + Plan::kBarBytes);
@@ -238,16 +255,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;    // 0 = leader of the pair
+  const int unit = blockIdx.x / CTAS;                            // persistent work unit (CTA or pair)
+  const int num_units = gridDim.x / CTAS;
 
   // ---- set-up: barriers, tile prefix, tensor memory
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), kFullArrivals);
       ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(afull_bar(s), kGatherThreads);
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), kEpilogueWarps);
+      ptx::mbar_init(tempty_bar(a), kEpilogueWarps * CTAS);
     }
     *abort_flag = 0;
     pm[0] = 0;
@@ -260,7 +281,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const long long o0 = p.offsets[e], o1 = p.offsets[e + 1];
     long long len = o1 - o0;
     if (len < 0) len = 0;
-    pm[e + 1] = static_cast<int>((len + kBM - 1) / kBM);
+    pm[e + 1] = static_cast<int>((len + kTileRows - 1) / kTileRows);
     soff[e] = static_cast<int>(o0);
     if (e == p.E - 1) soff[p.E] = static_cast<int>(o1 < o0 ? o0 : o1);
   }
@@ -282,11 +303,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
-    ptx::tmem_relinquish();
+    ptx::tmem_alloc<CTAS>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    ptx::tmem_relinquish<CTAS>();
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync_all();   // the peer's barriers exist before anything signals them
   ptx::tc_fence_after();
 
   const uint32_t tmem_base = *tmem_slot;
@@ -300,10 +322,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += num_units) {
         int e, mb, nb;
         walk.decode(t, e, mb, nb);
-        const int row0 = soff[e] + mb * kBM;
+        const int row0 = soff[e] + mb * kTileRows + static_cast<int>(rank) * kBM;
         const int n0 = nb * kTileN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
@@ -313,12 +335,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
-          const uint32_t bar = full_bar(stage);
-          ptx::mbar_arrive_expect_tx(bar, kStageTx);
           const int k0 = kb * kKElems;
-          if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
-          ptx::tma_load_3d(b_dst, &tmB0, bar, k0, n0, e);
-          if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+          if constexpr (!kPair) {
+            const uint32_t bar = full_bar(stage);
+            ptx::mbar_arrive_expect_tx(bar, kStageTx);
+            if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
+            ptx::tma_load_3d(b_dst, &tmB0, bar, k0, n0, e);
+            if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+          } else {
+            // Both CTAs report their bytes to the leader's barrier; only the leader arms it.
+            const uint32_t bar = ptx::mapa(full_bar(stage), 0);
+            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), kStageTx);
+            if constexpr (!GATHER) ptx::tma_load_2d_pair(a_dst, &tmA, bar, k0, row0);
+            if constexpr (DUAL) {
+              // leader stages the gate weights, its peer the up weights: 128 rows each
+              ptx::tma_load_3d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, k0, n0, e);
+            } else {
+              ptx::tma_load_3d_pair(b_dst, &tmB0, bar, k0, n0 + static_cast<int>(rank) * (kMmaN / 2), e);
+            }
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -327,35 +362,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    // =========================================================== MMA issuer (one thread)
-    if (lane == 0) {
+    // =========================================================== MMA issuer (one thread, leader CTA)
+    if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = unit; t < total_tiles && ok; t += num_units, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * MMA_N;
+        const uint32_t d_tmem = tmem_base + acc * kMmaN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
             ok = false;
             break;
           }
+          if constexpr (GATHER) ptx::fence_proxy_async_smem();   // rows written by cp.async (generic proxy)
           ptx::tc_fence_after();
           const uint32_t a_src = tiles_addr + stage * Plan::kStageBytes;
           const uint64_t da = ptx::umma_desc_k_sw128(a_src);
           const uint64_t db = ptx::umma_desc_k_sw128(a_src + kABytes);
 #pragma unroll
           for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
-            ptx::umma_ss<kKind>(d_tmem, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_ss<kKind, CTAS>(d_tmem, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
-          ptx::umma_commit(empty_bar(stage));      // stage reusable once these MMAs have read it
-          if (kb == num_kb - 1) ptx::umma_commit(tfull_bar(acc));
+          ptx::umma_commit<CTAS>(empty_bar(stage));      // stage reusable once these MMAs have read it
+          if (kb == num_kb - 1) ptx::umma_commit<CTAS>(tfull_bar(acc));
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -366,22 +402,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp < 2 + kEpilogueWarps) {
     // =========================================================== epilogue (8 warps)
     // A warp may only read the TMEM lanes of its quarter (warp id mod 4); two warps share a
-    // quarter and split the tile's columns. Each warp pulls its whole share of the accumulator
-    // into registers with back-to-back tcgen05.ld, waits once, hands the buffer back to the MMA
-    // warp, and only then does the arithmetic and the stores.
+    // quarter and split the tile's columns. Each round pulls 64 accumulator values per thread
+    // into registers; after the last round the buffer is handed back to the MMA thread, and
+    // only then come the arithmetic and the stores of that round.
     TileWalker walk(pm, p.n_tiles, p.E);
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    const int row_in_tile = q * 32 + lane;
+    const int row_in_tile = static_cast<int>(rank) * kBM + q * 32 + lane;
     constexpr bool fp8 = (ESIZE == 1);
     constexpr int kChunks = kTileN / 64;              // 32-column chunks per warp: 4 plain, 2 gated
-    const uint32_t stage_w = staging_addr + (warp - 2) * 2048;
     const int c_begin = half * kChunks * 32;
+    const uint32_t stage_w = staging_addr + (warp - 2) * 2048;
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int t = unit; t < total_tiles; t += num_units, ++it) {
       int e, mb, nb;
       walk.decode(t, e, mb, nb);
-      const long long row = static_cast<long long>(soff[e]) + mb * kBM + row_in_tile;
+      const long long row = static_cast<long long>(soff[e]) + mb * kTileRows + row_in_tile;
       const bool row_ok = row < soff[e + 1];
       float scale_a = 1.0f;
       if (fp8 && p.a_scale != nullptr && row_ok) {
@@ -418,7 +454,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       ptx::tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MMA_N + c_begin;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kMmaN + c_begin;
       // 64 accumulator registers in flight per round: two 32-column chunks (plain), or one chunk
       // of each of the two accumulators (gated)
       constexpr int kPerRound = DUAL ? 1 : 2;
@@ -436,7 +472,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           // last read of this accumulator buffer: the next tile's MMAs may overwrite it
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if constexpr (kPair) {
+              ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
+            } else {
+              ptx::mbar_arrive(tempty_bar(acc));
+            }
+          }
         }
 #pragma unroll
         for (int j = 0; j < kPerRound; ++j) {
@@ -473,14 +515,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
-  } else {
+  } else if (warp < 2 + kEpilogueWarps + kGatherWarps) {
     // =========================================================== activation-row gather (4 warps)
     // Thread g copies the 16-byte piece (g & 7) of rows (g >> 3) + 16 i, i = 0..7: eight
     // neighbouring threads read one full 128-byte line of a token row, and write it into the
     // 128-byte-swizzled tile (piece c of row r lands at r * 128 + ((c ^ (r & 7)) << 4)).
     if constexpr (GATHER) {
       TileWalker walk(pm, p.n_tiles, p.E);
-      const int g = threadIdx.x - kThreads;
+      const int g = threadIdx.x - kBaseThreads;
       const int piece = g & 7;
       const int rbase = g >> 3;
       const uint32_t dst_off = rbase * kRowBytes + ((piece ^ (rbase & 7)) << 4);
@@ -493,11 +535,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int e, mb, nb;
         walk.decode(t, e, mb, nb);
         const int seg1 = soff[e + 1];
-        const int row0 = soff[e] + mb * kBM;
+        const int tile0 = soff[e] + mb * kTileRows;
+        const int row0 = tile0 + static_cast<int>(rank) * kBM;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           int rr = row0 + rbase + 16 * i;
-          if (rr >= seg1) rr = row0;
+          if (rr >= seg1) rr = tile0;
           long long srow = p.index[rr] / p.index_div;
           if (srow < 0 || srow >= p.a_rows) {
             atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
@@ -506,18 +549,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           dst[i] = a_base + srow * lda_bytes + piece * 16;
         }
       };
-      constexpr int kLag = 2;   // stages between issuing a copy and publishing it (< kStages)
       int stage = 0;
-      int arr_stage = 0;
-      int issued = 0;
       uint32_t phase = 0;
       bool ok = true;
       const uint8_t* src[8];
       const uint8_t* nsrc[8];
-      if (static_cast<int>(blockIdx.x) < total_tiles) tile_rows(blockIdx.x, src);
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      if (unit < total_tiles) tile_rows(unit, src);
+      for (int t = unit; t < total_tiles && ok; t += num_units) {
         // the next tile's indices are fetched while this tile's K loop runs
-        const int t_next = t + gridDim.x;
+        const int t_next = t + num_units;
         if (t_next < total_tiles) {
           tile_rows(t_next, nsrc);
         } else {
@@ -538,35 +578,39 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int i = 0; i < 8; ++i) {
             ptx::cp_async_16(dst + i * 16 * kRowBytes, src[i] + (nbytes ? koff : 0), nbytes);
           }
-          ptx::cp_async_commit();
-          ++issued;
+          // one arrival per thread, delivered by the hardware when this thread's copies have landed
+          ptx::cp_async_mbar_arrive_noinc(kPair ? afull_bar(stage) : full_bar(stage));
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
-          }
-          // Publish the stage issued kLag iterations ago: by now its copies have normally landed,
-          // so the wait does not stall. One arrival per warp instead of one per thread keeps the
-          // mbarrier from becoming the bottleneck.
-          if (issued > kLag) {
-            ptx::cp_async_wait_group<kLag>();
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(full_bar(arr_stage));
-            if (++arr_stage == kStages) arr_stage = 0;
           }
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) src[i] = nsrc[i];
       }
-      // drain: publish what is still in flight
       ptx::cp_async_wait_all();
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (ok) {
-        const int left = issued < kLag ? issued : kLag;
-        for (int r = 0; r < left; ++r) {
-          if (lane == 0) ptx::mbar_arrive(full_bar(arr_stage));
-          if (++arr_stage == kStages) arr_stage = 0;
+    }
+  } else {
+    // =========================================================== relay (pairs that gather)
+    // "This CTA's gathered rows of stage s have landed" -> one arrival on the leader's full barrier.
+    if constexpr (GATHER && kPair) {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = unit; t < total_tiles && ok; t += num_units) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!ptx::mbar_wait_bounded(afull_bar(stage), phase, abort_flag, p.status, FMOE_DEV_WAIT_PRODUCER)) {
+              ok = false;
+              break;
+            }
+            ptx::fence_proxy_async_smem();   // cp.async wrote through the generic proxy; the MMA reads via the async proxy
+            ptx::mbar_arrive_cluster(ptx::mapa(full_bar(stage), 0));
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
         }
       }
     }
@@ -581,9 +625,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __nanosleep(2000000);
     __syncthreads();
   }
+  // a CTA of a pair must not leave while its peer can still signal its barriers or read its tiles
+  if constexpr (kPair) ptx::cluster_sync_all();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    ptx::tmem_dealloc<CTAS>(tmem_base, kTmemCols);
   }
 }
 
@@ -637,31 +683,54 @@ int make_tmap(CUtensorMap* m, int dt, int rank, const void* base, const cuuint64
 int g_launches = 0;
 int g_num_sms = 0;
 
-template <int ESIZE, int MMA_N, bool DUAL, bool GATHER, typename OutT>
+template <int ESIZE, int CTAS, bool DUAL, bool GATHER, typename OutT>
 int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const GemmParams& p,
              int grid, cudaStream_t stream) {
-  using Plan = SmemPlan<MMA_N>;
-  auto kern = grouped_gemm_kernel<ESIZE, MMA_N, DUAL, GATHER, OutT>;
+  using Plan = SmemPlan<CTAS>;
+  auto kern = grouped_gemm_kernel<ESIZE, CTAS, DUAL, GATHER, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
     FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal));
     attr_set = true;
   }
-  kern<<<grid, GATHER ? kThreads + kGatherThreads : kThreads, Plan::kTotal, stream>>>(tmA, tmB0, tmB1, p);
-  FMOE_CUDA_OK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(GATHER ? kGatherKernelThreads : kBaseThreads, 1, 1);
+  cfg.dynamicSmemBytes = Plan::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CTAS > 1 ? 1 : 0;
+  FMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB0, tmB1, p));
   ++g_launches;
   return FMOE_OK;
 }
 
 template <int ESIZE, typename OutT>
-int dispatch_shape(bool dual, bool gather, const CUtensorMap& tmA, const CUtensorMap& tmB0,
+int dispatch_shape(int ctas, bool dual, bool gather, const CUtensorMap& tmA, const CUtensorMap& tmB0,
                    const CUtensorMap& tmB1, const GemmParams& p, int grid, cudaStream_t stream) {
-  if (dual) {
-    return gather ? launch_t<ESIZE, 256, true, true, OutT>(tmA, tmB0, tmB1, p, grid, stream)
-                  : launch_t<ESIZE, 256, true, false, OutT>(tmA, tmB0, tmB1, p, grid, stream);
+#define FMOE_GO(C, D, G) return launch_t<ESIZE, C, D, G, OutT>(tmA, tmB0, tmB1, p, grid, stream)
+  if (ctas == 2) {
+    if (dual) { if (gather) FMOE_GO(2, true, true); else FMOE_GO(2, true, false); }
+    if (gather) FMOE_GO(2, false, true); else FMOE_GO(2, false, false);
   }
-  return gather ? launch_t<ESIZE, 256, false, true, OutT>(tmA, tmB0, tmB1, p, grid, stream)
-                : launch_t<ESIZE, 256, false, false, OutT>(tmA, tmB0, tmB1, p, grid, stream);
+  if (dual) { if (gather) FMOE_GO(1, true, true); else FMOE_GO(1, true, false); }
+  if (gather) FMOE_GO(1, false, true); else FMOE_GO(1, false, false);
+#undef FMOE_GO
+}
+
+// 0 = choose by shape, 1 / 2 = force lone CTAs / CTA pairs (environment FMOE_GEMM_CTAS, read once).
+int forced_ctas() {
+  static int v = -1;
+  if (v < 0) {
+    const char* s = getenv("FMOE_GEMM_CTAS");
+    v = (s && (s[0] == '1' || s[0] == '2') && s[1] == 0) ? s[0] - '0' : 0;
+  }
+  return v;
 }
 
 }  // namespace
@@ -705,6 +774,13 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   const bool dual = d.epilogue == FMOE_EPI_SWIGLU;
   const bool gather = d.index != nullptr;
   const int tile_n = dual ? 128 : 256;
+  // Lone CTAs by default. CTA pairs (256-row tiles) measured the same on contiguous rows and
+  // slower on gathered rows (the extra relay hop) at the sizes tried so far; they stay selectable
+  // for measurements.
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = 1;
+  if (g_num_sms < 2) ctas = 1;
+  const int box_n = (ctas == 2 || dual) ? 128 : 256;   // weight rows one TMA load brings in
   const int k_elems = kRowBytes / esize;
 
   CUtensorMap tmA, tmB0, tmB1;
@@ -718,7 +794,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   {
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.N), static_cast<cuuint64_t>(d.E)};
     cuuint64_t str[2] = {static_cast<cuuint64_t>(d.b_sn) * esize, static_cast<cuuint64_t>(d.b_se) * esize};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(tile_n), 1u};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(box_n), 1u};
     int rc = make_tmap(&tmB0, d.dtype, 3, d.b0, dims, str, box, "weights");
     if (rc != FMOE_OK) return rc;
     if (dual) {
@@ -758,19 +834,22 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.status = status;
 
   // Persistent grid: one CTA per SM, never more CTAs than the largest possible tile count.
-  const long long max_m_tiles = (d.total_rows + kBM - 1) / kBM + d.E;
-  long long max_tiles = max_m_tiles * p.n_tiles;
-  int grid = static_cast<int>(max_tiles < g_num_sms ? max_tiles : g_num_sms);
-  if (grid < 1) grid = 1;
+  const int tile_rows = kBM * ctas;
+  const long long max_m_tiles = (d.total_rows + tile_rows - 1) / tile_rows + d.E;
+  const long long max_tiles = max_m_tiles * p.n_tiles;
+  const int units_avail = g_num_sms / ctas;
+  int units = static_cast<int>(max_tiles < units_avail ? max_tiles : units_avail);
+  if (units < 1) units = 1;
+  const int grid = units * ctas;
 
   if (d.dtype == FMOE_BF16) {
-    if (d.out_dtype == FMOE_BF16) return dispatch_shape<2, __nv_bfloat16>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
-    return dispatch_shape<2, float>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    if (d.out_dtype == FMOE_BF16) return dispatch_shape<2, __nv_bfloat16>(ctas, dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    return dispatch_shape<2, float>(ctas, dual, gather, tmA, tmB0, tmB1, p, grid, stream);
   } else if (d.dtype == FMOE_F32) {
-    return dispatch_shape<4, float>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    return dispatch_shape<4, float>(ctas, dual, gather, tmA, tmB0, tmB1, p, grid, stream);
   } else {
-    if (d.out_dtype == FMOE_BF16) return dispatch_shape<1, __nv_bfloat16>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
-    return dispatch_shape<1, float>(dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    if (d.out_dtype == FMOE_BF16) return dispatch_shape<1, __nv_bfloat16>(ctas, dual, gather, tmA, tmB0, tmB1, p, grid, stream);
+    return dispatch_shape<1, float>(ctas, dual, gather, tmA, tmB0, tmB1, p, grid, stream);
   }
 }
 

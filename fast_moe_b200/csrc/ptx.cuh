@@ -93,6 +93,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return true;
 }
 
+// ---------------------------------------------------------------- thread-block clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address, in the cluster-wide shared window, of the same shared-memory offset in CTA `cta`.
+__device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta));
+  return r;
+}
+// Arrival on a barrier that may live in the peer CTA (address from mapa).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Every thread of every CTA of the cluster must call this (hardware barrier, not a spin).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -125,10 +146,34 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// The same loads issued by a CTA of a CTA pair (cta_group::2): the data lands in the issuing CTA's
+// shared memory, the byte count is reported to `bar`, a cluster-window address that names the
+// barrier of the pair's leader CTA. No multicast: each CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 // ---------------------------------------------------------------- cp.async (per-thread 16-byte copies)
 // Copies src_bytes (0 or 16) bytes from global memory and zero-fills the rest of the 16.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// The mbarrier receives one arrival once every cp.async this thread has issued so far has landed;
+// that arrival is one of the barrier's expected arrivals (.noinc).
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // Blocks until at most N of this thread's most recent cp.async groups are still in flight.
@@ -139,17 +184,33 @@ __device__ __forceinline__ void cp_async_wait_group() {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ---------------------------------------------------------------- tensor memory
+// CTAS = 1: the CTA's own tensor memory. CTAS = 2: one warp of EACH CTA of the pair executes the
+// instruction, with the same shared-memory slot offset; both receive the same address.
+template <int CTAS = 1>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot),
-               "r"(ncols)
-               : "memory");
+  if constexpr (CTAS == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
+                 : "memory");
+  }
 }
+template <int CTAS = 1>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (CTAS == 1) {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
 }
+template <int CTAS = 1>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
+  if constexpr (CTAS == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  } else {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  }
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -192,34 +253,54 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t ab_fmt, uint32_t m, u
 
 enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_F8 = 2 };
 
-template <int KIND>
+#define FMOE_UMMA_ASM(GROUP, KINDSTR)                                                         \
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                \
+               "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t}\n" ::"r"( \
+                   tmem_d),                                                                      \
+               "l"(da), "l"(db), "r"(idesc), "r"(accumulate)                                   \
+               : "memory")
+
+// D[tmem] (+)= A[smem] * B[smem]. CTAS = 2: issued by one thread of the pair's leader CTA; the
+// operand descriptors name shared-memory offsets that are read in both CTAs (each holds its
+// 128 rows of A and its half of B), and each CTA's tensor memory receives its 128 rows of D.
+template <int KIND, int CTAS = 1>
 __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
                                         uint32_t accumulate) {
-  if constexpr (KIND == KIND_F16) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else if constexpr (KIND == KIND_TF32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-        : "memory");
+  if constexpr (CTAS == 1) {
+    if constexpr (KIND == KIND_F16) {
+      FMOE_UMMA_ASM("1", "f16");
+    } else if constexpr (KIND == KIND_TF32) {
+      FMOE_UMMA_ASM("1", "tf32");
+    } else {
+      FMOE_UMMA_ASM("1", "f8f6f4");
+    }
   } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (KIND == KIND_F16) {
+      FMOE_UMMA_ASM("2", "f16");
+    } else if constexpr (KIND == KIND_TF32) {
+      FMOE_UMMA_ASM("2", "tf32");
+    } else {
+      FMOE_UMMA_ASM("2", "f8f6f4");
+    }
   }
 }
+#undef FMOE_UMMA_ASM
+
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has finished
 // (reads of shared memory included). Implies tcgen05.fence::before_thread_sync.
+// CTAS = 2: the arrival is delivered to the barrier at the same offset in both CTAs of the pair.
+template <int CTAS = 1>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
+  if constexpr (CTAS == 1) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+  } else {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(mask)
+        : "memory");
+  }
 }
 
 }  // namespace ptx
