@@ -143,9 +143,23 @@ def cpu_oracle_step(c, x_cpu, params, k):
                               params["w_down"], k)
 
 
-def cpu_params(c, tokens):
+def cpu_sample(c, tokens, seconds_per_step):
+    """Bounded CPU sample of a config: (tokens, experts). Large layers keep the per-expert row
+    count and the per-token FLOPs but use only a few of the experts (their fp32 weights would not
+    even fit in host memory otherwise); then tokens are halved until a step fits the time budget
+    at an assumed 0.2 TFLOP/s."""
+    E = c["E"]
+    e_s = E if c["d"] * c["h"] * E <= 4e8 else max(c["k"], 4)
+    sample = max(256, tokens * e_s // E)
+    cs = dict(c, E=e_s)
+    while layer_flops(cs, sample) / 2e11 > seconds_per_step and sample > 256:
+        sample //= 2
+    return sample, e_s
+
+
+def cpu_params(c, tokens, experts=None):
     g = torch.Generator().manual_seed(0)
-    E, d, h, o = c["E"], c["d"], c["h"], c["o"]
+    E, d, h, o = experts or c["E"], c["d"], c["h"], c["o"]
     return dict(
         gate_w=torch.randn(E, d, generator=g) * 0.02, gate_b=torch.zeros(E),
         w_gate=(torch.randn(E, h, d, generator=g) * 0.02).permute(0, 2, 1),
@@ -159,12 +173,8 @@ def time_cpu_baseline(c, tokens, budget_s=20.0):
     the token count is scaled down until one forward takes a few seconds."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    flops_full = layer_flops(c, tokens)
-    # assume >= 0.2 TFLOP/s; keep the sample's estimated cost under ~budget/4 per run
-    sample = tokens
-    while layer_flops(c, sample) / 2e11 > budget_s / 4 and sample > 256:
-        sample //= 2
-    p = cpu_params(c, sample)
+    sample, e_s = cpu_sample(c, tokens, budget_s / 4)
+    p = cpu_params(c, sample, e_s)
     x = torch.randn(1, sample, c["d"], generator=torch.Generator().manual_seed(99))
     with torch.no_grad():
         cpu_oracle_step(c, x, p, c["k"])   # warm-up
@@ -176,8 +186,32 @@ def time_cpu_baseline(c, tokens, budget_s=20.0):
             times.append(time.perf_counter() - t0)
     t = statistics.median(times)
     return dict(value=sample / t, unit="tokens/s", cores=cores, kind="port",
-                sample=f"{sample} of {tokens} tokens, fp32, torch CPU ({cores} threads), median of {len(times)} runs",
+                sample=f"{sample} of {tokens} tokens over {e_s} of {c['E']} experts, fp32, torch CPU ({cores} threads), "
+                       f"median of {len(times)} runs",
                 seconds_per_run=t)
+
+
+def time_ep_single_gpu(device, args):
+    """c5 (64 experts, d=4096, h=14336, 8192 tokens) with every expert on this GPU."""
+    from fast_moe_b200.modules.expert_parallel import ExpertParallelSwiGLUMoE
+
+    c = CONFIGS["c5"]
+    layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device)
+    x = make_inputs(c, 0, device).to(device)
+    steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        layer(x, c["k"])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer(x, c["k"])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return dict(value=c["tokens"] / (ms * 1e-3), unit="tokens/s", ms_per_step=ms, steps=steps,
+                layer_tflops=layer_flops(c, c["tokens"]) / (ms * 1e-3) / 1e12,
+                workload=workload_config(c, "c5", 1)["workload"])
 
 
 def run_reference(args, c, name):
@@ -188,10 +222,8 @@ def run_reference(args, c, name):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     tokens = c["tokens"]
-    sample = tokens
-    while layer_flops(c, sample) / 2e11 > 4.0 and sample > 256:
-        sample //= 2
-    p = cpu_params(c, sample)
+    sample, e_s = cpu_sample(c, tokens, 4.0)
+    p = cpu_params(c, sample, e_s)
     x = torch.randn(1, sample, c["d"], generator=torch.Generator().manual_seed(99))
     with torch.no_grad():
         for _ in range(max(1, min(args.warmup, 3))):
@@ -201,7 +233,8 @@ def run_reference(args, c, name):
             cpu_oracle_step(c, x, p, c["k"])
         dt = (time.perf_counter() - t0) / args.steps
     val = sample / dt
-    sample_desc = f"each step = {sample} of {tokens} tokens per rank, fp32, torch CPU, {cores} threads"
+    sample_desc = (f"each step = {sample} of {tokens} tokens per rank over {e_s} of {c['E']} experts, fp32, "
+                   f"torch CPU, {cores} threads")
     line = dict(
         impl="reference", metric="moe_layer_fwd_tokens_per_s", value=val, unit="tokens/s", n_gpus=args.gpus,
         steps=args.steps, warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak",
@@ -230,6 +263,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ep-reference", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -350,6 +384,12 @@ def main():
         )
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = time_cpu_baseline(c, c["tokens"])
+        if world == 1 and args.config is None and not args.no_ep_reference:
+            # the per-rank workload of the multi-GPU runs (c5, expert parallel) on one GPU: the
+            # denominator for weak-scaling efficiency of the N > 1 lines
+            del layer, y
+            torch.cuda.empty_cache()
+            line["c5_ep_1gpu"] = time_ep_single_gpu(device, args)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -25,98 +25,156 @@ __device__ __forceinline__ float to_f<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// One warp per token. Logits are accumulated in fp32 with the reduction order fixed by the
-// lane layout, so the same input always routes the same way.
+// Eight consecutive fp32 values of a row starting at element c (c a multiple of 8).
+__device__ __forceinline__ void load8(const float* row, int c, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(row + c);
+  const float4 b = *reinterpret_cast<const float4*>(row + c + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* row, int c, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+constexpr int kGateTokens = 4;   // tokens a warp handles at once (gate weights are read once for all of them)
+constexpr int kGateEC = 8;       // experts per pass over the rows
+
+// One warp per kGateTokens tokens. Logits are accumulated in fp32 with the reduction order fixed
+// by the lane layout, so the same input always routes the same way. x is read in 16-byte pieces
+// and each gate-weight piece is used for all the warp's tokens; HBM traffic is one pass over x.
 template <typename XT>
 __global__ void __launch_bounds__(kGateWarps * 32)
 gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ gw,
                  const float* __restrict__ gb, const float* __restrict__ logits_in, long long L, int d, int E,
-                 int k, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
+                 int k, int vec_ok, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
                  float* __restrict__ topk_score) {
-  __shared__ float s_logit[kGateWarps][kMaxGateExperts];
+  __shared__ float s_logit[kGateWarps][kGateTokens][kMaxGateExperts];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long t = static_cast<long long>(blockIdx.x) * kGateWarps + warp;
-  if (t >= L) return;
-  float* lg = s_logit[warp];
+  const long long t0 = (static_cast<long long>(blockIdx.x) * kGateWarps + warp) * kGateTokens;
+  if (t0 >= L) return;
+  const int nt = static_cast<int>(min(static_cast<long long>(kGateTokens), L - t0));
 
   if (logits_in != nullptr) {
-    for (int e = lane; e < E; e += 32) lg[e] = logits_in[t * E + e];
+    for (int j = 0; j < nt; ++j)
+      for (int e = lane; e < E; e += 32) s_logit[warp][j][e] = logits_in[(t0 + j) * E + e];
   } else {
-    const XT* xr = x + t * ldx;
-    constexpr int EC = 8;   // experts per pass over the row
-    for (int e0 = 0; e0 < E; e0 += EC) {
-      float acc[EC];
+    const int d8 = vec_ok ? (d & ~7) : 0;
+    for (int e0 = 0; e0 < E; e0 += kGateEC) {
+      float acc[kGateTokens][kGateEC];
 #pragma unroll
-      for (int i = 0; i < EC; ++i) acc[i] = 0.f;
-      for (int c = lane; c < d; c += 32) {
-        const float xv = to_f<XT>(xr[c]);
+      for (int j = 0; j < kGateTokens; ++j)
 #pragma unroll
-        for (int i = 0; i < EC; ++i) {
-          if (e0 + i < E) acc[i] = fmaf(xv, gw[static_cast<long long>(e0 + i) * d + c], acc[i]);
+        for (int i = 0; i < kGateEC; ++i) acc[j][i] = 0.f;
+      for (int c = lane * 8; c < d8; c += 256) {
+        float xv[kGateTokens][8];
+#pragma unroll
+        for (int j = 0; j < kGateTokens; ++j) {
+          if (j < nt) {
+            load8(x + (t0 + j) * ldx, c, xv[j]);
+          } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) xv[j][u] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kGateEC; ++i) {
+          if (e0 + i < E) {
+            float wv[8];
+            load8(gw + static_cast<long long>(e0 + i) * d, c, wv);
+#pragma unroll
+            for (int j = 0; j < kGateTokens; ++j)
+#pragma unroll
+              for (int u = 0; u < 8; ++u) acc[j][i] = fmaf(xv[j][u], wv[u], acc[j][i]);
+          }
+        }
+      }
+      for (int c = d8 + lane; c < d; c += 32) {   // tail, or everything when rows are not 16-byte aligned
+#pragma unroll
+        for (int i = 0; i < kGateEC; ++i) {
+          if (e0 + i < E) {
+            const float w = gw[static_cast<long long>(e0 + i) * d + c];
+#pragma unroll
+            for (int j = 0; j < kGateTokens; ++j)
+              if (j < nt) acc[j][i] = fmaf(to_f<XT>(x[(t0 + j) * ldx + c]), w, acc[j][i]);
+          }
         }
       }
 #pragma unroll
-      for (int i = 0; i < EC; ++i) {
-        float v = acc[i];
+      for (int j = 0; j < kGateTokens; ++j) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && e0 + i < E) lg[e0 + i] = v + (gb ? gb[e0 + i] : 0.f);
+        for (int i = 0; i < kGateEC; ++i) {
+          float v = acc[j][i];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == 0 && e0 + i < E) s_logit[warp][j][e0 + i] = v + (gb ? gb[e0 + i] : 0.f);
+        }
       }
     }
   }
   __syncwarp();
-  if (logits_out != nullptr) {
-    for (int e = lane; e < E; e += 32) logits_out[t * E + e] = lg[e];
-  }
-  // softmax over E
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+  for (int j = 0; j < nt; ++j) {
+    const long long t = t0 + j;
+    float* lg = s_logit[warp][j];
+    if (logits_out != nullptr) {
+      for (int e = lane; e < E; e += 32) logits_out[t * E + e] = lg[e];
+    }
+    // softmax over E
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float p = expf(lg[e] - mx);
-    lg[e] = p;
-    sum += p;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  __syncwarp();
-  // top-k by repeated arg-max; a taken entry is marked with -1 (scores are >= 0)
-  float norm = 0.f;
-  for (int j = 0; j < k; ++j) {
-    float best = -2.f;
-    int best_e = E;
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
-      const float v = lg[e];
-      if (v > best) {   // ascending e within the lane: first maximum wins
-        best = v;
-        best_e = e;
-      }
+      const float pr = expf(lg[e] - mx);
+      lg[e] = pr;
+      sum += pr;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ov > best || (ov == best && oe < best_e)) {
-        best = ov;
-        best_e = oe;
-      }
-    }
-    const float sc = best / sum;
-    norm += sc;
-    if (lane == 0) {
-      topk_idx[t * k + j] = best_e;
-      topk_score[t * k + j] = sc;
-      lg[best_e] = -1.f;
-    }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     __syncwarp();
-  }
-  // F.normalize(p=1, eps=1e-12) over the k kept scores
-  const float denom = fmaxf(norm, 1e-12f);
-  if (lane == 0) {
-    for (int j = 0; j < k; ++j) topk_score[t * k + j] = topk_score[t * k + j] / denom;
+    // top-k by repeated arg-max; a taken entry is marked with -1 (scores are >= 0)
+    float norm = 0.f;
+    for (int s = 0; s < k; ++s) {
+      float best = -2.f;
+      int best_e = E;
+      for (int e = lane; e < E; e += 32) {
+        const float v = lg[e];
+        if (v > best) {   // ascending e within the lane: first maximum wins
+          best = v;
+          best_e = e;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ov > best || (ov == best && oe < best_e)) {
+          best = ov;
+          best_e = oe;
+        }
+      }
+      const float sc = best / sum;
+      norm += sc;
+      if (lane == 0) {
+        topk_idx[t * k + s] = best_e;
+        topk_score[t * k + s] = sc;
+        lg[best_e] = -1.f;
+      }
+      __syncwarp();
+    }
+    // F.normalize(p=1, eps=1e-12) over the k kept scores
+    const float denom = fmaxf(norm, 1e-12f);
+    if (lane == 0) {
+      for (int s = 0; s < k; ++s) topk_score[t * k + s] = topk_score[t * k + s] / denom;
+    }
   }
 }
 
@@ -254,15 +312,20 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
   FMOE_REQUIRE(logits_in || x_dtype == FMOE_BF16 || x_dtype == FMOE_F32, "gate_topk: x must be bf16 or f32");
   if (L == 0) return FMOE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned grid = static_cast<unsigned>((L + kGateWarps - 1) / kGateWarps);
+  const long long per_block = static_cast<long long>(kGateWarps) * kGateTokens;
+  const unsigned grid = static_cast<unsigned>((L + per_block - 1) / per_block);
+  // 16-byte loads need aligned rows of x and of the gate weights
+  const int xs = x_dtype == FMOE_BF16 ? 2 : 4;
+  const int vec_ok = (logits_in == nullptr) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx * xs) % 16 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(gate_w) & 15) == 0) && (d % 8 == 0);
   long long* idx = reinterpret_cast<long long*>(topk_idx);
   if (logits_in || x_dtype == FMOE_F32) {
     gate_topk_kernel<float><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const float*>(x), ldx, gate_w, gate_b,
-                                                               logits_in, L, d, E, k, logits_out, idx, topk_score);
+                                                               logits_in, L, d, E, k, vec_ok, logits_out, idx, topk_score);
   } else {
     gate_topk_kernel<__nv_bfloat16><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx,
                                                                        gate_w, gate_b, logits_in, L, d, E, k,
-                                                                       logits_out, idx, topk_score);
+                                                                       vec_ok, logits_out, idx, topk_score);
   }
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;

@@ -267,15 +267,36 @@ def mul_merge_k_add(
     return out
 
 
+def gather_rows(src: torch.Tensor, index: torch.Tensor, index_div: int = 1) -> torch.Tensor:
+    """dst[r] = src[index[r] // index_div]: the index_select step of the up projection
+    (kernels/pytorch/moe.py:69-73) as a kernel of its own. The expert-parallel layer uses it to
+    pack the rows it sends in expert-sorted order."""
+    dev = _lib.require_cuda(src, index)
+    lib = _lib.load()
+    s = src if src.stride(-1) == 1 else src.contiguous()
+    idx = _index_i64(index.reshape(-1))
+    rows, cols = idx.numel(), s.shape[1]
+    out = torch.empty((rows, cols), dtype=s.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_gather_rows(s.data_ptr(), _lib.dtype_code(s.dtype), s.shape[0], s.stride(0), idx.data_ptr(),
+                                 index_div, rows, cols, out.data_ptr(), out.stride(0), _lib.stream_ptr(dev))
+        )
+    return out
+
+
 def silu_jagged_bmm(
     offsets: torch.Tensor,
     jagged: torch.Tensor,
     weight: torch.Tensor,
     bias: Optional[torch.Tensor],
     has_silu: bool = True,
+    out_row_index: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """[silu](jagged) @ weight[e] + bias[e] per expert segment; weight is logical [E, K, N]
-    (the GEMM half of silu_jagged_bmm_combine, kernels/pytorch/moe.py:255-275)."""
+    (the GEMM half of silu_jagged_bmm_combine, kernels/pytorch/moe.py:255-275).
+    ``out_row_index`` (a permutation of the rows, not part of the reference operator) makes row r
+    of the result land at out[out_row_index[r]]."""
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype
     dev = _lib.require_cuda(offsets, jagged, weight, bias)
@@ -290,12 +311,14 @@ def silu_jagged_bmm(
     off = _index_i64(offsets)
     out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
     scratch = torch.empty((rows, kp), dtype=jagged.dtype, device=dev) if has_silu else None
+    oidx = None if out_row_index is None else _index_i64(out_row_index.reshape(-1))
+    assert oidx is None or oidx.numel() == rows
     dt = _lib.dtype_code(jagged.dtype)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_silu_jagged_bmm(
                 off.data_ptr(), rows, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
-                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), None, None, out.data_ptr(), dt,
+                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), None, _lib.ptr(oidx), out.data_ptr(), dt,
                 out.stride(0),
                 _lib.stream_ptr(dev),
             )
