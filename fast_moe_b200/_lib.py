@@ -53,6 +53,7 @@ SIGNATURES = {
     "fmoe_gate_topk": (c_int, [P, c_int, I64, P, P, P, I64, c_int, c_int, c_int, P, P, P, P]),
     "fmoe_route_workspace_bytes": (c_size_t, [I64, c_int, c_int]),
     "fmoe_route_metadata": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P, c_size_t, P]),
+    "fmoe_route_metadata_static": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P]),
     "fmoe_index_select_jagged_bmm": (
         c_int,
         [P, P, c_int, I64, P, c_int, I64, I64, P, I64, I64, I64, P, I64, c_int, c_int, c_int, c_int, P, c_int, I64, P],

@@ -381,3 +381,67 @@ extern "C" int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, in
   }
   return FMOE_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Routing metadata for callers that cannot allocate device memory.
+//
+// Some callers of this library run where cudaMalloc is off the table: code executing inside a
+// framework's memory-planned region where every byte was reserved up front, plugins that are only
+// handed their input and output buffers, or services that run with a fixed device-memory budget.
+// fmoe_route_metadata needs a small scratch table (rows per expert for every block of 256 tokens)
+// that such callers have nowhere to put. This variant keeps that table in a file-scope device
+// array instead, so the caller passes inputs and outputs only.
+//
+// The array is part of the loaded library image: every GPU that loads the library holds these
+// 256 KiB until the process exits, whether or not this entry point is ever called.
+namespace fmoe {
+namespace {
+
+constexpr long long kStaticRouteInts = 1ll << 16;   // 65536 ints = 256 KiB
+static __device__ __align__(256) int g_route_scratch[kStaticRouteInts];
+
+// Device address of g_route_scratch on the current device. In host code the array's name is only
+// a handle for the runtime, not a device address, so the address is looked up once per device
+// (with that device current) and cached.
+int* static_route_scratch(int* err) {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = cuda_fail(e, "cudaGetDevice");
+    return nullptr;
+  }
+  if (ptrs[dev] == nullptr) {
+    int* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *err = cuda_fail(e, "cudaGetSymbolAddress(route scratch)");
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+}  // namespace
+}  // namespace fmoe
+
+extern "C" int fmoe_route_metadata_static(const int64_t* topk_idx, int64_t L, int E, int k, int64_t* lengths,
+                                          int64_t* offsets, int64_t* gate_index, int64_t* token_index,
+                                          int64_t* reverse_index, int64_t* max_len, void* stream) {
+  FMOE_REQUIRE(L >= 0 && E >= 1, "route_metadata_static: L=%lld E=%d", (long long)L, E);
+  const size_t need = fmoe_route_workspace_bytes(L, E, k);
+  if (need > static_cast<size_t>(kStaticRouteInts) * sizeof(int)) {
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "route_metadata_static: ceil(L/256)*E = %zu scratch entries exceed the built-in %lld "
+                "(L=%lld, E=%d); use fmoe_route_metadata with a caller-provided workspace",
+                need / sizeof(int), kStaticRouteInts, (long long)L, E);
+  }
+  int err = 0;
+  int* scratch = static_route_scratch(&err);
+  if (!scratch) return err;
+  // Nothing in the table has to start at zero: the counting pass overwrites every entry the scan
+  // and the placement pass read. The previous call's contents are simply left behind.
+  return fmoe_route_metadata(topk_idx, L, E, k, lengths, offsets, gate_index, token_index, reverse_index, max_len,
+                             scratch, static_cast<size_t>(kStaticRouteInts) * sizeof(int), stream);
+}

@@ -98,6 +98,21 @@ int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, int k, int64_
                         int64_t* gate_index, int64_t* token_index, int64_t* reverse_index, int64_t* max_len,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* fmoe_route_metadata without a workspace argument, for callers that cannot allocate device
+ * memory (code inside a pre-planned memory region, plugins that only receive their input and
+ * output buffers, fixed-budget services). It has no counterpart in the reference. The scratch
+ * table lives in a 256 KiB array inside the library image (held by every GPU that loads the
+ * library, until exit), so sizes are limited to ceil(L/256) * E <= 65536; larger problems get
+ * FMOE_ERR_UNSUPPORTED and should use fmoe_route_metadata. No cudaMalloc / cudaFree or other
+ * allocating call is made. The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current): make that first call outside any stream
+ * capture. All calls on a device share the one array, so two calls whose kernels can overlap on
+ * the GPU (different streams) race; calls on one stream are ordered and need no clearing between
+ * them. Results are identical to fmoe_route_metadata. */
+int fmoe_route_metadata_static(const int64_t* topk_idx, int64_t L, int E, int k, int64_t* lengths,
+                               int64_t* offsets, int64_t* gate_index, int64_t* token_index,
+                               int64_t* reverse_index, int64_t* max_len, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Up projection.
  * index_select_jagged_bmm (kernels/moe.py:39-68 -> kernels/pytorch/moe.py:40-84):
