@@ -264,6 +264,7 @@ def main():
     ap.add_argument("--config", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ep-reference", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -308,11 +309,23 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing
+    # Single GPU: the forward is captured once as a CUDA graph and a step is one replay (same
+    # kernels, one launch). The expert-parallel layer synchronises with the host for its split
+    # sizes and runs eagerly. A second, eager pass with CUDA events around each stage gives the
+    # per-kernel times the roofline figure uses.
     for _ in range(args.warmup):
         y = layer(x_dev, k)
     barrier()
-    timer = _lib.StageTimer()
-    _lib.set_stage_timer(timer)
+    captured = None
+    if world == 1 and not args.eager:
+        from fast_moe_b200 import CapturedForward
+
+        captured = CapturedForward(layer, x_dev, k)
+        step = captured.replay
+    else:
+        step = lambda: layer(x_dev, k)
+    for _ in range(args.warmup):
+        step()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -323,12 +336,27 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        y = layer(x_dev, k)
+        y = step()
     ev1.record()
     barrier()
-    t_wall1 = time.perf_counter()
     ms_total = ev0.elapsed_time(ev1)
-    launches = _lib.kernel_launch_count() - launches0
+    # eager pass with stage events (also what counts launches when the timed pass was a graph);
+    # graph capture empties the allocator cache, so the eager path is warmed up again first
+    for _ in range(3):
+        layer(x_dev, k)
+    barrier()
+    timer = _lib.StageTimer()
+    _lib.set_stage_timer(timer)
+    launches_eager0 = _lib.kernel_launch_count()
+    ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ee0.record()
+    for _ in range(args.steps):
+        layer(x_dev, k)
+    ee1.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    ms_eager = ee0.elapsed_time(ee1) / args.steps
+    launches = _lib.kernel_launch_count() - launches_eager0   # kernels per K steps (the graph replays the same ones)
     _lib.set_stage_timer(None)
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     stage_ms = {n: (tot / cnt) for n, (tot, cnt) in timer.totals_ms().items()}
@@ -336,15 +364,20 @@ def main():
 
     # ---- end to end: host tokens in, host result out, every step
     y_host = torch.empty((c["batch"], c["seq"], c["o"]), dtype=torch.bfloat16).pin_memory()
+    def e2e_step():
+        if captured is not None:
+            y_host.copy_(captured(x_host), non_blocking=True)       # H2D into the graph's input, replay, D2H
+        else:
+            xd = x_host.to(device, non_blocking=True)
+            y_host.copy_(layer(xd, k), non_blocking=True)
+
     for _ in range(3):
-        xd = x_host.to(device, non_blocking=True)
-        y_host.copy_(layer(xd, k), non_blocking=True)
+        e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        xd = x_host.to(device, non_blocking=True)
-        y_host.copy_(layer(xd, k), non_blocking=True)
+        e2e_step()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
@@ -376,6 +409,7 @@ def main():
             scaling="weak", vs_baseline=None, dtype="e4m3" if c.get("fp8") else "bf16", data="synthetic",
             config=workload_config(c, name, world),
             layer_tflops_per_gpu=layer_flops(c, c["tokens"]) / (ms_step * 1e-3) / 1e12,
+            launch_mode="cuda graph replay" if captured is not None else "eager", ms_per_step_eager=ms_eager,
             stage_ms=stage_ms, roofline=roofline, clocks=clocks, gpu_launches=int(launches),
             device_status=status,
             e2e=dict(value=tokens_total / (ms_e2e / args.steps * 1e-3), unit="tokens/s",

@@ -14,12 +14,13 @@ from .kernels.moe import (
 )
 from .kernels.routing import RoutingMetadata, gate_topk, route_metadata
 from .kernels.utils import KernelType
-from .modules.fast_moe_module import FastMoELayer, GatingNetwork, SwiGLUFastMoELayer
+from .modules.fast_moe_module import CapturedForward, FastMoELayer, GatingNetwork, SwiGLUFastMoELayer
 
 __all__ = [
     "FastMoELayer",
     "GatingNetwork",
     "SwiGLUFastMoELayer",
+    "CapturedForward",
     "KernelType",
     "IndexSelectJaggedBmmOption",
     "SiluJaggedBmmCombineOption",

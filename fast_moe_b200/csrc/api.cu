@@ -97,7 +97,7 @@ extern "C" int fmoe_index_select_jagged_bmm(const int64_t* offsets, const int64_
   FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "index_select_jagged_bmm: dtype must be bf16 or f32");
   FMOE_REQUIRE(epilogue == FMOE_EPI_NONE || epilogue == FMOE_EPI_SILU, "index_select_jagged_bmm: bad epilogue %d",
                epilogue);
-  FMOE_REQUIRE(index != nullptr && index_div >= 1, "index_select_jagged_bmm: index is required");
+  FMOE_REQUIRE(index == nullptr || index_div >= 1, "index_select_jagged_bmm: index_div must be >= 1");
   GemmDesc g;
   memset(&g, 0, sizeof(g));
   g.dtype = dtype;
@@ -122,7 +122,7 @@ extern "C" int fmoe_index_select_jagged_bmm_swiglu(const int64_t* offsets, const
                                                    const void* bias_p, int64_t bias_se, int E, int K, int N,
                                                    void* out, int out_dtype, int64_t ldo, void* stream) {
   FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "index_select_jagged_bmm_swiglu: dtype must be bf16 or f32");
-  FMOE_REQUIRE(index != nullptr && index_div >= 1, "index_select_jagged_bmm_swiglu: index is required");
+  FMOE_REQUIRE(index == nullptr || index_div >= 1, "index_select_jagged_bmm_swiglu: index_div must be >= 1");
   FMOE_REQUIRE(weight_p != nullptr, "index_select_jagged_bmm_swiglu: weight_p is NULL");
   GemmDesc g;
   memset(&g, 0, sizeof(g));

@@ -36,42 +36,68 @@ combine_kernel(const long long* __restrict__ reverse_index, const VT* __restrict
     float acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-    for (int j = 0; j < k; ++j) {
-      const long long p = reverse_index[t * k + j];
-      if (p < 0 || p >= n_rows) {
-        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
-        continue;
-      }
-      float g = 1.f;
-      if (weight != nullptr) {
-        long long wi = weight_index ? weight_index[p] : p;
-        if (wi < 0 || wi >= n_rows) {
+    // Rows are handled in groups of up to 4: first all their indices, then all gate weights and
+    // values, so that the loads of a group are in flight together instead of one dependent chain
+    // per row. The accumulation order stays ascending j.
+    constexpr int kGroup = 4;
+    for (int j0 = 0; j0 < k; j0 += kGroup) {
+      long long prow[kGroup];
+      float g[kGroup];
+      bool ok[kGroup];
+#pragma unroll
+      for (int jj = 0; jj < kGroup; ++jj) {
+        ok[jj] = j0 + jj < k;
+        prow[jj] = ok[jj] ? reverse_index[t * k + j0 + jj] : 0;
+        if (ok[jj] && (prow[jj] < 0 || prow[jj] >= n_rows)) {
           atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
-          continue;
+          ok[jj] = false;
         }
-        g = ldf(weight + wi);
       }
-      const VT* src = value + p * ldv + c0;
-      float v[VEC];
-      if (c0 + VEC <= D) {
-        if constexpr (sizeof(VT) * VEC == 16) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(src);
-          const VT* e = reinterpret_cast<const VT*>(&raw);
+      if (weight != nullptr) {
+        long long wi[kGroup];
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) v[i] = ldf(e + i);
-        } else {
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) v[i] = ldf(src + i);
+        for (int jj = 0; jj < kGroup; ++jj) {
+          wi[jj] = ok[jj] ? (weight_index ? weight_index[prow[jj]] : prow[jj]) : 0;
+          if (ok[jj] && (wi[jj] < 0 || wi[jj] >= n_rows)) {
+            atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+            ok[jj] = false;
+          }
         }
+#pragma unroll
+        for (int jj = 0; jj < kGroup; ++jj) g[jj] = ok[jj] ? ldf(weight + wi[jj]) : 0.f;
       } else {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] = (c0 + i < D) ? ldf(src + i) : 0.f;
+        for (int jj = 0; jj < kGroup; ++jj) g[jj] = 1.f;
+      }
+      float v[kGroup][VEC];
+#pragma unroll
+      for (int jj = 0; jj < kGroup; ++jj) {
+        if (!ok[jj]) continue;
+        const VT* src = value + prow[jj] * ldv + c0;
+        if (c0 + VEC <= D) {
+          if constexpr (sizeof(VT) * VEC == 16) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src);
+            const VT* e = reinterpret_cast<const VT*>(&raw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[jj][i] = ldf(e + i);
+          } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[jj][i] = ldf(src + i);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[jj][i] = (c0 + i < D) ? ldf(src + i) : 0.f;
+        }
       }
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float prod = weight != nullptr ? __fmul_rn(v[i], g) : v[i];
-        if (kRoundProduct && weight != nullptr) prod = __bfloat162float(__float2bfloat16_rn(prod));
-        acc[i] = __fadd_rn(acc[i], prod);
+      for (int jj = 0; jj < kGroup; ++jj) {
+        if (!ok[jj]) continue;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float prod = weight != nullptr ? __fmul_rn(v[jj][i], g[jj]) : v[jj][i];
+          if (kRoundProduct && weight != nullptr) prod = __bfloat162float(__float2bfloat16_rn(prod));
+          acc[i] = __fadd_rn(acc[i], prod);
+        }
       }
     }
     OT* dst = out + t * ldo + c0;

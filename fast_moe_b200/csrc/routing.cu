@@ -43,13 +43,13 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* row, int c, float (&v
   }
 }
 
-constexpr int kGateTokens = 4;   // tokens a warp handles at once (gate weights are read once for all of them)
+constexpr int kGateTokensMax = 4;   // tokens a warp handles at once (gate weights are read once for all of them)
 constexpr int kGateEC = 8;       // experts per pass over the rows
 
-// One warp per kGateTokens tokens. Logits are accumulated in fp32 with the reduction order fixed
+// One warp per kGateTokens tokens (4 when there are enough tokens to fill the GPU that way, else 1). Logits are accumulated in fp32 with the reduction order fixed
 // by the lane layout, so the same input always routes the same way. x is read in 16-byte pieces
 // and each gate-weight piece is used for all the warp's tokens; HBM traffic is one pass over x.
-template <typename XT>
+template <typename XT, int kGateTokens>
 __global__ void __launch_bounds__(kGateWarps * 32)
 gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ gw,
                  const float* __restrict__ gb, const float* __restrict__ logits_in, long long L, int d, int E,
@@ -312,21 +312,25 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
   FMOE_REQUIRE(logits_in || x_dtype == FMOE_BF16 || x_dtype == FMOE_F32, "gate_topk: x must be bf16 or f32");
   if (L == 0) return FMOE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long per_block = static_cast<long long>(kGateWarps) * kGateTokens;
+  // 4 tokens per warp amortise the gate-weight reads, but only pay off when that still leaves a
+  // few warps per scheduler on every SM
+  const int tok = (L >= 148ll * kGateWarps * kGateTokensMax * 4) ? kGateTokensMax : 1;
+  const long long per_block = static_cast<long long>(kGateWarps) * tok;
   const unsigned grid = static_cast<unsigned>((L + per_block - 1) / per_block);
   // 16-byte loads need aligned rows of x and of the gate weights
   const int xs = x_dtype == FMOE_BF16 ? 2 : 4;
   const int vec_ok = (logits_in == nullptr) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx * xs) % 16 == 0) &&
                      ((reinterpret_cast<uintptr_t>(gate_w) & 15) == 0) && (d % 8 == 0);
   long long* idx = reinterpret_cast<long long*>(topk_idx);
+#define FMOE_GATE(XT, TOK)                                                                                   \
+  gate_topk_kernel<XT, TOK><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const XT*>(x), ldx, gate_w, gate_b, \
+                                                              logits_in, L, d, E, k, vec_ok, logits_out, idx, topk_score)
   if (logits_in || x_dtype == FMOE_F32) {
-    gate_topk_kernel<float><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const float*>(x), ldx, gate_w, gate_b,
-                                                               logits_in, L, d, E, k, vec_ok, logits_out, idx, topk_score);
+    if (tok == 1) FMOE_GATE(float, 1); else FMOE_GATE(float, kGateTokensMax);
   } else {
-    gate_topk_kernel<__nv_bfloat16><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx,
-                                                                       gate_w, gate_b, logits_in, L, d, E, k,
-                                                                       vec_ok, logits_out, idx, topk_score);
+    if (tok == 1) FMOE_GATE(__nv_bfloat16, 1); else FMOE_GATE(__nv_bfloat16, kGateTokensMax);
   }
+#undef FMOE_GATE
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
   return FMOE_OK;

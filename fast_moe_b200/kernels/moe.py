@@ -155,8 +155,9 @@ def index_select_jagged_bmm_swiglu(
     kernel: KernelType = KernelType.PYTORCH,
 ) -> torch.Tensor:
     """silu(x @ weight[e] + bias[e]) * (x @ weight_p[e] + bias_p[e]) on the gathered rows, one
-    kernel, the activation row tile shared by both products (kernels/moe.py:156-189)."""
-    assert index.ndim == 2 and index.shape[0] == jagged.shape[0]
+    kernel, the activation row tile shared by both products (kernels/moe.py:156-189).
+    ``index=None`` (not in the reference) means ``jagged`` already holds the expert-sorted rows."""
+    assert index is None or (index.ndim == 2 and index.shape[0] == jagged.shape[0])
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype and weight_p.dtype == jagged.dtype
     assert weight.shape == weight_p.shape
@@ -165,7 +166,7 @@ def index_select_jagged_bmm_swiglu(
     L, K = jagged.shape
     E, Kw, N = weight.shape
     assert Kw == K
-    rows = index.numel()
+    rows = index.numel() if index is not None else L
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
     w, w_se, w_sn = prep_weight(weight, kp)
@@ -178,13 +179,13 @@ def index_select_jagged_bmm_swiglu(
     b = _prep_bias(bias, jagged.dtype)
     bp = _prep_bias(bias_p, jagged.dtype)
     off = _index_i64(offsets)
-    idx = _index_i64(index)
+    idx = None if index is None else _index_i64(index)
     out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm_swiglu(
-                off.data_ptr(), idx.data_ptr(), index.shape[1], rows, a.data_ptr(), dt, L, a.stride(0),
+                off.data_ptr(), _lib.ptr(idx), index.shape[1] if index is not None else 1, rows, a.data_ptr(), dt, L, a.stride(0),
                 w.data_ptr(), wp.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), _lib.ptr(bp), N, E, kp, N,
                 out.data_ptr(), dt, out.stride(0), _lib.stream_ptr(dev),
             )

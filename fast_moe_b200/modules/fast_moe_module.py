@@ -206,3 +206,40 @@ class SwiGLUFastMoELayer(_MoEBase):
                         gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
                     )
         return y.view(*shape[:-1], self.output_dim)
+
+
+class CapturedForward:
+    """One forward of a layer recorded as a CUDA graph and replayed with a single launch.
+
+    The layer's kernels are tiny next to their launch cost at small token counts (eight launches
+    per forward); replaying a captured graph removes the host work between them. Input and output
+    live in static buffers: ``__call__`` copies the new tokens in, replays, and returns the
+    static output tensor (overwritten by the next call). Shapes, dtype and ``k`` are fixed at
+    capture time; weights are read in place, so in-place weight updates are seen by later replays.
+    """
+
+    def __init__(self, layer: nn.Module, example: torch.Tensor, num_experts_per_tok: int, warmup: int = 3) -> None:
+        if not example.is_cuda:
+            raise RuntimeError("CapturedForward needs a CUDA tensor")
+        if _lib._stage_timer is not None:
+            raise RuntimeError("stage timing records events and cannot be captured; disable it first")
+        self.k = num_experts_per_tok
+        self.x = example.clone()
+        side = torch.cuda.Stream(device=example.device)
+        side.wait_stream(torch.cuda.current_stream(example.device))
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):      # first calls resolve symbols and set kernel attributes
+                layer(self.x, self.k)
+        torch.cuda.current_stream(example.device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.y = layer(self.x, self.k)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.y
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        self.x.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y

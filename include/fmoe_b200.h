@@ -117,7 +117,8 @@ int fmoe_route_metadata_static(const int64_t* topk_idx, int64_t L, int E, int k,
  * Up projection.
  * index_select_jagged_bmm (kernels/moe.py:39-68 -> kernels/pytorch/moe.py:40-84):
  *   out[r, :] = jagged[index[r] / index_div, :] @ weight[e] + bias[e],  offsets[e] <= r < offsets[e+1]
- *   offsets [E+1] int64; index [rows] int64 (the flattened [L, A] tensor, index_div = A)
+ *   offsets [E+1] int64; index [rows] int64 (the flattened [L, A] tensor, index_div = A);
+ *   index may be NULL when jagged already holds the rows in expert-sorted order (L = rows)
  *   jagged  [L, K] dtype (bf16, or f32 computed with tf32 tensor-core math), row stride ldj
  *   weight  logical [E, K, N], element strides (w_se, w_sk, w_sn), same dtype
  *   bias    [E, N] same dtype as out, expert stride bias_se, or NULL

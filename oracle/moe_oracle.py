@@ -304,3 +304,43 @@ def index_select_jagged_bmm_fp8(offsets, index, jagged, weight, bias) -> torch.T
         o = (acc / (sp[:, None] * ws[e][None, :])).to(out_dtype)
         outs.append(o + (bias[e] if bias is not None else 0))
     return torch.cat(outs, dim=0)
+
+
+def _fp8_linear(x: torch.Tensor, w_rows: torch.Tensor) -> torch.Tensor:
+    """x [rows, K] @ w_rows[N, K]^T with both operands quantised rowwise to e4m3 (rule of
+    kernels/pytorch/quant_fp8.py:13-34), exact products of the quantised values accumulated in
+    fp32 and divided by the scale product - the arithmetic of
+    pytorch_index_select_jagged_bmm_fp8 (kernels/pytorch/moe_fp8.py:98-139) without its
+    intermediate bf16 rounding."""
+    xq, xs = rowwise_quant_fp8(x)
+    wq, ws = rowwise_quant_fp8(w_rows)
+    xv = torch.from_numpy(e4m3fn_to_fp32(xq.numpy()))
+    wv = torch.from_numpy(e4m3fn_to_fp32(wq.numpy()))
+    return (xv @ wv.T) / (xs[:, None] * ws[None, :])
+
+
+def moe_layer_swiglu_fp8(x, gate_w, gate_b, w_gate_rows, w_up_rows, w_down_rows, k: int) -> torch.Tensor:
+    """FP8 SwiGLU layer, the composition the FP8 benchmark configuration describes: routing in
+    fp32, tokens quantised per row, expert weights quantised per output row ([E, N, K] storage),
+    hidden activations rounded to the activation type and quantised per row again before the down
+    projection, fp32 combine. Built only from the reference's quantisation rule and its FP8 GEMM
+    definition; there is no single reference function for the whole chain."""
+    shape = x.shape
+    dt = x.dtype
+    dense, idx = select_top_k(gating_scores(x.float(), gate_w, gate_b), k)
+    gate_index, token_index, scores_k, offsets, reverse, _ = routing_metadata(dense, idx)
+    xf = x.reshape(-1, shape[-1])
+    rows = xf[token_index]
+    seg = _segments(offsets)
+    outs = []
+    for e, r in enumerate(rows.split(seg)):
+        if r.shape[0] == 0:
+            outs.append(torch.zeros(0, w_down_rows.shape[1]))
+            continue
+        g = _fp8_linear(r, w_gate_rows[e])
+        u = _fp8_linear(r, w_up_rows[e])
+        hidden = (F.silu(g) * u).to(dt)
+        outs.append(_fp8_linear(hidden, w_down_rows[e]).to(dt).float())
+    y_rows = torch.cat(outs, dim=0)
+    y = mul_merge_k_add(token_index, y_rows.to(dt), k, scores_k.to(dt), gate_index)
+    return y.view(*shape[:-1], w_down_rows.shape[1])

@@ -1,0 +1,177 @@
+"""Layer-level parity at the sizes and routing distributions of the benchmark configurations,
+against the CPU oracle on the same seeded inputs, plus size-independent properties of the routing
+tensors (permutation, sortedness, inverse relations) at full size.
+
+Bars: bf16 outputs rtol 1e-2 / atol 1e-2 (tokens whose k-th / (k+1)-th gate scores nearly tie may
+route differently and are counted, not asserted); one FP8 GEMM within 6e-2 relative per row of the
+unquantised product, the two-GEMM FP8 layer no worse than the oracle's emulation of the same chain."""
+import pytest
+import torch
+
+import fast_moe_b200 as fm
+from fast_moe_b200 import _lib
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _cpu(p):
+    return p.detach().float().cpu()
+
+
+def _oracle_swiglu(layer, x, k):
+    return O.moe_layer_swiglu(x.float().cpu(), _cpu(layer.gate.gate.weight), _cpu(layer.gate.gate.bias),
+                              _cpu(layer.w_gate).permute(0, 2, 1), _cpu(layer.w_up).permute(0, 2, 1),
+                              _cpu(layer.w_down).permute(0, 2, 1), k)
+
+
+def _routing_properties(idx, meta, E, k):
+    L = idx.shape[0]
+    A = L * k
+    gi, ti, off, rev = meta.gate_index, meta.token_index, meta.offsets, meta.reverse_index
+    assert int(off[0]) == 0 and int(off[-1]) == A
+    assert bool((off[1:] >= off[:-1]).all())
+    # gate_index is a permutation of 0..A-1
+    assert torch.equal(gi.sort().values, torch.arange(A, device=gi.device))
+    # rows are grouped by expert, ascending; inside an expert ascending (token, slot): stable sort
+    experts_sorted = idx.reshape(-1)[gi]
+    assert bool((experts_sorted[1:] >= experts_sorted[:-1]).all())
+    same = experts_sorted[1:] == experts_sorted[:-1]
+    assert bool((gi[1:][same] > gi[:-1][same]).all())
+    assert torch.equal(ti, gi // k)
+    # histogram
+    assert torch.equal(off[1:] - off[:-1], torch.bincount(idx.reshape(-1), minlength=E))
+    # reverse_index lists each token's rows, ascending position
+    assert torch.equal(ti[rev.reshape(-1)], torch.arange(L, device=gi.device).repeat_interleave(k))
+    assert bool((rev[:, 1:] > rev[:, :-1]).all()) if k > 1 else True
+    assert int(meta.max_len) == int((off[1:] - off[:-1]).max())
+
+
+def test_c2_full_size_swiglu_layer_bf16():
+    torch.manual_seed(0)
+    B, T, d, h, o, E, k = 8, 512, 1024, 4096, 1024, 8, 2
+    layer = fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer.gate.gate.weight.normal_(0, 0.02)
+        layer.gate.gate.bias.zero_()
+    layer.to(DEV)
+    x = torch.randn(B, T, d).bfloat16()
+    y = layer(x.to(DEV), k)
+    assert _lib.device_status(torch.device(DEV)) == 0
+    ref = _oracle_swiglu(layer, x, k)
+    err = (y.float().cpu() - ref).abs()
+    bad_tokens = (err > 1e-2 + 1e-2 * ref.abs()).view(-1, o).any(dim=1).float().mean().item()
+    assert bad_tokens < 5e-3, f"{bad_tokens:.3%} of tokens outside tolerance"
+    # routing at full size
+    idx, score, _ = fm.gate_topk(x.view(-1, d).to(DEV), layer.gate.gate.weight, layer.gate.gate.bias, k)
+    meta = fm.route_metadata(idx, E)
+    _routing_properties(idx, meta, E, k)
+    lengths = (meta.offsets[1:] - meta.offsets[:-1]).float()
+    assert lengths.min() > 0.5 * lengths.mean(), "N(0, 0.02) gate should give roughly uniform loads"
+
+
+def test_c4_shaped_zipf_routing_with_empty_experts():
+    """64 experts, top-8, router biased to a Zipf(1.2) load: some experts get no tokens, the
+    largest gets a large share - the variable-rows tile schedule with empty segments."""
+    torch.manual_seed(1)
+    L, d, h, o, E, k = 8192, 1024, 2048, 1024, 64, 8
+    layer = fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer.gate.gate.weight.normal_(0, 0.02)
+        ranks = torch.randperm(E, generator=torch.Generator().manual_seed(7)).float() + 1.0
+        p = ranks.pow(-1.2)
+        bias = (p / p.sum()).log() * 3.0          # sharpened so that the tail experts stay empty
+        layer.gate.gate.bias.copy_(bias)
+    layer.to(DEV)
+    x = torch.randn(1, L, d).bfloat16()
+    idx, score, _ = fm.gate_topk(x.view(-1, d).to(DEV), layer.gate.gate.weight, layer.gate.gate.bias, k)
+    meta = fm.route_metadata(idx, E)
+    _routing_properties(idx, meta, E, k)
+    lengths = meta.offsets[1:] - meta.offsets[:-1]
+    assert int((lengths == 0).sum()) >= 1, "expected at least one empty expert"
+    assert lengths.max().item() >= 0.10 * L * k
+    y = layer(x.to(DEV), k)
+    assert _lib.device_status(torch.device(DEV)) == 0
+    ref = _oracle_swiglu(layer, x, k)
+    err = (y.float().cpu() - ref).abs()
+    bad_tokens = (err > 1e-2 + 1e-2 * ref.abs()).view(-1, o).any(dim=1).float().mean().item()
+    assert bad_tokens < 1e-2, f"{bad_tokens:.3%} of tokens outside tolerance"
+
+
+def test_c3_shaped_fp8_layer_with_outlier_rows():
+    """FP8 path: x ~ N(0,1) with 1 % of the rows scaled by 50, weights quantised per output row.
+    Per-row scales are exact (checked against the oracle's rule); outputs stay within 6e-2 of the
+    row's largest magnitude of the unquantised fp32 result."""
+    torch.manual_seed(2)
+    L, d, h, o, E, k = 2048, 1024, 2048, 1024, 8, 2
+    layer = fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.bfloat16, fp8=True)
+    with torch.no_grad():
+        layer.gate.gate.weight.normal_(0, 0.02)
+        layer.gate.gate.bias.zero_()
+    layer.to(DEV)
+    x = torch.randn(1, L, d)
+    rows = torch.randperm(L)[: L // 100]
+    x[0, rows] *= 50.0
+    x = x.bfloat16()
+    layer.quantize_weights()
+    # scales of activations and weights follow the reference rule exactly
+    from fast_moe_b200.kernels import moe_fp8
+    xq, xs = moe_fp8.rowwise_quant_fp8(x.view(-1, d).to(DEV))
+    oq, os_ = O.rowwise_quant_fp8(x.view(-1, d))
+    assert torch.equal(xs.cpu(), os_) and torch.equal(xq.cpu().view(torch.uint8), oq)
+    wq, ws = layer._q["w_gate"]
+    owq, ows = O.rowwise_quant_fp8(layer.w_gate.detach().cpu())
+    assert torch.equal(ws.cpu(), ows) and torch.equal(wq.cpu().view(torch.uint8), owq)
+    y = layer(x.to(DEV), k)
+    assert y.dtype == torch.bfloat16
+    assert _lib.device_status(torch.device(DEV)) == 0
+    # (1) against the oracle's emulation of the same FP8 chain (same quantised operands, exact
+    # products, fp32 accumulation): only summation order and bf16 rounding points differ
+    emu = O.moe_layer_swiglu_fp8(x.cpu(), _cpu(layer.gate.gate.weight), _cpu(layer.gate.gate.bias),
+                                 layer.w_gate.detach().cpu(), layer.w_up.detach().cpu(),
+                                 layer.w_down.detach().cpu(), k).float()
+    yv = y.float().cpu().view(-1, o)
+    emu = emu.view(-1, o)
+    row_scale = emu.abs().amax(dim=1, keepdim=True).clamp_min(1e-6)
+    close = ((yv - emu).abs() / row_scale).amax(dim=1)
+    assert (close > 2e-2).float().mean().item() < 5e-3, f"max {close.max().item():.3f} vs the FP8 emulation"
+    # (2) against the unquantised fp32 layer: the relative error of a row (Frobenius) stays within
+    # 6e-2 for a single quantised GEMM; this chain quantises twice (tokens, then hidden), so the
+    # bound is checked as "no worse than the emulation of the same chain" plus 6e-2 per GEMM
+    ref = _oracle_swiglu(layer, x, k).view(-1, o)
+    rel = (yv - ref).norm(dim=1) / ref.norm(dim=1).clamp_min(1e-6)
+    rel_emu = (emu - ref).norm(dim=1) / ref.norm(dim=1).clamp_min(1e-6)
+    assert rel.median().item() <= rel_emu.median().item() * 1.1 + 1e-3
+    assert rel.median().item() < 2 * 6e-2, f"median row error {rel.median().item():.3f}"
+    # (3) one quantised GEMM (the reference's FP8 operator) against the unquantised product:
+    # dequantised rows within 6e-2 relative (row norm)
+    idx, score, _ = fm.gate_topk(x.view(-1, d).to(DEV), layer.gate.gate.weight, layer.gate.gate.bias, k)
+    meta = fm.route_metadata(idx, E)
+    w_logical = layer.w_gate.detach().permute(0, 2, 1)
+    out8 = moe_fp8.index_select_jagged_bmm(0, meta.offsets, meta.gate_index.view(-1, k), x.view(-1, d).to(DEV),
+                                           w_logical, None, fp8=True)
+    ref1 = O.index_select_jagged_bmm(meta.offsets.cpu(), meta.gate_index.cpu().view(-1, k), x.view(-1, d).float(),
+                                     w_logical.float().cpu(), None)
+    rel1 = (out8.float().cpu() - ref1).norm(dim=1) / ref1.norm(dim=1).clamp_min(1e-6)
+    assert rel1.quantile(0.99).item() < 6e-2, f"p99 row error {rel1.quantile(0.99).item():.3f}"
+
+
+def test_mlp_layer_medium_size_matches_oracle():
+    """FastMoELayer as shipped (fc1 + bias -> SiLU -> fc2 + bias) at a mid size, bf16."""
+    torch.manual_seed(3)
+    B, T, d, h, o, E, k = 4, 512, 512, 1024, 384, 8, 2
+    layer = fm.FastMoELayer(d, h, o, E, dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer._experts_hidden_bias.normal_(0, 0.1)
+        layer._experts_bias.normal_(0, 0.1)
+    layer.to(DEV)
+    x = torch.randn(B, T, d).bfloat16()
+    y = layer(x.to(DEV), k)
+    ref = O.moe_layer_mlp(x.float(), _cpu(layer.gate.gate.weight), _cpu(layer.gate.gate.bias),
+                          _cpu(layer._experts_hidden_w), _cpu(layer._experts_hidden_bias),
+                          _cpu(layer._experts_w), _cpu(layer._experts_bias), k)
+    err = (y.float().cpu() - ref).abs()
+    bad_tokens = (err > 1e-2 + 1e-2 * ref.abs()).view(-1, o).any(dim=1).float().mean().item()
+    assert bad_tokens < 5e-3, f"{bad_tokens:.3%} of tokens outside tolerance"
+    assert _lib.device_status(torch.device(DEV)) == 0
