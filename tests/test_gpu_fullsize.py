@@ -127,7 +127,9 @@ def test_c3_shaped_fp8_layer_with_outlier_rows():
     assert y.dtype == torch.bfloat16
     assert _lib.device_status(torch.device(DEV)) == 0
     # (1) against the oracle's emulation of the same FP8 chain (same quantised operands, exact
-    # products, fp32 accumulation): only summation order and bf16 rounding points differ
+    # products, fp32 accumulation): summation order and bf16 rounding points differ, and a hidden
+    # value that sits on an e4m3 rounding boundary may take the neighbouring code (a 6 % step of
+    # that one element), so the bound is a few percent of the row's largest magnitude
     emu = O.moe_layer_swiglu_fp8(x.cpu(), _cpu(layer.gate.gate.weight), _cpu(layer.gate.gate.bias),
                                  layer.w_gate.detach().cpu(), layer.w_up.detach().cpu(),
                                  layer.w_down.detach().cpu(), k).float()
@@ -135,7 +137,7 @@ def test_c3_shaped_fp8_layer_with_outlier_rows():
     emu = emu.view(-1, o)
     row_scale = emu.abs().amax(dim=1, keepdim=True).clamp_min(1e-6)
     close = ((yv - emu).abs() / row_scale).amax(dim=1)
-    assert (close > 2e-2).float().mean().item() < 5e-3, f"max {close.max().item():.3f} vs the FP8 emulation"
+    assert (close > 4e-2).float().mean().item() < 5e-3, f"max {close.max().item():.3f} vs the FP8 emulation"
     # (2) against the unquantised fp32 layer: the relative error of a row (Frobenius) stays within
     # 6e-2 for a single quantised GEMM; this chain quantises twice (tokens, then hidden), so the
     # bound is checked as "no worse than the emulation of the same chain" plus 6e-2 per GEMM
