@@ -52,8 +52,8 @@ constexpr int kGateEC = 8;       // experts per pass over the rows
 template <typename XT, int kGateTokens>
 __global__ void __launch_bounds__(kGateWarps * 32)
 gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ gw,
-                 const float* __restrict__ gb, const float* __restrict__ logits_in, long long L, int d, int E,
-                 int k, int vec_ok, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
+                 const float* __restrict__ gb, const float* __restrict__ logits_in, long long ld_logits, int split,
+                 long long L, int d, int E, int k, int vec_ok, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
                  float* __restrict__ topk_score) {
   __shared__ float s_logit[kGateWarps][kGateTokens][kMaxGateExperts];
   const int warp = threadIdx.x >> 5;
@@ -63,8 +63,15 @@ gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restric
   const int nt = static_cast<int>(min(static_cast<long long>(kGateTokens), L - t0));
 
   if (logits_in != nullptr) {
+    // logits computed elsewhere (tensor-core product): row stride ld_logits; with `split` the
+    // product was done on a two-term bf16 expansion of the gate weights and the halves are summed
     for (int j = 0; j < nt; ++j)
-      for (int e = lane; e < E; e += 32) s_logit[warp][j][e] = logits_in[(t0 + j) * E + e];
+      for (int e = lane; e < E; e += 32) {
+        const float* row = logits_in + (t0 + j) * ld_logits;
+        float v = row[e];
+        if (split) v += row[E + e];
+        s_logit[warp][j][e] = v + (gb ? gb[e] : 0.f);
+      }
   } else {
     const int d8 = vec_ok ? (d & ~7) : 0;
     for (int e0 = 0; e0 < E; e0 += kGateEC) {
@@ -303,12 +310,14 @@ route_place_kernel(const long long* __restrict__ topk_idx, long long L, int E, i
 using namespace fmoe;
 
 extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
-                              const float* logits_in, int64_t L, int d, int E, int k, float* logits_out,
-                              int64_t* topk_idx, float* topk_score, void* stream) {
+                              const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E,
+                              int k, float* logits_out, int64_t* topk_idx, float* topk_score, void* stream) {
   FMOE_REQUIRE(L >= 0 && E >= 1 && E <= kMaxGateExperts, "gate_topk: E=%d outside [1, %d]", E, kMaxGateExperts);
   FMOE_REQUIRE(k >= 1 && k <= E, "gate_topk: k=%d must be in [1, E=%d]", k, E);
   FMOE_REQUIRE(topk_idx && topk_score, "gate_topk: output pointers must not be NULL");
   FMOE_REQUIRE(logits_in || (x && gate_w && d >= 1), "gate_topk: need either logits_in or x and gate_w");
+  FMOE_REQUIRE(!logits_in || ld_logits >= (logits_split ? 2 : 1) * static_cast<int64_t>(E),
+               "gate_topk: ld_logits=%lld too small for E=%d", (long long)ld_logits, E);
   FMOE_REQUIRE(logits_in || x_dtype == FMOE_BF16 || x_dtype == FMOE_F32, "gate_topk: x must be bf16 or f32");
   if (L == 0) return FMOE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -324,7 +333,7 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
   long long* idx = reinterpret_cast<long long*>(topk_idx);
 #define FMOE_GATE(XT, TOK)                                                                                   \
   gate_topk_kernel<XT, TOK><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const XT*>(x), ldx, gate_w, gate_b, \
-                                                              logits_in, L, d, E, k, vec_ok, logits_out, idx, topk_score)
+                                                              logits_in, ld_logits, logits_split, L, d, E, k, vec_ok, logits_out, idx, topk_score)
   if (logits_in || x_dtype == FMOE_F32) {
     if (tok == 1) FMOE_GATE(float, 1); else FMOE_GATE(float, kGateTokensMax);
   } else {

@@ -327,6 +327,32 @@ def silu_jagged_bmm(
     return out
 
 
+def silu_jagged_bmm_raw(offsets: torch.Tensor, jagged: torch.Tensor, weight: torch.Tensor,
+                        out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Plain grouped product rows @ weight[e] with a chosen output type (bf16 operands may write
+    f32): the building block the router uses for its logits. weight is logical [E, K, N]."""
+    dev = _lib.require_cuda(offsets, jagged, weight)
+    lib = _lib.load()
+    rows, K = jagged.shape
+    E, Kw, N = weight.shape
+    assert Kw == K and weight.dtype == jagged.dtype
+    kp = _pad_k(K, jagged.dtype)
+    a = prep_activation(jagged, kp)
+    w, w_se, w_sn = prep_weight(weight, kp)
+    od = out_dtype or jagged.dtype
+    out = torch.empty((rows, N), dtype=od, device=dev)
+    off = _index_i64(offsets)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_silu_jagged_bmm(
+                off.data_ptr(), rows, a.data_ptr(), _lib.dtype_code(jagged.dtype), a.stride(0), None, w.data_ptr(),
+                None, w_se, 1, w_sn, 0, None, 0, E, kp, N, 0, None, None, None, out.data_ptr(), _lib.dtype_code(od),
+                out.stride(0), _lib.stream_ptr(dev),
+            )
+        )
+    return out
+
+
 def silu_jagged_bmm_combine(
     max_seq_len: int,
     offsets: torch.Tensor,

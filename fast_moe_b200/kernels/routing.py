@@ -19,6 +19,17 @@ class RoutingMetadata(NamedTuple):
     max_len: torch.Tensor         # [1] int64, on the device
 
 
+def split_gate_weight(gate_weight: torch.Tensor) -> torch.Tensor:
+    """Two-term bf16 expansion of the fp32 gate weights, hi = bf16(W), lo = bf16(W - hi), stacked
+    as one [1, 2E, d] weight whose reduction dimension is contiguous. x @ hi + x @ lo reproduces
+    x @ W to about 2^-17 relative per weight while running on the bf16 tensor cores; it is what
+    ``gate_topk`` uses when a precomputed split is passed in (worth it once E * d is large)."""
+    w = gate_weight.detach().to(torch.float32)
+    hi = w.to(torch.bfloat16)
+    lo = (w - hi.to(torch.float32)).to(torch.bfloat16)
+    return torch.cat([hi, lo], dim=0).unsqueeze(0).contiguous()
+
+
 def gate_topk(
     x: Optional[torch.Tensor],
     gate_weight: Optional[torch.Tensor],
@@ -26,20 +37,26 @@ def gate_topk(
     k: int,
     logits: Optional[torch.Tensor] = None,
     return_logits: bool = False,
+    gate_split: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """softmax(x @ Wg^T + bg) -> top-k -> scores of the chosen experts renormalised to sum 1.
 
     x [L, d] (bf16 / f32), gate_weight [E, d], gate_bias [E] or None; the gate parameters are
-    used in fp32. Alternatively pass ``logits`` [L, E] f32 and no x. Returns
+    used in fp32. Alternatively pass ``logits`` [L, E] f32 and no x. With ``gate_split``
+    (see ``split_gate_weight``) and bf16 x, the logits are computed by the tensor-core grouped
+    GEMM instead of the CUDA-core loop. Returns
     (topk_idx [L, k] int64 with slots in descending score order, ties to the lower expert id;
     topk_score [L, k] f32; logits [L, E] f32 if requested).
     """
     lib = _lib.load()
+    split = 0
     if logits is not None:
         dev = _lib.require_cuda(logits)
         lg = logits.to(torch.float32).contiguous()
         L, E = lg.shape
-        xx = gw = gb = None
+        ld_lg = E
+        xx = gw = None
+        gb = None
         d = 0
         x_dt = _lib.F32
         ldx = 0
@@ -48,21 +65,32 @@ def gate_topk(
         dev = _lib.require_cuda(x, gate_weight, gate_bias)
         assert x.ndim == 2 and gate_weight.ndim == 2 and gate_weight.shape[1] == x.shape[1]
         xx = x if x.stride(1) == 1 else x.contiguous()
-        gw = gate_weight.to(torch.float32).contiguous()
-        gb = None if gate_bias is None else gate_bias.to(torch.float32).contiguous()
+        gb = None if gate_bias is None else gate_bias.detach().to(torch.float32).contiguous()
         L, d = xx.shape
-        E = gw.shape[0]
+        E = gate_weight.shape[0]
         x_dt = _lib.dtype_code(xx.dtype)
         ldx = xx.stride(0)
         lg = None
+        ld_lg = 0
+        gw = None
+        if gate_split is not None and xx.dtype == torch.bfloat16 and d % 8 == 0 and L > 0:
+            from .moe import silu_jagged_bmm_raw
+
+            off = torch.arange(2, dtype=torch.int64, device=dev) * L      # [0, L], built on the device
+            lg = silu_jagged_bmm_raw(off, xx, gate_split.permute(0, 2, 1), out_dtype=torch.float32)   # [L, 2E]
+            ld_lg = lg.stride(0)
+            split = 1
+            xx = None
+        else:
+            gw = gate_weight.detach().to(torch.float32).contiguous()
     idx = torch.empty((L, k), dtype=torch.int64, device=dev)
     score = torch.empty((L, k), dtype=torch.float32, device=dev)
     lout = torch.empty((L, E), dtype=torch.float32, device=dev) if return_logits else None
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_gate_topk(
-                _lib.ptr(xx), x_dt, ldx, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(lg), L, d, E, k, _lib.ptr(lout),
-                idx.data_ptr(), score.data_ptr(), _lib.stream_ptr(dev),
+                _lib.ptr(xx), x_dt, ldx, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(lg), ld_lg, split, L, d, E, k,
+                _lib.ptr(lout), idx.data_ptr(), score.data_ptr(), _lib.stream_ptr(dev),
             )
         )
     return idx, score, lout

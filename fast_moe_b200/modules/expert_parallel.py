@@ -29,7 +29,7 @@ import torch.nn as nn
 
 from .. import _lib
 from ..kernels import moe as ops
-from ..kernels.routing import gate_topk, route_metadata
+from .fast_moe_module import GateSplitCache, route_tokens
 
 
 def local_expert_plan(recv_lengths: torch.Tensor, total: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -113,6 +113,7 @@ class ExpertParallelSwiGLUMoE(nn.Module):
                 out[i] = (torch.randn(rows, cols, generator=ge, device=dev) * init_std).to(dtype)
             return nn.Parameter(out)
 
+        self._gate_split = GateSplitCache()
         self.w_gate = expert_weights(hidden_dim, input_dim, 1)
         self.w_up = expert_weights(hidden_dim, input_dim, 2)
         self.w_down = expert_weights(output_dim, hidden_dim, 3)
@@ -124,9 +125,7 @@ class ExpertParallelSwiGLUMoE(nn.Module):
         W, El = self.world, self.experts_local
         x_flat = x.reshape(-1, self.input_dim)
         dt = x.dtype
-        with _lib.stage("route"):
-            idx, score, _ = gate_topk(x_flat, self.gate.weight.detach(), self.gate.bias.detach(), k)
-            meta = route_metadata(idx, self.num_experts)
+        score, meta = route_tokens(x_flat, self.gate, k, self.num_experts, self._gate_split)
         wg = self.w_gate.detach().permute(0, 2, 1)
         wu = self.w_up.detach().permute(0, 2, 1)
         wd = self.w_down.detach().permute(0, 2, 1)
@@ -145,13 +144,15 @@ class ExpertParallelSwiGLUMoE(nn.Module):
             send_lengths = meta.lengths.view(W, El)
             recv_lengths = torch.empty_like(send_lengths)
             dist.all_to_all_single(recv_lengths.view(-1), send_lengths.reshape(-1).contiguous(), group=self.group)
+            # the pack kernel is queued before the host waits for the counts, so the GPU packs the
+            # rows while the host reads the split sizes back
+            send = ops.gather_rows(x_flat, meta.gate_index, k)
             counts = torch.stack([send_lengths.sum(1), recv_lengths.sum(1)]).cpu()   # the layer's one host sync
             send_counts, recv_counts = counts[0].tolist(), counts[1].tolist()
             validate_plan(send_counts, recv_counts, recv_lengths, W)
             n_recv = sum(recv_counts)
             offsets_local, perm = local_expert_plan(recv_lengths, n_recv)
         with _lib.stage("dispatch"):
-            send = ops.gather_rows(x_flat, meta.gate_index, k)
             recv = torch.empty((n_recv, self.input_dim), dtype=dt, device=x.device)
             dist.all_to_all_single(recv, send, recv_counts, send_counts, group=self.group)
         with _lib.stage("up"):

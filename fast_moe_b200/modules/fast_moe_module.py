@@ -19,7 +19,7 @@ from torch.autograd.profiler import record_function
 from .. import _lib
 from ..kernels import moe as ops
 from ..kernels import moe_fp8 as ops_fp8
-from ..kernels.routing import RoutingMetadata, gate_topk, route_metadata
+from ..kernels.routing import RoutingMetadata, gate_topk, route_metadata, split_gate_weight
 from ..kernels.utils import KernelType
 
 
@@ -62,15 +62,48 @@ class _CastCache:
         return t
 
 
+# Above this many multiply-adds the gate logits go through the tensor cores (two-term bf16
+# expansion of the fp32 gate weights); below it the CUDA-core kernel is as fast and exact in fp32.
+GATE_TENSOR_CORE_MACS = 1 << 28
+
+
+class GateSplitCache:
+    """split_gate_weight(weight), recomputed when the weight changes in place or moves."""
+
+    def __init__(self) -> None:
+        self._key = None
+        self._val: Optional[torch.Tensor] = None
+
+    def get(self, w: torch.Tensor) -> torch.Tensor:
+        key = (w._version, w.data_ptr(), w.device)
+        if key != self._key:
+            self._val = split_gate_weight(w)
+            self._key = key
+        assert self._val is not None
+        return self._val
+
+
+def route_tokens(x_flat: torch.Tensor, gate: nn.Linear, k: int, num_experts: int,
+                 cache: GateSplitCache) -> Tuple[torch.Tensor, RoutingMetadata]:
+    """Gate, top-k and routing metadata for one batch of tokens (shared by all layers here)."""
+    with _lib.stage("route"):
+        L, d = x_flat.shape
+        split = None
+        if x_flat.dtype == torch.bfloat16 and d % 8 == 0 and L * d * num_experts >= GATE_TENSOR_CORE_MACS:
+            split = cache.get(gate.weight)
+        idx, score, _ = gate_topk(x_flat, gate.weight.detach(), None if gate.bias is None else gate.bias.detach(), k,
+                                  gate_split=split)
+        meta = route_metadata(idx, num_experts)
+    return score, meta
+
+
 class _MoEBase(nn.Module):
     num_experts: int
 
     def _route(self, x_flat: torch.Tensor, k: int) -> Tuple[torch.Tensor, RoutingMetadata]:
-        gate: nn.Linear = self.gate.gate  # type: ignore[attr-defined]
-        with _lib.stage("route"):
-            idx, score, _ = gate_topk(x_flat, gate.weight.detach(), None if gate.bias is None else gate.bias.detach(), k)
-            meta = route_metadata(idx, self.num_experts)
-        return score, meta
+        if not hasattr(self, "_gate_split"):
+            self._gate_split = GateSplitCache()
+        return route_tokens(x_flat, self.gate.gate, k, self.num_experts, self._gate_split)  # type: ignore[attr-defined]
 
 
 class FastMoELayer(_MoEBase):

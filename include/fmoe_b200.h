@@ -70,14 +70,17 @@ long long fmoe_kernel_launch_count(void);
  * chosen experts renormalised to sum 1 (F.normalize p=1, eps 1e-12).
  *   x         [L, d] bf16 or f32 (x_dtype), row stride ldx; may be NULL when logits_in is given
  *   gate_w    [E, d] f32 row-major (nn.Linear weight), gate_b [E] f32 or NULL
- *   logits_in [L, E] f32 or NULL: when non-NULL the matrix product is skipped
+ *   logits_in f32 or NULL: when non-NULL the matrix product is skipped and row t of the logits is
+ *             read at logits_in + t * ld_logits (gate_b is still added). With logits_split != 0 the
+ *             row holds two halves [E | E] that are summed: the product was computed with tensor
+ *             cores on a two-term bf16 expansion (hi + lo) of the fp32 gate weights.
  *   logits_out[L, E] f32 or NULL
  *   topk_idx  [L, k] int64, topk_score [L, k] f32
  * 1 <= k <= E <= 256.
  */
 int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
-                   const float* logits_in, int64_t L, int d, int E, int k, float* logits_out,
-                   int64_t* topk_idx, float* topk_score, void* stream);
+                   const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E, int k,
+                   float* logits_out, int64_t* topk_idx, float* topk_score, void* stream);
 
 /* Replaces FastMoELayer._compute_routing_metadata (modules/fast_moe_module.py:107-144) and the
  * fbgemm op asynchronous_complete_cumsum it calls (:131): a stable counting sort of the L*k

@@ -44,7 +44,7 @@ def test_library_exports_every_declared_symbol():
 def test_argument_validation_returns_status_not_crash():
     lib = _lib.load()
     # k > E
-    rc = lib.fmoe_gate_topk(None, _lib.F32, 0, None, None, None, 4, 8, 4, 5, None, None, None, None)
+    rc = lib.fmoe_gate_topk(None, _lib.F32, 0, None, None, None, 0, 0, 4, 8, 4, 5, None, None, None, None)
     assert rc == _lib.FMOE_ERR_BAD_ARG
     assert b"k=5" in lib.fmoe_last_error()
     # missing workspace

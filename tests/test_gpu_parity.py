@@ -108,6 +108,27 @@ def test_gate_topk_against_oracle_bf16():
     clean_status()
 
 
+def test_gate_topk_tensor_core_logits_match_fp32_path():
+    """bf16 hi/lo expansion of the gate weights on the tensor cores: logits agree with the fp32
+    CUDA-core path to ~1e-5 and route identically wherever the k-th / (k+1)-th gap is not tiny."""
+    from fast_moe_b200.kernels.routing import split_gate_weight
+
+    torch.manual_seed(9)
+    L, d, E, k = 3000, 1024, 64, 8
+    x = torch.randn(L, d).bfloat16().to(DEV)
+    gw = (torch.randn(E, d) * 0.05).to(DEV)
+    gb = (torch.randn(E) * 0.1).to(DEV)
+    idx0, sc0, lg0 = fm.gate_topk(x, gw, gb, k, return_logits=True)
+    idx1, sc1, lg1 = fm.gate_topk(x, gw, gb, k, return_logits=True, gate_split=split_gate_weight(gw))
+    torch.testing.assert_close(lg1, lg0, atol=2e-4, rtol=1e-4)
+    srt = torch.softmax(lg0, dim=1).sort(dim=1, descending=True).values
+    safe = (srt[:, :k] - srt[:, 1 : k + 1]).min(dim=1).values > 1e-5
+    assert safe.float().mean() > 0.95
+    assert torch.equal(idx0[safe], idx1[safe])
+    torch.testing.assert_close(sc1[safe], sc0[safe], atol=1e-5, rtol=1e-3)
+    clean_status()
+
+
 # ------------------------------------------------------------------------------- operators
 def _logical(g, key, dev=True):
     w = g[key]
