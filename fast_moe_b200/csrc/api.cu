@@ -233,3 +233,50 @@ extern "C" int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t tota
   return fmoe_mul_merge_k_add(reverse_index, bmm_scratch, bmm_dtype, N, gating_scores, g_dtype, gates_index, L, k, N,
                               out, out_dtype, ldo, stream);
 }
+
+extern "C" int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_t total_rows, const void* jagged,
+                                                  int dtype, int64_t ldj, const float* jagged_scale,
+                                                  const void* weight, const float* weight_scale, int64_t w_se,
+                                                  int64_t w_sk, int64_t w_sn, int64_t ws_se, const void* bias,
+                                                  int64_t bias_se, const void* gating_scores, int g_dtype,
+                                                  const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
+                                                  int has_silu, void* act_scratch, void* out, int out_dtype,
+                                                  int64_t ldo, void* stream) {
+  const bool fp8 = dtype == FMOE_E4M3;
+  FMOE_REQUIRE(fp8 || dtype == FMOE_BF16 || dtype == FMOE_F32, "silu_jagged_bmm_combine_fused: bad dtype %d", dtype);
+  FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm_combine_fused: FP8 operands need their scales");
+  FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm_combine_fused: has_silu is not available on FP8 input");
+  FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm_combine_fused: has_silu needs act_scratch");
+  FMOE_REQUIRE(gating_scores && gates_index, "silu_jagged_bmm_combine_fused: gating_scores and gates_index are required");
+  FMOE_REQUIRE(g_dtype == FMOE_BF16 || g_dtype == FMOE_F32, "silu_jagged_bmm_combine_fused: gate weights must be bf16 or f32");
+  FMOE_REQUIRE(total_rows == L * k, "silu_jagged_bmm_combine_fused: rows %lld != L*k = %lld", (long long)total_rows,
+               (long long)(L * k));
+  FMOE_REQUIRE(out != nullptr && ldo >= N, "silu_jagged_bmm_combine_fused: bad output");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int os = dtype_size(out_dtype);
+  if (L > 0) FMOE_CUDA_OK(cudaMemset2DAsync(out, static_cast<size_t>(ldo) * os, 0, static_cast<size_t>(N) * os, L, st));
+  const void* a = jagged;
+  int64_t lda = ldj;
+  if (has_silu && total_rows > 0) {
+    int rc = launch_silu(jagged, dtype, ldj, act_scratch, K, total_rows, K, st);
+    if (rc != FMOE_OK) return rc;
+    a = act_scratch;
+    lda = K;
+  }
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = dtype;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = a; g.a_rows = total_rows; g.lda = lda;
+  g.b0 = weight;
+  int rc = set_weight(g, "silu_jagged_bmm_combine_fused", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.bias0 = bias; g.bias_se = bias_se;
+  g.a_scale = jagged_scale; g.b0_scale = weight_scale; g.bscale_se = ws_se;
+  g.epilogue = FMOE_EPI_NONE;
+  g.gate = gating_scores; g.gate_dtype = g_dtype; g.gate_index = gates_index; g.gate_div = k; g.combine_rows = L;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, st);
+}

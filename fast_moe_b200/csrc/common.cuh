@@ -68,6 +68,13 @@ struct GemmDesc {
   int64_t bscale_se;
   int epilogue;              // FMOE_EPI_*
   const int64_t* out_index;  // device [total_rows] or null: row r is stored at out[out_index[r]]
+  // fused combine (all null/0 when unused): row r is multiplied by gate[gate_index[r]] and added
+  // to out[gate_index[r] / gate_div]; out has combine_rows rows and must start at zero
+  const void* gate;
+  int gate_dtype;
+  const int64_t* gate_index;
+  int gate_div;
+  int64_t combine_rows;
   void* out;
   int out_dtype;             // FMOE_BF16 or FMOE_F32
   int64_t ldo;               // elements

@@ -74,6 +74,11 @@ struct GemmParams {
   const float* b1_scale;
   long long bscale_se;
   int epilogue;
+  // fused combine: row r is scaled by gate[gate_index[r]] and ADDED to out[gate_index[r] / gate_div]
+  const void* gate;
+  int gate_is_f32;
+  const long long* gate_index;
+  int gate_div;
   int vec_ok;        // output rows are 16-byte aligned: vector stores allowed
   int* status;
 };
@@ -143,9 +148,13 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int
 // writes one row's 64 contiguous bytes, 8 rows per instruction. Rows that do not exist (tail of
 // a segment) are skipped; rows may go anywhere (st_row), which also serves the scattered store.
 // For 4-byte outputs the chunk goes out in two halves of 16 columns.
+// With `accumulate` the 16-byte pieces are added to memory (red.global.add, four 4-byte
+// reductions per piece) instead of stored: the fused combine, where several expert rows land on
+// one token row.
 template <typename OutT>
 __device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, const float (&v)[32],
-                                                OutT* const (&st_row)[4], const bool (&st_ok)[4], int col0) {
+                                                OutT* const (&st_row)[4], const bool (&st_ok)[4], int col0,
+                                                bool accumulate) {
   constexpr int kHalves = sizeof(OutT) == 2 ? 1 : 2;
   const uint32_t my_row = stage_w + lane * 64;
   const int wsw = (lane >> 1) & 3;
@@ -186,7 +195,19 @@ __device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, cons
       if (st_ok[i]) {
         constexpr int kPieceElems = 16 / sizeof(OutT);
         OutT* dst = st_row[i] + col0 + (kHalves == 2 ? 16 * h : 0) + piece * kPieceElems;
-        *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
+        if (!accumulate) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
+        } else if constexpr (sizeof(OutT) == 2) {
+          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst), "r"(w0) : "memory");
+          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 2), "r"(w1) : "memory");
+          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 4), "r"(w2) : "memory");
+          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 6), "r"(w3) : "memory");
+        } else {
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(__uint_as_float(w0)) : "memory");
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + 1), "f"(__uint_as_float(w1)) : "memory");
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + 2), "f"(__uint_as_float(w2)) : "memory");
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + 3), "f"(__uint_as_float(w3)) : "memory");
+        }
       }
     }
     __syncwarp();
@@ -212,7 +233,7 @@ struct TileWalker {
   }
 };
 
-template <int ESIZE, int CTAS, bool DUAL, bool GATHER, typename OutT>
+template <int ESIZE, int CTAS, bool DUAL, bool GATHER, bool COMBINE, typename OutT>
 __global__ void __launch_bounds__(GATHER ? kGatherKernelThreads : kBaseThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
@@ -427,7 +448,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         scale_a = p.a_scale[src];
       }
       long long dst_row = row;
-      if (p.out_index != nullptr && row_ok) {
+      float gate_scale = 1.0f;
+      constexpr bool combine = COMBINE;   // compiled in only for the plain, contiguous-row kernels
+      if (combine && row_ok) {
+        const long long gi = p.gate_index[row];
+        if (gi < 0 || gi >= p.out_rows * p.gate_div) {
+          atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
+        } else {
+          dst_row = gi / p.gate_div;
+          gate_scale = p.gate_is_f32 ? reinterpret_cast<const float*>(p.gate)[gi]
+                                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.gate)[gi]);
+        }
+      }
+      if (p.out_index != nullptr && row_ok && !combine) {
         dst_row = p.out_index[row];
         if (dst_row < 0 || dst_row >= p.out_rows) {
           atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
@@ -507,10 +540,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
             }
           }
+          if (combine) {
+            // what the reference does in the activation type: round the GEMM row, multiply by the
+            // gate weight, round again (Tensor.mul), then accumulate
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float y = v[i];
+              if constexpr (sizeof(OutT) == 2) y = __bfloat162float(__float2bfloat16_rn(y));
+              v[i] = y * gate_scale;
+            }
+          }
           if (ncols == 32 && p.vec_ok) {
-            stage_and_store<OutT>(stage_w, lane, v, st_row, st_ok, col0);
+            stage_and_store<OutT>(stage_w, lane, v, st_row, st_ok, col0, combine);
           } else if (row_ok && ncols > 0) {
-            store_chunk<OutT>(out_row + col0, v, ncols, false);
+            if (combine) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (i < ncols) {
+                  if constexpr (sizeof(OutT) == 2) {
+                    atomicAdd(out_row + col0 + i, __float2bfloat16_rn(v[i]));
+                  } else {
+                    atomicAdd(out_row + col0 + i, v[i]);
+                  }
+                }
+              }
+            } else {
+              store_chunk<OutT>(out_row + col0, v, ncols, false);
+            }
           }
         }
       }
@@ -683,11 +739,11 @@ int make_tmap(CUtensorMap* m, int dt, int rank, const void* base, const cuuint64
 int g_launches = 0;
 int g_num_sms = 0;
 
-template <int ESIZE, int CTAS, bool DUAL, bool GATHER, typename OutT>
+template <int ESIZE, int CTAS, bool DUAL, bool GATHER, bool COMBINE, typename OutT>
 int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const GemmParams& p,
              int grid, cudaStream_t stream) {
   using Plan = SmemPlan<CTAS>;
-  auto kern = grouped_gemm_kernel<ESIZE, CTAS, DUAL, GATHER, OutT>;
+  auto kern = grouped_gemm_kernel<ESIZE, CTAS, DUAL, GATHER, COMBINE, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
     FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal));
@@ -713,7 +769,12 @@ int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap&
 template <int ESIZE, typename OutT>
 int dispatch_shape(int ctas, bool dual, bool gather, const CUtensorMap& tmA, const CUtensorMap& tmB0,
                    const CUtensorMap& tmB1, const GemmParams& p, int grid, cudaStream_t stream) {
-#define FMOE_GO(C, D, G) return launch_t<ESIZE, C, D, G, OutT>(tmA, tmB0, tmB1, p, grid, stream)
+#define FMOE_GO(C, D, G) return launch_t<ESIZE, C, D, G, false, OutT>(tmA, tmB0, tmB1, p, grid, stream)
+  if (p.gate_index != nullptr) {
+    // fused combine: plain epilogue on contiguous rows only (checked by the caller)
+    if (ctas == 2) return launch_t<ESIZE, 2, false, false, true, OutT>(tmA, tmB0, tmB1, p, grid, stream);
+    return launch_t<ESIZE, 1, false, false, true, OutT>(tmA, tmB0, tmB1, p, grid, stream);
+  }
   if (ctas == 2) {
     if (dual) { if (gather) FMOE_GO(2, true, true); else FMOE_GO(2, true, false); }
     if (gather) FMOE_GO(2, false, true); else FMOE_GO(2, false, false);
@@ -757,6 +818,9 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   if (d.index != nullptr && (static_cast<long long>(d.K) * esize) % 16 != 0) {
     return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: gathered rows need K to be a multiple of 16 bytes (K=%d x %d B); pad K",
                 d.K, esize);
+  }
+  if (d.gate_index != nullptr && (d.index != nullptr || d.epilogue != FMOE_EPI_NONE)) {
+    return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: the fused combine needs contiguous rows and the plain epilogue");
   }
   if (d.total_rows <= 0) return FMOE_OK;
   FMOE_REQUIRE(d.a_rows >= 1, "grouped_gemm: empty A source with %lld output rows", (long long)d.total_rows);
@@ -809,7 +873,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.offsets = reinterpret_cast<const long long*>(d.offsets);
   p.index = reinterpret_cast<const long long*>(d.index);
   p.out_index = reinterpret_cast<const long long*>(d.out_index);
-  p.out_rows = d.total_rows;
+  p.out_rows = d.gate_index ? d.combine_rows : d.total_rows;
   p.index_div = d.index_div > 0 ? d.index_div : 1;
   p.E = d.E;
   p.N = d.N;
@@ -829,6 +893,10 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.b1_scale = d.b1_scale;
   p.bscale_se = d.bscale_se;
   p.epilogue = d.epilogue;
+  p.gate = d.gate;
+  p.gate_is_f32 = d.gate_dtype == FMOE_F32 ? 1 : 0;
+  p.gate_index = reinterpret_cast<const long long*>(d.gate_index);
+  p.gate_div = d.gate_div > 0 ? d.gate_div : 1;
   const int osize = dtype_size(d.out_dtype);
   p.vec_ok = ((d.ldo * osize) % 16 == 0) && ((reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
   p.status = status;

@@ -366,9 +366,16 @@ def silu_jagged_bmm_combine(
     has_silu: bool = True,
     kernel: KernelType = KernelType.PYTORCH,
     triton_option: Optional[SiluJaggedBmmCombineOption] = None,
+    *,
+    fused: bool = False,
 ) -> torch.Tensor:
     """Down projection of every expert segment followed by the gate-weighted merge of each
-    token's k rows (kernels/moe.py:236-292): [L*k, D_in] -> [L, D_out]."""
+    token's k rows (kernels/moe.py:236-292): [L*k, D_in] -> [L, D_out].
+
+    Default: GEMM into a [L*k, D_out] scratch, then the deterministic gather-reduce. With
+    ``fused=True`` (needs gating_scores) the GEMM's epilogue multiplies by the gate weight and
+    adds straight into the token rows: one kernel and no intermediate; bit-identical for k <= 2,
+    last-bit order dependence for k > 2."""
     N = index.shape[0]
     L, K = reverse_index.shape
     _, D_in = jagged.shape
@@ -398,9 +405,20 @@ def silu_jagged_bmm_combine(
         gidx = _index_i64(gates_index)
         out_dtype = torch.promote_types(jagged.dtype, g.dtype)
     act_scratch = torch.empty((N, kp), dtype=jagged.dtype, device=dev) if has_silu else None
-    bmm_scratch = torch.empty((N, D_out), dtype=jagged.dtype, device=dev)
     out = torch.empty((L, D_out), dtype=out_dtype, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
+    if fused and g is not None and out_dtype == jagged.dtype:
+        with torch.cuda.device(dev):
+            _lib.check(
+                lib.fmoe_silu_jagged_bmm_combine_fused(
+                    off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
+                    _lib.ptr(b), D_out, g.data_ptr(), _lib.dtype_code(g.dtype), gidx.data_ptr(), L, K, E, kp, D_out,
+                    1 if has_silu else 0, _lib.ptr(act_scratch), out.data_ptr(), _lib.dtype_code(out_dtype),
+                    out.stride(0), _lib.stream_ptr(dev),
+                )
+            )
+        return out
+    bmm_scratch = torch.empty((N, D_out), dtype=jagged.dtype, device=dev)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_silu_jagged_bmm_combine(

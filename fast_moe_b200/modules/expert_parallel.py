@@ -137,7 +137,7 @@ class ExpertParallelSwiGLUMoE(nn.Module):
             with _lib.stage("down_combine"):
                 y = ops.silu_jagged_bmm_combine(0, meta.offsets, hidden, wd, None, meta.token_index,
                                                 meta.reverse_index, gating_scores=score.to(dt),
-                                                gates_index=meta.gate_index, has_silu=False)
+                                                gates_index=meta.gate_index, has_silu=False, fused=k <= 2)
             return y.view(*shape[:-1], self.output_dim)
 
         with _lib.stage("plan"):

@@ -99,6 +99,13 @@ def route_tokens(x_flat: torch.Tensor, gate: nn.Linear, k: int, num_experts: int
 
 class _MoEBase(nn.Module):
     num_experts: int
+    # Fold the gate-weighted combine into the down-projection GEMM (atomic adds into the token
+    # rows). "auto": only when k <= 2, where two commutative additions keep the result
+    # bit-reproducible; True / False force it on / off.
+    fused_combine = "auto"
+
+    def _use_fused_combine(self, k: int) -> bool:
+        return k <= 2 if self.fused_combine == "auto" else bool(self.fused_combine)
 
     def _route(self, x_flat: torch.Tensor, k: int) -> Tuple[torch.Tensor, RoutingMetadata]:
         if not hasattr(self, "_gate_split"):
@@ -153,6 +160,7 @@ class FastMoELayer(_MoEBase):
                 y = ops.silu_jagged_bmm_combine(
                     0, meta.offsets, hidden, w2, b2, meta.token_index, meta.reverse_index,
                     gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
+                    fused=self._use_fused_combine(k),
                 )
         return y.view(*shape[:-1], self.output_dim)
 
@@ -237,6 +245,7 @@ class SwiGLUFastMoELayer(_MoEBase):
                     y = ops.silu_jagged_bmm_combine(
                         0, meta.offsets, hidden, wd, None, meta.token_index, meta.reverse_index,
                         gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
+                        fused=self._use_fused_combine(k),
                     )
         return y.view(*shape[:-1], self.output_dim)
 

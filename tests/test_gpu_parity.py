@@ -314,3 +314,26 @@ def test_layers_against_golden(name):
     ysw = sw(cu(x), k)
     torch.testing.assert_close(ysw.cpu().view(-1, o)[safe], ref.view(-1, o)[safe], **TOL)
     clean_status()
+
+
+@pytest.mark.parametrize("name", G.names("ops_"))
+def test_fused_combine_epilogue_against_two_kernel_form(name):
+    """silu_jagged_bmm_combine(fused=True): the GEMM epilogue scales by the gate weight and adds
+    into the token rows. Same roundings as the two-kernel form; k <= 2 must match it bit for bit
+    in bf16, larger k within one bf16 ulp of accumulation order."""
+    g = G.load(name)
+    k = g["k"]
+    off = cu(g["offsets"])
+    w2 = _logical(g, "w2")
+    args = (0, off, cu(g["hid"]), w2, cu(g.get("b2")), cu(g["token_index"]), cu(g["reverse_index"]),
+            cu(g["gates"]), cu(g["gate_index"]))
+    for has_silu in (False, True):
+        two = fm.silu_jagged_bmm_combine(*args, has_silu=has_silu)
+        one = fm.silu_jagged_bmm_combine(*args, has_silu=has_silu, fused=True)
+        assert one.dtype == two.dtype and one.shape == two.shape
+        if k <= 2 and g["hid"].dtype == torch.bfloat16:
+            assert torch.equal(one, two)
+        else:
+            scale = max(1.0, two.float().abs().max().item())
+            torch.testing.assert_close(one.float(), two.float(), rtol=1e-2, atol=1e-2 * scale)
+    clean_status()
