@@ -37,6 +37,12 @@ CONFIGS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (up-projection
+# grouped GEMM), from the ncu capture summarised in profiles/grouped_gemm_c2.md. Only the
+# configuration that was captured has a figure; the others report null.
+NCU_TRAFFIC_BYTES = {"c2": 145.47e6 + 42.61e6}
+
+
 def layer_flops(c, tokens):
     A = tokens * c["k"]
     return 2 * tokens * c["d"] * c["E"] + 4 * A * c["d"] * c["h"] + 2 * A * c["h"] * c["o"]
@@ -401,7 +407,9 @@ def main():
             ach = up_flops / (up_ms * 1e-3) / 1e12
             roofline = dict(bound="tensor", kernel="grouped_gemm_kernel (gather + gate/up GEMM + SwiGLU)",
                             achieved=ach, peak=peak_tf, unit="TFLOP/s", frac=ach / peak_tf,
-                            traffic=None, peak_source=peaks["source"] + (" (2x bf16 burst for fp8)" if c.get("fp8") else " burst"),
+                            traffic=NCU_TRAFFIC_BYTES.get(name) if world == 1 else None,
+                            algorithmic_bytes=(2 * c["E"] * c["d"] * c["h"] + A * c["d"] + A * c["h"]) * (1 if c.get("fp8") else 2),
+                            peak_source=peaks["source"] + (" (2x bf16 burst for fp8)" if c.get("fp8") else " burst"),
                             flops_per_launch=up_flops, avg_launch_ms=up_ms)
         line = dict(
             metric="moe_layer_fwd_tokens_per_s", value=tokens_total / (ms_step * 1e-3), unit="tokens/s",

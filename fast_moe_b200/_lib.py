@@ -50,6 +50,7 @@ SIGNATURES = {
     "fmoe_last_error": (c_char_p, []),
     "fmoe_device_status": (c_int, [P, c_int, P]),
     "fmoe_kernel_launch_count": (c_longlong, []),
+    "fmoe_selftest_bounded_wait": (c_int, [I64, P]),
     "fmoe_gate_topk": (c_int, [P, c_int, I64, P, P, P, I64, c_int, I64, c_int, c_int, c_int, P, P, P, P]),
     "fmoe_route_workspace_bytes": (c_size_t, [I64, c_int, c_int]),
     "fmoe_route_metadata": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P, c_size_t, P]),

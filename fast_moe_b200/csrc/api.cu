@@ -89,6 +89,11 @@ extern "C" int fmoe_device_status(int* status_out, int reset, void* stream) {
   return FMOE_OK;
 }
 
+extern "C" int fmoe_selftest_bounded_wait(int64_t limit_us, void* stream) {
+  FMOE_REQUIRE(limit_us >= 1 && limit_us <= 1000000, "selftest_bounded_wait: limit must be 1 us .. 1 s");
+  return launch_selftest_wait(static_cast<unsigned long long>(limit_us) * 1000ull, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int fmoe_index_select_jagged_bmm(const int64_t* offsets, const int64_t* index, int index_div,
                                             int64_t total_rows, const void* jagged, int dtype, int64_t L,
                                             int64_t ldj, const void* weight, int64_t w_se, int64_t w_sk,

@@ -81,5 +81,6 @@ struct GemmDesc {
 };
 int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream);
 int grouped_gemm_launch_count();
+int launch_selftest_wait(unsigned long long limit_ns, cudaStream_t stream);
 
 }  // namespace fmoe

@@ -689,6 +689,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// One CTA waits on a barrier that nothing will ever signal, with a short limit. Exercises the
+// path every wait of the GEMM takes when it gives up: status code recorded, abort flag raised,
+// thread returns; nothing traps and the context stays usable.
+__global__ void selftest_wait_kernel(unsigned long long limit_ns, int* status) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, &abort_flag, status, FMOE_DEV_WAIT_PRODUCER, limit_ns, 64);
+  }
+  __syncthreads();
+  // a second waiter sees the abort flag and leaves at once
+  if (threadIdx.x == 32) {
+    ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, &abort_flag, status, FMOE_DEV_WAIT_MMA, 5000000000ull, 64);
+  }
+}
+
 // ------------------------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -797,6 +819,16 @@ int forced_ctas() {
 }  // namespace
 
 int grouped_gemm_launch_count() { return g_launches; }
+
+int launch_selftest_wait(unsigned long long limit_ns, cudaStream_t stream) {
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  selftest_wait_kernel<<<1, 64, 0, stream>>>(limit_ns, status);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_launches;
+  return FMOE_OK;
+}
 
 int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   const int esize = dtype_size(d.dtype);

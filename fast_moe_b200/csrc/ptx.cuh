@@ -66,16 +66,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // (first error wins). The caller must then leave its loop and fall through to the
 // common tear-down; nothing ever spins without a limit.
 //
-// The hot path is a bare try_wait loop: the first kFastSpins polls read no timer at all (reading
+// The hot path is a bare try_wait loop: the first fast_spins polls read no timer at all (reading
 // %globaltimer costs hundreds of cycles, which showed up as ~500 cycles per pipeline stage when
 // it sat in front of every wait that was not immediately ready). Only a wait that has already
 // spun for a long time starts looking at the clock, about once per 1024 polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag, int* status, int code,
-                                                  uint64_t limit_ns = 2000000000ull) {
-  constexpr uint32_t kFastSpins = 1u << 14;
+                                                  uint64_t limit_ns = 2000000000ull,
+                                                  uint32_t fast_spins = 1u << 14) {
 #pragma unroll 1
-  for (uint32_t i = 0; i < kFastSpins; ++i) {
+  for (uint32_t i = 0; i < fast_spins; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   const uint64_t t0 = globaltimer_ns();

@@ -59,6 +59,10 @@ const char* fmoe_last_error(void);
 /* Copies the device status word of the current device to *status_out (host), after synchronising
  * `stream`; clears it when reset != 0. */
 int fmoe_device_status(int* status_out, int reset, void* stream);
+/* Failure-path self test: one CTA waits, with the bounded wait every pipeline role uses, on a
+ * barrier that is never signalled; after limit_us it gives up, records FMOE_DEV_WAIT_PRODUCER in
+ * the device status word and returns. Nothing traps, the context stays usable. */
+int fmoe_selftest_bounded_wait(int64_t limit_us, void* stream);
 /* Number of kernels this library has launched in this process (all entry points). */
 long long fmoe_kernel_launch_count(void);
 
