@@ -368,25 +368,28 @@ def main():
     stage_ms = {n: (tot / cnt) for n, (tot, cnt) in timer.totals_ms().items()}
     status = _lib.device_status(device)
 
-    # ---- end to end: host tokens in, host result out, every step
-    y_host = torch.empty((c["batch"], c["seq"], c["o"]), dtype=torch.bfloat16).pin_memory()
-    def e2e_step():
-        if captured is not None:
-            y_host.copy_(captured(x_host), non_blocking=True)       # H2D into the graph's input, replay, D2H
-        else:
-            xd = x_host.to(device, non_blocking=True)
-            y_host.copy_(layer(xd, k), non_blocking=True)
+    # ---- end to end: host tokens in, host result out, every step, through the package's
+    # streaming executor: every step copies its tokens from pinned host memory and its result
+    # back to pinned host memory; the copies of neighbouring steps overlap the forward.
+    from fast_moe_b200 import StreamingForward
 
-    for _ in range(3):
-        e2e_step()
+    slots = 3
+    pipe = StreamingForward(layer, x_dev, k, slots=slots, capture=captured is not None)
+    y_hosts = [torch.empty((c["batch"], c["seq"], c["o"]), dtype=torch.bfloat16).pin_memory() for _ in range(slots)]
+    y_host = y_hosts[0]
+    for i in range(max(3, slots)):
+        pipe.submit(x_host, y_hosts[i % slots])
+    pipe.synchronize()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    for i in range(args.steps):
+        pipe.submit(x_host, y_hosts[i % slots])
+    pipe.drain()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
+    e2e_check = float((y_hosts[(args.steps - 1) % slots].float() - y.detach().float().cpu().view_as(y_host)).abs().max())
 
     t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
     if dist is not None:
@@ -422,7 +425,9 @@ def main():
             device_status=status,
             e2e=dict(value=tokens_total / (ms_e2e / args.steps * 1e-3), unit="tokens/s",
                      h2d_bytes_per_step=x_host.numel() * x_host.element_size(),
-                     d2h_bytes_per_step=y_host.numel() * y_host.element_size(), ms_per_step=ms_e2e / args.steps),
+                     d2h_bytes_per_step=y_host.numel() * y_host.element_size(), ms_per_step=ms_e2e / args.steps,
+                     mode="%d-slot pipeline: H2D, forward and D2H of consecutive steps overlap" % slots,
+                     max_abs_diff_vs_resident=e2e_check),
         )
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = time_cpu_baseline(c, c["tokens"])

@@ -14,13 +14,15 @@ from .kernels.moe import (
 )
 from .kernels.routing import RoutingMetadata, gate_topk, route_metadata
 from .kernels.utils import KernelType
-from .modules.fast_moe_module import CapturedForward, FastMoELayer, GatingNetwork, SwiGLUFastMoELayer
+from .modules.fast_moe_module import (CapturedForward, FastMoELayer, GatingNetwork, StreamingForward,
+                                      SwiGLUFastMoELayer)
 
 __all__ = [
     "FastMoELayer",
     "GatingNetwork",
     "SwiGLUFastMoELayer",
     "CapturedForward",
+    "StreamingForward",
     "KernelType",
     "IndexSelectJaggedBmmOption",
     "SiluJaggedBmmCombineOption",

@@ -304,6 +304,105 @@ route_place_kernel(const long long* __restrict__ topk_idx, long long L, int E, i
   }
 }
 
+// ---- counting sort, one block ------------------------------------------------------------------
+// The three passes above in a single launch, for problems whose whole bit-mask table
+// (ceil(L/32) x E words, twice) fits in shared memory: a 1024-thread block builds the masks of
+// all tokens, warps scan them per expert, and every thread places its rows. Same results as the
+// three-kernel path (the stable order is a property of the masks, not of the schedule).
+constexpr int kRouteOneBlockThreads = 1024;
+constexpr int kRouteOneBlockWords = 11 * 1024;   // mask words (and as many rank words) that fit: 2 x 44 KiB
+constexpr int kRouteOneBlockTokens = 8192;       // beyond this the three-pass grid is faster than one block
+
+__global__ void __launch_bounds__(kRouteOneBlockThreads)
+route_one_block_kernel(const long long* __restrict__ topk_idx, int L, int E, int k, long long* __restrict__ lengths,
+                       long long* __restrict__ offsets, long long* __restrict__ gate_index,
+                       long long* __restrict__ token_index, long long* __restrict__ reverse_index,
+                       long long* __restrict__ max_len, int* status) {
+  extern __shared__ unsigned sm_words[];
+  const int G = (L + 31) >> 5;                 // groups of 32 tokens
+  unsigned* masks = sm_words;                  // [G][E] which tokens of group g picked expert e
+  int* base = reinterpret_cast<int*>(sm_words + static_cast<size_t>(G) * E);   // [G][E] rows of e before group g
+  int* s_off = base + static_cast<size_t>(G) * E;                              // [E + 1]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < G * E; i += kRouteOneBlockThreads) masks[i] = 0u;
+  __syncthreads();
+  for (int t = threadIdx.x; t < L; t += kRouteOneBlockThreads) {
+    for (int s = 0; s < k; ++s) {
+      const long long e = topk_idx[static_cast<long long>(t) * k + s];
+      if (e < 0 || e >= E) {
+        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+        continue;
+      }
+      atomicOr(&masks[(t >> 5) * E + static_cast<int>(e)], 1u << (t & 31));
+    }
+  }
+  __syncthreads();
+  // per expert: exclusive prefix of the group counts (one warp per expert, 32 groups per step)
+  for (int e = warp; e < E; e += kRouteOneBlockThreads / 32) {
+    int carry = 0;
+    for (int g0 = 0; g0 < G; g0 += 32) {
+      const int g = g0 + lane;
+      const int c = g < G ? __popc(masks[g * E + e]) : 0;
+      int v = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      if (g < G) base[g * E + e] = carry + v - c;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) s_off[e + 1] = carry;       // length of e, turned into an offset below
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // lengths -> offsets (inclusive scan, 32 experts per step) and the longest segment
+    int carry = 0;
+    int mx = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int len = e < E ? s_off[e + 1] : 0;
+      if (e < E && lengths) lengths[e] = len;
+      mx = max(mx, len);
+      int v = len;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      if (e < E) s_off[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) {
+      s_off[0] = 0;
+      if (max_len) *max_len = mx;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += kRouteOneBlockThreads) offsets[e] = s_off[e];
+  if (!gate_index && !token_index && !reverse_index) return;
+  for (int t = threadIdx.x; t < L; t += kRouteOneBlockThreads) {
+    const unsigned lt = (1u << (t & 31)) - 1u;
+    const int g = t >> 5;
+    for (int s = 0; s < k; ++s) {
+      const long long e64 = topk_idx[static_cast<long long>(t) * k + s];
+      if (e64 < 0 || e64 >= E) continue;
+      const int e = static_cast<int>(e64);
+      const long long pos = s_off[e] + base[g * E + e] + __popc(masks[g * E + e] & lt);
+      if (gate_index) gate_index[pos] = static_cast<long long>(t) * k + s;
+      if (token_index) token_index[pos] = t;
+      if (reverse_index) {
+        int j = 0;
+        for (int s2 = 0; s2 < k; ++s2) j += (topk_idx[static_cast<long long>(t) * k + s2] < e64) ? 1 : 0;
+        reverse_index[static_cast<long long>(t) * k + j] = pos;
+      }
+    }
+  }
+}
+
 }  // namespace
 }  // namespace fmoe
 
@@ -371,6 +470,26 @@ extern "C" int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, in
   int* block_cnt = static_cast<int*>(workspace);
   const size_t smem = static_cast<size_t>(kRouteBlock / 32) * E * sizeof(unsigned);
   const long long* idx = reinterpret_cast<const long long*>(topk_idx);
+  // Small problems: everything in one block, one launch (the workspace is not touched).
+  const long long words = ((L + 31) / 32) * static_cast<long long>(E);
+  if (L > 0 && L <= kRouteOneBlockTokens && words <= kRouteOneBlockWords) {
+    const size_t one_smem = (2 * static_cast<size_t>(words) + E + 1) * sizeof(int);
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    FMOE_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      FMOE_CUDA_OK(cudaFuncSetAttribute(route_one_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>((2 * kRouteOneBlockWords + 4097) * sizeof(int))));
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    route_one_block_kernel<<<1, kRouteOneBlockThreads, one_smem, st>>>(
+        idx, static_cast<int>(L), E, k, reinterpret_cast<long long*>(lengths), reinterpret_cast<long long*>(offsets),
+        reinterpret_cast<long long*>(gate_index), reinterpret_cast<long long*>(token_index),
+        reinterpret_cast<long long*>(reverse_index), reinterpret_cast<long long*>(max_len), status);
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+    return FMOE_OK;
+  }
   if (smem > 48 * 1024) {
     FMOE_CUDA_OK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     FMOE_CUDA_OK(cudaFuncSetAttribute(route_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

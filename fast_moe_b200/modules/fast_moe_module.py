@@ -285,3 +285,83 @@ class CapturedForward:
         self.x.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.y
+
+
+class StreamingForward:
+    """Host-to-host forward over a stream of batches: tokens come from pinned host memory and the
+    result goes back to pinned host memory, with the three legs of consecutive batches overlapped.
+
+    Each of ``slots`` slots owns a device input buffer and (single-process layers) a CUDA graph of
+    the forward with its own output buffer. ``submit`` queues, without blocking the host, the
+    host-to-device copy on a copy-in stream, the forward on a compute stream and the
+    device-to-host copy on a copy-out stream; events order the legs of one batch and keep a slot's
+    buffers from being overwritten while an earlier batch still uses them. With two or more slots
+    the copy of batch i+1 and the read-back of batch i-1 run while batch i computes, so the
+    steady-state cost of a batch is the slowest leg instead of their sum. ``drain`` makes the
+    caller's stream wait for everything queued so far. Batches complete in submission order.
+
+    ``capture=False`` runs the layer eagerly on the compute stream (needed for layers that
+    synchronise with the host inside the forward, like the expert-parallel one).
+    """
+
+    def __init__(self, layer: nn.Module, example: torch.Tensor, num_experts_per_tok: int, slots: int = 2,
+                 capture: bool = True) -> None:
+        if not example.is_cuda:
+            raise RuntimeError("StreamingForward needs a CUDA example tensor (shape and dtype of one batch)")
+        if slots < 1:
+            raise ValueError("slots must be >= 1")
+        dev = example.device
+        self.layer = layer
+        self.k = num_experts_per_tok
+        self.device = dev
+        self.s_in = torch.cuda.Stream(device=dev)
+        self.s_run = torch.cuda.Stream(device=dev)
+        self.s_out = torch.cuda.Stream(device=dev)
+        self.graphs = [CapturedForward(layer, example, num_experts_per_tok) for _ in range(slots)] if capture else None
+        self.x = [g.x for g in self.graphs] if capture else [torch.empty_like(example) for _ in range(slots)]
+        self.y = [None] * slots
+        ev = lambda: torch.cuda.Event()
+        self.in_ready = [ev() for _ in range(slots)]
+        self.run_done = [ev() for _ in range(slots)]
+        self.out_done = [ev() for _ in range(slots)]
+        self.used = [False] * slots
+        self.count = 0
+        cur = torch.cuda.current_stream(dev)
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.wait_stream(cur)
+
+    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """Queue one batch: x_host (pinned) -> device -> forward -> y_host (pinned)."""
+        s = self.count % len(self.x)
+        self.count += 1
+        with torch.cuda.stream(self.s_in):
+            if self.used[s]:
+                self.s_in.wait_event(self.run_done[s])      # the slot's previous batch has been consumed
+            self.x[s].copy_(x_host, non_blocking=True)
+            self.in_ready[s].record(self.s_in)
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(self.in_ready[s])
+            if self.used[s]:
+                self.s_run.wait_event(self.out_done[s])     # the slot's previous result has left the device
+            if self.graphs is not None:
+                y = self.graphs[s].replay()
+            else:
+                y = self.layer(self.x[s], self.k)
+                y.record_stream(self.s_out)
+            self.y[s] = y
+            self.run_done[s].record(self.s_run)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.run_done[s])
+            y_host.copy_(y.view(y_host.shape), non_blocking=True)
+            self.out_done[s].record(self.s_out)
+        self.used[s] = True
+
+    def drain(self) -> None:
+        """Make the current stream wait for every batch submitted so far (no host block)."""
+        cur = torch.cuda.current_stream(self.device)
+        for st in (self.s_in, self.s_run, self.s_out):
+            cur.wait_stream(st)
+
+    def synchronize(self) -> None:
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.synchronize()

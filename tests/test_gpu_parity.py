@@ -71,7 +71,9 @@ def test_route_metadata_bit_exact_against_golden(name):
 
 
 @pytest.mark.parametrize("L,E,k,skew", [(1, 4, 1, 0.0), (255, 8, 2, 0.0), (257, 8, 8, 0.0), (1000, 64, 8, 3.0),
-                                        (4096, 8, 2, 0.0), (8192, 64, 8, 2.0), (5000, 256, 4, 1.0), (0, 4, 2, 0.0)])
+                                        (4096, 8, 2, 0.0), (8192, 64, 8, 2.0), (5000, 256, 4, 1.0), (0, 4, 2, 0.0),
+                                        # either side of the single-block / three-pass switch
+                                        (8192, 32, 4, 0.5), (8193, 8, 2, 0.0), (33, 300, 3, 0.0)])
 def test_route_metadata_against_oracle(L, E, k, skew):
     g = torch.Generator().manual_seed(L * 131 + E)
     logits = torch.randn(L, E, generator=g) - skew * torch.arange(E).float().log1p()
