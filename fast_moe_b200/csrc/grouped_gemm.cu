@@ -432,6 +432,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int row_in_tile = static_cast<int>(rank) * kBM + q * 32 + lane;
     constexpr bool fp8 = (ESIZE == 1);
     constexpr int kChunks = kTileN / 64;              // 32-column chunks per warp: 4 plain, 2 gated
+    const bool plain_math = p.bias0 == nullptr && p.bias1 == nullptr && !(fp8 && p.a_scale != nullptr);
     const int c_begin = half * kChunks * 32;
     const uint32_t stage_w = staging_addr + (warp - 2) * 2048;
     int it = 0;
@@ -518,6 +519,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int col0 = n0 + c_begin + 32 * (j0 + j);
           const int ncols = min(32, p.N - col0);
           float v[32];
+          if (DUAL && ncols == 32 && plain_math) {
+            // gated tile, whole chunk inside N, no bias, no dequantisation: straight-line arithmetic
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = silu_f(__uint_as_float(r0[j][i])) * __uint_as_float(r1[j][i]);
+          } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = col0 + i;
@@ -539,6 +545,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             } else {
               v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
             }
+          }
           }
           if (combine) {
             // what the reference does in the activation type: round the GEMM row, multiply by the
@@ -597,8 +604,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int i = 0; i < 8; ++i) {
           int rr = row0 + rbase + 16 * i;
           if (rr >= seg1) rr = tile0;
-          long long srow = p.index[rr] / p.index_div;
-          if (srow < 0 || srow >= p.a_rows) {
+          // indices and row counts are below 2^31 (the host checks the counts): 32-bit
+          // arithmetic, and no division at all in the common case of one row per index
+          const long long raw = p.index[rr];
+          unsigned srow = static_cast<unsigned>(raw);
+          if (p.index_div != 1) srow /= static_cast<unsigned>(p.index_div);
+          if (raw < 0 || raw > 0x7fffffffll || srow >= static_cast<unsigned>(p.a_rows)) {
             atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
             srow = 0;
           }

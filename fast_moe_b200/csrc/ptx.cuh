@@ -46,30 +46,37 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// One poll of a barrier phase. The hardware may park the thread until the phase completes or
+// kSuspendHintNs have passed, whichever is first, so a waiting warp issues a handful of
+// instructions per poll interval instead of spinning through the issue slots that the MMA and
+// TMA threads of the same scheduler need.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
 
 // Bounded wait on one phase of an mbarrier. Returns false when the wait gave up:
-// either another thread of the CTA raised *abort_flag, or this thread spun for longer
+// either another thread of the CTA raised *abort_flag, or this thread waited for longer
 // than limit_ns, in which case it raises the flag itself and records `code` in *status
 // (first error wins). The caller must then leave its loop and fall through to the
-// common tear-down; nothing ever spins without a limit.
+// common tear-down; nothing ever waits without a limit.
 //
 // The hot path is a bare try_wait loop: the first fast_spins polls read no timer at all (reading
 // %globaltimer costs hundreds of cycles, which showed up as ~500 cycles per pipeline stage when
 // it sat in front of every wait that was not immediately ready). Only a wait that has already
-// spun for a long time starts looking at the clock, about once per 1024 polls.
+// polled many times starts looking at the clock, once per 16 polls. A poll lasts between a few
+// hundred cycles and kSuspendHintNs, so the limit is overshot by at most
+// (fast_spins + 16) * kSuspendHintNs: a third of a second with the defaults.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag, int* status, int code,
                                                   uint64_t limit_ns = 2000000000ull,
@@ -81,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (((++spins) & 1023u) == 0u) {
+    if (((++spins) & 15u) == 0u) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
