@@ -148,8 +148,8 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int
 // writes one row's 64 contiguous bytes, 8 rows per instruction. Rows that do not exist (tail of
 // a segment) are skipped; rows may go anywhere (st_row), which also serves the scattered store.
 // For 4-byte outputs the chunk goes out in two halves of 16 columns.
-// With `accumulate` the 16-byte pieces are added to memory (red.global.add, four 4-byte
-// reductions per piece) instead of stored: the fused combine, where several expert rows land on
+// With `accumulate` the 16-byte pieces are added to memory (one vector red.global.add per
+// piece) instead of stored: the fused combine, where several expert rows land on
 // one token row.
 template <typename OutT>
 __device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, const float (&v)[32],
@@ -198,15 +198,14 @@ __device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, cons
         if (!accumulate) {
           *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
         } else if constexpr (sizeof(OutT) == 2) {
-          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst), "r"(w0) : "memory");
-          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 2), "r"(w1) : "memory");
-          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 4), "r"(w2) : "memory");
-          asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 6), "r"(w3) : "memory");
+          // one 16-byte reduction: eight independent bf16 additions
+          asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(w0), "r"(w1), "r"(w2),
+                       "r"(w3)
+                       : "memory");
         } else {
-          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(__uint_as_float(w0)) : "memory");
-          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + 1), "f"(__uint_as_float(w1)) : "memory");
-          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + 2), "f"(__uint_as_float(w2)) : "memory");
-          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + 3), "f"(__uint_as_float(w3)) : "memory");
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w0)),
+                       "f"(__uint_as_float(w1)), "f"(__uint_as_float(w2)), "f"(__uint_as_float(w3))
+                       : "memory");
         }
       }
     }
