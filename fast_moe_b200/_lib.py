@@ -21,6 +21,7 @@ FMOE_ERR_DEVICE = -4
 
 F32, BF16, E4M3 = 0, 1, 3
 EPI_NONE, EPI_SILU, EPI_SWIGLU = 0, 1, 2
+COMBINE_ACCUMULATE, COMBINE_ROUND_GATE = 1, 2      # flags of fmoe_silu_jagged_bmm_combine_fused
 
 DEV_STATUS_NAMES = {
     0: "ok",
@@ -83,7 +84,7 @@ SIGNATURES = {
     "fmoe_silu_jagged_bmm_combine_fused": (
         c_int,
         [P, I64, P, c_int, I64, P, P, P, I64, I64, I64, I64, P, I64, P, c_int, P, I64, c_int, c_int, c_int, c_int,
-         c_int, P, P, c_int, I64, P],
+         c_int, P, P, c_int, I64, c_int, P],
     ),
     "fmoe_rowwise_quant_fp8": (c_int, [P, c_int, I64, c_int, I64, c_int, c_int, P, I64, P, P]),
     "fmoe_bmm_weight_quant_fp8": (c_int, [P, c_int, c_int, c_int, c_int, P, P, P]),

@@ -246,9 +246,11 @@ extern "C" int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_
                                                   int64_t bias_se, const void* gating_scores, int g_dtype,
                                                   const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
                                                   int has_silu, void* act_scratch, void* out, int out_dtype,
-                                                  int64_t ldo, void* stream) {
+                                                  int64_t ldo, int flags, void* stream) {
   const bool fp8 = dtype == FMOE_E4M3;
   FMOE_REQUIRE(fp8 || dtype == FMOE_BF16 || dtype == FMOE_F32, "silu_jagged_bmm_combine_fused: bad dtype %d", dtype);
+  FMOE_REQUIRE((flags & ~(FMOE_COMBINE_ACCUMULATE | FMOE_COMBINE_ROUND_GATE)) == 0,
+               "silu_jagged_bmm_combine_fused: unknown flags 0x%x", flags);
   FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm_combine_fused: FP8 operands need their scales");
   FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm_combine_fused: has_silu is not available on FP8 input");
   FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm_combine_fused: has_silu needs act_scratch");
@@ -259,7 +261,9 @@ extern "C" int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_
   FMOE_REQUIRE(out != nullptr && ldo >= N, "silu_jagged_bmm_combine_fused: bad output");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int os = dtype_size(out_dtype);
-  if (L > 0) FMOE_CUDA_OK(cudaMemset2DAsync(out, static_cast<size_t>(ldo) * os, 0, static_cast<size_t>(N) * os, L, st));
+  if (L > 0 && !(flags & FMOE_COMBINE_ACCUMULATE)) {
+    FMOE_CUDA_OK(cudaMemset2DAsync(out, static_cast<size_t>(ldo) * os, 0, static_cast<size_t>(N) * os, L, st));
+  }
   const void* a = jagged;
   int64_t lda = ldj;
   if (has_silu && total_rows > 0) {
@@ -282,6 +286,7 @@ extern "C" int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_
   g.a_scale = jagged_scale; g.b0_scale = weight_scale; g.bscale_se = ws_se;
   g.epilogue = FMOE_EPI_NONE;
   g.gate = gating_scores; g.gate_dtype = g_dtype; g.gate_index = gates_index; g.gate_div = k; g.combine_rows = L;
+  g.gate_round = (flags & FMOE_COMBINE_ROUND_GATE) ? 1 : 0;
   g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
   return launch_grouped_gemm(g, st);
 }

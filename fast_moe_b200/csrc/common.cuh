@@ -74,6 +74,7 @@ struct GemmDesc {
   int gate_dtype;
   const int64_t* gate_index;
   int gate_div;
+  int gate_round;   // round f32 gate weights to the output type before use
   int64_t combine_rows;
   void* out;
   int out_dtype;             // FMOE_BF16 or FMOE_F32

@@ -77,6 +77,7 @@ struct GemmParams {
   // fused combine: row r is scaled by gate[gate_index[r]] and ADDED to out[gate_index[r] / gate_div]
   const void* gate;
   int gate_is_f32;
+  int gate_round;
   const long long* gate_index;
   int gate_div;
   int vec_ok;        // output rows are 16-byte aligned: vector stores allowed
@@ -458,6 +459,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           dst_row = gi / p.gate_div;
           gate_scale = p.gate_is_f32 ? reinterpret_cast<const float*>(p.gate)[gi]
                                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.gate)[gi]);
+          if (p.gate_round && sizeof(OutT) == 2) gate_scale = __bfloat162float(__float2bfloat16_rn(gate_scale));
         }
       }
       if (p.out_index != nullptr && row_ok && !combine) {
@@ -937,6 +939,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.epilogue = d.epilogue;
   p.gate = d.gate;
   p.gate_is_f32 = d.gate_dtype == FMOE_F32 ? 1 : 0;
+  p.gate_round = d.gate_round;
   p.gate_index = reinterpret_cast<const long long*>(d.gate_index);
   p.gate_div = d.gate_div > 0 ? d.gate_div : 1;
   const int osize = dtype_size(d.out_dtype);

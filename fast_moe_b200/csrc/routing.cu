@@ -43,23 +43,37 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* row, int c, float (&v
   }
 }
 
-constexpr int kGateTokensMax = 4;   // tokens a warp handles at once (gate weights are read once for all of them)
 constexpr int kGateEC = 8;       // experts per pass over the rows
 
-// One warp per kGateTokens tokens (4 when there are enough tokens to fill the GPU that way, else 1). Logits are accumulated in fp32 with the reduction order fixed
-// by the lane layout, so the same input always routes the same way. x is read in 16-byte pieces
-// and each gate-weight piece is used for all the warp's tokens; HBM traffic is one pass over x.
-template <typename XT, int kGateTokens>
+// One warp per kGateTokens tokens (4, 2 or 1: as many as still leave every SM a few warps per
+// scheduler). Logits are accumulated in fp32 with the reduction order fixed by the lane layout, so
+// the same input always routes the same way. x is read in 16-byte pieces and each gate-weight
+// piece is used for all the warp's tokens; HBM traffic is one pass over x.
+// W_SMEM: the block first copies the gate weights into shared memory and reads them from there.
+// Every token needs all of them, and read through L1 they were evicted by the streaming x rows
+// and came from L2 again and again (the kernel ran at a tenth of the HBM rate).
+template <typename XT, int kGateTokens, bool W_SMEM>
 __global__ void __launch_bounds__(kGateWarps * 32)
 gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ gw,
                  const float* __restrict__ gb, const float* __restrict__ logits_in, long long ld_logits, int split,
                  long long L, int d, int E, int k, int vec_ok, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
                  float* __restrict__ topk_score) {
   __shared__ float s_logit[kGateWarps][kGateTokens][kMaxGateExperts];
+  extern __shared__ __align__(16) float s_gw[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long t0 = (static_cast<long long>(blockIdx.x) * kGateWarps + warp) * kGateTokens;
-  if (t0 >= L) return;
+  if constexpr (W_SMEM) {
+    const int n4 = (E * d) >> 2;     // the host checked: E * d a multiple of 4, gw 16-byte aligned
+    for (int i = threadIdx.x; i < n4; i += kGateWarps * 32) {
+      reinterpret_cast<float4*>(s_gw)[i] = reinterpret_cast<const float4*>(gw)[i];
+    }
+    __syncthreads();
+    gw = s_gw;
+  }
+  const long long num_groups = (L + kGateTokens - 1) / kGateTokens;
+  for (long long grp = static_cast<long long>(blockIdx.x) * kGateWarps + warp; grp < num_groups;
+       grp += static_cast<long long>(gridDim.x) * kGateWarps) {
+  const long long t0 = grp * kGateTokens;
   const int nt = static_cast<int>(min(static_cast<long long>(kGateTokens), L - t0));
 
   if (logits_in != nullptr) {
@@ -183,6 +197,8 @@ gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restric
       for (int s = 0; s < k; ++s) topk_score[t * k + s] = topk_score[t * k + s] / denom;
     }
   }
+  __syncwarp();      // s_logit is reused by this warp's next group
+  }
 }
 
 // ---- counting sort -------------------------------------------------------------------------
@@ -304,66 +320,47 @@ route_place_kernel(const long long* __restrict__ topk_idx, long long L, int E, i
   }
 }
 
-// ---- counting sort, one block ------------------------------------------------------------------
-// The three passes above in a single launch, for problems whose whole bit-mask table
-// (ceil(L/32) x E words, twice) fits in shared memory: a 1024-thread block builds the masks of
-// all tokens, warps scan them per expert, and every thread places its rows. Same results as the
-// three-kernel path (the stable order is a property of the masks, not of the schedule).
-constexpr int kRouteOneBlockThreads = 1024;
-constexpr int kRouteOneBlockWords = 11 * 1024;   // mask words (and as many rank words) that fit: 2 x 44 KiB
-constexpr int kRouteOneBlockTokens = 8192;       // beyond this the three-pass grid is faster than one block
+// Passes 2 and 3 in one launch, for tables of block counts small enough that every block can
+// afford to read all of them (nb * E entries): each block sums the counts of the blocks before it
+// (its base) and of all blocks (the lengths), scans the lengths into offsets itself, and places
+// its rows. Block 0 also publishes lengths, offsets and max_len. Same results as the scan kernel
+// followed by route_place_kernel; one launch and no single-block serial pass.
+constexpr long long kPlaceScanMaxEntries = 32 * 1024;
 
-__global__ void __launch_bounds__(kRouteOneBlockThreads)
-route_one_block_kernel(const long long* __restrict__ topk_idx, int L, int E, int k, long long* __restrict__ lengths,
-                       long long* __restrict__ offsets, long long* __restrict__ gate_index,
-                       long long* __restrict__ token_index, long long* __restrict__ reverse_index,
-                       long long* __restrict__ max_len, int* status) {
-  extern __shared__ unsigned sm_words[];
-  const int G = (L + 31) >> 5;                 // groups of 32 tokens
-  unsigned* masks = sm_words;                  // [G][E] which tokens of group g picked expert e
-  int* base = reinterpret_cast<int*>(sm_words + static_cast<size_t>(G) * E);   // [G][E] rows of e before group g
-  int* s_off = base + static_cast<size_t>(G) * E;                              // [E + 1]
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < G * E; i += kRouteOneBlockThreads) masks[i] = 0u;
-  __syncthreads();
-  for (int t = threadIdx.x; t < L; t += kRouteOneBlockThreads) {
-    for (int s = 0; s < k; ++s) {
-      const long long e = topk_idx[static_cast<long long>(t) * k + s];
-      if (e < 0 || e >= E) {
-        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
-        continue;
-      }
-      atomicOr(&masks[(t >> 5) * E + static_cast<int>(e)], 1u << (t & 31));
+__global__ void __launch_bounds__(kRouteBlock)
+route_place_scan_kernel(const long long* __restrict__ topk_idx, long long L, int E, int k, int nb,
+                        const int* __restrict__ block_cnt, long long* __restrict__ lengths,
+                        long long* __restrict__ offsets, long long* __restrict__ max_len,
+                        long long* __restrict__ gate_index, long long* __restrict__ token_index,
+                        long long* __restrict__ reverse_index, int* status) {
+  extern __shared__ unsigned masks[];                         // [8][E]
+  int* s_base = reinterpret_cast<int*>(masks + (kRouteBlock / 32) * E);   // [E] rows of e in earlier blocks
+  int* s_off = s_base + E;                                    // [E + 1] lengths, then offsets
+  for (int e = threadIdx.x; e <= E; e += kRouteBlock) {
+    if (e < E) s_base[e] = 0;
+    s_off[e] = 0;
+  }
+  build_masks(topk_idx, L, E, k, masks, status);              // starts and ends with __syncthreads
+  const int entries = nb * E;
+  const int mine = static_cast<int>(blockIdx.x) * E;          // entries below this belong to earlier blocks
+  for (int i = threadIdx.x; i < entries; i += kRouteBlock) {
+    const int c = block_cnt[i];
+    if (c != 0) {
+      const int e = i % E;
+      atomicAdd(&s_off[e + 1], c);
+      if (i < mine) atomicAdd(&s_base[e], c);
     }
   }
   __syncthreads();
-  // per expert: exclusive prefix of the group counts (one warp per expert, 32 groups per step)
-  for (int e = warp; e < E; e += kRouteOneBlockThreads / 32) {
-    int carry = 0;
-    for (int g0 = 0; g0 < G; g0 += 32) {
-      const int g = g0 + lane;
-      const int c = g < G ? __popc(masks[g * E + e]) : 0;
-      int v = c;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += u;
-      }
-      if (g < G) base[g * E + e] = carry + v - c;
-      carry += __shfl_sync(0xffffffffu, v, 31);
-    }
-    if (lane == 0) s_off[e + 1] = carry;       // length of e, turned into an offset below
-  }
-  __syncthreads();
-  if (warp == 0) {
+  if (threadIdx.x < 32) {
     // lengths -> offsets (inclusive scan, 32 experts per step) and the longest segment
+    const int lane = threadIdx.x;
     int carry = 0;
     int mx = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
       const int e = e0 + lane;
       const int len = e < E ? s_off[e + 1] : 0;
-      if (e < E && lengths) lengths[e] = len;
+      if (blockIdx.x == 0 && e < E && lengths) lengths[e] = len;
       mx = max(mx, len);
       int v = len;
 #pragma unroll
@@ -376,29 +373,31 @@ route_one_block_kernel(const long long* __restrict__ topk_idx, int L, int E, int
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) {
-      s_off[0] = 0;
-      if (max_len) *max_len = mx;
-    }
+    if (blockIdx.x == 0 && lane == 0 && max_len) *max_len = mx;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += kRouteOneBlockThreads) offsets[e] = s_off[e];
-  if (!gate_index && !token_index && !reverse_index) return;
-  for (int t = threadIdx.x; t < L; t += kRouteOneBlockThreads) {
-    const unsigned lt = (1u << (t & 31)) - 1u;
-    const int g = t >> 5;
-    for (int s = 0; s < k; ++s) {
-      const long long e64 = topk_idx[static_cast<long long>(t) * k + s];
-      if (e64 < 0 || e64 >= E) continue;
-      const int e = static_cast<int>(e64);
-      const long long pos = s_off[e] + base[g * E + e] + __popc(masks[g * E + e] & lt);
-      if (gate_index) gate_index[pos] = static_cast<long long>(t) * k + s;
-      if (token_index) token_index[pos] = t;
-      if (reverse_index) {
-        int j = 0;
-        for (int s2 = 0; s2 < k; ++s2) j += (topk_idx[static_cast<long long>(t) * k + s2] < e64) ? 1 : 0;
-        reverse_index[static_cast<long long>(t) * k + j] = pos;
-      }
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e <= E; e += kRouteBlock) offsets[e] = s_off[e];
+  }
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long t = static_cast<long long>(blockIdx.x) * kRouteBlock + threadIdx.x;
+  if (t >= L || (!gate_index && !token_index && !reverse_index)) return;
+  const unsigned lt = (1u << lane) - 1u;
+  for (int s = 0; s < k; ++s) {
+    const long long e64 = topk_idx[t * k + s];
+    if (e64 < 0 || e64 >= E) continue;
+    const int e = static_cast<int>(e64);
+    int rank = s_base[e];
+    for (int w = 0; w < warp; ++w) rank += __popc(masks[w * E + e]);
+    rank += __popc(masks[warp * E + e] & lt);
+    const long long pos = static_cast<long long>(s_off[e]) + rank;
+    if (gate_index) gate_index[pos] = t * k + s;
+    if (token_index) token_index[pos] = t;
+    if (reverse_index) {
+      int j = 0;
+      for (int s2 = 0; s2 < k; ++s2) j += (topk_idx[t * k + s2] < e64) ? 1 : 0;
+      reverse_index[t * k + j] = pos;
     }
   }
 }
@@ -420,24 +419,49 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
   FMOE_REQUIRE(logits_in || x_dtype == FMOE_BF16 || x_dtype == FMOE_F32, "gate_topk: x must be bf16 or f32");
   if (L == 0) return FMOE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // 4 tokens per warp amortise the gate-weight reads, but only pay off when that still leaves a
-  // few warps per scheduler on every SM
-  const int tok = (L >= 148ll * kGateWarps * kGateTokensMax * 4) ? kGateTokensMax : 1;
-  const long long per_block = static_cast<long long>(kGateWarps) * tok;
-  const unsigned grid = static_cast<unsigned>((L + per_block - 1) / per_block);
   // 16-byte loads need aligned rows of x and of the gate weights
   const int xs = x_dtype == FMOE_BF16 ? 2 : 4;
   const int vec_ok = (logits_in == nullptr) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx * xs) % 16 == 0) &&
                      ((reinterpret_cast<uintptr_t>(gate_w) & 15) == 0) && (d % 8 == 0);
+  // Gate weights in shared memory when they fit beside the logits scratch (and a few blocks per SM)
+  const size_t w_bytes = logits_in ? 0 : static_cast<size_t>(E) * d * sizeof(float);
+  const bool w_smem = !logits_in && vec_ok && w_bytes <= 96 * 1024;
+  // Several tokens per warp amortise the gate-weight reads, but only pay off when that still
+  // leaves a few warps per scheduler on every SM
+  const long long warps_full = 148ll * kGateWarps * 2;
+  const int tok = (L >= warps_full * 4) ? 4 : ((w_smem && L >= warps_full) ? 2 : 1);
+  const long long per_block = static_cast<long long>(kGateWarps) * tok;
+  long long blocks = (L + per_block - 1) / per_block;
+  if (w_smem && blocks > 148 * 4) blocks = 148 * 4;     // persistent blocks: the weights are staged once per block
+  const unsigned grid = static_cast<unsigned>(blocks);
   long long* idx = reinterpret_cast<long long*>(topk_idx);
-#define FMOE_GATE(XT, TOK)                                                                                   \
-  gate_topk_kernel<XT, TOK><<<grid, kGateWarps * 32, 0, st>>>(static_cast<const XT*>(x), ldx, gate_w, gate_b, \
-                                                              logits_in, ld_logits, logits_split, L, d, E, k, vec_ok, logits_out, idx, topk_score)
+#define FMOE_GATE(XT, TOK, WS)                                                                                      \
+  do {                                                                                                              \
+    auto kern = gate_topk_kernel<XT, TOK, WS>;                                                                      \
+    if (WS && w_bytes > 16 * 1024) {                                                                                 \
+      FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));            \
+    }                                                                                                               \
+    kern<<<grid, kGateWarps * 32, WS ? w_bytes : 0, st>>>(static_cast<const XT*>(x), ldx, gate_w, gate_b, logits_in, \
+                                                          ld_logits, logits_split, L, d, E, k, vec_ok, logits_out,  \
+                                                          idx, topk_score);                                         \
+  } while (0)
+#define FMOE_GATE_T(XT)                                      \
+  do {                                                       \
+    if (w_smem) {                                            \
+      if (tok == 4) FMOE_GATE(XT, 4, true);                  \
+      else if (tok == 2) FMOE_GATE(XT, 2, true);             \
+      else FMOE_GATE(XT, 1, true);                           \
+    } else {                                                 \
+      if (tok == 4) FMOE_GATE(XT, 4, false);                 \
+      else FMOE_GATE(XT, 1, false);                          \
+    }                                                        \
+  } while (0)
   if (logits_in || x_dtype == FMOE_F32) {
-    if (tok == 1) FMOE_GATE(float, 1); else FMOE_GATE(float, kGateTokensMax);
+    FMOE_GATE_T(float);
   } else {
-    if (tok == 1) FMOE_GATE(__nv_bfloat16, 1); else FMOE_GATE(__nv_bfloat16, kGateTokensMax);
+    FMOE_GATE_T(__nv_bfloat16);
   }
+#undef FMOE_GATE_T
 #undef FMOE_GATE
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
@@ -470,26 +494,6 @@ extern "C" int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, in
   int* block_cnt = static_cast<int*>(workspace);
   const size_t smem = static_cast<size_t>(kRouteBlock / 32) * E * sizeof(unsigned);
   const long long* idx = reinterpret_cast<const long long*>(topk_idx);
-  // Small problems: everything in one block, one launch (the workspace is not touched).
-  const long long words = ((L + 31) / 32) * static_cast<long long>(E);
-  if (L > 0 && L <= kRouteOneBlockTokens && words <= kRouteOneBlockWords) {
-    const size_t one_smem = (2 * static_cast<size_t>(words) + E + 1) * sizeof(int);
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    FMOE_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-      FMOE_CUDA_OK(cudaFuncSetAttribute(route_one_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>((2 * kRouteOneBlockWords + 4097) * sizeof(int))));
-      if (dev >= 0 && dev < 64) attr_set[dev] = true;
-    }
-    route_one_block_kernel<<<1, kRouteOneBlockThreads, one_smem, st>>>(
-        idx, static_cast<int>(L), E, k, reinterpret_cast<long long*>(lengths), reinterpret_cast<long long*>(offsets),
-        reinterpret_cast<long long*>(gate_index), reinterpret_cast<long long*>(token_index),
-        reinterpret_cast<long long*>(reverse_index), reinterpret_cast<long long*>(max_len), status);
-    FMOE_CUDA_OK(cudaGetLastError());
-    ++g_misc_launches;
-    return FMOE_OK;
-  }
   if (smem > 48 * 1024) {
     FMOE_CUDA_OK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     FMOE_CUDA_OK(cudaFuncSetAttribute(route_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -498,6 +502,20 @@ extern "C" int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, in
     route_count_kernel<<<nb, kRouteBlock, smem, st>>>(idx, L, E, k, block_cnt, status);
     FMOE_CUDA_OK(cudaGetLastError());
     ++g_misc_launches;
+  }
+  if (nb > 0 && static_cast<long long>(nb) * E <= kPlaceScanMaxEntries) {
+    // small table of block counts: every placement block scans it itself, no separate scan launch
+    const size_t smem2 = smem + (2 * static_cast<size_t>(E) + 1) * sizeof(int);
+    if (smem2 > 48 * 1024) {
+      FMOE_CUDA_OK(cudaFuncSetAttribute(route_place_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+    }
+    route_place_scan_kernel<<<nb, kRouteBlock, smem2, st>>>(
+        idx, L, E, k, nb, block_cnt, reinterpret_cast<long long*>(lengths), reinterpret_cast<long long*>(offsets),
+        reinterpret_cast<long long*>(max_len), reinterpret_cast<long long*>(gate_index),
+        reinterpret_cast<long long*>(token_index), reinterpret_cast<long long*>(reverse_index), status);
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+    return FMOE_OK;
   }
   route_scan_kernel<<<1, 1024, 0, st>>>(block_cnt, nb, E, reinterpret_cast<long long*>(lengths),
                                         reinterpret_cast<long long*>(offsets), reinterpret_cast<long long*>(max_len));

@@ -368,6 +368,8 @@ def silu_jagged_bmm_combine(
     triton_option: Optional[SiluJaggedBmmCombineOption] = None,
     *,
     fused: bool = False,
+    out: Optional[torch.Tensor] = None,
+    round_scores: bool = False,
 ) -> torch.Tensor:
     """Down projection of every expert segment followed by the gate-weighted merge of each
     token's k rows (kernels/moe.py:236-292): [L*k, D_in] -> [L, D_out].
@@ -375,7 +377,12 @@ def silu_jagged_bmm_combine(
     Default: GEMM into a [L*k, D_out] scratch, then the deterministic gather-reduce. With
     ``fused=True`` (needs gating_scores) the GEMM's epilogue multiplies by the gate weight and
     adds straight into the token rows: one kernel and no intermediate; bit-identical for k <= 2,
-    last-bit order dependence for k > 2."""
+    last-bit order dependence for k > 2.
+
+    ``round_scores=True`` treats gating_scores as if they had been cast to the activation type
+    first (what the reference layer does before calling this operator) without a cast kernel.
+    ``out`` (fused form only): an [L, D_out] tensor of the activation type that the rows are ADDED
+    to - zeros prepared ahead of time, or a residual; it is returned."""
     N = index.shape[0]
     L, K = reverse_index.shape
     _, D_in = jagged.shape
@@ -403,18 +410,30 @@ def silu_jagged_bmm_combine(
         _check_float(gating_scores, "gating_scores")
         g = gating_scores.contiguous().view(-1)
         gidx = _index_i64(gates_index)
-        out_dtype = torch.promote_types(jagged.dtype, g.dtype)
+        if round_scores and not (fused and g.dtype == torch.float32):
+            g = g.to(jagged.dtype)          # the two-kernel form takes the cast scores
+        out_dtype = jagged.dtype if round_scores else torch.promote_types(jagged.dtype, g.dtype)
     act_scratch = torch.empty((N, kp), dtype=jagged.dtype, device=dev) if has_silu else None
-    out = torch.empty((L, D_out), dtype=out_dtype, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
-    if fused and g is not None and out_dtype == jagged.dtype:
+    use_fused = fused and g is not None and out_dtype == jagged.dtype
+    accumulate = out is not None
+    if out is not None:
+        if not use_fused:
+            raise ValueError("out= is only available with fused=True and gating scores of the activation type")
+        _lib.require_cuda(out)
+        if tuple(out.shape) != (L, D_out) or out.dtype != out_dtype or out.stride(1) != 1:
+            raise ValueError(f"out must be [{L}, {D_out}] {out_dtype} with contiguous rows")
+    else:
+        out = torch.empty((L, D_out), dtype=out_dtype, device=dev)
+    if use_fused:
+        flags = (_lib.COMBINE_ACCUMULATE if accumulate else 0) | (_lib.COMBINE_ROUND_GATE if round_scores else 0)
         with torch.cuda.device(dev):
             _lib.check(
                 lib.fmoe_silu_jagged_bmm_combine_fused(
                     off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
                     _lib.ptr(b), D_out, g.data_ptr(), _lib.dtype_code(g.dtype), gidx.data_ptr(), L, K, E, kp, D_out,
                     1 if has_silu else 0, _lib.ptr(act_scratch), out.data_ptr(), _lib.dtype_code(out_dtype),
-                    out.stride(0), _lib.stream_ptr(dev),
+                    out.stride(0), flags, _lib.stream_ptr(dev),
                 )
             )
         return out

@@ -144,6 +144,8 @@ class FastMoELayer(_MoEBase):
         shape = x.shape
         k = num_experts_per_tok
         x_flat = x.reshape(-1, self.input_dim)
+        _lib.require_cuda(x)
+        fused = self._use_fused_combine(k)
         score, meta = self._route(x_flat, k)
         with record_function("## expert_forward##"):
             dt = x.dtype
@@ -159,8 +161,8 @@ class FastMoELayer(_MoEBase):
             with _lib.stage("down_combine"):
                 y = ops.silu_jagged_bmm_combine(
                     0, meta.offsets, hidden, w2, b2, meta.token_index, meta.reverse_index,
-                    gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
-                    fused=self._use_fused_combine(k),
+                    gating_scores=score, gates_index=meta.gate_index, has_silu=False,
+                    fused=fused, round_scores=True,
                 )
         return y.view(*shape[:-1], self.output_dim)
 
@@ -211,6 +213,8 @@ class SwiGLUFastMoELayer(_MoEBase):
         shape = x.shape
         k = num_experts_per_tok
         x_flat = x.reshape(-1, self.input_dim)
+        _lib.require_cuda(x)
+        fused = self._use_fused_combine(k)
         score, meta = self._route(x_flat, k)
         dt = x.dtype
         index = meta.gate_index.view(-1, k)
@@ -244,8 +248,8 @@ class SwiGLUFastMoELayer(_MoEBase):
                 with _lib.stage("down_combine"):
                     y = ops.silu_jagged_bmm_combine(
                         0, meta.offsets, hidden, wd, None, meta.token_index, meta.reverse_index,
-                        gating_scores=score.to(dt), gates_index=meta.gate_index, has_silu=False,
-                        fused=self._use_fused_combine(k),
+                        gating_scores=score, gates_index=meta.gate_index, has_silu=False,
+                        fused=fused, round_scores=True,
                     )
         return y.view(*shape[:-1], self.output_dim)
 

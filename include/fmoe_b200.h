@@ -211,14 +211,21 @@ int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t total_rows, con
  * out[gates_index[r] / k]. For k <= 2 this equals fmoe_silu_jagged_bmm_combine bit for bit in
  * bf16 (two commutative additions); for k > 2 the order of the additions, hence the last bit, is
  * not fixed - use the two-kernel form when reproducibility matters. jagged_scale / weight_scale
- * select the FP8 form as in fmoe_silu_jagged_bmm. */
+ * select the FP8 form as in fmoe_silu_jagged_bmm.
+ * flags: FMOE_COMBINE_ACCUMULATE - `out` is not cleared; the rows are added to what it holds (a
+ *   buffer the caller zeroed earlier, off the critical path, or a residual to add the layer to);
+ *   FMOE_COMBINE_ROUND_GATE - f32 gating_scores are rounded to the output type before use, which
+ *   is what casting the scores to the activation type first (modules/fast_moe_module.py:215)
+ *   would give, without the separate cast. */
+#define FMOE_COMBINE_ACCUMULATE 1
+#define FMOE_COMBINE_ROUND_GATE 2
 int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype,
                                        int64_t ldj, const float* jagged_scale, const void* weight,
                                        const float* weight_scale, int64_t w_se, int64_t w_sk, int64_t w_sn,
                                        int64_t ws_se, const void* bias, int64_t bias_se, const void* gating_scores,
                                        int g_dtype, const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
                                        int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo,
-                                       void* stream);
+                                       int flags, void* stream);
 
 /* Row gather: dst[r, :] = src[index[r] / index_div, :], r < rows. The index_select step of
  * pytorch_index_select_jagged_bmm (kernels/pytorch/moe.py:69-73: jagged[index]) as a standalone
