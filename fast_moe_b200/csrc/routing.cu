@@ -201,6 +201,223 @@ gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restric
   }
 }
 
+// ---- gate logits on the warp-level tensor cores ---------------------------------------------
+// bf16 tokens, few experts: the logits are a skinny product [L, d] x [d, E] whose CUDA-core form
+// issues ~1200 instructions per token. Here a block of 8 warps takes 32 tokens: warp w multiplies
+// the 16 tokens of tile (w >> 2) by the quarter (w & 3) of the columns with mma.sync m16n8k16,
+// the four partial sums meet in shared memory, and 32 threads finish one token each (softmax,
+// top-k, renormalisation - the same arithmetic, in the same order, as gate_topk_kernel).
+// The fp32 gate weights are split on the fly into three bf16 terms (hi + mid + lo reproduces
+// every weight to 2^-24), so the products are exact and only the fp32 accumulation order
+// differs from the CUDA-core kernel.
+//
+// Fragment layout trick: the reduction index of an MMA may be any permutation of the columns as
+// long as both operands use the same one. Lane (g = lane / 4, q = lane % 4) therefore loads 16
+// contiguous bytes of token row g (and g + 8) at column k0 + 8 q, and 16 bytes of each weight
+// term of expert g at the same column: registers 0,1 feed one MMA, registers 2,3 the next.
+constexpr int kMmaGateWarps = 8;
+constexpr int kMmaGateTokens = 32;            // per block
+constexpr int kMmaGatePadBytes = 64;          // row padding of the weight terms: conflict-free 16-byte reads
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>   // experts handled = 8 * NT (E rounded up; the padding experts have zero weights)
+__global__ void __launch_bounds__(kMmaGateWarps * 32, 2)
+gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const float* __restrict__ gw,
+                     const float* __restrict__ gb, long long L, int d, int E, int k,
+                     float* __restrict__ logits_out, long long* __restrict__ topk_idx,
+                     float* __restrict__ topk_score) {
+  constexpr int EP = 8 * NT;
+  extern __shared__ __align__(16) uint8_t smem_gate[];
+  const int row_bytes = d * 2 + kMmaGatePadBytes;
+  uint8_t* s_w = smem_gate;                                            // [3 terms][EP][row_bytes]
+  float* s_part = reinterpret_cast<float*>(smem_gate + 3 * EP * row_bytes);   // [4][32][EP + 1]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int q = lane & 3;
+  const int tile = warp >> 2;
+  const int kc = warp & 3;
+  // this warp's columns: a quarter of d, rounded up to whole 32-column steps
+  const int chunk = ((d + 3) / 4 + 31) & ~31;
+  const int c_begin = kc * chunk;
+  const int c_end = min(d, c_begin + chunk);
+  const int steps = c_begin < c_end ? (c_end - c_begin + 31) >> 5 : 0;
+  const long long num_tiles = (L + kMmaGateTokens - 1) / kMmaGateTokens;
+
+  // Token rows of a block's 32-token tile, 16 bytes per lane and row, kDepth steps at a time.
+  constexpr int kDepth = 8;                       // 32-column steps held in registers at once
+  uint4 xa[kDepth], xb[kDepth];
+  auto load_rows = [&](long long tile_id, int s0) {
+    const long long r0 = tile_id * kMmaGateTokens + tile * 16 + g;
+    const __nv_bfloat16* row0 = x + r0 * ldx;
+    const __nv_bfloat16* row1 = x + (r0 + 8) * ldx;
+    const bool ok0 = r0 < L;
+    const bool ok1 = r0 + 8 < L;
+#pragma unroll
+    for (int i = 0; i < kDepth; ++i) {
+      const int c = c_begin + (s0 + i) * 32 + q * 8;
+      const bool in = (s0 + i) < steps && c < c_end;
+      xa[i] = (in && ok0) ? *reinterpret_cast<const uint4*>(row0 + c) : make_uint4(0, 0, 0, 0);
+      xb[i] = (in && ok1) ? *reinterpret_cast<const uint4*>(row1 + c) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  // the first tile's rows go out first (HBM latency); the weight staging runs underneath them
+  load_rows(blockIdx.x, 0);
+
+  // gate weights -> three bf16 terms in shared memory (zero rows for the padding experts),
+  // four weights per thread and step, four steps in flight
+  {
+    const int quads_per_row = d >> 2;
+    const int quads = EP * quads_per_row;
+    constexpr int kUnroll = 4;
+    for (int i0 = threadIdx.x; i0 < quads; i0 += kMmaGateWarps * 32 * kUnroll) {
+      float4 w[kUnroll];
+      int ee[kUnroll], cc[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int i = i0 + u * kMmaGateWarps * 32;
+        ee[u] = i / quads_per_row;
+        cc[u] = (i - ee[u] * quads_per_row) * 4;
+        w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < quads && ee[u] < E) w[u] = *reinterpret_cast<const float4*>(gw + static_cast<long long>(ee[u]) * d + cc[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (i0 + u * kMmaGateWarps * 32 < quads) {
+          const float wf[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+          uint32_t t3[3][2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(wf[2 * h], wf[2 * h + 1]);
+            const float2 hf = __bfloat1622float2(hi);
+            const float2 r1 = make_float2(wf[2 * h] - hf.x, wf[2 * h + 1] - hf.y);
+            const __nv_bfloat162 mid = __floats2bfloat162_rn(r1.x, r1.y);
+            const float2 mf = __bfloat1622float2(mid);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(r1.x - mf.x, r1.y - mf.y);
+            t3[0][h] = *reinterpret_cast<const uint32_t*>(&hi);
+            t3[1][h] = *reinterpret_cast<const uint32_t*>(&mid);
+            t3[2][h] = *reinterpret_cast<const uint32_t*>(&lo);
+          }
+          uint8_t* dst = s_w + ee[u] * row_bytes + cc[u] * 2;
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            *reinterpret_cast<uint2*>(dst + term * EP * row_bytes) = make_uint2(t3[term][0], t3[term][1]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  for (long long tile_id = blockIdx.x; tile_id < num_tiles; tile_id += gridDim.x) {
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+  for (int s0 = 0; s0 < steps; s0 += kDepth) {
+    if (s0 > 0) load_rows(tile_id, s0);
+#pragma unroll
+    for (int i = 0; i < kDepth; ++i) {
+      if (s0 + i < steps) {       // warp-uniform: mma.sync needs all 32 lanes
+        // Lanes whose 8 columns lie past the end hold zero token values; they read the last
+        // valid weight columns instead (finite numbers, multiplied by zero) and take part in
+        // the MMA like every other lane.
+        const int c = min(c_begin + (s0 + i) * 32 + q * 8, d - 8);
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          const uint8_t* wrow = s_w + (n * 8 + g) * row_bytes + c * 2;
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + term * EP * row_bytes);
+            mma_bf16_16816(acc[n], xa[i].x, xb[i].x, xa[i].y, xb[i].y, wv.x, wv.y);
+            mma_bf16_16816(acc[n], xa[i].z, xb[i].z, xa[i].w, xb[i].w, wv.z, wv.w);
+          }
+        }
+      }
+    }
+  }
+  // the next tile's rows travel while this one is finished
+  if (tile_id + gridDim.x < num_tiles) load_rows(tile_id + gridDim.x, 0);
+  // accumulator fragment: acc[n][0..1] = token row g, experts 8 n + 2 q + {0, 1}; acc[n][2..3] = row g + 8
+  {
+    float* part = s_part + (kc * kMmaGateTokens + tile * 16) * (EP + 1);
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      part[g * (EP + 1) + n * 8 + 2 * q] = acc[n][0];
+      part[g * (EP + 1) + n * 8 + 2 * q + 1] = acc[n][1];
+      part[(g + 8) * (EP + 1) + n * 8 + 2 * q] = acc[n][2];
+      part[(g + 8) * (EP + 1) + n * 8 + 2 * q + 1] = acc[n][3];
+    }
+  }
+  __syncthreads();
+  // all threads: sum the four partial logits of every (token, expert), add the bias
+  {
+    const long long t_first = tile_id * kMmaGateTokens;
+    for (int i = threadIdx.x; i < kMmaGateTokens * E; i += kMmaGateWarps * 32) {
+      const int tok = i / E;
+      const int e = i - tok * E;
+      float v = s_part[tok * (EP + 1) + e];
+#pragma unroll
+      for (int c = 1; c < 4; ++c) v += s_part[(c * kMmaGateTokens + tok) * (EP + 1) + e];
+      v += gb ? gb[e] : 0.f;
+      s_part[tok * (EP + 1) + e] = v;          // quarter 0's rows now hold the logits
+      if (logits_out && t_first + tok < L) logits_out[(t_first + tok) * E + e] = v;
+    }
+  }
+  __syncthreads();
+  // one thread per token: softmax / top-k / renormalise
+  if (threadIdx.x < kMmaGateTokens) {
+    const long long t = tile_id * kMmaGateTokens + threadIdx.x;
+    if (t < L) {
+      float* lg = s_part + threadIdx.x * (EP + 1);
+      float* sel = s_part + (kMmaGateTokens + threadIdx.x) * (EP + 1);   // quarter 1's row: the chosen scores
+      float mx = -INFINITY;
+      for (int e = 0; e < E; ++e) mx = fmaxf(mx, lg[e]);
+      for (int e = 0; e < E; ++e) lg[e] = expf(lg[e] - mx);
+      // Sum in the order gate_topk_kernel uses (one value per lane, then a butterfly), so that
+      // both kernels give bit-identical scores for the same logits (E <= 32 here).
+      float v[32];
+#pragma unroll
+      for (int l = 0; l < 32; ++l) v[l] = l < E ? lg[l] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int l = 0; l < o; ++l) v[l] += v[l + o];
+      const float sum = v[0];
+      float norm = 0.f;
+      for (int s = 0; s < k; ++s) {
+        float best = -2.f;
+        int best_e = E;
+        for (int e = 0; e < E; ++e) {
+          const float pv = lg[e];
+          if (pv > best) {     // ascending e: the first maximum wins
+            best = pv;
+            best_e = e;
+          }
+        }
+        const float sc = best / sum;
+        norm += sc;
+        topk_idx[t * k + s] = best_e;
+        sel[s] = sc;
+        lg[best_e] = -1.f;
+      }
+      const float denom = fmaxf(norm, 1e-12f);
+      for (int s = 0; s < k; ++s) topk_score[t * k + s] = sel[s] / denom;
+    }
+  }
+  __syncthreads();      // the partial sums are overwritten by the next tile
+  }
+}
+
 // ---- counting sort -------------------------------------------------------------------------
 // Pass 1: per block of kRouteBlock tokens, how many of its rows go to each expert.
 // A token never picks the same expert twice, so the stable order inside one expert is simply
@@ -423,6 +640,36 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
   const int xs = x_dtype == FMOE_BF16 ? 2 : 4;
   const int vec_ok = (logits_in == nullptr) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx * xs) % 16 == 0) &&
                      ((reinterpret_cast<uintptr_t>(gate_w) & 15) == 0) && (d % 8 == 0);
+  // bf16 tokens and few experts: logits on the warp-level tensor cores
+  if (!logits_in && x_dtype == FMOE_BF16 && vec_ok && E <= 32) {
+    const int nt = E <= 8 ? 1 : (E <= 16 ? 2 : 4);
+    const size_t smem = 3 * static_cast<size_t>(8 * nt) * (static_cast<size_t>(d) * 2 + kMmaGatePadBytes) +
+                        4 * static_cast<size_t>(kMmaGateTokens) * (8 * nt + 1) * sizeof(float);
+    if (smem <= 200 * 1024) {
+      // persistent blocks (the weights are staged once per block), two per SM: with the next
+      // tile's rows prefetched into registers each block holds 64 KB of loads in flight
+      long long nblk = (L + kMmaGateTokens - 1) / kMmaGateTokens;
+      int dev = 0, sms = 148;
+      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (nblk > 2ll * sms) nblk = 2ll * sms;
+      const unsigned blocks = static_cast<unsigned>(nblk);
+#define FMOE_GATE_MMA(NT)                                                                                          \
+  do {                                                                                                             \
+    auto kern = gate_topk_mma_kernel<NT>;                                                                          \
+    if (smem > 48 * 1024) {                                                                                        \
+      FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));          \
+    }                                                                                                              \
+    kern<<<blocks, kMmaGateWarps * 32, smem, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, gate_w, gate_b, L, d, \
+                                                   E, k, logits_out, reinterpret_cast<long long*>(topk_idx),      \
+                                                   topk_score);                                                    \
+  } while (0)
+      if (nt == 1) FMOE_GATE_MMA(1); else if (nt == 2) FMOE_GATE_MMA(2); else FMOE_GATE_MMA(4);
+#undef FMOE_GATE_MMA
+      FMOE_CUDA_OK(cudaGetLastError());
+      ++g_misc_launches;
+      return FMOE_OK;
+    }
+  }
   // Gate weights in shared memory when they fit beside the logits scratch (and a few blocks per SM)
   const size_t w_bytes = logits_in ? 0 : static_cast<size_t>(E) * d * sizeof(float);
   const bool w_smem = !logits_in && vec_ok && w_bytes <= 96 * 1024;

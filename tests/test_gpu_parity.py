@@ -110,6 +110,34 @@ def test_gate_topk_against_oracle_bf16():
     clean_status()
 
 
+@pytest.mark.parametrize("L,d,E,k", [(4096, 1024, 8, 2), (1000, 200, 8, 2), (77, 64, 5, 3), (513, 2048, 16, 4),
+                                     (300, 512, 24, 8), (31, 8, 32, 1)])
+def test_gate_topk_few_experts_warp_mma_path(L, d, E, k):
+    """bf16 tokens with E <= 32 take the mma.sync kernel (three-term bf16 expansion of the fp32 gate
+    weights): logits within fp32 rounding of the fp32 product, the same choice as the oracle away
+    from near-ties, and bit-identical scores to the kernel that is handed those logits."""
+    g = torch.Generator().manual_seed(L * 7 + E)
+    x = torch.randn(L, d, generator=g).bfloat16()
+    gw = torch.randn(E, d, generator=g) * 0.05
+    gb = torch.randn(E, generator=g) * 0.1
+    idx, score, logits = fm.gate_topk(cu(x), cu(gw), cu(gb), k, return_logits=True)
+    ref_logits = torch.nn.functional.linear(x.double(), gw.double(), gb.double()).float()
+    torch.testing.assert_close(logits.cpu(), ref_logits, atol=2e-6 * max(1.0, d ** 0.5 / 8), rtol=1e-5)
+    dense, oidx = O.select_top_k(torch.softmax(logits.cpu(), dim=1), k)
+    srt = torch.softmax(logits.cpu(), dim=1).sort(dim=1, descending=True).values
+    safe = (srt[:, :k] - srt[:, 1 : k + 1]).min(dim=1).values > 1e-7 if k < E else torch.ones(L, dtype=torch.bool)
+    assert torch.equal(idx.cpu()[safe], oidx[safe])
+    torch.testing.assert_close(score.cpu()[safe], dense.gather(1, oidx)[safe], atol=1e-6, rtol=1e-5)
+    idx2, score2, _ = fm.gate_topk(None, None, None, k, logits=logits)
+    assert torch.equal(idx2, idx) and torch.equal(score2, score)
+    # rows of a strided view (row stride > d)
+    wide = torch.zeros(L, d + 8, dtype=torch.bfloat16)
+    wide[:, :d] = x
+    idx3, score3, _ = fm.gate_topk(cu(wide)[:, :d], cu(gw), cu(gb), k)
+    assert torch.equal(idx3, idx) and torch.equal(score3, score)
+    clean_status()
+
+
 def test_gate_topk_tensor_core_logits_match_fp32_path():
     """bf16 hi/lo expansion of the gate weights on the tensor cores: logits agree with the fp32
     CUDA-core path to ~1e-5 and route identically wherever the k-th / (k+1)-th gap is not tiny."""
