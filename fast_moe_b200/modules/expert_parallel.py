@@ -136,8 +136,9 @@ class ExpertParallelSwiGLUMoE(nn.Module):
                                                             wg, None, wu, None)
             with _lib.stage("down_combine"):
                 y = ops.silu_jagged_bmm_combine(0, meta.offsets, hidden, wd, None, meta.token_index,
-                                                meta.reverse_index, gating_scores=score.to(dt),
-                                                gates_index=meta.gate_index, has_silu=False, fused=k <= 2)
+                                                meta.reverse_index, gating_scores=score,
+                                                gates_index=meta.gate_index, has_silu=False, fused=k <= 2,
+                                                round_scores=True)
             return y.view(*shape[:-1], self.output_dim)
 
         with _lib.stage("plan"):
