@@ -166,6 +166,32 @@ def graph_kernel_ms(fn, device, n=10):
     return e0.elapsed_time(e1) / n
 
 
+def routing_sweep(c, device):
+    """Gate + top-k and the counting sort alone at several token counts: device time per call from
+    a CUDA graph of 20 calls, warm and with a 256 MB L2 flush before every call (the flush's own
+    time, measured the same way, subtracted). Prints one JSON line."""
+    import fast_moe_b200 as fm
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    g = torch.Generator().manual_seed(5)
+    gw = (torch.randn(c["E"], c["d"], generator=g) * 0.02).to(device)
+    gb = torch.zeros(c["E"], device=device)
+    flush_ms = graph_kernel_ms(lambda: flush.zero_(), device, n=20)
+    rows = []
+    for tokens in (1024, 4096, 16384, 65536):
+        x = torch.randn(tokens, c["d"], generator=g).to(torch.bfloat16).to(device)
+        idx, _, _ = fm.gate_topk(x, gw, gb, c["k"])
+        gate = lambda: fm.gate_topk(x, gw, gb, c["k"])
+        sort = lambda: fm.route_metadata(idx, c["E"])
+        cold = lambda fn: (lambda: (flush.zero_(), fn()))
+        rows.append(dict(tokens=tokens,
+                         gate_warm_us=1e3 * graph_kernel_ms(gate, device, n=20),
+                         gate_cold_us=1e3 * (graph_kernel_ms(cold(gate), device, n=20) - flush_ms),
+                         sort_warm_us=1e3 * graph_kernel_ms(sort, device, n=20),
+                         sort_cold_us=1e3 * (graph_kernel_ms(cold(sort), device, n=20) - flush_ms)))
+    print(json.dumps(dict(routing_sweep=rows, d=c["d"], E=c["E"], k=c["k"])), flush=True)
+
+
 def up_projection_ms(layer, x_dev, k, fp8):
     """The dominant kernel alone (row gather + gate/up grouped GEMM + SwiGLU epilogue) on the
     routing of this batch, timed as graph_kernel_ms does."""
@@ -318,6 +344,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ep-reference", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
+    ap.add_argument("--routing-sweep", action="store_true",
+                    help="only time gate/top-k and the counting sort alone at several token counts")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -334,6 +362,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.routing_sweep:
+        if rank == 0:
+            routing_sweep(c, device)
+        return
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
