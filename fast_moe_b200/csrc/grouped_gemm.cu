@@ -524,6 +524,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // gated tile, whole chunk inside N, no bias, no dequantisation: straight-line arithmetic
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = silu_f(__uint_as_float(r0[j][i])) * __uint_as_float(r1[j][i]);
+          } else if (fp8 && ncols == 32 && p.a_scale != nullptr && p.bias0 == nullptr && p.bias1 == nullptr) {
+            // FP8, whole chunk inside N, no bias: lane i fetches the scale of column i once and the
+            // warp shares it. Dividing by s_row * s_col equals multiplying by the two reciprocals
+            // whenever the scales are powers of two, which the quantisation rule guarantees.
+            const long long so = static_cast<long long>(e) * p.bscale_se + col0 + lane;
+            const float inv_a = 1.0f / scale_a;
+            const float inv_b0 = 1.0f / p.b0_scale[so];
+            float inv_b1 = 0.f;
+            if constexpr (DUAL) inv_b1 = 1.0f / p.b1_scale[so];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r0[j][i]))) *
+                              (inv_a * __shfl_sync(0xffffffffu, inv_b0, i));
+              if constexpr (DUAL) {
+                const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r1[j][i]))) *
+                                (inv_a * __shfl_sync(0xffffffffu, inv_b1, i));
+                v[i] = silu_f(g) * u;
+              } else {
+                v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
+              }
+            }
           } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {

@@ -367,3 +367,42 @@ def test_fused_combine_epilogue_against_two_kernel_form(name):
             scale = max(1.0, two.float().abs().max().item())
             torch.testing.assert_close(one.float(), two.float(), rtol=1e-2, atol=1e-2 * scale)
     clean_status()
+
+
+@pytest.mark.parametrize("name", G.names("ops_"))
+def test_fused_combine_flags_round_scores_and_accumulate(name):
+    """round_scores=True with f32 scores equals casting the scores to the activation type first
+    (what the reference layer does, modules/fast_moe_module.py:215), in both forms; out= adds the
+    combined rows to what the buffer already holds (a residual) and returns that buffer."""
+    g = G.load(name)
+    k = g["k"]
+    hid = cu(g["hid"])
+    dt = hid.dtype
+    off = cu(g["offsets"])
+    w2 = _logical(g, "w2")
+    gates32 = cu(g["gates"]).float() * 0.731 + 0.013       # values that do not survive a bf16 round trip
+    common = (0, off, hid, w2, cu(g.get("b2")), cu(g["token_index"]), cu(g["reverse_index"]))
+    idx = cu(g["gate_index"])
+    for fused in (False, True):
+        cast_first = fm.silu_jagged_bmm_combine(*common, gates32.to(dt), idx, has_silu=False, fused=fused)
+        in_kernel = fm.silu_jagged_bmm_combine(*common, gates32, idx, has_silu=False, fused=fused, round_scores=True)
+        assert in_kernel.dtype == dt
+        if k <= 2 or not fused:
+            assert torch.equal(in_kernel, cast_first)
+        else:
+            scale = max(1.0, cast_first.float().abs().max().item())
+            torch.testing.assert_close(in_kernel.float(), cast_first.float(), rtol=1e-2, atol=1e-2 * scale)
+    # accumulate into a residual
+    base = fm.silu_jagged_bmm_combine(*common, gates32, idx, has_silu=False, fused=True, round_scores=True)
+    resid = torch.randn_like(base.float()).to(dt)
+    buf = resid.clone()
+    got = fm.silu_jagged_bmm_combine(*common, gates32, idx, has_silu=False, fused=True, round_scores=True, out=buf)
+    assert got.data_ptr() == buf.data_ptr()
+    scale = max(1.0, base.float().abs().max().item())
+    torch.testing.assert_close(got.float(), resid.float() + base.float(), rtol=1e-2, atol=1.6e-2 * scale)
+    with pytest.raises(ValueError):
+        fm.silu_jagged_bmm_combine(*common, gates32, idx, has_silu=False, fused=False, out=buf)
+    with pytest.raises(ValueError):
+        fm.silu_jagged_bmm_combine(*common, gates32, idx, has_silu=False, fused=True, round_scores=True,
+                                   out=buf[:, :-1])
+    clean_status()
