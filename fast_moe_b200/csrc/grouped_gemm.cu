@@ -524,22 +524,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // gated tile, whole chunk inside N, no bias, no dequantisation: straight-line arithmetic
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = silu_f(__uint_as_float(r0[j][i])) * __uint_as_float(r1[j][i]);
-          } else if (fp8 && ncols == 32 && p.a_scale != nullptr && p.bias0 == nullptr && p.bias1 == nullptr) {
-            // FP8, whole chunk inside N, no bias: lane i fetches the scale of column i once and the
-            // warp shares it. Dividing by s_row * s_col equals multiplying by the two reciprocals
-            // whenever the scales are powers of two, which the quantisation rule guarantees.
-            const long long so = static_cast<long long>(e) * p.bscale_se + col0 + lane;
-            const float inv_a = 1.0f / scale_a;
-            const float inv_b0 = 1.0f / p.b0_scale[so];
-            float inv_b1 = 0.f;
-            if constexpr (DUAL) inv_b1 = 1.0f / p.b1_scale[so];
+          } else if (!DUAL && !combine && ncols == 32 && plain_math && p.epilogue == FMOE_EPI_NONE) {
+            // plain tile, nothing to add or scale: the accumulator values as they are
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[j][i]);
+          } else if (ncols == 32) {
+            // Whole chunk inside N with scales and / or bias: lane i fetches the factors of column i
+            // once and the warp shares them by shuffle. Dividing by s_row * s_col equals
+            // multiplying by the two reciprocals whenever the scales are powers of two, which the
+            // quantisation rule guarantees.
+            const bool scaled = fp8 && p.a_scale != nullptr;
+            const bool has_b0 = p.bias0 != nullptr;
+            const bool has_b1 = DUAL && p.bias1 != nullptr;
+            float f0 = 1.f, f1 = 1.f, bb0 = 0.f, bb1 = 0.f;
+            const float inv_a = 1.0f / scale_a;          // this lane's row
+            if (scaled) {                                // column factors: lane i holds column i's
+              const long long so = static_cast<long long>(e) * p.bscale_se + col0 + lane;
+              f0 = 1.0f / p.b0_scale[so];
+              if constexpr (DUAL) f1 = 1.0f / p.b1_scale[so];
+            }
+            if (has_b0) bb0 = load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col0 + lane);
+            if (has_b1) bb1 = load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col0 + lane);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r0[j][i]))) *
-                              (inv_a * __shfl_sync(0xffffffffu, inv_b0, i));
+              float g = __uint_as_float(r0[j][i]);
+              float u = DUAL ? __uint_as_float(r1[j][i]) : 0.f;
+              if (scaled) {
+                g = __bfloat162float(__float2bfloat16_rn(g)) * (inv_a * __shfl_sync(0xffffffffu, f0, i));
+                if constexpr (DUAL) {
+                  u = __bfloat162float(__float2bfloat16_rn(u)) * (inv_a * __shfl_sync(0xffffffffu, f1, i));
+                }
+              }
+              if (has_b0) g += __shfl_sync(0xffffffffu, bb0, i);
+              if (has_b1) u += __shfl_sync(0xffffffffu, bb1, i);
               if constexpr (DUAL) {
-                const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r1[j][i]))) *
-                                (inv_a * __shfl_sync(0xffffffffu, inv_b1, i));
                 v[i] = silu_f(g) * u;
               } else {
                 v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
