@@ -270,3 +270,48 @@ def fp8_jagged_bmm_quantized(
             )
         )
     return out
+
+
+def fp8_jagged_bmm_combine_quantized(
+    offsets: torch.Tensor,
+    jagged_q: torch.Tensor,
+    jagged_scale: torch.Tensor,
+    weight_q: torch.Tensor,
+    weight_scale: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    gating_scores: torch.Tensor,
+    gates_index: torch.Tensor,
+    num_tokens: int,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """fp8_jagged_bmm_quantized followed by the gate-weighted combine, in one kernel: the GEMM
+    epilogue descales, adds the bias, rounds to ``out_dtype``, multiplies by the gate weight
+    (f32 scores are rounded to ``out_dtype`` first, as a cast of the scores would) and adds into
+    the token rows. [rows = num_tokens * k, K] -> [num_tokens, N]. Bit-identical to the
+    two-kernel form for k <= 2."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(offsets, jagged_q, jagged_scale, weight_q, weight_scale, bias, gating_scores, gates_index)
+    rows, K = jagged_q.shape
+    E, N, Kw = weight_q.shape
+    assert Kw == K and rows % max(num_tokens, 1) == 0 and gating_scores.numel() == rows == gates_index.numel()
+    k = rows // num_tokens if num_tokens else 1
+    xq, wq = _pad16(jagged_q.contiguous()), _pad16(weight_q.contiguous())
+    out = torch.empty((num_tokens, N), dtype=out_dtype, device=dev)
+    b = _prep_bias(bias, out_dtype)
+    off = _index_i64(offsets)
+    xs = jagged_scale.to(torch.float32).contiguous()
+    ws = weight_scale.to(torch.float32).contiguous()
+    g = gating_scores.contiguous().view(-1)
+    if g.dtype not in (torch.float32, torch.bfloat16):
+        g = g.to(torch.float32)
+    gidx = _index_i64(gates_index)
+    with torch.cuda.device(dev):
+        _lib.check(
+            lib.fmoe_silu_jagged_bmm_combine_fused(
+                off.data_ptr(), rows, xq.data_ptr(), _lib.E4M3, xq.stride(0), xs.data_ptr(), wq.data_ptr(),
+                ws.data_ptr(), wq.stride(0), 1, wq.stride(1), N, _lib.ptr(b), N, g.data_ptr(), _lib.dtype_code(g.dtype),
+                gidx.data_ptr(), num_tokens, k, E, xq.shape[1], N, 0, None, out.data_ptr(), _lib.dtype_code(out_dtype),
+                out.stride(0), _lib.COMBINE_ROUND_GATE, _lib.stream_ptr(dev),
+            )
+        )
+    return out

@@ -232,13 +232,19 @@ class SwiGLUFastMoELayer(_MoEBase):
                     )
                 with _lib.stage("quant_hidden"):
                     hq, hs = ops_fp8.rowwise_quant_fp8(hidden)
-                with _lib.stage("down"):
-                    y_rows = ops_fp8.fp8_jagged_bmm_quantized(meta.offsets, hq, hs, wd, sd, None, out_dtype=dt)
-                with _lib.stage("combine"):
-                    y = ops.mul_merge_k_add(
-                        meta.token_index, meta.reverse_index, y_rows, weight=score.to(dt),
-                        weight_index=meta.gate_index,
-                    )
+                if fused and dt == torch.bfloat16:
+                    with _lib.stage("down_combine"):
+                        y = ops_fp8.fp8_jagged_bmm_combine_quantized(
+                            meta.offsets, hq, hs, wd, sd, None, score, meta.gate_index, x_flat.shape[0], out_dtype=dt
+                        )
+                else:
+                    with _lib.stage("down"):
+                        y_rows = ops_fp8.fp8_jagged_bmm_quantized(meta.offsets, hq, hs, wd, sd, None, out_dtype=dt)
+                    with _lib.stage("combine"):
+                        y = ops.mul_merge_k_add(
+                            meta.token_index, meta.reverse_index, y_rows, weight=score.to(dt),
+                            weight_index=meta.gate_index,
+                        )
             else:
                 wg = self._cast.get("wg", self.w_gate, dt).permute(0, 2, 1)
                 wu = self._cast.get("wu", self.w_up, dt).permute(0, 2, 1)

@@ -406,3 +406,32 @@ def test_fused_combine_flags_round_scores_and_accumulate(name):
         fm.silu_jagged_bmm_combine(*common, gates32, idx, has_silu=False, fused=True, round_scores=True,
                                    out=buf[:, :-1])
     clean_status()
+
+
+@pytest.mark.parametrize("L,E,k,K,N", [(300, 4, 2, 256, 192), (64, 8, 1, 128, 64), (500, 8, 4, 512, 320)])
+def test_fp8_down_projection_with_fused_combine(L, E, k, K, N):
+    """e4m3 down projection with the combine in the epilogue against the two-kernel form on the
+    same quantised operands: bit-identical for k <= 2, accumulation order only for larger k."""
+    from fast_moe_b200.kernels import moe_fp8
+
+    g = torch.Generator().manual_seed(L + 17 * k)
+    logits = torch.randn(L, E, generator=g)
+    idx = logits.topk(k, dim=1).indices
+    meta = fm.route_metadata(cu(idx), E)
+    hid = cu((torch.randn(L * k, K, generator=g) * 2).bfloat16())
+    w = cu((torch.randn(E, N, K, generator=g) * 0.05).bfloat16())          # [E, N, K]: K contiguous
+    bias = cu((torch.randn(E, N, generator=g) * 0.1).bfloat16())
+    score = cu(torch.rand(L, k, generator=g))                               # f32, not bf16-representable
+    hq, hs = moe_fp8.rowwise_quant_fp8(hid)
+    wq, ws = moe_fp8.rowwise_quant_fp8(w)
+    rows = moe_fp8.fp8_jagged_bmm_quantized(meta.offsets, hq, hs, wq, ws, bias, out_dtype=torch.bfloat16)
+    two = fm.mul_merge_k_add(meta.token_index, meta.reverse_index, rows, weight=score.to(torch.bfloat16),
+                             weight_index=meta.gate_index)
+    one = moe_fp8.fp8_jagged_bmm_combine_quantized(meta.offsets, hq, hs, wq, ws, bias, score, meta.gate_index, L)
+    assert one.shape == two.shape and one.dtype == two.dtype
+    if k <= 2:
+        assert torch.equal(one, two)
+    else:
+        scale = max(1.0, two.float().abs().max().item())
+        torch.testing.assert_close(one.float(), two.float(), rtol=1e-2, atol=1e-2 * scale)
+    clean_status()
