@@ -435,3 +435,38 @@ def test_fp8_down_projection_with_fused_combine(L, E, k, K, N):
         scale = max(1.0, two.float().abs().max().item())
         torch.testing.assert_close(one.float(), two.float(), rtol=1e-2, atol=1e-2 * scale)
     clean_status()
+
+
+@pytest.mark.parametrize("cols", [1032, 4096, 14336, 16384])
+@pytest.mark.parametrize("apply_silu", [False, True])
+def test_rowwise_quant_single_pass_kernel_matches_generic_kernel_and_oracle(cols, apply_silu):
+    """Wide 16-byte-aligned bf16 rows take the register-resident single-pass kernel; a view that
+    starts 2 bytes later takes the generic two-pass kernel. Payload and scales must be identical,
+    and equal to the CPU oracle's."""
+    from fast_moe_b200.kernels import moe_fp8
+
+    g = torch.Generator().manual_seed(cols + int(apply_silu))
+    rows = 37
+    big = torch.randn(rows, cols + 8, generator=g) * torch.logspace(-3, 3, rows).view(-1, 1)
+    big[3, 5] = float("nan")
+    big[4] = 0.0
+    big[5, 7] = float("inf")
+    big = big.bfloat16()
+    a = big[:, :cols].contiguous()
+    fast_q, fast_s = moe_fp8.rowwise_quant_fp8(cu(a), apply_silu=apply_silu)
+    # same values at an odd element offset: the generic kernel
+    shifted = torch.empty(rows * cols + 1, dtype=torch.bfloat16, device=DEV)
+    shifted[1:] = cu(a).view(-1)
+    lib = _lib.load()
+    q2 = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=DEV)
+    s2 = torch.empty(rows, dtype=torch.float32, device=DEV)
+    _lib.check(lib.fmoe_rowwise_quant_fp8(shifted.data_ptr() + 2, _lib.BF16, rows, cols, cols, int(apply_silu), 0,
+                                          q2.data_ptr(), cols, s2.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert torch.equal(fast_s.cpu().view(torch.int32), s2.cpu().view(torch.int32))
+    assert torch.equal(fast_q.view(torch.uint8), q2.view(torch.uint8))
+    if not apply_silu:
+        oq, os_ = O.rowwise_quant_fp8(a[6:])        # the rows without NaN / inf / all-zero specials
+        assert torch.equal(fast_s.cpu()[6:].view(torch.int32), os_.view(torch.int32))
+        assert torch.equal(fast_q.cpu()[6:].view(torch.uint8), oq.view(torch.uint8))
+    clean_status()
