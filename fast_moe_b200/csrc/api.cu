@@ -154,7 +154,7 @@ extern "C" int fmoe_index_select_jagged_bmm_fp8(const int64_t* offsets, const in
                                                 int64_t w_sn, int64_t ws_se, const void* bias, const void* bias_p,
                                                 int64_t bias_se, int E, int K, int N, int epilogue, void* out,
                                                 int out_dtype, int64_t ldo, void* stream) {
-  FMOE_REQUIRE(index != nullptr && index_div >= 1, "index_select_jagged_bmm_fp8: index is required");
+  FMOE_REQUIRE(index == nullptr || index_div >= 1, "index_select_jagged_bmm_fp8: index_div must be >= 1");
   FMOE_REQUIRE(jagged_scale && weight_scale, "index_select_jagged_bmm_fp8: scales are required");
   FMOE_REQUIRE((weight_p_q == nullptr) == (weight_p_scale == nullptr),
                "index_select_jagged_bmm_fp8: weight_p_q and weight_p_scale go together");

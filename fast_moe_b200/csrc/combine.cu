@@ -145,9 +145,11 @@ gather_rows_kernel(const uint8_t* __restrict__ src, long long src_rows, long lon
        w += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = w / vec_per_row;
     const int c = static_cast<int>(w - r * vec_per_row);
-    long long s = index[r] / div;
+    long long s = index[r];
+    if (div != 1) s /= div;
     if (s < 0 || s >= src_rows) {
       atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+      reinterpret_cast<V*>(dst + r * ldd_bytes)[c] = V{};      // a row that does not exist reads as zeros
       continue;
     }
     reinterpret_cast<V*>(dst + r * ldd_bytes)[c] = reinterpret_cast<const V*>(src + s * lds_bytes)[c];

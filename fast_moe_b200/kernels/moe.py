@@ -97,6 +97,19 @@ def _index_i64(t: torch.Tensor) -> torch.Tensor:
     return t if t.is_contiguous() else t.contiguous()
 
 
+# From this many output rows and columns on (both products of a gated GEMM counted), the rows are
+# gathered once by the copy kernel and the GEMM reads them as contiguous TMA tiles. The in-kernel
+# gather (16-byte cp.async by four warps) re-fetches a row tile for every column block and shares
+# issue slots with the MMA thread: at 4096 x top-2 tokens, d=1024, h=4096 it costs 140 us against
+# 8 + 111 us for copy + contiguous GEMM; with few column blocks the single pass of the fused form wins.
+PREGATHER_MIN_ROWS = 1024
+PREGATHER_MIN_COLS = 1024
+
+
+def _gather_first(rows: int, total_cols: int) -> bool:
+    return rows >= PREGATHER_MIN_ROWS and total_cols >= PREGATHER_MIN_COLS
+
+
 def index_select_jagged_bmm(
     max_seq_len: int,
     offsets: torch.Tensor,
@@ -130,12 +143,15 @@ def index_select_jagged_bmm(
     b = _prep_bias(bias, jagged.dtype)
     off = _index_i64(offsets)
     idx = _index_i64(index)
+    div = index.shape[1]
+    if _gather_first(rows, N):
+        a, idx, div, L = gather_rows(a, idx, div), None, 1, rows
     out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm(
-                off.data_ptr(), idx.data_ptr(), index.shape[1], rows, a.data_ptr(), dt, L, a.stride(0),
+                off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
                 w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, _epilogue, out.data_ptr(), dt, out.stride(0),
                 _lib.stream_ptr(dev),
             )
@@ -180,12 +196,15 @@ def index_select_jagged_bmm_swiglu(
     bp = _prep_bias(bias_p, jagged.dtype)
     off = _index_i64(offsets)
     idx = None if index is None else _index_i64(index)
+    div = index.shape[1] if index is not None else 1
+    if idx is not None and _gather_first(rows, 2 * N):
+        a, idx, div, L = gather_rows(a, idx, div), None, 1, rows
     out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm_swiglu(
-                off.data_ptr(), _lib.ptr(idx), index.shape[1] if index is not None else 1, rows, a.data_ptr(), dt, L, a.stride(0),
+                off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
                 w.data_ptr(), wp.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), _lib.ptr(bp), N, E, kp, N,
                 out.data_ptr(), dt, out.stride(0), _lib.stream_ptr(dev),
             )

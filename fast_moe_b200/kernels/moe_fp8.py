@@ -7,7 +7,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
-from .moe import _index_i64, _prep_bias
+from .moe import _gather_first, _index_i64, _prep_bias, gather_rows
 from .utils import KernelType
 
 
@@ -120,11 +120,12 @@ def index_select_jagged_bmm_fp8_quantized(
 ) -> torch.Tensor:
     """FP8 up projection on operands that are already quantised: jagged_q [L, K] e4m3 with
     jagged_scale [L]; weight_q [E, N, K] e4m3 (K contiguous) with weight_scale [E, N].
-    out = (q_x . q_w) / (s_x * s_w) + bias, rows gathered by index // A. With weight_p_q the
-    SwiGLU form of the same product is computed."""
+    out = (q_x . q_w) / (s_x * s_w) + bias, rows gathered by index // A (``index=None``: jagged_q
+    and jagged_scale already hold the expert-sorted rows). With weight_p_q the SwiGLU form of the
+    same product is computed."""
     lib = _lib.load()
     dev = _lib.require_cuda(offsets, index, jagged_q, jagged_scale, weight_q, weight_scale, bias)
-    assert index.ndim == 2 and index.shape[0] == jagged_q.shape[0]
+    assert index is None or (index.ndim == 2 and index.shape[0] == jagged_q.shape[0])
     L, K = jagged_q.shape
     E, N, Kw = weight_q.shape
     assert Kw == K
@@ -134,19 +135,25 @@ def index_select_jagged_bmm_fp8_quantized(
     kp = xq.shape[1]
     if weight_p_q is not None:
         epilogue = _lib.EPI_SWIGLU
-    rows = index.numel()
+    rows = index.numel() if index is not None else L
     out = torch.empty((rows, N), dtype=out_dtype, device=dev)
     b = _prep_bias(bias, out_dtype)
     bp = _prep_bias(bias_p, out_dtype)
     off = _index_i64(offsets)
-    idx = _index_i64(index)
+    idx = None if index is None else _index_i64(index)
     xs = jagged_scale.to(torch.float32).contiguous()
     ws = weight_scale.to(torch.float32).contiguous()
     wps = None if weight_p_scale is None else weight_p_scale.to(torch.float32).contiguous()
+    div = index.shape[1] if index is not None else 1
+    if idx is not None and _gather_first(rows, N * (2 if weight_p_q is not None else 1)):
+        # rows (and their scales) gathered once by the copy kernel; the GEMM reads contiguous tiles
+        xq = gather_rows(xq, idx, div)
+        xs = gather_rows(xs.view(-1, 1), idx, div).view(-1)
+        idx, div, L = None, 1, rows
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm_fp8(
-                off.data_ptr(), idx.data_ptr(), index.shape[1], rows, xq.data_ptr(), xs.data_ptr(), L, xq.stride(0),
+                off.data_ptr(), _lib.ptr(idx), div, rows, xq.data_ptr(), xs.data_ptr(), L, xq.stride(0),
                 wq.data_ptr(), ws.data_ptr(), _lib.ptr(wpq), _lib.ptr(wps), wq.stride(0), 1, wq.stride(1), N,
                 _lib.ptr(b), _lib.ptr(bp), N, E, kp, N, epilogue, out.data_ptr(), _lib.dtype_code(out_dtype),
                 out.stride(0), _lib.stream_ptr(dev),

@@ -125,7 +125,11 @@ int fmoe_route_metadata_static(const int64_t* topk_idx, int64_t L, int E, int k,
  * index_select_jagged_bmm (kernels/moe.py:39-68 -> kernels/pytorch/moe.py:40-84):
  *   out[r, :] = jagged[index[r] / index_div, :] @ weight[e] + bias[e],  offsets[e] <= r < offsets[e+1]
  *   offsets [E+1] int64; index [rows] int64 (the flattened [L, A] tensor, index_div = A);
- *   index may be NULL when jagged already holds the rows in expert-sorted order (L = rows)
+ *   index may be NULL when jagged already holds the rows in expert-sorted order (L = rows).
+ *   With an index the kernel gathers the rows itself (16-byte cp.async, once per column block);
+ *   from about 1024 rows and 1024 output columns on, fmoe_gather_rows into a scratch followed
+ *   by this call with index = NULL is faster (contiguous TMA tiles, CTA pairs) - the Python
+ *   mirror does that.
  *   jagged  [L, K] dtype (bf16, or f32 computed with tf32 tensor-core math), row stride ldj
  *   weight  logical [E, K, N], element strides (w_se, w_sk, w_sn), same dtype
  *   bias    [E, N] same dtype as out, expert stride bias_se, or NULL
@@ -154,7 +158,8 @@ int fmoe_index_select_jagged_bmm_swiglu(const int64_t* offsets, const int64_t* i
  * fmoe_rowwise_quant_fp8: jagged_q [L, K] e4m3 with jagged_scale [L]; weight_q logical [E, K, N]
  * e4m3, K contiguous, with weight_scale [E, N] (expert stride ws_se). Scales are the multipliers
  * used at quantisation; the epilogue divides by their product, then adds bias.
- * weight_p_q / weight_p_scale non-NULL selects the SwiGLU form of the same product. */
+ * weight_p_q / weight_p_scale non-NULL selects the SwiGLU form of the same product.
+ * index may be NULL (rows and their scales already gathered, L = rows). */
 int fmoe_index_select_jagged_bmm_fp8(const int64_t* offsets, const int64_t* index, int index_div,
                                      int64_t total_rows, const void* jagged_q, const float* jagged_scale, int64_t L,
                                      int64_t ldj, const void* weight_q, const float* weight_scale,
