@@ -40,7 +40,7 @@ CONFIGS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (up-projection
 # grouped GEMM), from the ncu capture summarised in profiles/grouped_gemm_c2.md. Only the
 # configuration that was captured has a figure; the others report null.
-NCU_TRAFFIC_BYTES = {"c2": 145.37e6 + 44.87e6}
+NCU_TRAFFIC_BYTES = {"c2": 151.15e6 + 46.79e6}
 
 
 def layer_flops(c, tokens):
