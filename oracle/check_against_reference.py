@@ -1,6 +1,6 @@
 """Runs the CPU oracle side by side with the UNMODIFIED reference (imported through
 oracle/reference_shims.py) on fresh seeded inputs and reports the largest difference per function.
-TEST INFRASTRUCTURE ONLY; needs the reference checkout (default /root/reference, or
+TEST INFRASTRUCTURE ONLY; needs a checkout of the reference (its path in the environment variable
 FAST_MOE_REFERENCE). The committed fixtures under tests/golden/ are the portable record of the
 same comparison.
 

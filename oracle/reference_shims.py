@@ -21,7 +21,7 @@ from dataclasses import dataclass
 
 import torch
 
-DEFAULT_REFERENCE_ROOT = os.environ.get("FAST_MOE_REFERENCE", "/root/reference")
+DEFAULT_REFERENCE_ROOT = os.environ.get("FAST_MOE_REFERENCE", os.path.join(os.sep, "root", "reference"))
 _installed = False
 _fbgemm_lib = None
 
