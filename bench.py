@@ -475,8 +475,11 @@ def main():
     e2e_check = float((y_hosts[(args.steps - 1) % slots].float() - y.detach().float().cpu().view_as(y_host)).abs().max())
 
     t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
+    stage_ms_ranks = None
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        stage_ms_ranks = [None] * world
+        dist.all_gather_object(stage_ms_ranks, {n: round(v, 4) for n, v in stage_ms.items()})
     ms_total, ms_e2e = t.tolist()
 
     if rank == 0:
@@ -508,7 +511,7 @@ def main():
             config=workload_config(c, name, world),
             layer_tflops_per_gpu=layer_flops(c, c["tokens"]) / (ms_step * 1e-3) / 1e12,
             launch_mode="cuda graph replay" if captured is not None else "eager", ms_per_step_eager=ms_eager,
-            stage_ms=stage_ms, roofline=roofline, clocks=clocks, gpu_launches=int(launches),
+            stage_ms=stage_ms, stage_ms_per_rank=stage_ms_ranks, roofline=roofline, clocks=clocks, gpu_launches=int(launches),
             device_status=status,
             e2e=dict(value=tokens_total / (ms_e2e / args.steps * 1e-3), unit="tokens/s",
                      h2d_bytes_per_step=x_host.numel() * x_host.element_size(),

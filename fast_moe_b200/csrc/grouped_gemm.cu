@@ -921,12 +921,14 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   const bool dual = d.epilogue == FMOE_EPI_SWIGLU;
   const bool gather = d.index != nullptr;
   const int tile_n = dual ? 128 : 256;
-  // Contiguous rows with a few hundred rows per expert: CTA pairs (256-row tiles, each CTA stages
-  // half of the weight tile, a third fewer operand bytes per SM and FLOP): 8-12 % faster than lone
-  // CTAs on the down projections measured. Gathered rows stay on lone CTAs: a pair needs a relay
-  // hop for the peer's gathered rows and runs at half speed. FMOE_GEMM_CTAS forces either.
+  // Contiguous rows with a thousand or more rows per expert on average: CTA pairs (256-row tiles,
+  // each CTA stages half of the weight tile, a third fewer operand bytes per SM and FLOP): 8-12 %
+  // faster than lone CTAs on the down projections measured. With fewer rows per expert the
+  // half-empty last tile of every segment costs more than that (512 rows per expert: pairs 5 %
+  // slower). Gathered rows stay on lone CTAs: a pair needs a relay hop for the peer's gathered
+  // rows and runs at half speed. FMOE_GEMM_CTAS forces either.
   int ctas = forced_ctas();
-  if (ctas == 0) ctas = (!gather && d.total_rows / d.E >= 512) ? 2 : 1;
+  if (ctas == 0) ctas = (!gather && d.total_rows / d.E >= 1024) ? 2 : 1;
   if (g_num_sms < 2) ctas = 1;
   const int box_n = (ctas == 2 || dual) ? 128 : 256;   // weight rows one TMA load brings in
   const int k_elems = kRowBytes / esize;
