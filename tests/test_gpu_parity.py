@@ -470,3 +470,28 @@ def test_rowwise_quant_single_pass_kernel_matches_generic_kernel_and_oracle(cols
         assert torch.equal(fast_s.cpu()[6:].view(torch.int32), os_.view(torch.int32))
         assert torch.equal(fast_q.cpu()[6:].view(torch.uint8), oq.view(torch.uint8))
     clean_status()
+
+
+@pytest.mark.parametrize("L,k,D,dt,wdt", [(300, 2, 1024, torch.bfloat16, torch.bfloat16), (77, 8, 64, torch.bfloat16, torch.bfloat16),
+                                          (513, 1, 8, torch.bfloat16, torch.float32), (40, 33, 256, torch.bfloat16, torch.bfloat16),
+                                          (129, 4, 1000, torch.float32, torch.float32), (64, 3, 1001, torch.bfloat16, torch.bfloat16),
+                                          (2000, 8, 2048, torch.bfloat16, torch.bfloat16)])
+def test_mul_merge_k_add_both_kernels_bit_exact_against_oracle(L, k, D, dt, wdt):
+    """Aligned rows with k <= 32 take the warp-per-token kernel, everything else the generic one
+    (k = 33, D = 1001 here); both must reproduce the oracle's fp32 ascending-order sum bit for bit,
+    with and without gate weights."""
+    g = torch.Generator().manual_seed(L * 3 + k)
+    E = max(k, 8)
+    idx = torch.rand(L, E, generator=g).topk(k, dim=1).indices
+    meta = fm.route_metadata(cu(idx), E)
+    value = torch.randn(L * k, D, generator=g).to(dt)
+    weight = torch.rand(L, k, generator=g).to(wdt)
+    ti, gi = meta.token_index.cpu(), meta.gate_index.cpu()
+    want = O.mul_merge_k_add(ti, value, k, weight, gi)
+    got = fm.mul_merge_k_add(meta.token_index, meta.reverse_index, cu(value), weight=cu(weight), weight_index=meta.gate_index)
+    assert got.dtype == want.dtype
+    assert torch.equal(got.cpu(), want)
+    want2 = O.mul_merge_k_add(ti, value, k)
+    got2 = fm.mul_merge_k_add(meta.token_index, meta.reverse_index, cu(value))
+    assert torch.equal(got2.cpu(), want2)
+    clean_status()
