@@ -177,19 +177,46 @@ def routing_sweep(c, device):
     gw = (torch.randn(c["E"], c["d"], generator=g) * 0.02).to(device)
     gb = torch.zeros(c["E"], device=device)
     flush_ms = graph_kernel_ms(lambda: flush.zero_(), device, n=20)
-    rows = []
+    rows_out = []
     for tokens in (1024, 4096, 16384, 65536):
         x = torch.randn(tokens, c["d"], generator=g).to(torch.bfloat16).to(device)
         idx, _, _ = fm.gate_topk(x, gw, gb, c["k"])
         gate = lambda: fm.gate_topk(x, gw, gb, c["k"])
         sort = lambda: fm.route_metadata(idx, c["E"])
         cold = lambda fn: (lambda: (flush.zero_(), fn()))
-        rows.append(dict(tokens=tokens,
+        rows_out.append(dict(tokens=tokens,
                          gate_warm_us=1e3 * graph_kernel_ms(gate, device, n=20),
                          gate_cold_us=1e3 * (graph_kernel_ms(cold(gate), device, n=20) - flush_ms),
                          sort_warm_us=1e3 * graph_kernel_ms(sort, device, n=20),
                          sort_cold_us=1e3 * (graph_kernel_ms(cold(sort), device, n=20) - flush_ms)))
-    print(json.dumps(dict(routing_sweep=rows, d=c["d"], E=c["E"], k=c["k"])), flush=True)
+    # the HBM-bound kernels of the path at the benchmark shapes: algorithmic bytes / device time
+    from fast_moe_b200.kernels import moe as ops
+    from fast_moe_b200.kernels import moe_fp8 as ops_fp8
+
+    peak = load_peaks().get("hbm_gbs")
+    hbm = []
+
+    def add(name, shape, fn, nbytes):
+        ms = graph_kernel_ms(fn, device, n=10)
+        hbm.append(dict(kernel=name, shape=shape, us=1e3 * ms, algorithmic_mb=nbytes / 1e6,
+                        achieved_gbs=nbytes / ms / 1e6, frac_of_measured_hbm=(nbytes / ms / 1e6) / peak if peak else None))
+
+    for shape, L, E, k, D in (("c2", 4096, 8, 2, 1024), ("c4", 8192, 64, 8, 2048), ("c5", 8192, 64, 2, 4096)):
+        idx = torch.rand(L, E, generator=g).topk(k, dim=1).indices.to(device)
+        meta = fm.route_metadata(idx, E)
+        x = torch.randn(L, D, generator=g).to(torch.bfloat16).to(device)
+        rows = torch.randn(L * k, D, generator=g).to(torch.bfloat16).to(device)
+        w = torch.rand(L, k, generator=g).to(torch.bfloat16).to(device)
+        add("gather_rows", shape, lambda: ops.gather_rows(x, meta.gate_index, k), 2 * L * k * D * 2)
+        add("mul_merge_k_add", shape,
+            lambda: ops.mul_merge_k_add(meta.token_index, meta.reverse_index, rows, weight=w, weight_index=meta.gate_index),
+            (L * k * D + L * D) * 2)
+    for shape, R, C in (("c3 tokens", 16384, 4096), ("c3 hidden", 32768, 14336)):
+        a = torch.randn(R, C, generator=g).to(torch.bfloat16).to(device)
+        add("rowwise_quant_fp8", shape, lambda: ops_fp8.rowwise_quant_fp8(a), R * C * 3 + 4 * R)
+        del a
+    print(json.dumps(dict(routing_sweep=rows_out, d=c["d"], E=c["E"], k=c["k"], hbm_kernels=hbm,
+                          hbm_peak_gbs=peak)), flush=True)
 
 
 def up_projection_ms(layer, x_dev, k, fp8):
@@ -348,7 +375,7 @@ def main():
     ap.add_argument("--no-ep-reference", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--routing-sweep", action="store_true",
-                    help="only time gate/top-k and the counting sort alone at several token counts")
+                    help="only time the routing operators and the HBM-bound kernels alone (one JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
