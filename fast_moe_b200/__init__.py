@@ -7,6 +7,7 @@ from .kernels.moe import (
     SiluJaggedBmmCombineOption,
     index_select_jagged_bmm,
     index_select_jagged_bmm_swiglu,
+    index_select_jagged_bmm_3D,
     index_select_jagged_gating_bmm,
     mul_merge_k_add,
     silu_jagged_bmm,
@@ -27,6 +28,7 @@ __all__ = [
     "IndexSelectJaggedBmmOption",
     "SiluJaggedBmmCombineOption",
     "index_select_jagged_bmm",
+    "index_select_jagged_bmm_3D",
     "index_select_jagged_bmm_swiglu",
     "index_select_jagged_gating_bmm",
     "mul_merge_k_add",

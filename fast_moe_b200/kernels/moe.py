@@ -121,6 +121,7 @@ def index_select_jagged_bmm(
     triton_option: Optional[IndexSelectJaggedBmmOption] = None,
     *,
     _epilogue: int = _lib.EPI_NONE,
+    _rows_checked: bool = False,
 ) -> torch.Tensor:
     """out[r] = jagged[index.view(-1)[r] // A] @ weight[e] + bias[e] for the rows r of expert e.
 
@@ -128,7 +129,7 @@ def index_select_jagged_bmm(
     jagged [L, K], weight [E, K, N] (any strides), bias [E, N] or None -> [L*A, N].
     ``max_seq_len`` is accepted and not needed: the tile list is built on the device.
     """
-    assert index.ndim == 2 and index.shape[0] == jagged.shape[0]
+    assert index.ndim == 2 and (_rows_checked or index.shape[0] == jagged.shape[0])
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype, f"{weight.dtype=} {jagged.dtype=}"
     dev = _lib.require_cuda(offsets, index, jagged, weight, bias)
@@ -157,6 +158,32 @@ def index_select_jagged_bmm(
             )
         )
     return out
+
+
+def index_select_jagged_bmm_3D(
+    max_seq_len: int,
+    offsets: torch.Tensor,
+    index: torch.Tensor,
+    jagged: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    kernel: KernelType = KernelType.PYTORCH,
+) -> torch.Tensor:
+    """index_select_jagged_bmm on a [L, E, K] input: the rows of expert e read slice e of their
+    token (kernels/moe.py:118-153 -> kernels/pytorch/moe.py:224-252). Runs as the 2-D operator on
+    the [L*E, K] view with the row index token * E + e; the expert of every sorted row comes
+    from ``offsets`` on the device (no host synchronisation)."""
+    assert index.ndim == 2 and index.shape[0] == jagged.shape[0] and jagged.ndim == 3
+    _lib.require_cuda(offsets, index, jagged, weight, bias)
+    L, E, K = jagged.shape
+    assert weight.shape[0] == E and weight.shape[1] == K
+    rows = index.numel()
+    off = _index_i64(offsets)
+    tok = _index_i64(index).reshape(-1) // index.shape[1]
+    expert = torch.searchsorted(off[1:].contiguous(), torch.arange(rows, device=tok.device), right=True)
+    flat_index = (tok * E + expert.clamp_(max=E - 1)).view(-1, 1)
+    x2d = jagged.reshape(L * E, K)
+    return index_select_jagged_bmm(max_seq_len, off, flat_index, x2d, weight, bias, _rows_checked=True)
 
 
 def index_select_jagged_bmm_swiglu(

@@ -101,6 +101,17 @@ def index_select_jagged_bmm(offsets, index, jagged, weight, bias) -> torch.Tenso
     return torch.cat(outs, dim=0)
 
 
+def index_select_jagged_bmm_3D(offsets, index, jagged, weight, bias) -> torch.Tensor:
+    """jagged is [L, E, K]: the rows of expert e read slice e of their token, then weight[e] and
+    bias[e] as in index_select_jagged_bmm. pytorch_index_select_jagged_bmm_3D,
+    kernels/pytorch/moe.py:224-252."""
+    tok = index.reshape(-1) // index.shape[-1]
+    parts = jagged[tok].contiguous().split(_segments(offsets))
+    wt = weight.permute(0, 2, 1)
+    outs = [F.linear(p[:, e, :], wt[e], None if bias is None else bias[e]) for e, p in enumerate(parts)]
+    return torch.cat(outs, dim=0)
+
+
 def index_select_jagged_bmm_swiglu(offsets, index, jagged, weight, bias, weight_p, bias_p) -> torch.Tensor:
     """silu(x W + b) * (x Wp + bp) per expert. pytorch_index_select_jagged_bmm_swiglu,
     kernels/pytorch/moe.py:87-146."""

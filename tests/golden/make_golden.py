@@ -236,16 +236,47 @@ def fp8_cases(ref):
                                    out=out, out_unquantised=raw))
 
 
+def op3d_cases(ref):
+    """index_select_jagged_bmm_3D (kernels/moe.py:118-153): jagged is [L, E, K], the rows of expert
+    e read slice e of their token."""
+    cases = [
+        # (L, E, k, K, N, dtype, kmajor, bias, seed)
+        (24, 4, 2, 16, 32, torch.float32, False, True, 30),
+        (200, 8, 2, 64, 48, torch.bfloat16, True, True, 31),
+        (90, 16, 4, 32, 24, torch.bfloat16, True, False, 32),    # some experts empty
+    ]
+    for ci, (L, E, k, K, N, dtype, kmajor, use_bias, seed) in enumerate(cases):
+        torch.manual_seed(seed)
+        idx, gi, ti, off, rev = routing_case(ref, L, E, k, seed)
+        x = torch.empty(L, E, K).uniform_(-1, 1).to(dtype)
+        if kmajor:
+            w = torch.empty(E, N, K).uniform_(-1, 1).to(dtype).permute(0, 2, 1)
+        else:
+            w = torch.empty(E, K, N).uniform_(-1, 1).to(dtype)
+        b = torch.empty(E, N).uniform_(-1, 1).to(dtype) if use_bias else None
+        f32 = lambda t: None if t is None else t.float()
+        msl = int((off[1:] - off[:-1]).max())
+        out = ref.moe.index_select_jagged_bmm_3D(msl, off, gi.view(-1, k), f32(x), f32(w), f32(b))
+        d = dict(k=k, E=E, kmajor=int(kmajor), x=x, w=w.contiguous() if not kmajor else w.permute(0, 2, 1).contiguous(),
+                 topk_idx=idx, gate_index=gi, offsets=off, out=out)
+        if use_bias:
+            d.update(b=b)
+        save(f"ops3d_{ci}", d)
+
+
+GROUPS = {"layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=reference_shims.DEFAULT_REFERENCE_ROOT)
+    ap.add_argument("--only", default=None, choices=sorted(GROUPS), help="regenerate one group of fixtures")
     a = ap.parse_args()
     torch.set_num_threads(1)   # one thread: summation order of the CPU BLAS is then fixed
     ref = reference_shims.modules(a.reference)
-    layer_cases(ref)
-    op_cases(ref)
-    combine_cases(ref)
-    fp8_cases(ref)
+    for name, fn in GROUPS.items():
+        if a.only in (None, name):
+            fn(ref)
 
 
 if __name__ == "__main__":

@@ -64,6 +64,7 @@ def test_argument_validation_returns_status_not_crash():
 REFERENCE_SIGNATURES = {
     # kernels/moe.py:39-48, :71-80, :156-166, :192-203, :236-249
     moe.index_select_jagged_bmm: ["max_seq_len", "offsets", "index", "jagged", "weight", "bias", "kernel", "triton_option"],
+    moe.index_select_jagged_bmm_3D: ["max_seq_len", "offsets", "index", "jagged", "weight", "bias", "kernel"],   # :118-126
     moe.mul_merge_k_add: ["index", "reverse_index", "value", "stable_sorting", "weight", "weight_index", "kernel",
                           "triton_cc_version"],
     moe.index_select_jagged_bmm_swiglu: ["max_seq_len", "offsets", "index", "jagged", "weight", "bias", "weight_p",

@@ -187,6 +187,25 @@ def test_up_projection_operators_against_golden(name):
     clean_status()
 
 
+@pytest.mark.parametrize("name", G.names("ops3d_"))
+def test_index_select_jagged_bmm_3d_against_golden(name):
+    """[L, E, K] input: rows of expert e read slice e of their token (kernels/moe.py:118-153)."""
+    g = G.load(name)
+    k = g["k"]
+    x = cu(g["x"])
+    out = fm.index_select_jagged_bmm_3D(0, cu(g["offsets"]), cu(g["gate_index"]).view(-1, k), x, _logical(g, "w"),
+                                        cu(g.get("b")))
+    assert out.dtype == x.dtype and out.shape == g["out"].shape
+    torch.testing.assert_close(out.float().cpu(), g["out"], **TOL)
+    # a non-contiguous [L, E, K] view gives the same rows
+    wide = torch.zeros(x.shape[0], x.shape[1], x.shape[2] + 8, dtype=x.dtype, device=x.device)
+    wide[..., : x.shape[2]] = x
+    out2 = fm.index_select_jagged_bmm_3D(0, cu(g["offsets"]), cu(g["gate_index"]).view(-1, k), wide[..., : x.shape[2]],
+                                         _logical(g, "w"), cu(g.get("b")))
+    assert torch.equal(out2, out)
+    clean_status()
+
+
 @pytest.mark.parametrize("name", G.names("ops_"))
 def test_down_projection_combine_against_golden(name):
     g = G.load(name)

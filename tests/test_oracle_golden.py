@@ -87,6 +87,15 @@ def test_operators(name):
     assert torch.equal(off2, off) and torch.equal(rev, g["reverse_index"])
 
 
+@pytest.mark.parametrize("name", G.names("ops3d_"))
+def test_index_select_jagged_bmm_3d(name):
+    g = G.load(name)
+    w = g["w"].permute(0, 2, 1) if g["kmajor"] else g["w"]
+    out = O.index_select_jagged_bmm_3D(g["offsets"], g["gate_index"].view(-1, g["k"]), g["x"].float(), w.float(),
+                                       g["b"].float() if "b" in g else None)
+    torch.testing.assert_close(out, g["out"], atol=1e-5, rtol=1e-5)
+
+
 @pytest.mark.parametrize("name", G.names("combine_"))
 def test_mul_merge_k_add_bit_exact(name):
     g = G.load(name)
