@@ -32,7 +32,8 @@ from ..kernels import moe as ops
 from .fast_moe_module import GateSplitCache, route_tokens
 
 
-def local_expert_plan(recv_lengths: torch.Tensor, total: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+def local_expert_plan(recv_lengths: torch.Tensor, total: Optional[int] = None,
+                      capacity: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """recv_lengths [W, E_local]: rows received from each source rank for each local expert, in
     the order they sit in the receive buffer (source-major, expert-minor).
 
@@ -40,6 +41,11 @@ def local_expert_plan(recv_lengths: torch.Tensor, total: Optional[int] = None) -
     experts and perm[p] is the receive-buffer row that belongs at expert-major position p
     (within an expert: by source rank, then in arrival order). Pure index arithmetic on small
     tensors; runs on whatever device recv_lengths lives on.
+
+    With ``capacity`` (an upper bound of the row count known without looking at the counts) the
+    whole plan is computed without any host-side size: perm comes back with ``capacity`` entries
+    of which the first n are the plan and the rest are padding, so the caller can queue this
+    before it reads the counts back and slice afterwards.
     """
     W, El = recv_lengths.shape
     dev = recv_lengths.device
@@ -52,6 +58,12 @@ def local_expert_plan(recv_lengths: torch.Tensor, total: Optional[int] = None) -
     len_dst = recv_lengths.t().reshape(-1)
     start_src = seg_start_recv.view(W, El).t().reshape(-1)
     start_dst = torch.cumsum(len_dst, 0) - len_dst
+    if capacity is not None:
+        # row p belongs to the destination segment whose [start, end) contains it
+        end_dst = torch.cumsum(len_dst, 0)
+        p = torch.arange(capacity, device=dev)
+        seg = torch.searchsorted(end_dst, p, right=True).clamp_(max=W * El - 1)
+        return offsets, start_src[seg] + (p - start_dst[seg])
     if total is None:
         total = int(flat.sum().item())   # callers that already know the row count pass it and skip this sync
     seg_of_row = torch.repeat_interleave(torch.arange(W * El, device=dev), len_dst, output_size=total)
@@ -148,11 +160,13 @@ class ExpertParallelSwiGLUMoE(nn.Module):
             # the pack kernel is queued before the host waits for the counts, so the GPU packs the
             # rows while the host reads the split sizes back
             send = ops.gather_rows(x_flat, meta.gate_index, k)
+            # the local plan too: at most every rank sends all of its rows here
+            offsets_local, perm_padded = local_expert_plan(recv_lengths, capacity=x_flat.shape[0] * k * W)
             counts = torch.stack([send_lengths.sum(1), recv_lengths.sum(1)]).cpu()   # the layer's one host sync
             send_counts, recv_counts = counts[0].tolist(), counts[1].tolist()
             validate_plan(send_counts, recv_counts, recv_lengths, W)
             n_recv = sum(recv_counts)
-            offsets_local, perm = local_expert_plan(recv_lengths, n_recv)
+            perm = perm_padded[:n_recv]
         with _lib.stage("dispatch"):
             recv = torch.empty((n_recv, self.input_dim), dtype=dt, device=x.device)
             dist.all_to_all_single(recv, send, recv_counts, send_counts, group=self.group)

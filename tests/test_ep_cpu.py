@@ -28,6 +28,24 @@ def test_local_expert_plan_small():
     assert off.tolist() == [0, 0, 0, 0] and perm.numel() == 0
 
 
+def test_local_expert_plan_with_capacity_matches_exact_form():
+    """The capacity form needs no row count from the host: its first n entries are the exact plan
+    (empty segments, empty plans and a capacity equal to n included)."""
+    g = torch.Generator().manual_seed(11)
+    for trial in range(30):
+        W, El = int(torch.randint(1, 6, (1,), generator=g)), int(torch.randint(1, 9, (1,), generator=g))
+        rl = torch.randint(0, 7, (W, El), generator=g)
+        if trial % 7 == 0:
+            rl.zero_()
+        n = int(rl.sum())
+        off, perm = local_expert_plan(rl)
+        for cap in (n, n + 1, n + 50):
+            off2, padded = local_expert_plan(rl, capacity=cap)
+            assert padded.numel() == cap
+            assert torch.equal(off2, off)
+            assert torch.equal(padded[:n], perm)
+
+
 def test_local_expert_plan_random_is_a_grouping_permutation():
     g = torch.Generator().manual_seed(3)
     for _ in range(20):
