@@ -246,6 +246,37 @@ gather_rows_kernel(const uint8_t* __restrict__ src, long long src_rows, long lon
   }
 }
 
+// 16-byte-aligned rows of at least 512 bytes: one warp per row. The row index is read once per
+// row (no division per 16-byte piece), and a lane has up to four loads in flight before its
+// first store. No warp-level primitives: lanes are independent.
+__global__ void __launch_bounds__(256)
+gather_rows_warp_kernel(const uint8_t* __restrict__ src, long long src_rows, long long lds_bytes,
+                        const long long* __restrict__ index, int div, long long rows, int vec_per_row,
+                        uint8_t* __restrict__ dst, long long ldd_bytes, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    long long s = index[r];
+    if (div != 1) s /= div;
+    uint4* d = reinterpret_cast<uint4*>(dst + r * ldd_bytes);
+    if (s < 0 || s >= src_rows) {
+      if (lane == 0) atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+      for (int c = lane; c < vec_per_row; c += 32) d[c] = make_uint4(0, 0, 0, 0);   // a row that does not exist reads as zeros
+      continue;
+    }
+    const uint4* a = reinterpret_cast<const uint4*>(src + s * lds_bytes);
+    for (int c0 = lane; c0 < vec_per_row; c0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + 32 * u < vec_per_row) v[u] = a[c0 + 32 * u];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + 32 * u < vec_per_row) d[c0 + 32 * u] = v[u];
+    }
+  }
+}
+
 template <typename VT, typename WT, typename OT>
 int launch_combine(const long long* rev, const void* value, long long ldv, const void* weight, const long long* widx,
                    long long L, int k, int D, void* out, long long ldo, int* status, cudaStream_t st) {
@@ -327,7 +358,13 @@ extern "C" int fmoe_gather_rows(const void* src, int dtype, int64_t src_rows, in
   long long blocks = (work + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   const long long* idx = reinterpret_cast<const long long*>(index);
-  if (v16)
+  if (v16 && row_bytes >= 512) {
+    long long wb = (rows * 32 + 255) / 256;     // one warp per row
+    if (wb > 148 * 16) wb = 148 * 16;
+    gather_rows_warp_kernel<<<static_cast<unsigned>(wb), 256, 0, st>>>(
+        static_cast<const uint8_t*>(src), src_rows, lds * es, idx, index_div, rows, row_bytes / 16,
+        static_cast<uint8_t*>(dst), ldd * es, status);
+  } else if (v16)
     gather_rows_kernel<uint4><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
         static_cast<const uint8_t*>(src), src_rows, lds * es, idx, index_div, rows, row_bytes,
         static_cast<uint8_t*>(dst), ldd * es, status);

@@ -514,3 +514,33 @@ def test_mul_merge_k_add_both_kernels_bit_exact_against_oracle(L, k, D, dt, wdt)
     got2 = fm.mul_merge_k_add(meta.token_index, meta.reverse_index, cu(value))
     assert torch.equal(got2.cpu(), want2)
     clean_status()
+
+
+@pytest.mark.parametrize("src_rows,rows,cols,dt,div", [(300, 1000, 256, torch.bfloat16, 1), (64, 500, 1000, torch.bfloat16, 2),
+                                                       (100, 257, 64, torch.bfloat16, 1), (50, 99, 7, torch.float32, 3),
+                                                       (128, 4096, 1024, torch.float32, 1), (77, 300, 4096, torch.float8_e4m3fn, 1)])
+def test_gather_rows_all_kernel_forms(src_rows, rows, cols, dt, div):
+    """Row gather: warp-per-row form (16-byte-aligned rows of 512 bytes or more), 16-byte piece
+    form and byte form against torch indexing; an index outside the source is reported and its
+    row reads as zeros."""
+    g = torch.Generator().manual_seed(rows + cols)
+    if dt == torch.float8_e4m3fn:
+        src = torch.randint(0, 255, (src_rows, cols), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    else:
+        src = torch.randn(src_rows, cols, generator=g).to(dt)
+    index = torch.randint(0, src_rows * div, (rows,), generator=g)
+    as_bytes = lambda t: t.contiguous().view(torch.uint8)
+    want = as_bytes(src)[index // div]
+    got = fm.kernels.moe.gather_rows(cu(src), cu(index), div)
+    assert got.dtype == src.dtype and tuple(got.shape) == (rows, cols)
+    assert torch.equal(as_bytes(got.cpu()), want)
+    clean_status()
+    bad = index.clone()
+    bad[3] = src_rows * div + 5
+    got = as_bytes(fm.kernels.moe.gather_rows(cu(src), cu(bad), div).cpu())
+    assert _lib.device_status(DEV) == 1
+    assert int(got[3].count_nonzero()) == 0
+    keep = torch.ones(rows, dtype=torch.bool)
+    keep[3] = False
+    assert torch.equal(got[keep], want[keep])
+    clean_status()
