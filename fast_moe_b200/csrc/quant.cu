@@ -155,14 +155,17 @@ rowwise_quant_kernel(const T* __restrict__ in, long long ldi, long long rows, in
 // between the absmax reduction and the cast, and writes 8 payload bytes per piece. Same
 // arithmetic per element as rowwise_quant_kernel (bit-identical results); the row is read from
 // HBM once instead of once from HBM and once from L2, with 16-byte instead of 2-byte accesses.
-constexpr int kRegVecs = 8;     // 256 threads x 8 pieces x 8 values: rows up to 16384 columns
+constexpr int kRegVecsMax = 8;  // 256 threads x 8 pieces x 8 values: rows up to 16384 columns
 
 __device__ __forceinline__ float act_bf16(float v, bool apply_silu) {
   if (apply_silu) v = __bfloat162float(__float2bfloat16_rn(v / (1.0f + expf(-v))));
   return v;
 }
 
-__global__ void __launch_bounds__(256)
+// kRegVecs = 2 serves rows up to 4096 columns with a quarter of the registers, so that eight
+// blocks fit on an SM: short rows need more rows in flight to cover the HBM latency.
+template <int kRegVecs>
+__global__ void __launch_bounds__(256, kRegVecs <= 2 ? 8 : 1)
 rowwise_quant_bf16_regs_kernel(const __nv_bfloat16* __restrict__ in, long long ldi, long long rows, int cols,
                                int apply_silu, int store_reciprocal, uint8_t* __restrict__ q, long long ldq,
                                float* __restrict__ scale_out) {
@@ -310,10 +313,15 @@ extern "C" int fmoe_rowwise_quant_fp8(const void* in, int in_dtype, int64_t rows
   const long long blocks = wide ? rows : (rows + 7) / 8;
   FMOE_REQUIRE(blocks < (1ll << 31), "rowwise_quant_fp8: too many rows");
   const unsigned g = static_cast<unsigned>(blocks);
-  if (in_dtype == FMOE_BF16 && wide && cols % 8 == 0 && cols <= 256 * 8 * kRegVecs && (ldi * 2) % 16 == 0 &&
+  if (in_dtype == FMOE_BF16 && wide && cols % 8 == 0 && cols <= 256 * 8 * kRegVecsMax && (ldi * 2) % 16 == 0 &&
       (reinterpret_cast<uintptr_t>(in) & 15) == 0 && ldq % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
-    rowwise_quant_bf16_regs_kernel<<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), ldi, rows, cols, apply_silu,
-                                                      store_reciprocal, qq, ldq, scale_out);
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(in);
+    if (cols <= 256 * 8 * 2) {
+      rowwise_quant_bf16_regs_kernel<2><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq, scale_out);
+    } else {
+      rowwise_quant_bf16_regs_kernel<kRegVecsMax><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq,
+                                                                    scale_out);
+    }
   } else if (in_dtype == FMOE_BF16) {
     const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(in);
     if (wide) rowwise_quant_kernel<__nv_bfloat16, 256><<<g, 256, 0, st>>>(p, ldi, rows, cols, apply_silu, store_reciprocal, qq, ldq, scale_out);
