@@ -155,22 +155,40 @@ combine_warp_kernel(const long long* __restrict__ reverse_index, const VT* __res
       for (int u = 0; u < kPieces; ++u)
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[u][i] = 0.f;
-      for (int j = 0; j < k; ++j) {
-        const long long pj = __shfl_sync(0xffffffffu, prow, j);
-        const float gj = __shfl_sync(0xffffffffu, g, j);
-        if (pj < 0) continue;                      // warp-uniform: a skipped (bad) row
-        const VT* src = value + pj * ldv + c0;
+      // rows in groups of four: all their value loads go out before the first sum, so a lane has
+      // up to 4 x kPieces loads in flight; the sums stay in ascending j order
+      constexpr int kGroup = 4;
+      for (int j0 = 0; j0 < k; j0 += kGroup) {
+        uint4 raw[kGroup][kPieces];
+        float gj[kGroup];
+        bool use[kGroup];
 #pragma unroll
-        for (int u = 0; u < kPieces; ++u) {
-          if (c0 + u * 32 * VEC < D) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + u * 32 * VEC);
-            const VT* e = reinterpret_cast<const VT*>(&raw);
+        for (int jj = 0; jj < kGroup; ++jj) {
+          const long long pj = __shfl_sync(0xffffffffu, prow, (j0 + jj) & 31);
+          gj[jj] = __shfl_sync(0xffffffffu, g, (j0 + jj) & 31);
+          use[jj] = (j0 + jj < k) && pj >= 0;          // warp-uniform
+          if (use[jj]) {
+            const VT* src = value + pj * ldv + c0;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-              const float v = ldf(e + i);
-              float prod = weight != nullptr ? __fmul_rn(v, gj) : v;
-              if (kRoundProduct && weight != nullptr) prod = __bfloat162float(__float2bfloat16_rn(prod));
-              acc[u][i] = __fadd_rn(acc[u][i], prod);
+            for (int u = 0; u < kPieces; ++u) {
+              if (c0 + u * 32 * VEC < D) raw[jj][u] = *reinterpret_cast<const uint4*>(src + u * 32 * VEC);
+            }
+          }
+        }
+#pragma unroll
+        for (int jj = 0; jj < kGroup; ++jj) {
+          if (!use[jj]) continue;
+#pragma unroll
+          for (int u = 0; u < kPieces; ++u) {
+            if (c0 + u * 32 * VEC < D) {
+              const VT* e = reinterpret_cast<const VT*>(&raw[jj][u]);
+#pragma unroll
+              for (int i = 0; i < VEC; ++i) {
+                const float v = ldf(e + i);
+                float prod = weight != nullptr ? __fmul_rn(v, gj[jj]) : v;
+                if (kRoundProduct && weight != nullptr) prod = __bfloat162float(__float2bfloat16_rn(prod));
+                acc[u][i] = __fadd_rn(acc[u][i], prod);
+              }
             }
           }
         }
