@@ -817,10 +817,13 @@ int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap&
              int grid, cudaStream_t stream) {
   using Plan = SmemPlan<CTAS>;
   auto kern = grouped_gemm_kernel<ESIZE, CTAS, DUAL, GATHER, COMBINE, OutT>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // function attributes belong to a device's context: set once per device
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FMOE_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
     FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal));
-    attr_set = true;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
