@@ -81,6 +81,10 @@ long long fmoe_kernel_launch_count(void);
  *   logits_out[L, E] f32 or NULL
  *   topk_idx  [L, k] int64, topk_score [L, k] f32
  * 1 <= k <= E <= 256.
+ * bf16 x with 16-byte-aligned rows, E <= 32 and gate weights that fit in shared memory run the
+ * product on the warp-level tensor cores with the fp32 weights expanded on the fly into three
+ * bf16 terms (exact products, fp32 accumulation); other cases use fp32 FMAs. Both give the same
+ * scores for the same logits, bit for bit.
  */
 int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                    const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E, int k,
