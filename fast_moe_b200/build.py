@@ -17,7 +17,11 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libfmoe_b200.so"
-SOURCES = ["api.cu", "grouped_gemm.cu", "routing.cu", "combine.cu", "quant.cu"]
+# (source, object stem, extra flags). The grouped GEMM, by far the longest compile, is built as
+# four objects in parallel: host code and one set of kernel instantiations per operand size.
+UNITS = [("api.cu", "api", []), ("routing.cu", "routing", []), ("combine.cu", "combine", []), ("quant.cu", "quant", [])]
+UNITS += [("grouped_gemm.cu", f"grouped_gemm_p{part}", [f"-DFMOE_GEMM_PART={part}"]) for part in range(4)]
+SOURCES = sorted({u[0] for u in UNITS})
 HEADERS = [CSRC / "common.cuh", CSRC / "ptx.cuh", PKG_DIR.parent / "include" / "fmoe_b200.h"]
 
 NVCC_FLAGS = [
@@ -49,11 +53,11 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     obj_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
     jobs = []
-    for src in SOURCES:
+    for src, stem, extra in UNITS:
         s = CSRC / src
-        o = obj_dir / (src[:-3] + ".o")
+        o = obj_dir / (stem + ".o")
         if force or _stale(o, [s, *HEADERS]):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(s), "-o", str(o)]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(s), "-o", str(o)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -67,8 +71,8 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
             if verbose or r.returncode != 0:
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
             if r.returncode != 0:
-                raise RuntimeError(f"nvcc failed on {cmd[-3]}")
-    objs = [str(obj_dir / (s[:-3] + ".o")) for s in SOURCES]
+                raise RuntimeError(f"nvcc failed on {cmd[-3]} -> {cmd[-1]}")
+    objs = [str(obj_dir / (stem + ".o")) for _, stem, _ in UNITS]
     if force or jobs or _stale(LIB_PATH, objs):
         cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True)

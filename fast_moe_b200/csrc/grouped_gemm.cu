@@ -38,8 +38,17 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
+// The file compiles either as one object (FMOE_GEMM_PART undefined) or in four parts that build
+// in parallel: part 0 holds the host code, parts 1 / 2 / 3 the kernel instantiations for 2-byte,
+// 4-byte and 1-byte operands.
+#ifndef FMOE_GEMM_PART
+#define FMOE_GEMM_PART -1
+#endif
+#define FMOE_GEMM_HOST (FMOE_GEMM_PART <= 0)
+#define FMOE_GEMM_KERNELS (FMOE_GEMM_PART != 0)
+
 namespace fmoe {
-namespace {
+namespace gemm_detail {
 
 constexpr int kBM = 128;            // rows per CTA and tile (= TMEM lanes)
 constexpr int kMmaN = 256;          // accumulator columns per tile
@@ -740,6 +749,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+#if FMOE_GEMM_HOST
 // One CTA waits on a barrier that nothing will ever signal, with a short limit. Exercises the
 // path every wait of the GEMM takes when it gives up: status code recorded, abort flag raised,
 // thread returns; nothing traps and the context stays usable.
@@ -811,7 +821,15 @@ int make_tmap(CUtensorMap* m, int dt, int rank, const void* base, const cuuint64
 
 int g_launches = 0;
 int g_num_sms = 0;
+#else
+extern int g_launches;
+#endif  // FMOE_GEMM_HOST
 
+template <int ESIZE, typename OutT>
+int dispatch_shape(int ctas, bool dual, bool gather, const CUtensorMap& tmA, const CUtensorMap& tmB0,
+                   const CUtensorMap& tmB1, const GemmParams& p, int grid, cudaStream_t stream);
+
+#if FMOE_GEMM_KERNELS
 template <int ESIZE, int CTAS, bool DUAL, bool GATHER, bool COMBINE, typename OutT>
 int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmB1, const GemmParams& p,
              int grid, cudaStream_t stream) {
@@ -859,7 +877,23 @@ int dispatch_shape(int ctas, bool dual, bool gather, const CUtensorMap& tmA, con
   if (gather) FMOE_GO(1, false, true); else FMOE_GO(1, false, false);
 #undef FMOE_GO
 }
+#if FMOE_GEMM_PART == 1
+template int dispatch_shape<2, __nv_bfloat16>(int, bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                                              const GemmParams&, int, cudaStream_t);
+template int dispatch_shape<2, float>(int, bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                                      const GemmParams&, int, cudaStream_t);
+#elif FMOE_GEMM_PART == 2
+template int dispatch_shape<4, float>(int, bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                                      const GemmParams&, int, cudaStream_t);
+#elif FMOE_GEMM_PART == 3
+template int dispatch_shape<1, __nv_bfloat16>(int, bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                                              const GemmParams&, int, cudaStream_t);
+template int dispatch_shape<1, float>(int, bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                                      const GemmParams&, int, cudaStream_t);
+#endif
+#endif  // FMOE_GEMM_KERNELS
 
+#if FMOE_GEMM_HOST
 // 0 = choose by shape, 1 / 2 = force lone CTAs / CTA pairs (environment FMOE_GEMM_CTAS, read once).
 int forced_ctas() {
   static int v = -1;
@@ -870,7 +904,12 @@ int forced_ctas() {
   return v;
 }
 
-}  // namespace
+#endif  // FMOE_GEMM_HOST
+
+}  // namespace gemm_detail
+
+#if FMOE_GEMM_HOST
+using namespace gemm_detail;
 
 int grouped_gemm_launch_count() { return g_launches; }
 
@@ -1010,5 +1049,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
     return dispatch_shape<1, float>(ctas, dual, gather, tmA, tmB0, tmB1, p, grid, stream);
   }
 }
+
+#endif  // FMOE_GEMM_HOST
 
 }  // namespace fmoe
