@@ -5,18 +5,28 @@
 
 A step is one forward pass of the layer over one batch of synthetic tokens.
   N = 1   "c2": 4096 tokens (8 x 512), d=1024, h=4096, 8 SwiGLU experts, top-2, bf16.
+          The line also carries sub-records for "c3" (FP8 e4m3 rowwise, 16384 tokens, d=4096,
+          h=14336), "c4" (Zipf-skewed routing over 64 experts, top-8) and "c5_ep_1gpu" (the
+          per-rank workload of the multi-GPU runs with all 64 experts on one GPU), a `sustained`
+          record (the same step replayed for at least a second) and a `parity` block.
   N > 1   "c5": expert parallel, 64 experts sharded over the ranks, d=4096, h=14336, top-2, bf16,
-          8192 tokens per rank (weak scaling); launched by torchrun, one rank per GPU.
+          8192 tokens per rank (weak scaling); launched by torchrun, one rank per GPU. Rank 0
+          first times the per-rank workload alone on its GPU: `weak_scaling` holds that time, the
+          efficiency t1 / tN and the compute / HBM bounds of both.
 `value` is tokens/s of the whole job with inputs resident in HBM; `e2e` is the same metric with
 the step's tokens copied host->device and its output copied device->host inside the timed
-region. `--impl reference` times the CPU restatement of the reference's PYTORCH path
+region. `parity` compares the benchmarked layer's output, outside the timed region, with the CPU
+oracle: routing tensors bit for bit on the whole batch, outputs on a seeded sample of tokens.
+`--impl reference` times the CPU restatement of the reference's PYTORCH path
 (oracle/moe_oracle.py) on the host cores instead.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -32,20 +42,27 @@ CONFIGS = {
     # name: tokens (per rank), d, h, o, E (total), k
     "c2": dict(tokens=4096, batch=8, seq=512, d=1024, h=4096, o=1024, E=8, k=2, fp8=False),
     "c3": dict(tokens=16384, batch=32, seq=512, d=4096, h=14336, o=4096, E=8, k=2, fp8=True),
-    "c4": dict(tokens=8192, batch=16, seq=512, d=2048, h=8192, o=2048, E=64, k=8, fp8=False, zipf=1.2),
+    # Zipf(1.2) expert loads. With top-8 of 64 experts an expert can receive at most one row per
+    # token, i.e. 1/8 of the assignments (not the 25 % a top-1 router could give it); the bias is
+    # sharpened (x 1.5) so that the most loaded experts sit at that cap, a long tail of experts
+    # receives a handful of rows and several receive none.
+    "c4": dict(tokens=8192, batch=16, seq=512, d=2048, h=8192, o=2048, E=64, k=8, fp8=False, zipf=1.2,
+               zipf_sharpen=1.5),
     "c5": dict(tokens=8192, batch=16, seq=512, d=4096, h=14336, o=4096, E=64, k=2, fp8=False),
 }
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (up-projection
-# grouped GEMM), from the ncu capture summarised in profiles/grouped_gemm_c2.md. Only the
-# configuration that was captured has a figure; the others report null.
-NCU_TRAFFIC_BYTES = {"c2": 151.15e6 + 46.79e6}
 
 
 def layer_flops(c, tokens):
     A = tokens * c["k"]
     return 2 * tokens * c["d"] * c["E"] + 4 * A * c["d"] * c["h"] + 2 * A * c["h"] * c["o"]
+
+
+def layer_min_bytes(c, tokens, experts_local=None):
+    """Weights read once + tokens in + result out + hidden written and read."""
+    E = experts_local if experts_local is not None else c["E"]
+    w = 1 if c.get("fp8") else 2
+    A = tokens * c["k"]
+    return E * (2 * c["d"] * c["h"] + c["h"] * c["o"]) * w + tokens * c["d"] * 2 + tokens * c["o"] * 2 + 2 * A * c["h"] * w
 
 
 def load_peaks():
@@ -56,6 +73,22 @@ def load_peaks():
         return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
                     bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def ncu_traffic(name):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, read
+    from the committed ncu summary of that configuration (a line `traffic_bytes_per_launch:
+    <bytes> ... commit <hash>` in profiles/grouped_gemm_<name>.md). None when there is no capture."""
+    path = os.path.join(ROOT, "profiles", f"grouped_gemm_{name}.md")
+    try:
+        with open(path) as f:
+            text = f.read()
+    except OSError:
+        return None, None
+    m = re.search(r"traffic_bytes_per_launch:\s*([0-9.eE+]+)(?:.*?commit\s+([0-9a-f]{7,40}))?", text)
+    if not m:
+        return None, None
+    return float(m.group(1)), m.group(2)
 
 
 class ClockSampler:
@@ -87,16 +120,9 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self, t0: float, t1: float):
-        if self.proc is None:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
+    def window(self, t0: float, t1: float):
+        """Summary of the samples taken between two perf_counter times."""
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         rows = [l for t, l in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines]
         for l in rows:
@@ -106,40 +132,64 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                pw.append(float(f[3]))
             except ValueError:
                 continue
             for n, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=sorted(reasons), samples=len(sm))
+                    power_w=statistics.median(pw) if pw else None, reasons=sorted(reasons), samples=len(sm))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        return self.window(t0, t1)
 
 
-def make_inputs(c, rank, device, dtype=torch.bfloat16):
-    """Seeded synthetic data: x ~ N(0,1) (per-rank seed), weights / gate ~ N(0, 0.02) (shared seed)."""
+# ------------------------------------------------------------------------------------ workloads
+def make_inputs(c, rank):
+    """Seeded synthetic tokens [batch, seq, d] bf16 on the host: x ~ N(0,1) (per-rank seed); the FP8
+    configuration scales 1 % of the rows by 50 to stress the per-row scales."""
     g = torch.Generator().manual_seed(1234 + rank)
     x = torch.randn(c["batch"], c["seq"], c["d"], generator=g)
     if c.get("fp8"):
         rows = torch.randperm(c["tokens"], generator=g)[: c["tokens"] // 100]
         x.view(-1, c["d"])[rows] *= 50.0
-    return x.to(dtype)
+    return x.to(torch.bfloat16)
 
 
-def build_layer(c, device, e_local=None, e_first=0):
+def zipf_gate_bias(E, s, sharpen=1.0, seed=7):
+    """Router bias that makes expert loads follow Zipf(s) over a seeded permutation of the
+    experts: log of the target probabilities, times `sharpen`."""
+    g = torch.Generator().manual_seed(seed)
+    ranks = torch.randperm(E, generator=g).float() + 1.0
+    p = ranks.pow(-s)
+    return (p / p.sum()).log() * sharpen
+
+
+def build_layer(c, device):
+    """SwiGLU layer of configuration c with seeded N(0, 0.02) weights, created on the device."""
     import fast_moe_b200 as fm
 
     torch.manual_seed(0)
-    layer = fm.SwiGLUFastMoELayer(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, fp8=bool(c.get("fp8")))
+    torch.cuda.manual_seed(0)
+    with torch.device(device):
+        layer = fm.SwiGLUFastMoELayer(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, fp8=bool(c.get("fp8")))
     with torch.no_grad():
         layer.gate.gate.weight.normal_(0, 0.02)
         layer.gate.gate.bias.zero_()
         if c.get("zipf"):
-            # biased router: expert loads follow Zipf(s) over a seeded permutation of the experts
-            g = torch.Generator().manual_seed(7)
-            ranks = torch.randperm(c["E"], generator=g).float() + 1.0
-            p = ranks.pow(-c["zipf"])
-            layer.gate.gate.bias.copy_((p / p.sum()).log())
-    return layer.to(device)
+            layer.gate.gate.bias.copy_(zipf_gate_bias(c["E"], c["zipf"], c.get("zipf_sharpen", 1.0)).to(device))
+    if c.get("fp8"):
+        layer.quantize_weights()
+    return layer
 
 
 def graph_kernel_ms(fn, device, n=10):
@@ -219,32 +269,153 @@ def routing_sweep(c, device):
                           hbm_peak_gbs=peak)), flush=True)
 
 
-def up_projection_ms(layer, x_dev, k, fp8):
-    """The dominant kernel alone (gate/up grouped GEMM + SwiGLU epilogue on the expert-sorted rows
-    of this batch's routing), timed as graph_kernel_ms does. The rows are gathered beforehand by
-    the copy kernel, as the operator itself does at these sizes; the copy is not in this time."""
+def gemm_alone_ms(layer, x_dev, k, fp8):
+    """The two grouped GEMMs alone on this batch's routing, each timed as graph_kernel_ms does:
+    (gate/up GEMM + SwiGLU epilogue on the expert-sorted rows, down GEMM + fused combine). The
+    rows are gathered beforehand by the copy kernel, as the operator itself does at these sizes;
+    the copy is not in the first time. For k > 2 the layers use the two-kernel combine, so the
+    second time is the down GEMM + the combine kernel."""
     from fast_moe_b200.kernels import moe as ops
     from fast_moe_b200.kernels import moe_fp8 as ops_fp8
 
     with torch.no_grad():
         x_flat = x_dev.reshape(-1, x_dev.shape[-1])
-        _, meta = layer._route(x_flat, k)
+        score, meta = layer._route(x_flat, k)
         dt = x_flat.dtype
+        fused = k <= 2
         if fp8:
-            (wg, sg), (wu, su) = layer._q["w_gate"], layer._q["w_up"]
+            (wg, sg), (wu, su), (wd, sd) = layer._q["w_gate"], layer._q["w_up"], layer._q["w_down"]
             xq, xs = ops_fp8.rowwise_quant_fp8(x_flat)
             xq = ops.gather_rows(xq, meta.gate_index, k)
             xs = ops.gather_rows(xs.view(-1, 1), meta.gate_index, k).view(-1)
-            fn = lambda: ops_fp8.index_select_jagged_bmm_fp8_quantized(
+            up = lambda: ops_fp8.index_select_jagged_bmm_fp8_quantized(
                 meta.offsets, None, xq, xs, wg, sg, None, out_dtype=dt, weight_p_q=wu, weight_p_scale=su)
+            hq, hs = ops_fp8.rowwise_quant_fp8(up())
+            down = lambda: ops_fp8.fp8_jagged_bmm_combine_quantized(
+                meta.offsets, hq, hs, wd, sd, None, score, meta.gate_index, x_flat.shape[0], out_dtype=dt)
         else:
             wg = layer._cast.get("wg", layer.w_gate, dt).permute(0, 2, 1)
             wu = layer._cast.get("wu", layer.w_up, dt).permute(0, 2, 1)
+            wd = layer._cast.get("wd", layer.w_down, dt).permute(0, 2, 1)
             xg = ops.gather_rows(x_flat, meta.gate_index, k)
-            fn = lambda: ops.index_select_jagged_bmm_swiglu(0, meta.offsets, None, xg, wg, None, wu, None)
-        return graph_kernel_ms(fn, x_dev.device)
+            up = lambda: ops.index_select_jagged_bmm_swiglu(0, meta.offsets, None, xg, wg, None, wu, None)
+            hidden = up()
+            down = lambda: ops.silu_jagged_bmm_combine(
+                0, meta.offsets, hidden, wd, None, meta.token_index, meta.reverse_index, gating_scores=score,
+                gates_index=meta.gate_index, has_silu=False, fused=fused, round_scores=True)
+        return graph_kernel_ms(up, x_dev.device), graph_kernel_ms(down, x_dev.device)
 
 
+def fp8_dense_peak(device):
+    """Yardstick for the e4m3 GEMMs, measured in this run: cuBLASLt's dense e4m3 x e4m3 -> bf16
+    product (torch._scaled_mm, 8192^3, per-tensor scales), best of 10 launches, CUDA events."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=device)
+        fn = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            fn()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = min(best, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception as exc:   # the yardstick is optional; say why it is missing
+        return f"unavailable: {type(exc).__name__}: {exc}"[:200]
+
+
+# ------------------------------------------------------------------------------------ parity
+def _routing_block(idx_gpu, score_gpu, meta, x_rows_cpu, gate_w, gate_b, k, E):
+    """Routing of the whole batch against the oracle: expert sets per token (near ties counted
+    apart), renormalised scores, and - given the GPU's own top-k slots - offsets, gate_index,
+    token_index and reverse_index bit for bit."""
+    from oracle import moe_oracle as O
+    from oracle import sampled as S
+
+    idx_ref, scores_ref, _, _, _, _, gap = S.route_full(x_rows_cpu, gate_w, gate_b, k)
+    blk = S.routing_exactness(idx_gpu, idx_ref, gap)
+    ig = idx_gpu.cpu()
+    dense = torch.zeros(ig.shape[0], E).scatter_(1, ig, score_gpu.float().cpu())
+    # scores of the chosen experts, compared per (token, expert)
+    dense_ref = torch.zeros(ig.shape[0], E).scatter_(1, idx_ref, scores_ref)
+    same = (torch.sort(ig, 1).values == torch.sort(idx_ref, 1).values).all(1)
+    blk["max_score_diff"] = float((dense[same] - dense_ref[same]).abs().max()) if bool(same.any()) else 0.0
+    gi, ti, _, off, rev, _ = O.routing_metadata(dense.clamp_min(1e-30) * (dense > 0), ig)
+    lengths_ok = torch.equal(O.histogram_lengths(ig, E), (meta.offsets[1:] - meta.offsets[:-1]).cpu())
+    blk["metadata_bit_exact"] = bool(
+        lengths_ok and torch.equal(gi, meta.gate_index.cpu()) and torch.equal(ti, meta.token_index.cpu())
+        and torch.equal(rev, meta.reverse_index.cpu()) and int(meta.offsets[-1]) == ig.numel())
+    return blk, idx_ref, gap
+
+
+def parity_block(layer, c, x_cpu, y_dev, expert_weights, gate, n_sample=96, seed=0, max_experts=None):
+    """Compares one forward of the benchmarked layer (y_dev) with the CPU oracle, outside any timed
+    region. Routing tensors: whole batch, bit for bit. Outputs: a seeded sample of tokens (the
+    oracle needs only those rows and their experts' weights). bf16: |y - ref| <= 1e-2 max(1, S) +
+    1e-2 |ref| per element against the fp32 oracle on the same bf16-rounded inputs, S = the
+    largest gate-weighted expert row of the token (1 whenever outputs stay below 1, as at c2;
+    see oracle/sampled.py:compare_tokens); the count under plain rtol / atol is reported too. FP8: against the oracle's
+    quantise -> e4m3 product -> descale chain within 4e-2 of the row's largest magnitude, and the
+    row-wise relative error against the unquantised fp32 oracle (bound 6e-2 per quantised GEMM,
+    two GEMMs in the chain)."""
+    import fast_moe_b200 as fm
+    from oracle import sampled as S
+
+    k, E, d = c["k"], c["E"], c["d"]
+    dev = y_dev.device
+    x_rows = x_cpu.reshape(-1, d)
+    gate_w, gate_b = gate.weight.detach().float().cpu(), gate.bias.detach().float().cpu()
+    x_dev = x_rows.to(dev)
+    idx_gpu, score_gpu, _ = fm.gate_topk(x_dev, gate.weight.detach(), gate.bias.detach(), k)
+    meta = fm.route_metadata(idx_gpu, E)
+    routing, idx_ref, gap = _routing_block(idx_gpu, score_gpu, meta, x_rows, gate_w, gate_b, k, E)
+    experts = None
+    if max_experts is not None and max_experts < E:
+        # the most loaded experts that fit the host budget (ties broken by id)
+        load = torch.bincount(idx_ref.reshape(-1), minlength=E)
+        experts = torch.argsort(load, descending=True, stable=True)[:max_experts].tolist()
+    sel = S.pick_tokens(idx_ref, n_sample, seed=seed, experts=experts, gap=gap)
+    y_rows = y_dev.reshape(-1, c["o"])[sel.to(dev)].float().cpu()
+    out = dict(routing=routing, sample=dict(tokens=int(sel.numel()), of=int(x_rows.shape[0]), seed=seed,
+                                            experts_held=len(experts) if experts else E))
+    if sel.numel() == 0:
+        out["ok"] = False
+        out["error"] = "no token qualifies for the sample"
+        return out
+    y_ref, _, op_scale = S.swiglu_layer_on_tokens(x_rows[sel], gate_w, gate_b, k, expert_weights, with_operand_scale=True)
+    if c.get("fp8"):
+        y_emu, _ = S.swiglu_fp8_layer_on_tokens(x_rows[sel], gate_w, gate_b, k, expert_weights)
+        y_emu = y_emu.float()
+        row = y_emu.abs().amax(dim=1, keepdim=True).clamp_min(1e-6)
+        close = ((y_rows - y_emu).abs() / row).amax(dim=1)
+        rel = (y_rows - y_ref).norm(dim=1) / y_ref.norm(dim=1).clamp_min(1e-6)
+        rel_emu = (y_emu - y_ref).norm(dim=1) / y_ref.norm(dim=1).clamp_min(1e-6)
+        out["outputs"] = dict(
+            tokens=int(sel.numel()), bound_vs_fp8_oracle="max |y - emu| / rowmax <= 4e-2",
+            tokens_out_of_tolerance=int((close > 4e-2).sum()), max_vs_fp8_oracle=float(close.max()),
+            rel_err_vs_fp32_median=float(rel.median()), rel_err_vs_fp32_max=float(rel.max()),
+            fp8_oracle_rel_err_vs_fp32_median=float(rel_emu.median()),
+            bound_vs_fp32="row-wise relative error <= 6e-2 per quantised GEMM (two in the chain)")
+        ok_out = out["outputs"]["tokens_out_of_tolerance"] == 0 and float(rel.median()) < 2 * 6e-2
+    else:
+        out["outputs"] = S.compare_tokens(y_rows, y_ref, operand_scale=op_scale)
+        ok_out = out["outputs"]["tokens_out_of_tolerance"] == 0
+    out["ok"] = bool(ok_out and routing["mismatched"] == 0 and routing["metadata_bit_exact"])
+    return out
+
+
+def layer_expert_weights(layer):
+    """e -> (w_gate [h, d], w_up [h, d], w_down [o, h]) on the host, from a single-GPU layer."""
+    return lambda e: (layer.w_gate.detach()[e].cpu(), layer.w_up.detach()[e].cpu(), layer.w_down.detach()[e].cpu())
+
+
+# ------------------------------------------------------------------------------------ CPU arm
 def cpu_oracle_step(c, x_cpu, params, k):
     from oracle import moe_oracle as O
 
@@ -300,29 +471,6 @@ def time_cpu_baseline(c, tokens, budget_s=20.0):
                 seconds_per_run=t)
 
 
-def time_ep_single_gpu(device, args):
-    """c5 (64 experts, d=4096, h=14336, 8192 tokens) with every expert on this GPU."""
-    from fast_moe_b200.modules.expert_parallel import ExpertParallelSwiGLUMoE
-
-    c = CONFIGS["c5"]
-    layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device)
-    x = make_inputs(c, 0, device).to(device)
-    steps = max(3, min(args.steps, 10))
-    for _ in range(3):
-        layer(x, c["k"])
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        layer(x, c["k"])
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    return dict(value=c["tokens"] / (ms * 1e-3), unit="tokens/s", ms_per_step=ms, steps=steps,
-                layer_tflops=layer_flops(c, c["tokens"]) / (ms * 1e-3) / 1e12,
-                workload=workload_config(c, "c5", 1)["workload"])
-
-
 def run_reference(args, c, name):
     """Reference arm: the CPU restatement of the reference's PYTORCH path, all host threads."""
     rank = int(os.environ.get("RANK", "0"))
@@ -357,11 +505,168 @@ def run_reference(args, c, name):
 def workload_config(c, name, n_gpus):
     return dict(
         workload=f"{name}: SwiGLU MoE layer forward, {c['tokens']} tokens/rank, d={c['d']}, h={c['h']}, "
-                 f"E={c['E']}, top-{c['k']}" + (", fp8 e4m3 rowwise" if c.get("fp8") else ", bf16"),
+                 f"E={c['E']}, top-{c['k']}" + (", fp8 e4m3 rowwise" if c.get("fp8") else ", bf16")
+                 + (f", Zipf({c['zipf']}) expert loads" if c.get("zipf") else ""),
         tokens_per_rank=c["tokens"], global_tokens=c["tokens"] * n_gpus, d=c["d"], h=c["h"], E=c["E"], k=c["k"],
         parallelism="single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} ({c['E'] // n_gpus} experts/rank)",
         l2="working set (weights + activations) is larger than the 126 MB L2; no explicit flush",
     )
+
+
+# ------------------------------------------------------------------------------------ timing
+def time_steps(step, steps, sync):
+    """CUDA-event time of `steps` calls of step() on the current stream, synchronised on both sides."""
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    out = None
+    for _ in range(steps):
+        out = step()
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1), out
+
+
+def sustained_record(step, ms_step_hint, c, tokens, sampler, peaks, seconds=1.2):
+    """The same step repeated for at least `seconds` of device time, with the clocks sampled
+    alongside: what the part sustains under its power cap (the headline's K steps may be a burst)."""
+    n = max(10, int(math.ceil(seconds * 1e3 / max(ms_step_hint, 1e-3))))
+    t0 = time.perf_counter()
+    ms, _ = time_steps(step, n, torch.cuda.synchronize)
+    t1 = time.perf_counter()
+    ms_step = ms / n
+    tf = layer_flops(c, tokens) / (ms_step * 1e-3) / 1e12
+    rec = dict(steps=n, seconds=ms * 1e-3, ms_per_step=ms_step, value=tokens / (ms_step * 1e-3), unit="tokens/s",
+               layer_tflops=tf, frac_of_sustained_peak=None if c.get("fp8") else tf / peaks["bf16_tflops_sustained"],
+               sustained_peak_tflops=peaks["bf16_tflops_sustained"], peak_source=peaks["source"])
+    if sampler is not None:
+        rec["clocks"] = sampler.window(t0, t1)
+    return rec
+
+
+def single_gpu_record(name, device, args, peaks, fp8_peak, sampler=None, sustained=False, parity=True):
+    """Builds configuration `name` on this GPU and measures it: graph-replay step time, the two
+    GEMMs alone, a parity block. Used for the c3 / c4 sub-records of the N = 1 line."""
+    from fast_moe_b200 import CapturedForward, _lib
+
+    c = CONFIGS[name]
+    k = c["k"]
+    layer = build_layer(c, device)
+    x_cpu = make_inputs(c, 0)
+    x_dev = x_cpu.to(device)
+    for _ in range(3):
+        y = layer(x_dev, k)
+    torch.cuda.synchronize()
+    cap = CapturedForward(layer, x_dev, k)
+    for _ in range(3):
+        cap.replay()
+    steps = max(3, min(args.steps, 10))
+    ms, y = time_steps(cap.replay, steps, torch.cuda.synchronize)
+    ms_step = ms / steps
+    timer = _lib.StageTimer()
+    _lib.set_stage_timer(timer)
+    for _ in range(3):
+        layer(x_dev, k)
+    _lib.set_stage_timer(None)
+    stage_ms = {n: tot / cnt for n, (tot, cnt) in timer.totals_ms().items()}
+    up_ms, down_ms = gemm_alone_ms(layer, x_dev, k, bool(c.get("fp8")))
+    A = c["tokens"] * k
+    gemm_peak = fp8_peak if (c.get("fp8") and isinstance(fp8_peak, float)) else peaks["bf16_tflops"]
+    up_tf = 4 * A * c["d"] * c["h"] / (up_ms * 1e-3) / 1e12
+    down_tf = 2 * A * c["h"] * c["o"] / (down_ms * 1e-3) / 1e12
+    rec = dict(
+        workload=workload_config(c, name, 1)["workload"], value=c["tokens"] / (ms_step * 1e-3), unit="tokens/s",
+        ms_per_step=ms_step, steps=steps, launch_mode="cuda graph replay",
+        layer_tflops=layer_flops(c, c["tokens"]) / (ms_step * 1e-3) / 1e12, stage_ms_eager=stage_ms,
+        up_gemm=dict(ms=up_ms, tflops=up_tf, frac=up_tf / gemm_peak),
+        down_gemm=dict(ms=down_ms, tflops=down_tf, frac=down_tf / gemm_peak,
+                       includes="combine fused in the epilogue" if k <= 2 else "separate combine kernel"),
+        gemm_peak_tflops=gemm_peak,
+        gemm_peak_source=("torch._scaled_mm e4m3 8192^3, this run" if c.get("fp8") and isinstance(fp8_peak, float)
+                          else peaks["source"] + " bf16 burst"),
+        device_status=_lib.device_status(device),
+    )
+    hbm = peaks["hbm_gbs"]
+    if c.get("fp8"):
+        # the activation quantisation kernels of the FP8 layer: algorithmic bytes / eager stage time
+        for st, nbytes in (("quant_x", c["tokens"] * c["d"] * 3), ("quant_hidden", A * c["h"] * 3)):
+            if st in stage_ms:
+                rec[st] = dict(ms=stage_ms[st], gbs=nbytes / stage_ms[st] / 1e6, frac_of_hbm=nbytes / stage_ms[st] / 1e6 / hbm)
+    if "combine" in stage_ms:
+        nbytes = (A + c["tokens"]) * c["o"] * 2
+        rec["combine"] = dict(ms=stage_ms["combine"], gbs=nbytes / stage_ms["combine"] / 1e6,
+                              frac_of_hbm=nbytes / stage_ms["combine"] / 1e6 / hbm)
+    if c.get("zipf"):
+        idx = None
+        import fast_moe_b200 as fm
+
+        idx, _, _ = fm.gate_topk(x_dev.reshape(-1, c["d"]), layer.gate.gate.weight.detach(), layer.gate.gate.bias.detach(), k)
+        load = torch.bincount(idx.reshape(-1), minlength=c["E"]).float()
+        rec["expert_load"] = dict(max_share_of_assignments=float(load.max() / load.sum()),
+                                  empty_experts=int((load == 0).sum()), min_nonzero=int(load[load > 0].min()))
+    if sustained:
+        rec["sustained"] = sustained_record(cap.replay, ms_step, c, c["tokens"], sampler, peaks)
+    if parity:
+        torch.set_num_threads(os.cpu_count() or 1)
+        rec["parity"] = parity_block(layer, c, x_cpu, y, layer_expert_weights(layer), layer.gate.gate,
+                                     n_sample=64, max_experts=3 if c.get("fp8") else 24)
+    del cap, layer, y, x_dev
+    torch.cuda.empty_cache()
+    return rec
+
+
+def ep_single_gpu_record(device, args, peaks, with_e2e=True, parity=True):
+    """c5 (64 experts, d=4096, h=14336, 8192 tokens) with every expert on this GPU: the per-rank
+    workload of the multi-GPU runs, i.e. the denominator of their weak-scaling efficiency."""
+    from fast_moe_b200 import CapturedForward, StreamingForward, _lib
+    from fast_moe_b200.modules.expert_parallel import ExpertParallelSwiGLUMoE
+
+    c = CONFIGS["c5"]
+    k = c["k"]
+    layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device, world_size=1)
+    x_cpu = make_inputs(c, 0)
+    x_host = x_cpu.pin_memory()
+    x = x_host.to(device)
+    steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        layer(x, k)
+    torch.cuda.synchronize()
+    cap = CapturedForward(layer, x, k)
+    for _ in range(3):
+        cap.replay()
+    ms, y = time_steps(cap.replay, steps, torch.cuda.synchronize)
+    ms /= steps
+    rec = dict(value=c["tokens"] / (ms * 1e-3), unit="tokens/s", ms_per_step=ms, steps=steps,
+               launch_mode="cuda graph replay",
+               layer_tflops=layer_flops(c, c["tokens"]) / (ms * 1e-3) / 1e12,
+               bound_ms_compute=layer_flops(c, c["tokens"]) / (peaks["bf16_tflops"] * 1e12) * 1e3,
+               bound_ms_hbm=layer_min_bytes(c, c["tokens"]) / (peaks["hbm_gbs"] * 1e9) * 1e3,
+               workload=workload_config(c, "c5", 1)["workload"], device_status=_lib.device_status(device))
+    if with_e2e:
+        slots = 3
+        pipe = StreamingForward(layer, x, k, slots=slots, capture=True)
+        y_hosts = [torch.empty((c["batch"], c["seq"], c["o"]), dtype=torch.bfloat16).pin_memory() for _ in range(slots)]
+        for i in range(slots):
+            pipe.submit(x_host, y_hosts[i])
+        pipe.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            pipe.submit(x_host, y_hosts[i % slots])
+        pipe.drain()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / steps
+        rec["e2e"] = dict(value=c["tokens"] / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e,
+                          h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=y_hosts[0].numel() * 2)
+        del pipe
+    if parity:
+        torch.set_num_threads(os.cpu_count() or 1)
+        rec["parity"] = parity_block(layer, c, x_cpu, y, lambda e: tuple(t.cpu() for t in layer.materialize_expert(e)),
+                                     layer.gate, n_sample=64, max_experts=8)
+    del cap, layer, y, x
+    torch.cuda.empty_cache()
+    return rec
 
 
 def main():
@@ -372,7 +677,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-ep-reference", action="store_true")
+    ap.add_argument("--no-ep-reference", action="store_true", help="skip the 1-GPU run of the multi-GPU workload")
+    ap.add_argument("--no-sub-records", action="store_true", help="N = 1: skip the c3 / c4 sub-records")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison (profiling runs)")
+    ap.add_argument("--no-sustained", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--routing-sweep", action="store_true",
                     help="only time the routing operators and the HBM-bound kernels alone (one JSON line)")
@@ -396,6 +704,7 @@ def main():
         if rank == 0:
             routing_sweep(c, device)
         return
+    peaks = load_peaks()
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -405,8 +714,21 @@ def main():
 
     from fast_moe_b200 import _lib
 
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- N > 1: rank 0 first times the per-rank workload alone (all 64 experts on its GPU)
+    t1_rec = None
+    if world > 1 and not args.no_ep_reference:
+        if rank == 0:
+            t1_rec = ep_single_gpu_record(device, args, peaks, with_e2e=True, parity=False)
+        barrier()
+
     k = c["k"]
-    x_host = make_inputs(c, rank, device).pin_memory()
+    x_cpu = make_inputs(c, rank)
+    x_host = x_cpu.pin_memory()
     x_dev = x_host.to(device)
     if world > 1:
         from fast_moe_b200.modules.expert_parallel import ExpertParallelSwiGLUMoE
@@ -415,19 +737,11 @@ def main():
         layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device)
     else:
         layer = build_layer(c, device)
-    if c.get("fp8"):
-        layer.quantize_weights()
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
 
     # ---- device-resident timing
     # Single GPU: the forward is captured once as a CUDA graph and a step is one replay (same
-    # kernels, one launch). The expert-parallel layer synchronises with the host for its split
-    # sizes and runs eagerly. A second, eager pass with CUDA events around each stage gives the
-    # per-kernel times the roofline figure uses.
+    # kernels, one launch). A second, eager pass with CUDA events around each stage gives the
+    # per-stage times.
     for _ in range(args.warmup):
         y = layer(x_dev, k)
     barrier()
@@ -445,16 +759,8 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
-    launches0 = _lib.kernel_launch_count()
-    barrier()
     t_wall0 = time.perf_counter()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        y = step()
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
+    ms_total, y = time_steps(step, args.steps, barrier)
     # eager pass with stage events (also what counts launches when the timed pass was a graph);
     # graph capture empties the allocator cache, so the eager path is warmed up again first
     for _ in range(3):
@@ -463,20 +769,21 @@ def main():
     timer = _lib.StageTimer()
     _lib.set_stage_timer(timer)
     launches_eager0 = _lib.kernel_launch_count()
-    ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ee0.record()
-    for _ in range(args.steps):
-        layer(x_dev, k)
-    ee1.record()
-    barrier()
+    ms_eager, _ = time_steps(lambda: layer(x_dev, k), args.steps, barrier)
+    ms_eager /= args.steps
     t_wall1 = time.perf_counter()
-    ms_eager = ee0.elapsed_time(ee1) / args.steps
     launches = _lib.kernel_launch_count() - launches_eager0   # kernels per K steps (the graph replays the same ones)
     _lib.set_stage_timer(None)
-    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    clocks = sampler.window(t_wall0, t_wall1) if rank == 0 else None
     stage_ms = {n: (tot / cnt) for n, (tot, cnt) in timer.totals_ms().items()}
-    up_alone_ms = up_projection_ms(layer, x_dev, k, bool(c.get("fp8"))) if world == 1 else None
+    up_alone_ms = down_alone_ms = None
+    if world == 1:
+        up_alone_ms, down_alone_ms = gemm_alone_ms(layer, x_dev, k, bool(c.get("fp8")))
     status = _lib.device_status(device)
+
+    sustained = None
+    if world == 1 and not args.no_sustained:
+        sustained = sustained_record(step, ms_total / args.steps, c, c["tokens"], sampler if rank == 0 else None, peaks)
 
     # ---- end to end: host tokens in, host result out, every step, through the package's
     # streaming executor: every step copies its tokens from pinned host memory and its result
@@ -500,37 +807,72 @@ def main():
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     e2e_check = float((y_hosts[(args.steps - 1) % slots].float() - y.detach().float().cpu().view_as(y_host)).abs().max())
+    e2e_legs = pipe.leg_times_ms() if hasattr(pipe, "leg_times_ms") else None
+    del pipe
+
+    # ---- parity of this very layer and batch against the CPU oracle (outside the timed regions)
+    parity = None
+    if not args.no_parity:
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))
+        if world > 1:
+            mine = parity_block(layer, c, x_cpu, y, lambda e: tuple(t.cpu() for t in layer.materialize_expert(e)),
+                                layer.gate, n_sample=48, seed=rank, max_experts=8)
+            mine["rank"] = rank
+            allp = [None] * world
+            dist.all_gather_object(allp, mine)
+            parity = dict(ok=all(p["ok"] for p in allp),
+                          tokens=sum(p["sample"]["tokens"] for p in allp),
+                          tokens_out_of_tolerance=sum(p["outputs"]["tokens_out_of_tolerance"] for p in allp if "outputs" in p),
+                          routing_mismatched=sum(p["routing"]["mismatched"] for p in allp),
+                          oracle="oracle/sampled.py on every rank's own tokens, the weights of the sampled experts "
+                                 "rebuilt from their global seed", per_rank=allp)
+        else:
+            parity = parity_block(layer, c, x_cpu, y, layer_expert_weights(layer), layer.gate.gate,
+                                  n_sample=c["tokens"] if name == "c2" else 64,
+                                  max_experts=None if name == "c2" else (3 if c.get("fp8") else 24))
 
     t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
     stage_ms_ranks = None
+    legs_ranks = None
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         stage_ms_ranks = [None] * world
         dist.all_gather_object(stage_ms_ranks, {n: round(v, 4) for n, v in stage_ms.items()})
+        legs_ranks = [None] * world
+        dist.all_gather_object(legs_ranks, e2e_legs)
     ms_total, ms_e2e = t.tolist()
 
     if rank == 0:
-        peaks = load_peaks()
+        sampler.stop(t_wall0, t_wall1)
         ms_step = ms_total / args.steps
         tokens_total = c["tokens"] * world
         A = c["tokens"] * k
+        fp8_peak = fp8_dense_peak(device) if (world == 1 and (c.get("fp8") or not args.no_sub_records)) else None
         # the dominant kernel's duration: alone, back to back in a graph (single GPU), else the
         # eager stage events (which include host launch gaps when the host is the slower side)
         up_ms = up_alone_ms if up_alone_ms is not None else stage_ms.get("up")
         up_flops = 4 * A * c["d"] * c["h"]
         # the up-projection kernel is timed alone between two events: burst peak is its yardstick
-        peak_tf = peaks["bf16_tflops"] * (2.0 if c.get("fp8") else 1.0)
+        if c.get("fp8") and isinstance(fp8_peak, float):
+            peak_tf, peak_src = fp8_peak, "torch._scaled_mm e4m3 8192^3 measured in this run"
+        else:
+            peak_tf, peak_src = peaks["bf16_tflops"], peaks["source"] + " burst"
         roofline = None
         if up_ms:
             ach = up_flops / (up_ms * 1e-3) / 1e12
+            traffic, traffic_commit = ncu_traffic(name) if world == 1 else (None, None)
             roofline = dict(bound="tensor", kernel="grouped_gemm_kernel (gate/up GEMM + SwiGLU on expert-sorted rows)",
                             achieved=ach, peak=peak_tf, unit="TFLOP/s", frac=ach / peak_tf,
-                            traffic=NCU_TRAFFIC_BYTES.get(name) if world == 1 else None,
+                            traffic=traffic, traffic_source=(f"profiles/grouped_gemm_{name}.md, captured at commit "
+                                                             f"{traffic_commit}") if traffic else None,
                             algorithmic_bytes=(2 * c["E"] * c["d"] * c["h"] + A * c["d"] + A * c["h"]) * (1 if c.get("fp8") else 2),
-                            peak_source=peaks["source"] + (" (2x bf16 burst for fp8)" if c.get("fp8") else " burst"),
+                            peak_source=peak_src,
                             flops_per_launch=up_flops, avg_launch_ms=up_ms,
                             timing="10 launches back to back in a CUDA graph, CUDA events" if up_alone_ms is not None
                             else "CUDA events around the eager launch")
+            if down_alone_ms:
+                dtf = 2 * A * c["h"] * c["o"] / (down_alone_ms * 1e-3) / 1e12
+                roofline["down_gemm"] = dict(ms=down_alone_ms, tflops=dtf, frac=dtf / peak_tf)
         line = dict(
             metric="moe_layer_fwd_tokens_per_s", value=tokens_total / (ms_step * 1e-3), unit="tokens/s",
             n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,
@@ -539,21 +881,36 @@ def main():
             layer_tflops_per_gpu=layer_flops(c, c["tokens"]) / (ms_step * 1e-3) / 1e12,
             launch_mode="cuda graph replay" if captured is not None else "eager", ms_per_step_eager=ms_eager,
             stage_ms=stage_ms, stage_ms_per_rank=stage_ms_ranks, roofline=roofline, clocks=clocks, gpu_launches=int(launches),
-            device_status=status,
+            device_status=status, parity=parity, sustained=sustained,
             e2e=dict(value=tokens_total / (ms_e2e / args.steps * 1e-3), unit="tokens/s",
                      h2d_bytes_per_step=x_host.numel() * x_host.element_size(),
                      d2h_bytes_per_step=y_host.numel() * y_host.element_size(), ms_per_step=ms_e2e / args.steps,
                      mode="%d-slot pipeline: H2D, forward and D2H of consecutive steps overlap" % slots,
-                     max_abs_diff_vs_resident=e2e_check),
+                     max_abs_diff_vs_resident=e2e_check, leg_ms_per_rank=legs_ranks if legs_ranks else e2e_legs),
         )
+        if world > 1 and t1_rec is not None:
+            El = c["E"] // world
+            line["weak_scaling"] = dict(
+                t1_ms=t1_rec["ms_per_step"], tN_ms=ms_step, efficiency=t1_rec["ms_per_step"] / ms_step,
+                t1=t1_rec,
+                e2e_efficiency=(t1_rec["e2e"]["ms_per_step"] / (ms_e2e / args.steps)) if "e2e" in t1_rec else None,
+                bound_ms_compute=layer_flops(c, c["tokens"]) / (peaks["bf16_tflops"] * 1e12) * 1e3,
+                bound_ms_hbm=layer_min_bytes(c, c["tokens"], El) / (peaks["hbm_gbs"] * 1e9) * 1e3,
+                bound_ms_nvlink=2 * A * c["d"] * 2 * (world - 1) / world / 770e9 * 1e3,
+                note="t1 = the same per-rank workload (8192 tokens, all 64 experts) alone on rank 0's GPU in this run; "
+                     "efficiency = t1 / tN; above 1 because one GPU streams 64 experts' weights (HBM-bound) and a "
+                     "rank of the sharded run only its own")
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = time_cpu_baseline(c, c["tokens"])
-        if world == 1 and args.config is None and not args.no_ep_reference:
-            # the per-rank workload of the multi-GPU runs (c5, expert parallel) on one GPU: the
-            # denominator for weak-scaling efficiency of the N > 1 lines
-            del layer, y
+        if world == 1 and args.config is None:
+            del layer, y, captured, step
             torch.cuda.empty_cache()
-            line["c5_ep_1gpu"] = time_ep_single_gpu(device, args)
+            line["fp8_dense_peak_tflops"] = fp8_peak
+            if not args.no_sub_records:
+                for sub in ("c3", "c4"):
+                    line[sub] = single_gpu_record(sub, device, args, peaks, fp8_peak, parity=not args.no_parity)
+            if not args.no_ep_reference:
+                line["c5_ep_1gpu"] = ep_single_gpu_record(device, args, peaks, with_e2e=True, parity=not args.no_parity)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

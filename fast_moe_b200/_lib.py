@@ -100,11 +100,13 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not _LIB_PATH.exists():
-        if not build_if_missing:
-            raise FileNotFoundError(f"{_LIB_PATH} is missing; run `python -m fast_moe_b200.build`")
-        from .build import build_library
+    from .build import build_library, library_is_current
 
+    if not library_is_current():
+        # missing, or built from other sources than the ones next to it: never run a stale library
+        if not build_if_missing:
+            raise FileNotFoundError(
+                f"{_LIB_PATH} is missing or was not built from the sources beside it; run `python -m fast_moe_b200.build`")
         build_library()
     lib = ctypes.CDLL(os.fspath(_LIB_PATH))
     for name, (res, args) in SIGNATURES.items():

@@ -39,6 +39,31 @@ def _nvcc() -> str:
     return cand
 
 
+STAMP_PATH = LIB_DIR / "build_stamp.txt"
+
+
+def source_digest() -> str:
+    """SHA-256 over the CUDA sources, the headers and the compiler flags: what the library on
+    disk must have been built from. Independent of file times, which a copy of the tree may not
+    preserve."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for path in [CSRC / s for s in SOURCES] + HEADERS:
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def library_is_current() -> bool:
+    """True when libfmoe_b200.so exists and its stamp matches the sources next to it."""
+    try:
+        return LIB_PATH.exists() and STAMP_PATH.read_text().strip() == source_digest()
+    except OSError:
+        return False
+
+
 def _stale(target: Path, deps) -> bool:
     if not target.exists():
         return True
@@ -52,6 +77,8 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     obj_dir = LIB_DIR / "obj"
     obj_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
+    if LIB_PATH.exists() and STAMP_PATH.exists() and not library_is_current():
+        force = True      # sources changed under a library whose file times may not show it
     jobs = []
     for src, stem, extra in UNITS:
         s = CSRC / src
@@ -79,6 +106,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("linking libfmoe_b200.so failed")
+    STAMP_PATH.write_text(source_digest() + "\n")
     return LIB_PATH
 
 

@@ -4,6 +4,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -30,26 +32,37 @@ int cuda_fail(cudaError_t e, const char* what) {
   return fail(FMOE_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
 }
 
-int* device_status_ptr(int* err) {
-  // One address per device; a process drives one device in practice, but look it up per device
-  // to stay correct when it does not.
-  static int* ptrs[64] = {nullptr};
+int current_device_slot(int* dev_out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) {
-    *err = cuda_fail(e, "cudaGetDevice");
-    return nullptr;
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) {
+    return fail(FMOE_ERR_UNSUPPORTED, "device ordinal %d is outside the %d per-device slots this library keeps", dev,
+                kMaxDevices);
   }
-  if (ptrs[dev] == nullptr) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_dev_status);
-    if (e != cudaSuccess) {
+  *dev_out = dev;
+  return FMOE_OK;
+}
+
+int* device_status_ptr(int* err) {
+  // One address per device; a process drives one device in practice, but look it up per device
+  // to stay correct when it does not. Two host threads that make the first call together both
+  // look the address up and store the same value: the slot is atomic, the lookup idempotent.
+  static std::atomic<int*> ptrs[kMaxDevices];
+  int dev = 0;
+  if ((*err = current_device_slot(&dev)) != FMOE_OK) return nullptr;
+  int* p = ptrs[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    void* sym = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&sym, g_dev_status);
+    if (e != cudaSuccess || sym == nullptr) {
       *err = cuda_fail(e, "cudaGetSymbolAddress(status word)");
       return nullptr;
     }
-    ptrs[dev] = static_cast<int*>(p);
+    p = static_cast<int*>(sym);
+    ptrs[dev].store(p, std::memory_order_release);
   }
-  return ptrs[dev];
+  return p;
 }
 
 namespace {
@@ -226,7 +239,7 @@ extern "C" int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t tota
                                             const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
                                             int has_silu, void* act_scratch, void* bmm_scratch, void* out,
                                             int out_dtype, int64_t ldo, void* stream) {
-  FMOE_REQUIRE(bmm_scratch != nullptr, "silu_jagged_bmm_combine: bmm_scratch is NULL");
+  FMOE_REQUIRE(L == 0 || bmm_scratch != nullptr, "silu_jagged_bmm_combine: bmm_scratch is NULL");
   FMOE_REQUIRE(total_rows == L * k, "silu_jagged_bmm_combine: rows %lld != L*k = %lld", (long long)total_rows,
                (long long)(L * k));
   // the GEMM result has the activation type, as F.linear returns it
@@ -254,11 +267,13 @@ extern "C" int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_
   FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm_combine_fused: FP8 operands need their scales");
   FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm_combine_fused: has_silu is not available on FP8 input");
   FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm_combine_fused: has_silu needs act_scratch");
-  FMOE_REQUIRE(gating_scores && gates_index, "silu_jagged_bmm_combine_fused: gating_scores and gates_index are required");
+  FMOE_REQUIRE(L == 0 || (gating_scores && gates_index),
+               "silu_jagged_bmm_combine_fused: gating_scores and gates_index are required");
   FMOE_REQUIRE(g_dtype == FMOE_BF16 || g_dtype == FMOE_F32, "silu_jagged_bmm_combine_fused: gate weights must be bf16 or f32");
   FMOE_REQUIRE(total_rows == L * k, "silu_jagged_bmm_combine_fused: rows %lld != L*k = %lld", (long long)total_rows,
                (long long)(L * k));
-  FMOE_REQUIRE(out != nullptr && ldo >= N, "silu_jagged_bmm_combine_fused: bad output");
+  FMOE_REQUIRE((L == 0 || out != nullptr) && ldo >= N, "silu_jagged_bmm_combine_fused: bad output");
+  if (L == 0) return FMOE_OK;   // an empty batch is valid input (its tensors have NULL data pointers)
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int os = dtype_size(out_dtype);
   if (L > 0 && !(flags & FMOE_COMBINE_ACCUMULATE)) {

@@ -399,7 +399,7 @@ extern "C" int fmoe_mul_merge_k_add(const int64_t* reverse_index, const void* va
                                     const void* weight, int w_dtype, const int64_t* weight_index, int64_t L, int k,
                                     int D, void* out, int out_dtype, int64_t ldo, void* stream) {
   FMOE_REQUIRE(L >= 0 && k >= 1 && D >= 1, "mul_merge_k_add: L=%lld k=%d D=%d", (long long)L, k, D);
-  FMOE_REQUIRE(reverse_index && value && out, "mul_merge_k_add: NULL pointer argument");
+  FMOE_REQUIRE(L == 0 || (reverse_index && value && out), "mul_merge_k_add: NULL pointer argument");
   FMOE_REQUIRE(v_dtype == FMOE_BF16 || v_dtype == FMOE_F32, "mul_merge_k_add: value must be bf16 or f32");
   FMOE_REQUIRE(weight == nullptr || w_dtype == FMOE_BF16 || w_dtype == FMOE_F32,
                "mul_merge_k_add: weight must be bf16 or f32");

@@ -30,6 +30,10 @@ int cuda_fail(cudaError_t e, const char* what);
 // problem they meet (a wait that ran out, an index out of range) and return; they never
 // trap. Defined in api.cu; the address is resolved once per device.
 int* device_status_ptr(int* err);
+// Ordinal of the current device, checked against the per-device tables (kMaxDevices slots) the
+// library keeps for cached symbol addresses and kernel attributes. FMOE_OK or an error status.
+constexpr int kMaxDevices = 64;
+int current_device_slot(int* dev_out);
 
 static inline int dtype_size(int dt) {
   switch (dt) {

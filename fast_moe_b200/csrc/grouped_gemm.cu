@@ -35,6 +35,8 @@
 #include <stdlib.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -459,11 +461,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       long long dst_row = row;
       float gate_scale = 1.0f;
+      bool store_ok = row_ok;             // false: the row exists but its destination does not - nothing is written
       constexpr bool combine = COMBINE;   // compiled in only for the plain, contiguous-row kernels
       if (combine && row_ok) {
         const long long gi = p.gate_index[row];
         if (gi < 0 || gi >= p.out_rows * p.gate_div) {
           atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
+          store_ok = false;
         } else {
           dst_row = gi / p.gate_div;
           gate_scale = p.gate_is_f32 ? reinterpret_cast<const float*>(p.gate)[gi]
@@ -476,6 +480,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (dst_row < 0 || dst_row >= p.out_rows) {
           atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
           dst_row = row;
+          store_ok = false;
         }
       }
       OutT* out_row = reinterpret_cast<OutT*>(p.out) + dst_row * p.ldo;
@@ -489,7 +494,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const unsigned long long ptr_bits =
             __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out_row), src_lane);
         st_row[i] = reinterpret_cast<OutT*>(ptr_bits);
-        st_ok[i] = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, src_lane) != 0;
+        st_ok[i] = __shfl_sync(0xffffffffu, store_ok ? 1 : 0, src_lane) != 0;
       }
       const int n0 = nb * kTileN;
       const int acc = it & 1;
@@ -563,6 +568,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if constexpr (DUAL) {
                   u = __bfloat162float(__float2bfloat16_rn(u)) * (inv_a * __shfl_sync(0xffffffffu, f1, i));
                 }
+                // the reference casts the descaled product to the output type BEFORE it adds the
+                // bias (kernels/pytorch/moe_fp8.py:126-133)
+                if constexpr (sizeof(OutT) == 2) {
+                  if (has_b0) g = __bfloat162float(__float2bfloat16_rn(g));
+                  if (has_b1) u = __bfloat162float(__float2bfloat16_rn(u));
+                }
               }
               if (has_b0) g += __shfl_sync(0xffffffffu, bb0, i);
               if (has_b1) u += __shfl_sync(0xffffffffu, bb1, i);
@@ -583,6 +594,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const long long so = static_cast<long long>(e) * p.bscale_se + col;
                 g = __bfloat162float(__float2bfloat16_rn(g)) / (scale_a * p.b0_scale[so]);
                 if constexpr (DUAL) u = __bfloat162float(__float2bfloat16_rn(u)) / (scale_a * p.b1_scale[so]);
+                if constexpr (sizeof(OutT) == 2) {   // cast, then bias: see the fast path above
+                  if (p.bias0) g = __bfloat162float(__float2bfloat16_rn(g));
+                  if (DUAL && p.bias1) u = __bfloat162float(__float2bfloat16_rn(u));
+                }
               }
               if (p.bias0) g += load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col);
               if constexpr (DUAL) {
@@ -608,7 +623,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           if (ncols == 32 && p.vec_ok) {
             stage_and_store<OutT>(stage_w, lane, v, st_row, st_ok, col0, combine);
-          } else if (row_ok && ncols > 0) {
+          } else if (store_ok && ncols > 0) {
             if (combine) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
@@ -836,12 +851,13 @@ int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap&
   using Plan = SmemPlan<CTAS>;
   auto kern = grouped_gemm_kernel<ESIZE, CTAS, DUAL, GATHER, COMBINE, OutT>;
   // function attributes belong to a device's context: set once per device
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[kMaxDevices];
   int dev = 0;
-  FMOE_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+  int rc = current_device_slot(&dev);
+  if (rc != FMOE_OK) return rc;
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     FMOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal));
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
@@ -928,6 +944,10 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   FMOE_REQUIRE(esize != 0, "grouped_gemm: unknown operand dtype %d", d.dtype);
   FMOE_REQUIRE(d.E >= 1 && d.E <= kMaxExperts, "grouped_gemm: E=%d outside [1, %d]", d.E, kMaxExperts);
   FMOE_REQUIRE(d.N >= 1 && d.K >= 1, "grouped_gemm: N=%d K=%d must be positive", d.N, d.K);
+  // No rows: nothing to compute. Checked before the pointers, because an empty tensor's data
+  // pointer is NULL and an empty batch (a rank of an expert-parallel job that receives no rows)
+  // is valid input.
+  if (d.total_rows <= 0) return FMOE_OK;
   FMOE_REQUIRE(d.offsets && d.a && d.b0 && d.out, "grouped_gemm: null pointer argument");
   FMOE_REQUIRE(d.out_dtype == FMOE_BF16 || d.out_dtype == FMOE_F32, "grouped_gemm: output must be bf16 or f32");
   FMOE_REQUIRE(d.dtype != FMOE_F32 || d.out_dtype == FMOE_F32, "grouped_gemm: f32 operands need an f32 output");
@@ -947,7 +967,6 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   if (d.gate_index != nullptr && (d.index != nullptr || d.epilogue != FMOE_EPI_NONE)) {
     return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: the fused combine needs contiguous rows and the plain epilogue");
   }
-  if (d.total_rows <= 0) return FMOE_OK;
   FMOE_REQUIRE(d.a_rows >= 1, "grouped_gemm: empty A source with %lld output rows", (long long)d.total_rows);
   FMOE_REQUIRE(d.a_rows < (1ll << 31) && d.total_rows < (1ll << 31), "grouped_gemm: more than 2^31 rows");
 

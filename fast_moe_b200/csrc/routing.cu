@@ -6,6 +6,8 @@
 // softmax, topk, scatter_, mul, normalize, two stable sorts, floor-divide, sum, gather, cumsum,
 // max + device-to-host sync). All of this is integer / HBM-bound work: one pass over x for the
 // logits, one pass over the [L, k] indices for the histogram and one for the placement.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -629,6 +631,7 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
                               int k, float* logits_out, int64_t* topk_idx, float* topk_score, void* stream) {
   FMOE_REQUIRE(L >= 0 && E >= 1 && E <= kMaxGateExperts, "gate_topk: E=%d outside [1, %d]", E, kMaxGateExperts);
   FMOE_REQUIRE(k >= 1 && k <= E, "gate_topk: k=%d must be in [1, E=%d]", k, E);
+  if (L == 0) return FMOE_OK;   // an empty batch is valid input (its tensors have NULL data pointers)
   FMOE_REQUIRE(topk_idx && topk_score, "gate_topk: output pointers must not be NULL");
   FMOE_REQUIRE(logits_in || (x && gate_w && d >= 1), "gate_topk: need either logits_in or x and gate_w");
   FMOE_REQUIRE(!logits_in || ld_logits >= (logits_split ? 2 : 1) * static_cast<int64_t>(E),
@@ -801,23 +804,20 @@ static __device__ __align__(256) int g_route_scratch[kStaticRouteInts];
 // a handle for the runtime, not a device address, so the address is looked up once per device
 // (with that device current) and cached.
 int* static_route_scratch(int* err) {
-  static int* ptrs[64] = {nullptr};
+  // atomic slots: two host threads making the first call together store the same address
+  static std::atomic<int*> ptrs[kMaxDevices];
   int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) {
-    *err = cuda_fail(e, "cudaGetDevice");
-    return nullptr;
-  }
-  if (ptrs[dev] == nullptr) {
-    int* p = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_scratch);
+  if ((*err = current_device_slot(&dev)) != FMOE_OK) return nullptr;
+  int* p = ptrs[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_scratch);
     if (e != cudaSuccess || p == nullptr) {
       *err = cuda_fail(e, "cudaGetSymbolAddress(route scratch)");
       return nullptr;
     }
-    ptrs[dev] = p;
+    ptrs[dev].store(p, std::memory_order_release);
   }
-  return ptrs[dev];
+  return p;
 }
 
 }  // namespace

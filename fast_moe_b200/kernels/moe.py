@@ -426,7 +426,11 @@ def silu_jagged_bmm_combine(
     last-bit order dependence for k > 2.
 
     ``round_scores=True`` treats gating_scores as if they had been cast to the activation type
-    first (what the reference layer does before calling this operator) without a cast kernel.
+    first, without a cast kernel. The reference has no such cast: its gate is an nn.Linear that
+    runs in the dtype of x (modules/fast_moe_module.py:21-27), so with bf16 tokens the scores it
+    hands to this operator are already bf16 and ``value * weight`` rounds to bf16
+    (kernels/pytorch/moe.py:27). The layers here compute the router in fp32 (a deliberate
+    deviation: exact top-k needs it) and use this flag to land on the same operand types.
     ``out`` (fused form only): an [L, D_out] tensor of the activation type that the rows are ADDED
     to - zeros prepared ahead of time, or a residual; it is returned."""
     N = index.shape[0]

@@ -96,11 +96,17 @@ class ExpertParallelSwiGLUMoE(nn.Module):
     def __init__(self, input_dim: int, hidden_dim: int, output_dim: int, num_experts: int,
                  dtype: torch.dtype = torch.bfloat16, init_std: float = 0.02,
                  device: Optional[torch.device] = None, group: Optional[dist.ProcessGroup] = None,
-                 seed: int = 0) -> None:
+                 seed: int = 0, world_size: Optional[int] = None) -> None:
         super().__init__()
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if world_size is not None:
+            # world_size=1 keeps every expert on this process even inside a larger job
+            if world_size != 1 and world_size != self.world:
+                raise ValueError(f"world_size={world_size} does not match the process group ({self.world} ranks)")
+            if world_size == 1:
+                self.world, self.rank = 1, 0
         if num_experts % self.world != 0:
             raise ValueError(f"{num_experts} experts cannot be split evenly over {self.world} ranks")
         self.input_dim, self.hidden_dim, self.output_dim = input_dim, hidden_dim, output_dim
@@ -117,18 +123,32 @@ class ExpertParallelSwiGLUMoE(nn.Module):
             self.gate.weight.copy_(gate_w)
             self.gate.bias.zero_()
 
+        self._init = (seed, init_std, dev)
+
         def expert_weights(rows, cols, salt):
             out = torch.empty(self.experts_local, rows, cols, dtype=dtype, device=dev)
             for i in range(self.experts_local):
-                ge = torch.Generator(device=dev)
-                ge.manual_seed(seed * 1000003 + (self.first_expert + i) * 7 + salt)
-                out[i] = (torch.randn(rows, cols, generator=ge, device=dev) * init_std).to(dtype)
+                out[i] = self._expert_matrix(self.first_expert + i, rows, cols, salt)
             return nn.Parameter(out)
 
         self._gate_split = GateSplitCache()
         self.w_gate = expert_weights(hidden_dim, input_dim, 1)
         self.w_up = expert_weights(hidden_dim, input_dim, 2)
         self.w_down = expert_weights(output_dim, hidden_dim, 3)
+
+    def _expert_matrix(self, expert: int, rows: int, cols: int, salt: int) -> torch.Tensor:
+        seed, init_std, dev = self._init
+        ge = torch.Generator(device=dev)
+        ge.manual_seed(seed * 1000003 + expert * 7 + salt)
+        return (torch.randn(rows, cols, generator=ge, device=dev) * init_std).to(self.dtype)
+
+    def materialize_expert(self, expert: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """The initial (w_gate [h, d], w_up [h, d], w_down [o, h]) of GLOBAL expert id ``expert``,
+        rebuilt from its seed on this rank's device whichever rank owns it: what a re-sharding, or
+        a check of one rank's result against the whole model, needs without moving weights."""
+        return (self._expert_matrix(expert, self.hidden_dim, self.input_dim, 1),
+                self._expert_matrix(expert, self.hidden_dim, self.input_dim, 2),
+                self._expert_matrix(expert, self.output_dim, self.hidden_dim, 3))
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
@@ -160,13 +180,12 @@ class ExpertParallelSwiGLUMoE(nn.Module):
             # the pack kernel is queued before the host waits for the counts, so the GPU packs the
             # rows while the host reads the split sizes back
             send = ops.gather_rows(x_flat, meta.gate_index, k)
-            # the local plan too: at most every rank sends all of its rows here
-            offsets_local, perm_padded = local_expert_plan(recv_lengths, capacity=x_flat.shape[0] * k * W)
             counts = torch.stack([send_lengths.sum(1), recv_lengths.sum(1)]).cpu()   # the layer's one host sync
             send_counts, recv_counts = counts[0].tolist(), counts[1].tolist()
             validate_plan(send_counts, recv_counts, recv_lengths, W)
             n_recv = sum(recv_counts)
-            perm = perm_padded[:n_recv]
+            # ranks may hold different numbers of tokens, so the plan is sized by what actually arrives
+            offsets_local, perm = local_expert_plan(recv_lengths, total=n_recv)
         with _lib.stage("dispatch"):
             recv = torch.empty((n_recv, self.input_dim), dtype=dt, device=x.device)
             dist.all_to_all_single(recv, send, recv_counts, send_counts, group=self.group)

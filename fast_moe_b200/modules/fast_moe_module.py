@@ -330,7 +330,10 @@ class StreamingForward:
         self.graphs = [CapturedForward(layer, example, num_experts_per_tok) for _ in range(slots)] if capture else None
         self.x = [g.x for g in self.graphs] if capture else [torch.empty_like(example) for _ in range(slots)]
         self.y = [None] * slots
-        ev = lambda: torch.cuda.Event()
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        self.in_start = [ev() for _ in range(slots)]
+        self.run_start = [ev() for _ in range(slots)]
+        self.out_start = [ev() for _ in range(slots)]
         self.in_ready = [ev() for _ in range(slots)]
         self.run_done = [ev() for _ in range(slots)]
         self.out_done = [ev() for _ in range(slots)]
@@ -347,12 +350,14 @@ class StreamingForward:
         with torch.cuda.stream(self.s_in):
             if self.used[s]:
                 self.s_in.wait_event(self.run_done[s])      # the slot's previous batch has been consumed
+            self.in_start[s].record(self.s_in)
             self.x[s].copy_(x_host, non_blocking=True)
             self.in_ready[s].record(self.s_in)
         with torch.cuda.stream(self.s_run):
             self.s_run.wait_event(self.in_ready[s])
             if self.used[s]:
                 self.s_run.wait_event(self.out_done[s])     # the slot's previous result has left the device
+            self.run_start[s].record(self.s_run)
             if self.graphs is not None:
                 y = self.graphs[s].replay()
             else:
@@ -362,6 +367,7 @@ class StreamingForward:
             self.run_done[s].record(self.s_run)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(self.run_done[s])
+            self.out_start[s].record(self.s_out)
             y_host.copy_(y.view(y_host.shape), non_blocking=True)
             self.out_done[s].record(self.s_out)
         self.used[s] = True
@@ -375,3 +381,15 @@ class StreamingForward:
     def synchronize(self) -> None:
         for st in (self.s_in, self.s_run, self.s_out):
             st.synchronize()
+
+    def leg_times_ms(self) -> Dict[str, float]:
+        """Device time of the three legs of the most recent batch of every slot (host-to-device
+        copy, forward, device-to-host copy), averaged over the slots in use: shows which leg a
+        pipeline that is slower than its forward is waiting for. Synchronises."""
+        self.synchronize()
+        used = [s for s in range(len(self.x)) if self.used[s]]
+        if not used:
+            return {}
+        avg = lambda a, b: sum(a[s].elapsed_time(b[s]) for s in used) / len(used)
+        return dict(h2d=avg(self.in_start, self.in_ready), forward=avg(self.run_start, self.run_done),
+                    d2h=avg(self.out_start, self.out_done))

@@ -223,9 +223,10 @@ int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t total_rows, con
  * select the FP8 form as in fmoe_silu_jagged_bmm.
  * flags: FMOE_COMBINE_ACCUMULATE - `out` is not cleared; the rows are added to what it holds (a
  *   buffer the caller zeroed earlier, off the critical path, or a residual to add the layer to);
- *   FMOE_COMBINE_ROUND_GATE - f32 gating_scores are rounded to the output type before use, which
- *   is what casting the scores to the activation type first (modules/fast_moe_module.py:215)
- *   would give, without the separate cast. */
+ *   FMOE_COMBINE_ROUND_GATE - f32 gating_scores are rounded to the output type before use: the
+ *   operand types the reference's own layer produces, whose gate runs in the dtype of the tokens
+ *   (modules/fast_moe_module.py:21-27) so that bf16 tokens come with bf16 scores. The layers
+ *   here route in fp32 and round in the epilogue instead of running a separate cast. */
 #define FMOE_COMBINE_ACCUMULATE 1
 #define FMOE_COMBINE_ROUND_GATE 2
 int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype,

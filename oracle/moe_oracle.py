@@ -221,39 +221,46 @@ def fp32_to_e4m3fn(v: np.ndarray) -> np.ndarray:
     c10::Float8_e4m3fn that Tensor.to(torch.float8_e4m3fn) performs
     (call site: kernels/pytorch/quant_fp8.py:33)."""
     f = np.ascontiguousarray(v, dtype=np.float32)
-    bits = f.view(np.uint32).astype(np.uint64)
-    sign = (bits >> 24) & 0x80
-    mag = bits & 0x7FFFFFFF
-    out = np.empty(f.shape, dtype=np.uint64)
-    over = mag >= (1087 << 20)                  # >= 480.0, inf, NaN
-    small = mag < (121 << 23)                   # < 2^-6: lands in the e4m3 subnormals
-    normal = ~(over | small)
-    out[over] = 0x7F
-    if small.any():
-        # adding 2^14 * 2^... magic: let the fp32 adder do the RNE at the subnormal spacing 2^-9
-        magic = np.float32(2.0 ** (141 - 127))
-        fm = mag[small].astype(np.uint32).view(np.float32)
-        with np.errstate(over="ignore"):
-            summed = (fm + magic).astype(np.float32)
-        out[small] = summed.view(np.uint32).astype(np.uint64) - (141 << 23)
-    if normal.any():
-        m = mag[normal]
-        odd = (m >> 20) & 1
-        m = m + (((7 - 127) << 23) & 0xFFFFFFFF) + 0x7FFFF + odd
-        m &= 0xFFFFFFFF
-        out[normal] = m >> 20
-    return ((out & 0xFF) | sign).astype(np.uint8)
+    flat = f.reshape(-1)
+    out = np.empty(flat.shape, dtype=np.uint8)
+    magic = np.float32(2.0 ** (141 - 127))
+    step = 1 << 22                               # chunks keep the temporaries inside the cache
+    for lo in range(0, flat.size, step):
+        bits = flat[lo : lo + step].view(np.uint32)
+        sign = ((bits >> np.uint32(24)) & np.uint32(0x80)).astype(np.uint8)
+        mag = bits & np.uint32(0x7FFFFFFF)
+        # normal range: re-bias the exponent, add half an e4m3 ulp (+1 when the kept bit is odd:
+        # round to nearest even) and drop the 20 low mantissa bits; uint32 arithmetic wraps
+        odd = (mag >> np.uint32(20)) & np.uint32(1)
+        m_norm = (mag + np.uint32(((7 - 127) << 23) & 0xFFFFFFFF) + np.uint32(0x7FFFF) + odd) >> np.uint32(20)
+        # below 2^-6 the value lands in the e4m3 subnormals: adding 2^14 lets the fp32 adder do
+        # the round-to-nearest-even at the subnormal spacing 2^-9
+        small = mag < np.uint32(121 << 23)
+        fm = np.where(small, mag, np.uint32(0)).view(np.float32)
+        m_small = (fm + magic).astype(np.float32).view(np.uint32) - np.uint32(141 << 23)
+        over = mag >= np.uint32(1087 << 20)      # >= 480.0, inf, NaN
+        code = np.where(over, np.uint32(0x7F), np.where(small, m_small, m_norm))
+        out[lo : lo + step] = (code & np.uint32(0xFF)).astype(np.uint8) | sign
+    return out.reshape(f.shape)
 
 
-def e4m3fn_to_fp32(b: np.ndarray) -> np.ndarray:
-    """float8_e4m3fn bytes -> float32 (exact)."""
-    b = np.asarray(b, dtype=np.uint8).astype(np.int32)
+def _e4m3fn_table() -> np.ndarray:
+    b = np.arange(256, dtype=np.int32)
     sign = np.where(b & 0x80, -1.0, 1.0).astype(np.float32)
     exp = (b >> 3) & 0xF
     man = b & 0x7
     val = np.where(exp == 0, man * 2.0**-9, (1.0 + man / 8.0) * np.exp2(exp.astype(np.float32) - 7.0))
     val = np.where((exp == 15) & (man == 7), np.nan, val)
     return (sign * val).astype(np.float32)
+
+
+_E4M3FN_TABLE = _e4m3fn_table()
+
+
+def e4m3fn_to_fp32(b: np.ndarray) -> np.ndarray:
+    """float8_e4m3fn bytes -> float32 (exact): sign, 4 exponent bits (bias 7), 3 mantissa bits,
+    subnormals at exponent 0, 0x7F / 0xFF = NaN, no infinities. Table of the 256 codes."""
+    return _E4M3FN_TABLE[np.asarray(b, dtype=np.uint8)]
 
 
 def calculate_scale(a_max: torch.Tensor) -> torch.Tensor:
@@ -315,6 +322,41 @@ def index_select_jagged_bmm_fp8(offsets, index, jagged, weight, bias) -> torch.T
         o = (acc / (sp[:, None] * ws[e][None, :])).to(out_dtype)
         outs.append(o + (bias[e] if bias is not None else 0))
     return torch.cat(outs, dim=0)
+
+
+def silu_jagged_bmm_fp8(offsets, jagged, weight, bias, has_silu: bool = True) -> torch.Tensor:
+    """FP8 down projection, [silu](jagged) @ weight[e] + bias[e] with e4m3 operands; weight is
+    logical [E, K, N]. PARITY UNPINNED in the reference: the PYTORCH branch of silu_jagged_bmm_fp8
+    (kernels/moe_fp8.py:98-124 -> kernels/pytorch/moe_fp8.py:46-75) quantises its operands, throws
+    the result away and returns the unquantised product, and no reference test calls the
+    operator. This restatement is therefore assembled from the pinned pieces, in the shape of the
+    one FP8 GEMM the reference does define (pytorch_index_select_jagged_bmm_fp8,
+    kernels/pytorch/moe_fp8.py:98-139): activations quantised per row after SiLU
+    (pytorch_silu_jagged_fp8, :17-33, or the plain rowwise rule without SiLU), weight quantised
+    per (expert, output column) over K, bf16 matmul of the e4m3 values, division by the scale
+    product, cast to the activation type, bias added afterwards."""
+    out_dtype = jagged.dtype
+    xq, xs = silu_jagged_fp8(jagged) if has_silu else rowwise_quant_fp8(jagged)
+    wq, ws = rowwise_quant_fp8(weight.permute(0, 2, 1))      # [E, N, K], [E, N]
+    xv = torch.from_numpy(e4m3fn_to_fp32(xq.numpy())).to(torch.bfloat16)
+    wv = torch.from_numpy(e4m3fn_to_fp32(wq.numpy())).to(torch.bfloat16)
+    seg = _segments(offsets)
+    outs = []
+    for e, (xp, sp) in enumerate(zip(xv.split(seg), xs.split(seg))):
+        acc = torch.matmul(xp, wv[e].T)
+        o = (acc / (sp[:, None] * ws[e][None, :])).to(out_dtype)
+        outs.append(o + (bias[e] if bias is not None else 0))
+    return torch.cat(outs, dim=0)
+
+
+def silu_jagged_bmm_combine_fp8(offsets, jagged, weight, bias, index, k, gating_scores=None, gates_index=None,
+                                has_silu: bool = True) -> torch.Tensor:
+    """silu_jagged_bmm_fp8 followed by the gate-weighted merge (pytorch_mul_merge_k_add,
+    kernels/pytorch/moe.py:14-37): the quantised meaning of silu_jagged_bmm_combine_fp8
+    (kernels/moe_fp8.py:127-182). PARITY UNPINNED in the reference for the same reason as
+    silu_jagged_bmm_fp8: its PYTORCH branch falls back to the unquantised operator."""
+    y = silu_jagged_bmm_fp8(offsets, jagged, weight, bias, has_silu)
+    return mul_merge_k_add(index, y, k, gating_scores, gates_index)
 
 
 def _fp8_linear(x: torch.Tensor, w_rows: torch.Tensor) -> torch.Tensor:

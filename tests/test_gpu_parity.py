@@ -315,6 +315,54 @@ def test_fp8_up_projection_against_golden(name):
     clean_status()
 
 
+@pytest.mark.parametrize("L,E,k,K,N,dt,bias,has_silu", [
+    (300, 4, 2, 256, 192, torch.bfloat16, True, True),
+    (64, 8, 1, 128, 64, torch.bfloat16, False, True),
+    (500, 8, 4, 512, 320, torch.bfloat16, True, False),
+    (200, 16, 2, 64, 128, torch.float32, True, True),
+])
+def test_fp8_down_projection_operators_against_oracle(L, E, k, K, N, dt, bias, has_silu):
+    """moe_fp8.silu_jagged_bmm_fp8 and silu_jagged_bmm_combine_fp8 (kernels/moe_fp8.py:98-182)
+    against the oracle's "quantise -> e4m3 product -> descale (-> combine)" chain built from the
+    reference's quantisation rule and its one defined FP8 GEMM. The reference itself leaves these
+    two operators unpinned (its PYTORCH branch returns the unquantised product and no test calls
+    them), so the bars are the ones its FP8 up-projection test uses: rtol / atol 1e-2 against the
+    emulation (kernels/tests/moe_fp8_test.py:337-370), and no further from the unquantised
+    product than the emulation itself is."""
+    g = torch.Generator().manual_seed(L + 31 * k + N)
+    idx = torch.randn(L, E, generator=g).topk(k, dim=1).indices
+    meta = fm.route_metadata(cu(idx), E)
+    hid = (torch.rand(L * k, K, generator=g) * 2 - 1).to(dt)            # U(-1, 1), as the reference's tests
+    w = ((torch.rand(E, K, N, generator=g) * 2 - 1) * 0.2).to(dt)       # logical [E, K, N], plain contiguous
+    b = ((torch.rand(E, N, generator=g) * 2 - 1) * 0.1).to(dt) if bias else None
+    score = torch.rand(L, k, generator=g).to(dt)
+    off = meta.offsets.cpu()
+    if has_silu:
+        rows = moe_fp8.silu_jagged_bmm_fp8(meta.offsets, 0, cu(hid), cu(w), cu(b))
+        want_rows = O.silu_jagged_bmm_fp8(off, hid, w, b, has_silu=True)
+        raw = O.silu_jagged_bmm(off, hid.float(), w.float(), None if b is None else b.float(), has_silu=True)
+        assert rows.dtype == dt and rows.shape == (L * k, N)
+        scale = max(1.0, raw.abs().max().item())
+        torch.testing.assert_close(rows.float().cpu(), want_rows.float(), rtol=1e-2, atol=1e-2 * scale)
+        err = (rows.float().cpu() - raw).abs().amax(dim=1) / raw.abs().amax(dim=1).clamp_min(1e-6)
+        err_emu = (want_rows.float() - raw).abs().amax(dim=1) / raw.abs().amax(dim=1).clamp_min(1e-6)
+        assert err.max().item() <= err_emu.max().item() * 1.1 + 1e-2
+    got = moe_fp8.silu_jagged_bmm_combine_fp8(0, meta.offsets, cu(hid), cu(w), cu(b), meta.token_index,
+                                              meta.reverse_index, gating_scores=cu(score),
+                                              gates_index=meta.gate_index, has_silu=has_silu)
+    want = O.silu_jagged_bmm_combine_fp8(off, hid, w, b, meta.token_index.cpu(), k, score, meta.gate_index.cpu(),
+                                         has_silu=has_silu)
+    unq = O.silu_jagged_bmm_combine(off, hid.float(), w.float(), None if b is None else b.float(),
+                                    meta.token_index.cpu(), k, score.float(), meta.gate_index.cpu(), has_silu=has_silu)
+    assert got.dtype == dt and got.shape == (L, N)
+    scale = max(1.0, unq.abs().max().item())
+    torch.testing.assert_close(got.float().cpu(), want.float(), rtol=1e-2, atol=1e-2 * scale)
+    # within the 6e-2 relative bound of one quantised GEMM against the unquantised operator
+    rel = (got.float().cpu() - unq).norm(dim=1) / unq.norm(dim=1).clamp_min(1e-6)
+    assert rel.quantile(0.99).item() < 6e-2, rel.quantile(0.99).item()
+    clean_status()
+
+
 # ------------------------------------------------------------------------------- layers
 def _near_tie_mask(g):
     E = g["gate_w"].shape[0]

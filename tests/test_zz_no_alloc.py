@@ -42,7 +42,10 @@ def _route(entry, idx, E, with_workspace):
 def test_static_scratch_routing_equals_workspace_routing_twice():
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(11)
-    cases = [(3000, 64, 8), (777, 8, 2)]          # second call reuses the table the first one filled
+    # every call reuses the table the previous one filled; the third case (157 blocks x 256 experts
+    # = 40192 entries) is past the size the single-launch placement handles and takes the
+    # count -> scan -> place path on the built-in table
+    cases = [(3000, 64, 8), (777, 8, 2), (40000, 256, 2), (1000, 16, 4)]
     for L, E, k in cases:
         idx = torch.randn(L, E, generator=g).topk(k, dim=1).indices.to(DEV)
         rc_ref, ref = _route("fmoe_route_metadata", idx, E, True)
