@@ -681,6 +681,8 @@ def main():
     ap.add_argument("--no-sub-records", action="store_true", help="N = 1: skip the c3 / c4 sub-records")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison (profiling runs)")
     ap.add_argument("--no-sustained", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: rows through peer-mapped buffers (default) or NCCL all-to-all")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--routing-sweep", action="store_true",
                     help="only time the routing operators and the HBM-bound kernels alone (one JSON line)")
@@ -734,7 +736,8 @@ def main():
         from fast_moe_b200.modules.expert_parallel import ExpertParallelSwiGLUMoE
 
         torch.manual_seed(0)
-        layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device)
+        layer = ExpertParallelSwiGLUMoE(c["d"], c["h"], c["o"], c["E"], dtype=torch.bfloat16, device=device,
+                                        exchange=args.exchange, max_tokens_per_rank=c["tokens"])
     else:
         layer = build_layer(c, device)
 

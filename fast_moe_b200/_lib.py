@@ -86,6 +86,11 @@ SIGNATURES = {
         [P, I64, P, c_int, I64, P, P, P, I64, I64, I64, I64, P, I64, P, c_int, P, I64, c_int, c_int, c_int, c_int,
          c_int, P, P, c_int, I64, c_int, P],
     ),
+    "fmoe_ep_plan": (c_int, [P, c_int, c_int, c_int, I64, P, P, P]),
+    "fmoe_ep_dispatch": (c_int, [P, c_int, I64, I64, c_int, P, P, I64, c_int, c_int, c_int, P, P, P, I64, I64, P]),
+    "fmoe_ep_up_projection": (c_int, [P, I64, I64, P, c_int, I64, P, P, I64, I64, c_int, c_int, c_int, P, I64, P]),
+    "fmoe_ep_down_projection": (c_int, [P, I64, I64, P, c_int, I64, P, I64, I64, c_int, c_int, c_int, P, P, c_int, I64,
+                                        I64, P]),
     "fmoe_rowwise_quant_fp8": (c_int, [P, c_int, I64, c_int, I64, c_int, c_int, P, I64, P, P]),
     "fmoe_bmm_weight_quant_fp8": (c_int, [P, c_int, c_int, c_int, c_int, P, P, P]),
 }

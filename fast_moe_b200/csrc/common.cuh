@@ -72,6 +72,16 @@ struct GemmDesc {
   int64_t bscale_se;
   int epilogue;              // FMOE_EPI_*
   const int64_t* out_index;  // device [total_rows] or null: row r is stored at out[out_index[r]]
+  // Stores into several output buffers (the expert-parallel return path): when out_peers is
+  // non-null it is a DEVICE array of n_peers base addresses (buffers of peer_rows rows each, 16-byte
+  // aligned, possibly in another GPU's memory, written with plain stores) and out_index[r] is
+  // (peer << 40) | row.
+  const int64_t* out_peers;
+  int n_peers;
+  int64_t peer_rows;
+  // total_rows may be a capacity rather than a row count; rows_hint (> 0) then tells the tile-shape
+  // heuristic how many rows to expect
+  int64_t rows_hint;
   // fused combine (all null/0 when unused): row r is multiplied by gate[gate_index[r]] and added
   // to out[gate_index[r] / gate_div]; out has combine_rows rows and must start at zero
   const void* gate;

@@ -67,6 +67,8 @@ struct GemmParams {
   const long long* offsets;
   const long long* index;
   const long long* out_index;
+  const long long* out_peers;   // device array of output base addresses, or null (see GemmDesc)
+  int n_peers;
   int index_div;
   int E, N, K;
   int num_kb;
@@ -475,15 +477,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (p.gate_round && sizeof(OutT) == 2) gate_scale = __bfloat162float(__float2bfloat16_rn(gate_scale));
         }
       }
+      OutT* out_base = reinterpret_cast<OutT*>(p.out);
       if (p.out_index != nullptr && row_ok && !combine) {
         dst_row = p.out_index[row];
+        if (p.out_peers != nullptr) {
+          // (peer << 40) | row: the row goes to that peer's buffer (plain stores, possibly over NVLink)
+          const long long peer = dst_row >> 40;
+          dst_row &= (1ll << 40) - 1;
+          if (peer < 0 || peer >= p.n_peers) {
+            dst_row = -1;
+          } else {
+            out_base = reinterpret_cast<OutT*>(p.out_peers[peer]);
+          }
+        }
         if (dst_row < 0 || dst_row >= p.out_rows) {
           atomicCAS(p.status, 0, FMOE_DEV_BAD_INDEX);
-          dst_row = row;
+          dst_row = 0;
           store_ok = false;
         }
       }
-      OutT* out_row = reinterpret_cast<OutT*>(p.out) + dst_row * p.ldo;
+      OutT* out_row = out_base + dst_row * p.ldo;
       // Coalesced store phase: lane l writes the 16-byte piece (l & 3) of rows (l >> 2) + 8 i.
       // It needs those rows' destinations, which live in the lanes that own them.
       OutT* st_row[4];
@@ -964,6 +977,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
     return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: gathered rows need K to be a multiple of 16 bytes (K=%d x %d B); pad K",
                 d.K, esize);
   }
+  FMOE_REQUIRE(d.out_peers == nullptr || (d.out_index != nullptr && d.gate_index == nullptr && d.n_peers >= 1),
+               "grouped_gemm: peer stores need a route table and exclude the fused combine");
   if (d.gate_index != nullptr && (d.index != nullptr || d.epilogue != FMOE_EPI_NONE)) {
     return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: the fused combine needs contiguous rows and the plain epilogue");
   }
@@ -989,7 +1004,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   // slower). Gathered rows stay on lone CTAs: a pair needs a relay hop for the peer's gathered
   // rows and runs at half speed. FMOE_GEMM_CTAS forces either.
   int ctas = forced_ctas();
-  if (ctas == 0) ctas = (!gather && d.total_rows / d.E >= 1024) ? 2 : 1;
+  const long long expect_rows = d.rows_hint > 0 ? d.rows_hint : d.total_rows;
+  if (ctas == 0) ctas = (!gather && expect_rows / d.E >= 1024) ? 2 : 1;
   if (g_num_sms < 2) ctas = 1;
   const int box_n = (ctas == 2 || dual) ? 128 : 256;   // weight rows one TMA load brings in
   const int k_elems = kRowBytes / esize;
@@ -1020,7 +1036,9 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.offsets = reinterpret_cast<const long long*>(d.offsets);
   p.index = reinterpret_cast<const long long*>(d.index);
   p.out_index = reinterpret_cast<const long long*>(d.out_index);
-  p.out_rows = d.gate_index ? d.combine_rows : d.total_rows;
+  p.out_rows = d.gate_index ? d.combine_rows : (d.out_peers ? d.peer_rows : d.total_rows);
+  p.out_peers = reinterpret_cast<const long long*>(d.out_peers);
+  p.n_peers = d.n_peers;
   p.index_div = d.index_div > 0 ? d.index_div : 1;
   p.E = d.E;
   p.N = d.N;
@@ -1046,7 +1064,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.gate_index = reinterpret_cast<const long long*>(d.gate_index);
   p.gate_div = d.gate_div > 0 ? d.gate_div : 1;
   const int osize = dtype_size(d.out_dtype);
-  p.vec_ok = ((d.ldo * osize) % 16 == 0) && ((reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
+  // peer buffers are 16-byte aligned by contract (their addresses live on the device)
+  p.vec_ok = ((d.ldo * osize) % 16 == 0) && (d.out_peers != nullptr || (reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
   p.status = status;
 
   // Persistent grid: one CTA per SM, never more CTAs than the largest possible tile count.

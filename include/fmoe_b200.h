@@ -246,6 +246,48 @@ int fmoe_gather_rows(const void* src, int dtype, int64_t src_rows, int64_t lds, 
                      int index_div, int64_t rows, int cols, void* dst, int64_t ldd, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Expert parallelism over peer memory (one process per GPU, experts split in contiguous blocks of
+ * E / world over the ranks, tokens stay on their rank). The reference names an expert-parallel
+ * layer in its README (README.md:100-113, :162) but ships no such file, so these four entry points
+ * have no reference interface to cite; the contract is that the sharded layer equals the
+ * single-GPU one. Peer buffers (receive rows, route table, return rows) are allocated and mapped
+ * by the caller (e.g. torch symmetric memory); the library only needs their addresses, passed as
+ * DEVICE arrays of `world` int64 pointers. Kernels touch peer memory with plain loads and stores
+ * only. The caller orders the steps across ranks (a collective on the same stream after
+ * fmoe_ep_dispatch and after fmoe_ep_down_projection).
+ *
+ * fmoe_ep_plan: counts [world, E] int64, counts[s, e] = rows rank s routes to global expert e
+ *   (every rank's `lengths`, all-gathered). Outputs, for the calling rank:
+ *   dst_base [E]: row of the owner's receive buffer where this rank's rows for expert e start.
+ *   The receive buffer is expert-major: (local expert, source rank, source's row order).
+ *   offsets_local [E/world + 1]: jagged offsets of the local experts over the rows received.
+ *   A total beyond `capacity` rows sets FMOE_DEV_BAD_INDEX in the device status word.
+ * fmoe_ep_dispatch: one row per entry of this rank's expert-sorted order (offsets [E+1],
+ *   token_index [rows], as fmoe_route_metadata produced them): row p of expert e is copied from
+ *   x[token_index[p]] to recv_ptrs[e / (E/world)] + (dst_base[e] + p - offsets[e]) * ld_recv, and
+ *   route_ptrs[owner][that row] = (rank << 40) | p, the row's return address.
+ * fmoe_ep_up_projection: the SwiGLU up projection (fmoe_index_select_jagged_bmm_swiglu without an
+ *   index) on the receive buffer; `capacity` bounds the rows, offsets_local[E_local] is their
+ *   number, rows_hint (> 0) the expected number (chooses the tile shape).
+ *   weight / weight_p: [E_local, N, K] storage, K contiguous, strides (w_se, w_sn) in elements.
+ * fmoe_ep_down_projection: the down projection whose epilogue stores result row r at its return
+ *   address: back_ptrs[route[r] >> 40] + (route[r] & (2^40 - 1)) * ld_back. back_rows = rows of
+ *   each return buffer (addresses beyond it are recorded in the status word and skipped). */
+int fmoe_ep_plan(const int64_t* counts, int world, int E, int rank, int64_t capacity, int64_t* dst_base,
+                 int64_t* offsets_local, void* stream);
+int fmoe_ep_dispatch(const void* x, int dtype, int64_t x_rows, int64_t ldx, int cols, const int64_t* offsets,
+                     const int64_t* token_index, int64_t rows, int E, int world, int rank, const int64_t* dst_base,
+                     const int64_t* recv_ptrs, const int64_t* route_ptrs, int64_t ld_recv, int64_t capacity,
+                     void* stream);
+int fmoe_ep_up_projection(const int64_t* offsets_local, int64_t capacity, int64_t rows_hint, const void* recv,
+                          int dtype, int64_t ld_recv, const void* weight, const void* weight_p, int64_t w_se,
+                          int64_t w_sn, int E_local, int K, int N, void* out, int64_t ldo, void* stream);
+int fmoe_ep_down_projection(const int64_t* offsets_local, int64_t capacity, int64_t rows_hint, const void* hidden,
+                            int dtype, int64_t ldh, const void* weight, int64_t w_se, int64_t w_sn, int E_local,
+                            int K, int N, const int64_t* route, const int64_t* back_ptrs, int world,
+                            int64_t back_rows, int64_t ld_back, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * FP8 rowwise quantisation.
  * pytorch_rowwise_quant_fp8 + calculate_scale (kernels/pytorch/quant_fp8.py:13-34), and with
  * apply_silu != 0 pytorch_silu_jagged_fp8 (kernels/pytorch/moe_fp8.py:17-33):

@@ -16,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, exchange="peer"):
     import torch.distributed as dist
 
     from fast_moe_b200 import _lib
@@ -25,14 +25,16 @@ def _worker(rank, world, port, q):
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"        # no NVLink multicast objects in a test whose ranks come and go
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         E, k, d, h, o, L = 8, 2, 128, 256, 128, 300 + 17 * rank
-        layer = ExpertParallelSwiGLUMoE(d, h, o, E, dtype=torch.bfloat16, device=dev, seed=5)
+        layer = ExpertParallelSwiGLUMoE(d, h, o, E, dtype=torch.bfloat16, device=dev, seed=5, exchange=exchange)
         x = torch.randn(1, L, d, generator=torch.Generator().manual_seed(50 + rank)).bfloat16()
-        y = layer(x.to(dev), k)
+        for _ in range(3):                      # later passes reuse the peer buffers of the earlier ones
+            y = layer(x.to(dev), k)
         torch.cuda.synchronize()
         status = _lib.device_status(dev)
         # full weight set on every rank (test-side collective), then the CPU oracle
@@ -52,14 +54,18 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_matches_oracle_on_every_rank():
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_expert_parallel_matches_oracle_on_every_rank(exchange):
+    """Ranks hold different numbers of tokens (300 + 17 * rank). ``peer``: rows and results move
+    through peer-mapped buffers, no host synchronisation inside the forward; ``nccl``:
+    all_to_all_single both ways."""
     import torch.multiprocessing as mp
 
     world = min(torch.cuda.device_count(), 4)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     res = sorted(q.get(timeout=300) for _ in range(world))

@@ -82,10 +82,10 @@ def _bench():
     return bench
 
 
-def _assert_parity(par):
+def _assert_parity(par, score_tol=1e-5):
     assert par["routing"]["mismatched"] == 0, par["routing"]
     assert par["routing"]["metadata_bit_exact"], par["routing"]
-    assert par["routing"]["max_score_diff"] < 1e-5, par["routing"]
+    assert par["routing"]["max_score_diff"] < score_tol, par["routing"]
     assert par["sample"]["tokens"] >= 16, par["sample"]
     assert par["outputs"]["tokens_out_of_tolerance"] == 0, par["outputs"]
     assert par["ok"], par
@@ -164,7 +164,10 @@ def test_c3_true_size_fp8_layer_with_outlier_rows():
     assert y.dtype == torch.bfloat16
     assert _lib.device_status(torch.device(DEV)) == 0
     par = B.parity_block(layer, c, x, y, B.layer_expert_weights(layer), layer.gate.gate, n_sample=96, max_experts=3)
-    _assert_parity(par)
+    # the outlier rows carry logits 50 times larger than the rest, and an fp32 sum of 4096 products
+    # taken in another order differs by about 1e-6 of the logit's size: the scores of those rows
+    # agree to 1e-4 rather than 1e-5 (the expert choice itself is compared exactly)
+    _assert_parity(par, score_tol=2e-4)
     assert par["outputs"]["rel_err_vs_fp32_median"] < 2 * 6e-2, par["outputs"]
     assert par["outputs"]["rel_err_vs_fp32_median"] <= par["outputs"]["fp8_oracle_rel_err_vs_fp32_median"] * 1.1 + 1e-3
 
