@@ -9,7 +9,9 @@ from .kernels.moe import (
     index_select_jagged_bmm_swiglu,
     index_select_jagged_bmm_3D,
     index_select_jagged_gating_bmm,
+    fp32_uses_tf32,
     mul_merge_k_add,
+    set_fp32_matmul,
     silu_jagged_bmm,
     silu_jagged_bmm_combine,
 )
@@ -34,6 +36,8 @@ __all__ = [
     "mul_merge_k_add",
     "silu_jagged_bmm",
     "silu_jagged_bmm_combine",
+    "set_fp32_matmul",
+    "fp32_uses_tf32",
     "gate_topk",
     "route_metadata",
     "RoutingMetadata",

@@ -53,6 +53,11 @@ SIGNATURES = {
     "fmoe_kernel_launch_count": (c_longlong, []),
     "fmoe_selftest_bounded_wait": (c_int, [I64, P]),
     "fmoe_gate_topk": (c_int, [P, c_int, I64, P, P, P, I64, c_int, I64, c_int, c_int, c_int, P, P, P, P]),
+    "fmoe_gate_topk_counts_supported": (c_int, [P, c_int, I64, P, I64, c_int, c_int]),
+    "fmoe_route_group_counts_bytes": (c_size_t, [I64, c_int]),
+    "fmoe_gate_topk_counts": (c_int, [P, c_int, I64, P, P, I64, c_int, c_int, c_int, P, P, P, P, P]),
+    "fmoe_route_metadata_gather": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P, P, c_int, I64, c_int, P, I64, P,
+                                           c_int, I64, c_int, P]),
     "fmoe_route_workspace_bytes": (c_size_t, [I64, c_int, c_int]),
     "fmoe_route_metadata": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P, c_size_t, P]),
     "fmoe_route_metadata_static": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P]),
@@ -74,6 +79,7 @@ SIGNATURES = {
         [P, I64, P, c_int, I64, P, P, P, I64, I64, I64, I64, P, I64, c_int, c_int, c_int, c_int, P, P, P, P, c_int,
          I64, P],
     ),
+    "fmoe_split_f32_bf16x3": (c_int, [P, I64, c_int, I64, c_int, c_int, c_int, P, I64, P]),
     "fmoe_gather_rows": (c_int, [P, c_int, I64, I64, P, c_int, I64, c_int, P, I64, P]),
     "fmoe_mul_merge_k_add": (c_int, [P, P, c_int, I64, P, c_int, P, I64, c_int, c_int, P, c_int, I64, P]),
     "fmoe_silu_jagged_bmm_combine": (

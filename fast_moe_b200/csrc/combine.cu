@@ -240,6 +240,39 @@ silu_kernel(const T* __restrict__ in, long long ldi, T* __restrict__ out, long l
   }
 }
 
+// fp32 -> three bf16 terms, hi + mid + lo = x to about 2^-24 relative (hi = bf16(x), mid =
+// bf16(x - hi), lo = bf16(x - hi - mid); the subtractions are exact in fp32). The six partial
+// products a_i * b_j with i + j <= 2 reproduce a * b to fp32 accuracy, and each of them is exact
+// in the tensor core's fp32 accumulator, so an fp32 product can run as ONE bf16 GEMM over a
+// reduction dimension six times as long: the left operand's row is laid out as
+// [hi | hi | mid | hi | lo | mid] (pattern 0), the right operand's as [hi | mid | hi | lo | hi | mid]
+// (pattern 1). This is the path fp32 callers get when TF32 is not allowed, which is the
+// default of torch.backends.cuda.matmul.allow_tf32 that the reference's kernels follow
+// (kernels/triton/triton_moe.py:592).
+__global__ void __launch_bounds__(256)
+split_bf16x3_kernel(const float* __restrict__ in, long long ldi, long long rows, int cols, int cols_out, int pattern,
+                    int apply_silu, __nv_bfloat16* __restrict__ out, long long ldo) {
+  const long long total = rows * cols_out;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols_out;
+    const int c = static_cast<int>(i - r * cols_out);
+    float x = c < cols ? in[r * ldi + c] : 0.f;          // columns beyond `cols` are zero padding
+    if (apply_silu) x = x / (1.0f + expf(-x));
+    const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    __nv_bfloat16* o = out + r * ldo + c;
+    const long long s = cols_out;
+    if (pattern == 0) {
+      o[0] = hi; o[s] = hi; o[2 * s] = mid; o[3 * s] = hi; o[4 * s] = lo; o[5 * s] = mid;
+    } else {
+      o[0] = hi; o[s] = mid; o[2 * s] = hi; o[3 * s] = lo; o[4 * s] = hi; o[5 * s] = mid;
+    }
+  }
+}
+
 // dst[r, :] = src[index[r] / div, :] in 16-byte pieces (or bytes when rows are not 16-byte
 // aligned). One warp-sized group of threads walks a row, so reads and writes are coalesced.
 template <typename V>
@@ -422,4 +455,22 @@ extern "C" int fmoe_mul_merge_k_add(const int64_t* reverse_index, const void* va
   if (v_dtype == FMOE_F32 && wf32)
     return launch_combine<float, float, float>(rev, value, ldv, weight, widx, L, k, D, out, ldo, status, st);
   return launch_combine<float, __nv_bfloat16, float>(rev, value, ldv, weight, widx, L, k, D, out, ldo, status, st);
+}
+
+extern "C" int fmoe_split_f32_bf16x3(const float* in, int64_t rows, int cols, int64_t ldi, int cols_padded, int pattern,
+                                     int apply_silu, void* out, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(rows >= 0 && cols >= 1 && cols_padded >= cols, "split_f32_bf16x3: rows=%lld cols=%d cols_padded=%d",
+               (long long)rows, cols, cols_padded);
+  FMOE_REQUIRE(pattern == 0 || pattern == 1, "split_f32_bf16x3: pattern must be 0 (left operand) or 1 (right operand)");
+  FMOE_REQUIRE(ldo >= 6ll * cols_padded, "split_f32_bf16x3: output rows need 6 * cols_padded = %lld elements",
+               6ll * cols_padded);
+  if (rows == 0) return FMOE_OK;
+  FMOE_REQUIRE(in && out, "split_f32_bf16x3: NULL pointer argument");
+  long long blocks = (rows * cols_padded + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  split_bf16x3_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      in, ldi, rows, cols, cols_padded, pattern, apply_silu, static_cast<__nv_bfloat16*>(out), ldo);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
 }

@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(kMmaGateWarps * 32, 2)
 gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const float* __restrict__ gw,
                      const float* __restrict__ gb, long long L, int d, int E, int k,
                      float* __restrict__ logits_out, long long* __restrict__ topk_idx,
-                     float* __restrict__ topk_score) {
+                     float* __restrict__ topk_score, int* __restrict__ group_counts) {
   constexpr int EP = 8 * NT;
   extern __shared__ __align__(16) uint8_t smem_gate[];
   const int row_bytes = d * 2 + kMmaGatePadBytes;
@@ -379,6 +379,7 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const f
   // one thread per token: softmax / top-k / renormalise
   if (threadIdx.x < kMmaGateTokens) {
     const long long t = tile_id * kMmaGateTokens + threadIdx.x;
+    unsigned picked = 0u;                      // bit e: this token chose expert e (E <= 32 here)
     if (t < L) {
       float* lg = s_part + threadIdx.x * (EP + 1);
       float* sel = s_part + (kMmaGateTokens + threadIdx.x) * (EP + 1);   // quarter 1's row: the chosen scores
@@ -411,9 +412,26 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const f
         topk_idx[t * k + s] = best_e;
         sel[s] = sc;
         lg[best_e] = -1.f;
+        if (best_e < E) picked |= 1u << best_e;
       }
       const float denom = fmaxf(norm, 1e-12f);
       for (int s = 0; s < k; ++s) topk_score[t * k + s] = sel[s] / denom;
+    }
+    if (group_counts != nullptr) {
+      // Rows per expert in each group of 16 tokens (the first stage of the counting sort, which
+      // then needs no pass of its own over the indices): the 32 finishing threads are one warp.
+      int c_lo = 0, c_hi = 0;
+      for (int e = 0; e < E; ++e) {
+        const unsigned b = __ballot_sync(0xffffffffu, (picked >> e) & 1u);
+        if (static_cast<int>(threadIdx.x) == e) {
+          c_lo = __popc(b & 0xffffu);
+          c_hi = __popc(b >> 16);
+        }
+      }
+      if (static_cast<int>(threadIdx.x) < E) {
+        group_counts[(2 * tile_id) * E + threadIdx.x] = c_lo;
+        group_counts[(2 * tile_id + 1) * E + threadIdx.x] = c_hi;
+      }
     }
   }
   __syncthreads();      // the partial sums are overwritten by the next tile
@@ -621,14 +639,226 @@ route_place_scan_kernel(const long long* __restrict__ topk_idx, long long L, int
   }
 }
 
+// Placement for small batches, fused with the two memory passes that follow it in the layers:
+// one block per group of 16 tokens. The per-group counts come from the gate kernel, so the
+// indices are read once. Every block reads the whole table of group counts (at most 32 k entries),
+// derives its own base and the offsets, places its rows, and then
+//   - copies each of its tokens' rows to the k expert-sorted positions it has just computed
+//     (the index_select of the up projection: x is read once, each row written k times), and
+//   - clears its tokens' rows of the buffer the down projection's epilogue accumulates into.
+// Same tensors, bit for bit, as route_count_kernel + route_place_scan_kernel followed by the row
+// gather kernel and a memset.
+constexpr int kGroupTokens = 16;
+
+__global__ void __launch_bounds__(256)
+route_place_gather_kernel(const long long* __restrict__ topk_idx, long long L, int E, int k, int ng,
+                          const int* __restrict__ group_counts, long long* __restrict__ lengths,
+                          long long* __restrict__ offsets, long long* __restrict__ max_len,
+                          long long* __restrict__ gate_index, long long* __restrict__ token_index,
+                          long long* __restrict__ reverse_index, const uint8_t* __restrict__ x, long long ldx_bytes,
+                          int row_bytes, uint8_t* __restrict__ x_sorted, long long lds_bytes,
+                          uint8_t* __restrict__ zero_rows, long long ldz_bytes, int zero_row_bytes, int* status) {
+  extern __shared__ int s_int[];
+  int* s_base = s_int;                         // [E] rows of expert e in earlier groups
+  int* s_off = s_base + E;                     // [E + 1] lengths, then offsets
+  unsigned* s_mask = reinterpret_cast<unsigned*>(s_off + E + 1);   // [E] which of the 16 tokens picked e
+  int* s_dst = reinterpret_cast<int*>(s_mask + E);                 // [16 * k] sorted position of (token, slot)
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    if (e < E) {
+      s_base[e] = 0;
+      s_mask[e] = 0u;
+    }
+    s_off[e] = 0;
+  }
+  for (int i = threadIdx.x; i < kGroupTokens * k; i += blockDim.x) s_dst[i] = -1;
+  __syncthreads();
+  const long long t0 = static_cast<long long>(blockIdx.x) * kGroupTokens;
+  if (threadIdx.x < kGroupTokens && t0 + threadIdx.x < L) {
+    const long long t = t0 + threadIdx.x;
+    for (int s = 0; s < k; ++s) {
+      const long long e = topk_idx[t * k + s];
+      if (e < 0 || e >= E) {
+        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+        continue;
+      }
+      atomicOr(&s_mask[static_cast<int>(e)], 1u << threadIdx.x);
+    }
+  }
+  const int entries = ng * E;
+  const int mine = static_cast<int>(blockIdx.x) * E;
+  if ((E & (E - 1)) == 0) {
+    // E a power of two (it divides the block size): a thread only ever meets one expert, keeps
+    // its two sums in registers, lanes of a warp that share the expert combine by shuffle, and
+    // one lane per (warp, expert) touches shared memory - instead of one contended shared-memory
+    // atomic per table entry.
+    const int e = threadIdx.x & (E - 1);
+    int all = 0, before = 0;
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+      const int c = group_counts[i];
+      all += c;
+      if (i < mine) before += c;
+    }
+    for (int o = E; o < 32; o <<= 1) {
+      all += __shfl_xor_sync(0xffffffffu, all, o);
+      before += __shfl_xor_sync(0xffffffffu, before, o);
+    }
+    if ((threadIdx.x & 31) < E) {
+      if (all != 0) atomicAdd(&s_off[e + 1], all);
+      if (before != 0) atomicAdd(&s_base[e], before);
+    }
+  } else {
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+      const int c = group_counts[i];
+      if (c != 0) {
+        const int e = i % E;
+        atomicAdd(&s_off[e + 1], c);
+        if (i < mine) atomicAdd(&s_base[e], c);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int carry = 0;
+    int mx = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int len = e < E ? s_off[e + 1] : 0;
+      if (blockIdx.x == 0 && e < E && lengths) lengths[e] = len;
+      mx = max(mx, len);
+      int v = len;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      if (e < E) s_off[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (blockIdx.x == 0 && lane == 0 && max_len) *max_len = mx;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = s_off[e];
+  }
+  if (threadIdx.x < kGroupTokens && t0 + threadIdx.x < L) {
+    const long long t = t0 + threadIdx.x;
+    const unsigned lt = (1u << threadIdx.x) - 1u;
+    for (int s = 0; s < k; ++s) {
+      const long long e64 = topk_idx[t * k + s];
+      if (e64 < 0 || e64 >= E) continue;
+      const int e = static_cast<int>(e64);
+      const long long pos = static_cast<long long>(s_off[e]) + s_base[e] + __popc(s_mask[e] & lt);
+      if (gate_index) gate_index[pos] = t * k + s;
+      if (token_index) token_index[pos] = t;
+      if (reverse_index) {
+        int j = 0;
+        for (int s2 = 0; s2 < k; ++s2) j += (topk_idx[t * k + s2] < e64) ? 1 : 0;
+        reverse_index[t * k + j] = pos;
+      }
+      s_dst[threadIdx.x * k + s] = static_cast<int>(pos);
+    }
+  }
+  if (x_sorted == nullptr && zero_rows == nullptr) return;
+  __syncthreads();
+  // memory passes: warp w serves tokens w and w + 8 of the group
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int tt = warp; tt < kGroupTokens; tt += 8) {
+    const long long t = t0 + tt;
+    if (t >= L) break;
+    if (x_sorted != nullptr) {
+      const uint4* a = reinterpret_cast<const uint4*>(x + t * ldx_bytes);
+      const int vec = row_bytes >> 4;
+      for (int c0 = lane; c0 < vec; c0 += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c0 + 32 * u < vec) v[u] = a[c0 + 32 * u];
+        for (int s = 0; s < k; ++s) {
+          const int pos = s_dst[tt * k + s];
+          if (pos < 0) continue;
+          uint4* d = reinterpret_cast<uint4*>(x_sorted + static_cast<long long>(pos) * lds_bytes);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (c0 + 32 * u < vec) d[c0 + 32 * u] = v[u];
+        }
+      }
+    }
+    if (zero_rows != nullptr) {
+      uint4* z = reinterpret_cast<uint4*>(zero_rows + t * ldz_bytes);
+      const int vec = zero_row_bytes >> 4;
+      for (int c = lane; c < vec; c += 32) z[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+constexpr long long kGroupTableMaxEntries = 32 * 1024;
+
 }  // namespace
 }  // namespace fmoe
 
 using namespace fmoe;
 
+namespace {
+int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
+                   const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E, int k,
+                   float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, void* stream);
+
+// Conditions under which the tensor-core gate kernel runs (and with it the per-group counts).
+bool gate_mma_path(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* logits_in, int d, int E,
+                   size_t* smem_out) {
+  if (logits_in != nullptr || x_dtype != FMOE_BF16 || E > 32 || d < 8 || d % 8 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (ldx * 2) % 16 != 0 || (reinterpret_cast<uintptr_t>(gate_w) & 15) != 0)
+    return false;
+  const int nt = E <= 8 ? 1 : (E <= 16 ? 2 : 4);
+  const size_t smem = 3 * static_cast<size_t>(8 * nt) * (static_cast<size_t>(d) * 2 + kMmaGatePadBytes) +
+                      4 * static_cast<size_t>(kMmaGateTokens) * (8 * nt + 1) * sizeof(float);
+  if (smem_out) *smem_out = smem;
+  return smem <= 200 * 1024;
+}
+}  // namespace
+
 extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                               const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E,
                               int k, float* logits_out, int64_t* topk_idx, float* topk_score, void* stream) {
+  return gate_topk_impl(x, x_dtype, ldx, gate_w, gate_b, logits_in, ld_logits, logits_split, L, d, E, k, logits_out,
+                        topk_idx, topk_score, nullptr, stream);
+}
+
+extern "C" size_t fmoe_route_group_counts_bytes(int64_t L, int E) {
+  if (L < 0 || E < 1) return 0;
+  const int64_t tiles = (L + kMmaGateTokens - 1) / kMmaGateTokens;
+  return static_cast<size_t>((tiles > 0 ? tiles : 1) * 2 * E) * sizeof(int);
+}
+
+extern "C" int fmoe_gate_topk_counts_supported(const void* x, int x_dtype, int64_t ldx, const float* gate_w, int64_t L,
+                                               int d, int E) {
+  if (L <= 0 || E < 1) return 0;
+  const int64_t tiles = (L + kMmaGateTokens - 1) / kMmaGateTokens;
+  if (tiles * 2 * E > kGroupTableMaxEntries) return 0;
+  return gate_mma_path(x, x_dtype, ldx, gate_w, nullptr, d, E, nullptr) ? 1 : 0;
+}
+
+extern "C" int fmoe_gate_topk_counts(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
+                                     const float* gate_b, int64_t L, int d, int E, int k, float* logits_out,
+                                     int64_t* topk_idx, float* topk_score, int* group_counts, void* stream) {
+  FMOE_REQUIRE(group_counts != nullptr, "gate_topk_counts: group_counts is NULL");
+  if (!fmoe_gate_topk_counts_supported(x, x_dtype, ldx, gate_w, L, d, E)) {
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "gate_topk_counts: needs bf16 tokens with 16-byte aligned rows, E <= 32, d a multiple of 8 and a "
+                "small batch (L=%lld, d=%d, E=%d); use fmoe_gate_topk + fmoe_route_metadata", (long long)L, d, E);
+  }
+  return gate_topk_impl(x, x_dtype, ldx, gate_w, gate_b, nullptr, 0, 0, L, d, E, k, logits_out, topk_idx, topk_score,
+                        group_counts, stream);
+}
+
+namespace {
+int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
+                   const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E,
+                   int k, float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, void* stream) {
   FMOE_REQUIRE(L >= 0 && E >= 1 && E <= kMaxGateExperts, "gate_topk: E=%d outside [1, %d]", E, kMaxGateExperts);
   FMOE_REQUIRE(k >= 1 && k <= E, "gate_topk: k=%d must be in [1, E=%d]", k, E);
   if (L == 0) return FMOE_OK;   // an empty batch is valid input (its tensors have NULL data pointers)
@@ -664,7 +894,7 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
     }                                                                                                              \
     kern<<<blocks, kMmaGateWarps * 32, smem, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, gate_w, gate_b, L, d, \
                                                    E, k, logits_out, reinterpret_cast<long long*>(topk_idx),      \
-                                                   topk_score);                                                    \
+                                                   topk_score, group_counts);                                      \
   } while (0)
       if (nt == 1) FMOE_GATE_MMA(1); else if (nt == 2) FMOE_GATE_MMA(2); else FMOE_GATE_MMA(4);
 #undef FMOE_GATE_MMA
@@ -672,6 +902,9 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
       ++g_misc_launches;
       return FMOE_OK;
     }
+  }
+  if (group_counts != nullptr) {
+    return fail(FMOE_ERR_UNSUPPORTED, "gate_topk_counts: the per-group counts come from the tensor-core gate kernel only");
   }
   // Gate weights in shared memory when they fit beside the logits scratch (and a few blocks per SM)
   const size_t w_bytes = logits_in ? 0 : static_cast<size_t>(E) * d * sizeof(float);
@@ -717,6 +950,8 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
   ++g_misc_launches;
   return FMOE_OK;
 }
+
+}  // namespace
 
 extern "C" size_t fmoe_route_workspace_bytes(int64_t L, int E, int k) {
   (void)k;
@@ -779,6 +1014,61 @@ extern "C" int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, in
     FMOE_CUDA_OK(cudaGetLastError());
     ++g_misc_launches;
   }
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_route_metadata_gather(const int64_t* topk_idx, int64_t L, int E, int k, const int* group_counts,
+                                          int64_t* lengths, int64_t* offsets, int64_t* gate_index,
+                                          int64_t* token_index, int64_t* reverse_index, int64_t* max_len,
+                                          const void* x, int x_dtype, int64_t ldx, int cols, void* x_sorted,
+                                          int64_t ld_sorted, void* zero_rows, int zero_dtype, int64_t ld_zero,
+                                          int zero_cols, void* stream) {
+  FMOE_REQUIRE(E >= 1 && E <= 32, "route_metadata_gather: E=%d outside [1, 32]", E);
+  FMOE_REQUIRE(k >= 1 && k <= E, "route_metadata_gather: k=%d must be in [1, E=%d]", k, E);
+  FMOE_REQUIRE(L >= 0 && L * k < (1ll << 31), "route_metadata_gather: L*k must be below 2^31");
+  FMOE_REQUIRE(offsets != nullptr, "route_metadata_gather: NULL offsets");
+  const int64_t ng = 2 * ((L + kMmaGateTokens - 1) / kMmaGateTokens);
+  FMOE_REQUIRE(ng * E <= kGroupTableMaxEntries,
+               "route_metadata_gather: table of %lld group counts exceeds %lld; use fmoe_route_metadata",
+               (long long)(ng * E), (long long)kGroupTableMaxEntries);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (L == 0) {
+    FMOE_CUDA_OK(cudaMemsetAsync(offsets, 0, (E + 1) * sizeof(int64_t), st));
+    if (lengths) FMOE_CUDA_OK(cudaMemsetAsync(lengths, 0, E * sizeof(int64_t), st));
+    if (max_len) FMOE_CUDA_OK(cudaMemsetAsync(max_len, 0, sizeof(int64_t), st));
+    return FMOE_OK;
+  }
+  FMOE_REQUIRE(topk_idx && group_counts, "route_metadata_gather: NULL topk_idx or group_counts");
+  int row_bytes = 0, zero_row_bytes = 0;
+  const int xs = dtype_size(x_dtype), zs = dtype_size(zero_dtype);
+  if (x_sorted != nullptr) {
+    FMOE_REQUIRE(x != nullptr && xs != 0 && cols >= 1, "route_metadata_gather: gather needs x, its dtype and cols");
+    row_bytes = cols * xs;
+    const bool ok = (row_bytes % 16 == 0) && ((ldx * xs) % 16 == 0) && ((ld_sorted * xs) % 16 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(x_sorted) & 15) == 0);
+    if (!ok) return fail(FMOE_ERR_UNSUPPORTED, "route_metadata_gather: rows must be 16-byte aligned multiples of 16 bytes");
+  }
+  if (zero_rows != nullptr) {
+    FMOE_REQUIRE(zs != 0 && zero_cols >= 1, "route_metadata_gather: zero fill needs a dtype and a column count");
+    zero_row_bytes = zero_cols * zs;
+    const bool ok = (zero_row_bytes % 16 == 0) && ((ld_zero * zs) % 16 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(zero_rows) & 15) == 0);
+    if (!ok) return fail(FMOE_ERR_UNSUPPORTED, "route_metadata_gather: cleared rows must be 16-byte aligned multiples of 16 bytes");
+  }
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  const size_t smem = (static_cast<size_t>(3 * E + 1) + static_cast<size_t>(kGroupTokens) * k) * sizeof(int);
+  const int64_t blocks = (L + kGroupTokens - 1) / kGroupTokens;
+  route_place_gather_kernel<<<static_cast<unsigned>(blocks), 256, smem, st>>>(
+      reinterpret_cast<const long long*>(topk_idx), L, E, k, static_cast<int>(ng), group_counts,
+      reinterpret_cast<long long*>(lengths), reinterpret_cast<long long*>(offsets), reinterpret_cast<long long*>(max_len),
+      reinterpret_cast<long long*>(gate_index), reinterpret_cast<long long*>(token_index),
+      reinterpret_cast<long long*>(reverse_index), static_cast<const uint8_t*>(x), ldx * xs, row_bytes,
+      static_cast<uint8_t*>(x_sorted), ld_sorted * xs, static_cast<uint8_t*>(zero_rows), ld_zero * zs, zero_row_bytes,
+      status);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
   return FMOE_OK;
 }
 

@@ -97,6 +97,60 @@ def _index_i64(t: torch.Tensor) -> torch.Tensor:
     return t if t.is_contiguous() else t.contiguous()
 
 
+# ---------------------------------------------------------------------------- fp32 operands
+# None: follow torch.backends.cuda.matmul.allow_tf32 at call time, as the reference's kernels do
+# (kernels/triton/triton_moe.py:592; the default is False). "tf32" / "fp32" force either.
+_FP32_MATMUL: Optional[str] = None
+
+
+def set_fp32_matmul(mode: Optional[str]) -> None:
+    """How float32 operands are multiplied: "tf32" (tensor cores round the operands to 10 mantissa
+    bits), "fp32" (operands expanded into three bf16 terms each, one bf16 GEMM over a six times
+    longer reduction: fp32 accuracy at about a third of the tf32 speed), or None to follow
+    ``torch.backends.cuda.matmul.allow_tf32``."""
+    global _FP32_MATMUL
+    if mode not in (None, "tf32", "fp32"):
+        raise ValueError("mode must be None, 'tf32' or 'fp32'")
+    _FP32_MATMUL = mode
+
+
+def fp32_uses_tf32() -> bool:
+    if _FP32_MATMUL is not None:
+        return _FP32_MATMUL == "tf32"
+    return bool(torch.backends.cuda.matmul.allow_tf32)
+
+
+def split_f32_rows(t: torch.Tensor, pattern: int, apply_silu: bool = False) -> torch.Tensor:
+    """[rows, K] float32 -> [rows, 6 * Kp] bfloat16 (Kp = K padded to 4): the three-term expansion
+    laid out for the left (pattern 0) or right (pattern 1) operand of the fp32-accurate product."""
+    dev = _lib.require_cuda(t)
+    lib = _lib.load()
+    assert t.ndim == 2 and t.dtype == torch.float32
+    src = t if t.stride(1) == 1 else t.contiguous()
+    rows, K = src.shape
+    kp = (K + 3) // 4 * 4
+    out = torch.empty((rows, 6 * kp), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.fmoe_split_f32_bf16x3(src.data_ptr(), rows, K, src.stride(0) if rows else K, kp, pattern,
+                                             1 if apply_silu else 0, out.data_ptr(), 6 * kp, _lib.stream_ptr(dev)))
+    return out
+
+
+def split_f32_weight(weight: torch.Tensor) -> torch.Tensor:
+    """Logical [E, K, N] float32 weight -> logical [E, 6 * Kp, N] bfloat16 weight whose reduction
+    dimension is contiguous (the right-operand expansion of every output column's K vector)."""
+    E, K, N = weight.shape
+    wt = weight.permute(0, 2, 1)                      # [E, N, K]
+    if not wt.is_contiguous():
+        wt = wt.contiguous()
+    w6 = split_f32_rows(wt.view(E * N, K), 1)
+    return w6.view(E, N, -1).permute(0, 2, 1)
+
+
+def _wants_fp32_split(*tensors: torch.Tensor) -> bool:
+    return all(t.dtype == torch.float32 for t in tensors) and not fp32_uses_tf32()
+
+
 # From this many output rows and columns on (both products of a gated GEMM counted), the rows are
 # gathered once by the copy kernel and the GEMM reads them as contiguous TMA tiles. The in-kernel
 # gather (16-byte cp.async by four warps) re-fetches a row tile for every column block and shares
@@ -122,39 +176,47 @@ def index_select_jagged_bmm(
     *,
     _epilogue: int = _lib.EPI_NONE,
     _rows_checked: bool = False,
+    _out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """out[r] = jagged[index.view(-1)[r] // A] @ weight[e] + bias[e] for the rows r of expert e.
 
     Same contract as the reference operator (kernels/moe.py:39-68): offsets [E+1], index [L, A],
     jagged [L, K], weight [E, K, N] (any strides), bias [E, N] or None -> [L*A, N].
     ``max_seq_len`` is accepted and not needed: the tile list is built on the device.
+    float32 operands are multiplied in fp32 accuracy unless TF32 is allowed (``set_fp32_matmul``).
+    ``index=None`` (not in the reference) means ``jagged`` already holds the expert-sorted rows.
     """
-    assert index.ndim == 2 and (_rows_checked or index.shape[0] == jagged.shape[0])
+    assert index is None or (index.ndim == 2 and (_rows_checked or index.shape[0] == jagged.shape[0]))
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype, f"{weight.dtype=} {jagged.dtype=}"
+    if _out_dtype is None and _wants_fp32_split(jagged, weight):
+        return index_select_jagged_bmm(max_seq_len, offsets, index, split_f32_rows(jagged, 0), split_f32_weight(weight),
+                                       bias, _epilogue=_epilogue, _rows_checked=_rows_checked,
+                                       _out_dtype=torch.float32)
+    od = _out_dtype or jagged.dtype
     dev = _lib.require_cuda(offsets, index, jagged, weight, bias)
     lib = _lib.load()
     L, K = jagged.shape
     E, Kw, N = weight.shape
     assert Kw == K, f"weight {tuple(weight.shape)} does not match jagged {tuple(jagged.shape)}"
-    rows = index.numel()
+    rows = index.numel() if index is not None else L
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
     w, w_se, w_sn = prep_weight(weight, kp)
-    b = _prep_bias(bias, jagged.dtype)
+    b = _prep_bias(bias, od)
     off = _index_i64(offsets)
-    idx = _index_i64(index)
-    div = index.shape[1]
-    if _gather_first(rows, N):
+    idx = None if index is None else _index_i64(index)
+    div = index.shape[1] if index is not None else 1
+    if idx is not None and _gather_first(rows, N):
         a, idx, div, L = gather_rows(a, idx, div), None, 1, rows
-    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    out = torch.empty((rows, N), dtype=od, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm(
                 off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
-                w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, _epilogue, out.data_ptr(), dt, out.stride(0),
-                _lib.stream_ptr(dev),
+                w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, _epilogue, out.data_ptr(), _lib.dtype_code(od),
+                out.stride(0), _lib.stream_ptr(dev),
             )
         )
     return out
@@ -196,6 +258,8 @@ def index_select_jagged_bmm_swiglu(
     weight_p: torch.Tensor,
     bias_p: Optional[torch.Tensor],
     kernel: KernelType = KernelType.PYTORCH,
+    *,
+    _out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """silu(x @ weight[e] + bias[e]) * (x @ weight_p[e] + bias_p[e]) on the gathered rows, one
     kernel, the activation row tile shared by both products (kernels/moe.py:156-189).
@@ -204,6 +268,11 @@ def index_select_jagged_bmm_swiglu(
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype and weight_p.dtype == jagged.dtype
     assert weight.shape == weight_p.shape
+    if _out_dtype is None and _wants_fp32_split(jagged, weight, weight_p):
+        return index_select_jagged_bmm_swiglu(max_seq_len, offsets, index, split_f32_rows(jagged, 0),
+                                              split_f32_weight(weight), bias, split_f32_weight(weight_p), bias_p,
+                                              _out_dtype=torch.float32)
+    od = _out_dtype or jagged.dtype
     dev = _lib.require_cuda(offsets, index, jagged, weight, weight_p, bias, bias_p)
     lib = _lib.load()
     L, K = jagged.shape
@@ -219,21 +288,21 @@ def index_select_jagged_bmm_swiglu(
         w = w.contiguous()
         wp = wp.contiguous()
         w_se, w_sn = w.stride(0), w.stride(1)
-    b = _prep_bias(bias, jagged.dtype)
-    bp = _prep_bias(bias_p, jagged.dtype)
+    b = _prep_bias(bias, od)
+    bp = _prep_bias(bias_p, od)
     off = _index_i64(offsets)
     idx = None if index is None else _index_i64(index)
     div = index.shape[1] if index is not None else 1
     if idx is not None and _gather_first(rows, 2 * N):
         a, idx, div, L = gather_rows(a, idx, div), None, 1, rows
-    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    out = torch.empty((rows, N), dtype=od, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm_swiglu(
                 off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
                 w.data_ptr(), wp.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), _lib.ptr(bp), N, E, kp, N,
-                out.data_ptr(), dt, out.stride(0), _lib.stream_ptr(dev),
+                out.data_ptr(), _lib.dtype_code(od), out.stride(0), _lib.stream_ptr(dev),
             )
         )
     return out
@@ -339,6 +408,8 @@ def silu_jagged_bmm(
     bias: Optional[torch.Tensor],
     has_silu: bool = True,
     out_row_index: Optional[torch.Tensor] = None,
+    *,
+    _out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """[silu](jagged) @ weight[e] + bias[e] per expert segment; weight is logical [E, K, N]
     (the GEMM half of silu_jagged_bmm_combine, kernels/pytorch/moe.py:255-275).
@@ -346,6 +417,11 @@ def silu_jagged_bmm(
     of the result land at out[out_row_index[r]]."""
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype
+    if _out_dtype is None and _wants_fp32_split(jagged, weight):
+        # SiLU is applied while the activations are expanded
+        return silu_jagged_bmm(offsets, split_f32_rows(jagged, 0, apply_silu=has_silu), split_f32_weight(weight), bias,
+                               has_silu=False, out_row_index=out_row_index, _out_dtype=torch.float32)
+    od = _out_dtype or jagged.dtype
     dev = _lib.require_cuda(offsets, jagged, weight, bias)
     lib = _lib.load()
     rows, K = jagged.shape
@@ -354,9 +430,9 @@ def silu_jagged_bmm(
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
     w, w_se, w_sn = prep_weight(weight, kp)
-    b = _prep_bias(bias, jagged.dtype)
+    b = _prep_bias(bias, od)
     off = _index_i64(offsets)
-    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    out = torch.empty((rows, N), dtype=od, device=dev)
     scratch = torch.empty((rows, kp), dtype=jagged.dtype, device=dev) if has_silu else None
     oidx = None if out_row_index is None else _index_i64(out_row_index.reshape(-1))
     assert oidx is None or oidx.numel() == rows
@@ -365,8 +441,8 @@ def silu_jagged_bmm(
         _lib.check(
             lib.fmoe_silu_jagged_bmm(
                 off.data_ptr(), rows, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
-                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), None, _lib.ptr(oidx), out.data_ptr(), dt,
-                out.stride(0),
+                _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), None, _lib.ptr(oidx), out.data_ptr(),
+                _lib.dtype_code(od), out.stride(0),
                 _lib.stream_ptr(dev),
             )
         )
@@ -443,6 +519,14 @@ def silu_jagged_bmm_combine(
         raise NotImplementedError("TRITON_CC is not supported for silu_jagged_bmm_combine")
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype
+    if _wants_fp32_split(jagged, weight) and out is None:
+        # fp32 accuracy: the GEMM on the expanded operands (f32 result rows), then the
+        # deterministic fp32 merge; the operand types of the merge are those of the reference
+        rows_f32 = silu_jagged_bmm(offsets, jagged, weight, bias, has_silu=has_silu)
+        g32 = gating_scores
+        if g32 is not None and round_scores:
+            g32 = g32.to(jagged.dtype)
+        return mul_merge_k_add(index, reverse_index, rows_f32, weight=g32, weight_index=gates_index)
     dev = _lib.require_cuda(offsets, jagged, weight, bias, reverse_index, gating_scores, gates_index)
     lib = _lib.load()
     kp = _pad_k(D_in, jagged.dtype)

@@ -124,3 +124,65 @@ def route_metadata(topk_idx: torch.Tensor, num_experts: int) -> RoutingMetadata:
             )
         )
     return RoutingMetadata(gate_index, token_index, offsets, reverse, lengths, max_len)
+
+
+def fused_routing_supported(x: torch.Tensor, gate_weight: torch.Tensor) -> bool:
+    """True when ``route_tokens_fused`` can serve these tokens: bf16 rows that are 16-byte aligned,
+    at most 32 experts, and a batch small enough for the single-launch placement."""
+    if not x.is_cuda or x.ndim != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[0] == 0:
+        return False
+    if gate_weight.dtype != torch.float32 or not gate_weight.is_contiguous():
+        return False
+    lib = _lib.load()
+    return bool(lib.fmoe_gate_topk_counts_supported(x.data_ptr(), _lib.BF16, x.stride(0), gate_weight.data_ptr(),
+                                                    x.shape[0], x.shape[1], gate_weight.shape[0]))
+
+
+def route_tokens_fused(
+    x: torch.Tensor,
+    gate_weight: torch.Tensor,
+    gate_bias: Optional[torch.Tensor],
+    k: int,
+    gather_rows: bool = False,
+    zero_rows: Optional[Tuple[int, torch.dtype]] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, RoutingMetadata, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """``gate_topk`` + ``route_metadata`` for small batches as two launches that read the expert
+    choices once: the gate kernel also emits the rows per expert of every group of 16 tokens, and
+    the placement kernel starts from those counts. The placement kernel can take two memory passes
+    along that the layers would otherwise run as launches of their own:
+      ``gather_rows``  returns x_sorted [L*k, d] with x_sorted[p] = x[token_index[p]] (the
+                       index_select of the up projection; x is read once);
+      ``zero_rows``    (cols, dtype): returns a cleared [L, cols] buffer (what a fused combine
+                       accumulates into).
+    Every tensor is bit-identical to what the separate operators produce. Returns
+    (topk_idx, topk_score, RoutingMetadata, x_sorted or None, cleared buffer or None)."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, gate_weight, gate_bias)
+    L, d = x.shape
+    E = gate_weight.shape[0]
+    gb = None if gate_bias is None else gate_bias.detach().to(torch.float32).contiguous()
+    gw = gate_weight.detach()
+    i64 = dict(dtype=torch.int64, device=dev)
+    idx = torch.empty((L, k), **i64)
+    score = torch.empty((L, k), dtype=torch.float32, device=dev)
+    counts = torch.empty(int(lib.fmoe_route_group_counts_bytes(L, E)) // 4, dtype=torch.int32, device=dev)
+    A = L * k
+    lengths = torch.empty(E, **i64)
+    offsets = torch.empty(E + 1, **i64)
+    gate_index = torch.empty(A, **i64)
+    token_index = torch.empty(A, **i64)
+    reverse = torch.empty((L, k), **i64)
+    max_len = torch.empty(1, **i64)
+    x_sorted = torch.empty((A, d), dtype=x.dtype, device=dev) if gather_rows else None
+    zbuf = torch.empty((L, zero_rows[0]), dtype=zero_rows[1], device=dev) if zero_rows is not None else None
+    with torch.cuda.device(dev):
+        st = _lib.stream_ptr(dev)
+        _lib.check(lib.fmoe_gate_topk_counts(x.data_ptr(), _lib.BF16, x.stride(0), gw.data_ptr(), _lib.ptr(gb), L, d, E, k,
+                                             None, idx.data_ptr(), score.data_ptr(), counts.data_ptr(), st))
+        _lib.check(lib.fmoe_route_metadata_gather(
+            idx.data_ptr(), L, E, k, counts.data_ptr(), lengths.data_ptr(), offsets.data_ptr(), gate_index.data_ptr(),
+            token_index.data_ptr(), reverse.data_ptr(), max_len.data_ptr(),
+            x.data_ptr(), _lib.BF16, x.stride(0), d, _lib.ptr(x_sorted), d,
+            _lib.ptr(zbuf), _lib.dtype_code(zbuf.dtype) if zbuf is not None else 0, zbuf.stride(0) if zbuf is not None else 0,
+            zbuf.shape[1] if zbuf is not None else 0, st))
+    return idx, score, RoutingMetadata(gate_index, token_index, offsets, reverse, lengths, max_len), x_sorted, zbuf

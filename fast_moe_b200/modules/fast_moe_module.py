@@ -19,7 +19,8 @@ from torch.autograd.profiler import record_function
 from .. import _lib
 from ..kernels import moe as ops
 from ..kernels import moe_fp8 as ops_fp8
-from ..kernels.routing import RoutingMetadata, gate_topk, route_metadata, split_gate_weight
+from ..kernels.routing import (RoutingMetadata, fused_routing_supported, gate_topk, route_metadata,
+                               route_tokens_fused, split_gate_weight)
 from ..kernels.utils import KernelType
 
 
@@ -62,6 +63,33 @@ class _CastCache:
         return t
 
 
+class _SplitCache:
+    """Three-term bf16 expansions of float32 weights (ops.split_f32_weight), recomputed when the
+    parameter changes in place or moves: what a float32 forward multiplies with when TF32 is not
+    allowed. Done once per weight update instead of once per forward."""
+
+    def __init__(self) -> None:
+        self._store: Dict[str, Tuple[int, int, torch.Tensor]] = {}
+
+    def get(self, name: str, p: torch.Tensor) -> torch.Tensor:
+        """p: parameter stored [E, N, K] float32 -> logical [E, 6 * Kp, N] bf16 weight."""
+        hit = self._store.get(name)
+        if hit is not None and hit[0] == p._version and hit[1] == p.data_ptr():
+            return hit[2]
+        t = ops.split_f32_weight(p.detach().to(torch.float32).permute(0, 2, 1))
+        self._store[name] = (p._version, p.data_ptr(), t)
+        return t
+
+
+def _fp32_exact(dt: torch.dtype) -> bool:
+    return dt == torch.float32 and not ops.fp32_uses_tf32()
+
+
+def _combine_rows_f32(rows: torch.Tensor, meta: RoutingMetadata, score: torch.Tensor) -> torch.Tensor:
+    return ops.mul_merge_k_add(meta.token_index, meta.reverse_index, rows, weight=score.to(rows.dtype),
+                               weight_index=meta.gate_index)
+
+
 # Above this many multiply-adds the gate logits go through the tensor cores (two-term bf16
 # expansion of the fp32 gate weights); below it the CUDA-core kernel is as fast and exact in fp32.
 GATE_TENSOR_CORE_MACS = 1 << 28
@@ -81,6 +109,26 @@ class GateSplitCache:
             self._key = key
         assert self._val is not None
         return self._val
+
+
+def route_tokens_with_passes(x_flat: torch.Tensor, gate: nn.Linear, k: int, num_experts: int, cache: GateSplitCache,
+                             gather_rows: bool = False, zero_rows: Optional[Tuple[int, torch.dtype]] = None):
+    """route_tokens that, for small bf16 batches, runs as the two-launch fused form and lets the
+    placement kernel also gather the token rows into expert order and / or clear the buffer the
+    fused combine accumulates into. Returns (score, meta, x_sorted or None, cleared buffer or None);
+    the last two are None whenever the fused form does not apply (the caller then runs those
+    passes the usual way)."""
+    L, d = x_flat.shape
+    tensor_core_logits = x_flat.dtype == torch.bfloat16 and d % 8 == 0 and L * d * num_experts >= GATE_TENSOR_CORE_MACS
+    w = gate.weight.detach()
+    if not tensor_core_logits and w.dtype == torch.float32 and fused_routing_supported(x_flat, w):
+        with _lib.stage("route"):
+            _, score, meta, xs, zbuf = route_tokens_fused(
+                x_flat, w, None if gate.bias is None else gate.bias.detach(), k, gather_rows=gather_rows,
+                zero_rows=zero_rows)
+        return score, meta, xs, zbuf
+    score, meta = route_tokens(x_flat, gate, k, num_experts, cache)
+    return score, meta, None, None
 
 
 def route_tokens(x_flat: torch.Tensor, gate: nn.Linear, k: int, num_experts: int,
@@ -112,6 +160,17 @@ class _MoEBase(nn.Module):
             self._gate_split = GateSplitCache()
         return route_tokens(x_flat, self.gate.gate, k, self.num_experts, self._gate_split)  # type: ignore[attr-defined]
 
+    def _route_with_passes(self, x_flat: torch.Tensor, k: int, up_cols: int, out_cols: int, fused: bool):
+        """Routing plus, when the fused small-batch form applies, the expert-sorted copy of the
+        token rows (if the up projection would gather them first anyway) and the cleared
+        accumulation buffer of the fused combine."""
+        if not hasattr(self, "_gate_split"):
+            self._gate_split = GateSplitCache()
+        gather = ops._gather_first(x_flat.shape[0] * k, up_cols)
+        zero = (out_cols, x_flat.dtype) if fused and x_flat.dtype == torch.bfloat16 else None
+        return route_tokens_with_passes(x_flat, self.gate.gate, k, self.num_experts, self._gate_split,  # type: ignore[attr-defined]
+                                        gather_rows=gather, zero_rows=zero)
+
 
 class FastMoELayer(_MoEBase):
     def __init__(
@@ -138,6 +197,7 @@ class FastMoELayer(_MoEBase):
         self._experts_w = nn.Parameter(_xavier_stack(num_experts, output_dim, hidden_dim).to(dtype))
         self._experts_bias = nn.Parameter(torch.zeros(num_experts, output_dim, dtype=dtype))
         self._cast = _CastCache()
+        self._split = _SplitCache()
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
@@ -146,7 +206,25 @@ class FastMoELayer(_MoEBase):
         x_flat = x.reshape(-1, self.input_dim)
         _lib.require_cuda(x)
         fused = self._use_fused_combine(k)
-        score, meta = self._route(x_flat, k)
+        if _fp32_exact(x.dtype):
+            score, meta = self._route(x_flat, k)
+            # float32 without TF32: operands expanded into bf16 terms (weights once per update)
+            with record_function("## expert_forward##"):
+                b1 = self._cast.get("b1", self._experts_hidden_bias, x.dtype)
+                b2 = self._cast.get("b2", self._experts_bias, x.dtype)
+                with _lib.stage("up"):
+                    hidden = ops.index_select_jagged_bmm(
+                        0, meta.offsets, meta.gate_index.view(-1, k), ops.split_f32_rows(x_flat, 0),
+                        self._split.get("w1", self._experts_hidden_w), b1, _epilogue=_lib.EPI_SILU,
+                        _out_dtype=torch.float32)
+                with _lib.stage("down"):
+                    rows = ops.silu_jagged_bmm(meta.offsets, ops.split_f32_rows(hidden, 0),
+                                               self._split.get("w2", self._experts_w), b2, has_silu=False,
+                                               _out_dtype=torch.float32)
+                with _lib.stage("combine"):
+                    y = _combine_rows_f32(rows, meta, score)
+            return y.view(*shape[:-1], self.output_dim)
+        score, meta, x_sorted, y_buf = self._route_with_passes(x_flat, k, self.hidden_dim, self.output_dim, fused)
         with record_function("## expert_forward##"):
             dt = x.dtype
             w1 = self._cast.get("w1", self._experts_hidden_w, dt).permute(0, 2, 1)
@@ -155,14 +233,17 @@ class FastMoELayer(_MoEBase):
             b2 = self._cast.get("b2", self._experts_bias, dt)
             # SiLU is applied in the first GEMM's epilogue rather than on the second GEMM's input
             with _lib.stage("up"):
-                hidden = ops.index_select_jagged_bmm(
-                    0, meta.offsets, meta.gate_index.view(-1, k), x_flat, w1, b1, _epilogue=_lib.EPI_SILU
-                )
+                if x_sorted is not None:
+                    hidden = ops.index_select_jagged_bmm(0, meta.offsets, None, x_sorted, w1, b1, _epilogue=_lib.EPI_SILU)
+                else:
+                    hidden = ops.index_select_jagged_bmm(
+                        0, meta.offsets, meta.gate_index.view(-1, k), x_flat, w1, b1, _epilogue=_lib.EPI_SILU
+                    )
             with _lib.stage("down_combine"):
                 y = ops.silu_jagged_bmm_combine(
                     0, meta.offsets, hidden, w2, b2, meta.token_index, meta.reverse_index,
                     gating_scores=score, gates_index=meta.gate_index, has_silu=False,
-                    fused=fused, round_scores=True,
+                    fused=fused, round_scores=True, out=y_buf,
                 )
         return y.view(*shape[:-1], self.output_dim)
 
@@ -198,6 +279,7 @@ class SwiGLUFastMoELayer(_MoEBase):
         self.w_up = nn.Parameter((torch.randn(num_experts, hidden_dim, input_dim) * init_std).to(dtype))
         self.w_down = nn.Parameter((torch.randn(num_experts, output_dim, hidden_dim) * init_std).to(dtype))
         self._cast = _CastCache()
+        self._split = _SplitCache()
         self._q: Optional[Dict[str, Tuple[torch.Tensor, torch.Tensor]]] = None
 
     @torch.no_grad()
@@ -215,8 +297,12 @@ class SwiGLUFastMoELayer(_MoEBase):
         x_flat = x.reshape(-1, self.input_dim)
         _lib.require_cuda(x)
         fused = self._use_fused_combine(k)
-        score, meta = self._route(x_flat, k)
         dt = x.dtype
+        x_sorted = y_buf = None
+        if self.fp8 or _fp32_exact(dt):
+            score, meta = self._route(x_flat, k)
+        else:
+            score, meta, x_sorted, y_buf = self._route_with_passes(x_flat, k, 2 * self.hidden_dim, self.output_dim, fused)
         index = meta.gate_index.view(-1, k)
         with record_function("## expert_forward##"):
             if self.fp8:
@@ -245,17 +331,31 @@ class SwiGLUFastMoELayer(_MoEBase):
                             meta.token_index, meta.reverse_index, y_rows, weight=score.to(dt),
                             weight_index=meta.gate_index,
                         )
+            elif _fp32_exact(dt):
+                with _lib.stage("up"):
+                    hidden = ops.index_select_jagged_bmm_swiglu(
+                        0, meta.offsets, index, ops.split_f32_rows(x_flat, 0), self._split.get("wg", self.w_gate), None,
+                        self._split.get("wu", self.w_up), None, _out_dtype=torch.float32)
+                with _lib.stage("down"):
+                    rows = ops.silu_jagged_bmm(meta.offsets, ops.split_f32_rows(hidden, 0),
+                                               self._split.get("wd", self.w_down), None, has_silu=False,
+                                               _out_dtype=torch.float32)
+                with _lib.stage("combine"):
+                    y = _combine_rows_f32(rows, meta, score)
             else:
                 wg = self._cast.get("wg", self.w_gate, dt).permute(0, 2, 1)
                 wu = self._cast.get("wu", self.w_up, dt).permute(0, 2, 1)
                 wd = self._cast.get("wd", self.w_down, dt).permute(0, 2, 1)
                 with _lib.stage("up"):
-                    hidden = ops.index_select_jagged_bmm_swiglu(0, meta.offsets, index, x_flat, wg, None, wu, None)
+                    if x_sorted is not None:
+                        hidden = ops.index_select_jagged_bmm_swiglu(0, meta.offsets, None, x_sorted, wg, None, wu, None)
+                    else:
+                        hidden = ops.index_select_jagged_bmm_swiglu(0, meta.offsets, index, x_flat, wg, None, wu, None)
                 with _lib.stage("down_combine"):
                     y = ops.silu_jagged_bmm_combine(
                         0, meta.offsets, hidden, wd, None, meta.token_index, meta.reverse_index,
                         gating_scores=score, gates_index=meta.gate_index, has_silu=False,
-                        fused=fused, round_scores=True,
+                        fused=fused, round_scores=True, out=y_buf,
                     )
         return y.view(*shape[:-1], self.output_dim)
 

@@ -109,6 +109,32 @@ int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, int k, int64_
                         int64_t* gate_index, int64_t* token_index, int64_t* reverse_index, int64_t* max_len,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* Small batches: the two routing steps chained so that the indices are read once, plus the two
+ * memory passes the layers run right after routing. No counterpart in the reference beyond the
+ * functions fmoe_gate_topk and fmoe_route_metadata already stand in for
+ * (modules/fast_moe_module.py:93-144) and the index_select of the up projection
+ * (kernels/pytorch/moe.py:69-73); results are bit-identical to those entry points.
+ *   fmoe_gate_topk_counts_supported: 1 when fmoe_gate_topk_counts can run on these arguments (bf16
+ *     tokens with 16-byte aligned rows, E <= 32, d a multiple of 8, ceil(L/32) * 2 * E <= 32768).
+ *   fmoe_gate_topk_counts: fmoe_gate_topk (x given, no precomputed logits) that also writes, for
+ *     every group of 16 tokens, the rows per expert: group_counts, fmoe_route_group_counts_bytes(L, E)
+ *     bytes.
+ *   fmoe_route_metadata_gather: fmoe_route_metadata from those counts (one launch, no workspace),
+ *     which optionally also (a) writes x_sorted[p, :] = x[token_index[p], :] for every sorted row p
+ *     - the row gather of the up projection, x read once - and (b) clears rows 0..L-1 of zero_rows
+ *     ([L, zero_cols], the buffer a fused combine accumulates into). Either may be NULL. */
+int fmoe_gate_topk_counts_supported(const void* x, int x_dtype, int64_t ldx, const float* gate_w, int64_t L, int d,
+                                    int E);
+size_t fmoe_route_group_counts_bytes(int64_t L, int E);
+int fmoe_gate_topk_counts(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
+                          int64_t L, int d, int E, int k, float* logits_out, int64_t* topk_idx, float* topk_score,
+                          int* group_counts, void* stream);
+int fmoe_route_metadata_gather(const int64_t* topk_idx, int64_t L, int E, int k, const int* group_counts,
+                               int64_t* lengths, int64_t* offsets, int64_t* gate_index, int64_t* token_index,
+                               int64_t* reverse_index, int64_t* max_len, const void* x, int x_dtype, int64_t ldx,
+                               int cols, void* x_sorted, int64_t ld_sorted, void* zero_rows, int zero_dtype,
+                               int64_t ld_zero, int zero_cols, void* stream);
+
 /* fmoe_route_metadata without a workspace argument, for callers that cannot allocate device
  * memory (code inside a pre-planned memory region, plugins that only receive their input and
  * output buffers, fixed-budget services). It has no counterpart in the reference. The scratch
@@ -236,6 +262,19 @@ int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_t total_row
                                        int g_dtype, const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
                                        int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo,
                                        int flags, void* stream);
+
+/* fp32 operands without TF32. The tensor-core path for FMOE_F32 operands rounds them to tf32
+ * (10 mantissa bits); the reference's kernels do that only when
+ * torch.backends.cuda.matmul.allow_tf32 is set (kernels/triton/triton_moe.py:592, default off) and
+ * otherwise multiply in full fp32, which is also what its PYTORCH path does. For that case the
+ * operands are expanded into three bf16 terms each (hi + mid + lo = x to about 2^-24) and laid out
+ * so that ONE bf16 grouped GEMM over a reduction dimension of 6 * cols_padded reproduces the fp32
+ * product: left operand rows [hi | hi | mid | hi | lo | mid] (pattern 0), right operand rows
+ * [hi | mid | hi | lo | hi | mid] (pattern 1); every partial product is exact in the fp32
+ * accumulator. in [rows, cols] f32 (row stride ldi); out [rows, 6 * cols_padded] bf16 (row stride
+ * ldo), columns cols..cols_padded-1 of every term are zero. apply_silu != 0 expands silu(in). */
+int fmoe_split_f32_bf16x3(const float* in, int64_t rows, int cols, int64_t ldi, int cols_padded, int pattern,
+                          int apply_silu, void* out, int64_t ldo, void* stream);
 
 /* Row gather: dst[r, :] = src[index[r] / index_div, :], r < rows. The index_select step of
  * pytorch_index_select_jagged_bmm (kernels/pytorch/moe.py:69-73: jagged[index]) as a standalone

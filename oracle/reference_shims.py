@@ -21,7 +21,18 @@ from dataclasses import dataclass
 
 import torch
 
-DEFAULT_REFERENCE_ROOT = os.environ.get("FAST_MOE_REFERENCE", os.path.join(os.sep, "root", "reference"))
+
+def reference_root(root=None) -> str:
+    """The reference checkout to import from: the argument, else the FAST_MOE_REFERENCE environment
+    variable. There is no built-in default: the location is the caller's to state."""
+    root = root or os.environ.get("FAST_MOE_REFERENCE")
+    if not root:
+        raise FileNotFoundError(
+            "no reference checkout given: pass its path (--reference) or set FAST_MOE_REFERENCE to a clone of "
+            "meta-recsys/fast_moe")
+    return root
+
+
 _installed = False
 _fbgemm_lib = None
 
@@ -34,12 +45,13 @@ def _namespace(name: str, path: str) -> types.ModuleType:
     return m
 
 
-def install(root: str = DEFAULT_REFERENCE_ROOT) -> None:
+def install(root=None) -> None:
     """Registers ``fast_moe`` and its sub-packages as namespace modules pointing into `root`
     (so the root __init__ never runs) and stubs what the PYTORCH path does not need."""
     global _installed, _fbgemm_lib
     if _installed:
         return
+    root = reference_root(root)
     if not os.path.isdir(root):
         raise FileNotFoundError(f"reference checkout not found at {root}")
     _namespace("fast_moe", root)
@@ -107,7 +119,7 @@ def install(root: str = DEFAULT_REFERENCE_ROOT) -> None:
     _installed = True
 
 
-def modules(root: str = DEFAULT_REFERENCE_ROOT):
+def modules(root=None):
     """Returns the reference modules on the MoE forward path, imported in place."""
     install(root)
     names = {

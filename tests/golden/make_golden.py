@@ -269,7 +269,8 @@ GROUPS = {"layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8"
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=reference_shims.DEFAULT_REFERENCE_ROOT)
+    ap.add_argument("--reference", default=None,
+                    help="checkout of meta-recsys/fast_moe (default: the FAST_MOE_REFERENCE environment variable)")
     ap.add_argument("--only", default=None, choices=sorted(GROUPS), help="regenerate one group of fixtures")
     a = ap.parse_args()
     torch.set_num_threads(1)   # one thread: summation order of the CPU BLAS is then fixed

@@ -91,6 +91,39 @@ def test_operator_signatures_match_reference():
         assert params == names, fn.__name__
 
 
+@pytest.mark.skipif(not os.environ.get("FAST_MOE_REFERENCE"), reason="FAST_MOE_REFERENCE (a reference checkout) is not set")
+def test_operator_signatures_match_the_live_reference():
+    """With a checkout of the reference at hand, the hand-written table above is checked against
+    inspect.signature of the reference's own callables (imported unmodified through the shims)."""
+    from oracle import reference_shims
+
+    ref = reference_shims.modules()
+    pairs = [
+        (moe.index_select_jagged_bmm, ref.moe.index_select_jagged_bmm),
+        (moe.mul_merge_k_add, ref.moe.mul_merge_k_add),
+        (moe.index_select_jagged_bmm_3D, ref.moe.index_select_jagged_bmm_3D),
+        (moe.index_select_jagged_bmm_swiglu, ref.moe.index_select_jagged_bmm_swiglu),
+        (moe.index_select_jagged_gating_bmm, ref.moe.index_select_jagged_gating_bmm),
+        (moe.silu_jagged_bmm_combine, ref.moe.silu_jagged_bmm_combine),
+        (moe_fp8.silu_jagged_fp8, ref.moe_fp8.silu_jagged_fp8),
+        (moe_fp8.bmm_weight_rowwise_quant_fp8, ref.moe_fp8.bmm_weight_rowwise_quant_fp8),
+        (moe_fp8.silu_jagged_bmm_fp8, ref.moe_fp8.silu_jagged_bmm_fp8),
+        (moe_fp8.silu_jagged_bmm_combine_fp8, ref.moe_fp8.silu_jagged_bmm_combine_fp8),
+        (moe_fp8.index_select_jagged_bmm, ref.moe_fp8.index_select_jagged_bmm),
+    ]
+    for ours, theirs in pairs:
+        mine = [(p.name, p.default if p.default is inspect.Parameter.empty or not hasattr(p.default, "name") else p.default.name)
+                for p in inspect.signature(ours).parameters.values() if p.kind != p.KEYWORD_ONLY]
+        want = [(p.name, p.default if p.default is inspect.Parameter.empty or not hasattr(p.default, "name") else p.default.name)
+                for p in inspect.signature(theirs).parameters.values()]
+        assert mine == want, ours.__name__
+    rl, ol = ref.layer.FastMoELayer, fm.FastMoELayer
+    assert list(inspect.signature(ol.__init__).parameters) == list(inspect.signature(rl.__init__).parameters)
+    assert list(inspect.signature(ol.forward).parameters) == list(inspect.signature(rl.forward).parameters)
+    torch.manual_seed(0)
+    assert sorted(ol(8, 16, 8, 2).state_dict()) == sorted(rl(8, 16, 8, 2).state_dict())
+
+
 def test_layer_keeps_reference_parameter_names_and_signature():
     layer = fm.FastMoELayer(16, 32, 24, 4, fm.KernelType.PYTORCH, torch.float32)
     assert sorted(layer.state_dict()) == ["_experts_bias", "_experts_hidden_bias", "_experts_hidden_w", "_experts_w",

@@ -138,6 +138,56 @@ def test_gate_topk_few_experts_warp_mma_path(L, d, E, k):
     clean_status()
 
 
+@pytest.mark.parametrize("L,d,E,k", [(1, 64, 4, 1), (15, 64, 8, 2), (16, 128, 8, 8), (17, 64, 5, 3), (33, 256, 16, 4),
+                                     (1000, 200, 32, 8), (4096, 1024, 8, 2), (5000, 512, 32, 2)])
+def test_fused_small_batch_routing_is_bit_identical(L, d, E, k):
+    """gate kernel that also emits per-group counts + single-launch placement that also gathers
+    the token rows and clears the combine buffer, against the separate operators: every tensor
+    must be equal bit for bit."""
+    from fast_moe_b200.kernels.routing import fused_routing_supported, route_tokens_fused
+
+    g = torch.Generator().manual_seed(L * 7 + E)
+    x = cu(torch.randn(L, d, generator=g).bfloat16())
+    gw = cu(torch.randn(E, d, generator=g) * 0.3)
+    gb = cu(torch.randn(E, generator=g) * 0.1)
+    assert fused_routing_supported(x, gw)
+    idx0, score0, _ = fm.gate_topk(x, gw, gb, k)
+    meta0 = fm.route_metadata(idx0, E)
+    rows0 = moe.gather_rows(x, meta0.gate_index, k)
+    idx, score, meta, xs, zbuf = route_tokens_fused(x, gw, gb, k, gather_rows=True, zero_rows=(264, torch.bfloat16))
+    assert torch.equal(idx, idx0) and torch.equal(score, score0)
+    for name in ("gate_index", "token_index", "offsets", "reverse_index", "lengths", "max_len"):
+        assert torch.equal(getattr(meta, name), getattr(meta0, name)), name
+    assert torch.equal(xs, rows0)
+    assert zbuf.shape == (L, 264) and int((zbuf != 0).sum()) == 0
+    # without the optional passes
+    _, _, meta2, xs2, z2 = route_tokens_fused(x, gw, None, k)
+    assert xs2 is None and z2 is None
+    idx1, _, _ = fm.gate_topk(x, gw, None, k)
+    assert torch.equal(meta2.gate_index, fm.route_metadata(idx1, E).gate_index)
+    clean_status()
+
+
+def test_layers_with_and_without_fused_routing_agree_bitwise(monkeypatch):
+    import fast_moe_b200.modules.fast_moe_module as M
+
+    torch.manual_seed(4)
+    d, h, o, E, k = 256, 1024, 256, 8, 2
+    x = cu(torch.randn(3, 400, d).bfloat16())            # 1200 tokens: rows are gathered first
+    for layer in (fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(DEV),
+                  fm.FastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(DEV)):
+        y_fused = layer(x, k)
+        with monkeypatch.context() as mp:
+            mp.setattr(M, "fused_routing_supported", lambda *a, **kw: False)
+            y_plain = layer(x, k)
+        assert torch.equal(y_fused, y_plain)
+        y8 = layer(x[:, :40], k)                          # small batch: in-kernel gather, fused routing still on
+        with monkeypatch.context() as mp:
+            mp.setattr(M, "fused_routing_supported", lambda *a, **kw: False)
+            assert torch.equal(y8, layer(x[:, :40], k))
+    clean_status()
+
+
 def test_gate_topk_tensor_core_logits_match_fp32_path():
     """bf16 hi/lo expansion of the gate weights on the tensor cores: logits agree with the fp32
     CUDA-core path to ~1e-5 and route identically wherever the k-th / (k+1)-th gap is not tiny."""
@@ -410,6 +460,67 @@ def test_layers_against_golden(name):
                              g["w_out"].permute(0, 2, 1), k)
     ysw = sw(cu(x), k)
     torch.testing.assert_close(ysw.cpu().view(-1, o)[safe], ref.view(-1, o)[safe], **TOL)
+    clean_status()
+
+
+@pytest.mark.parametrize("name", G.names("layer_"))
+def test_fp32_layers_at_the_reference_fp32_tolerance(name):
+    """float32 tokens and weights with TF32 not allowed - the default of
+    torch.backends.cuda.matmul.allow_tf32, which the reference's kernels follow
+    (kernels/triton/triton_moe.py:592) - must hold the tolerance of the reference's own fp32
+    end-to-end parity test, atol 1e-4 (modules/tests/test_kernel_parity.py:29-90). Operands are
+    expanded into three bf16 terms and multiplied by one bf16 tensor-core GEMM over a six times
+    longer reduction. With TF32 allowed the same call runs the tf32 kernels at the 1e-2 bound."""
+    g = G.load(name)
+    k = g["k"]
+    x = g["x"]
+    B, T, d = x.shape
+    E, h, _ = g["w_hidden"].shape
+    o = g["w_out"].shape[1]
+    layer = fm.FastMoELayer(d, h, o, E, fm.KernelType.PYTORCH, torch.float32)
+    layer.load_state_dict({
+        "gate.gate.weight": g["gate_w"], "gate.gate.bias": g["gate_b"], "_experts_hidden_w": g["w_hidden"],
+        "_experts_hidden_bias": g["b_hidden"], "_experts_w": g["w_out"], "_experts_bias": g["b_out"]})
+    layer.to(DEV)
+    sw = fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.float32)
+    with torch.no_grad():
+        sw.gate.gate.weight.copy_(g["gate_w"]); sw.gate.gate.bias.copy_(g["gate_b"])
+        sw.w_gate.copy_(g["w_hidden"]); sw.w_up.copy_(g["w_up"].permute(0, 2, 1)); sw.w_down.copy_(g["w_out"])
+    sw.to(DEV)
+    ref_sw = O.moe_layer_swiglu(x, g["gate_w"], g["gate_b"], g["w_hidden"].permute(0, 2, 1), g["w_up"],
+                                g["w_out"].permute(0, 2, 1), k)
+    safe = _near_tie_mask(g)
+    assert torch.backends.cuda.matmul.allow_tf32 is False and not fm.fp32_uses_tf32()
+    try:
+        y = layer(cu(x), k)
+        assert y.dtype == torch.float32
+        torch.testing.assert_close(y.cpu().view(-1, o)[safe], g["y_mlp"].view(-1, o)[safe], rtol=1e-5, atol=1e-4)
+        ysw = sw(cu(x), k)
+        torch.testing.assert_close(ysw.cpu().view(-1, o)[safe], ref_sw.view(-1, o)[safe], rtol=1e-5, atol=1e-4)
+        # the cached expansion follows in-place weight updates
+        with torch.no_grad():
+            layer._experts_w.mul_(0.5)
+            layer._experts_bias.mul_(0.5)
+        y_half = layer(cu(x), k)
+        torch.testing.assert_close(y_half.cpu().view(-1, o)[safe], 0.5 * g["y_mlp"].view(-1, o)[safe], rtol=1e-5, atol=1e-4)
+        # operators on float32 tensors take the same path
+        off, gi = cu(g["offsets"]), cu(g["gate_index"])
+        xf = cu(x.reshape(-1, d))
+        w1 = cu(g["w_hidden"]).permute(0, 2, 1)
+        up = fm.index_select_jagged_bmm(0, off, gi.view(-1, k), xf, w1, cu(g["b_hidden"]))
+        want = O.index_select_jagged_bmm(g["offsets"], g["gate_index"].view(-1, k), x.reshape(-1, d),
+                                         g["w_hidden"].permute(0, 2, 1), g["b_hidden"])
+        torch.testing.assert_close(up.cpu(), want, rtol=1e-5, atol=1e-4)
+        # TF32 allowed: the tf32 kernels, at their own bound; visibly less accurate than the above
+        fm.set_fp32_matmul("tf32")
+        assert fm.fp32_uses_tf32()
+        with torch.no_grad():
+            layer._experts_w.mul_(2.0)
+            layer._experts_bias.mul_(2.0)
+        y_tf32 = layer(cu(x), k)
+        torch.testing.assert_close(y_tf32.cpu().view(-1, o)[safe], g["y_mlp"].view(-1, o)[safe], **TOL)
+    finally:
+        fm.set_fp32_matmul(None)
     clean_status()
 
 
