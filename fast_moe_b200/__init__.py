@@ -15,10 +15,11 @@ from .kernels.moe import (
     silu_jagged_bmm,
     silu_jagged_bmm_combine,
 )
-from .kernels.routing import RoutingMetadata, gate_topk, route_metadata
+from .kernels.routing import RoutingMetadata, gate_topk, gate_topk_normalized, route_metadata, token_norm
 from .kernels.utils import KernelType
 from .modules.fast_moe_module import (CapturedForward, FastMoELayer, GatingNetwork, StreamingForward,
                                       SwiGLUFastMoELayer)
+from .modules.sg_moe import MRNOutput, SGConfig, SGMoELayer
 
 __all__ = [
     "FastMoELayer",
@@ -38,6 +39,11 @@ __all__ = [
     "silu_jagged_bmm_combine",
     "set_fp32_matmul",
     "fp32_uses_tf32",
+    "SGMoELayer",
+    "SGConfig",
+    "MRNOutput",
+    "gate_topk_normalized",
+    "token_norm",
     "gate_topk",
     "route_metadata",
     "RoutingMetadata",

@@ -47,6 +47,15 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* row, int c, float (&v
 
 constexpr int kGateEC = 8;       // experts per pass over the rows
 
+// What happens between the logits and the k scores:
+//   kRouterSoftmaxRenorm  softmax over the experts, top-k, the k scores renormalised to sum 1
+//                         (FastMoELayer._select_top_k_experts, modules/fast_moe_module.py:93-105)
+//   kRouterNormalised     logits divided by their L2 norm, softmax over the experts, top-k, the k
+//                         probabilities kept as they are (OrigSGMoEImpl._orig_noisy_gating without
+//                         noise, kernels/pytorch/mrn.py:236-252; utils/utils.py:139-164)
+constexpr int kRouterSoftmaxRenorm = 0;
+constexpr int kRouterNormalised = 1;
+
 // One warp per kGateTokens tokens (4, 2 or 1: as many as still leave every SM a few warps per
 // scheduler). Logits are accumulated in fp32 with the reduction order fixed by the lane layout, so
 // the same input always routes the same way. x is read in 16-byte pieces and each gate-weight
@@ -59,7 +68,7 @@ __global__ void __launch_bounds__(kGateWarps * 32)
 gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ gw,
                  const float* __restrict__ gb, const float* __restrict__ logits_in, long long ld_logits, int split,
                  long long L, int d, int E, int k, int vec_ok, float* __restrict__ logits_out, long long* __restrict__ topk_idx,
-                 float* __restrict__ topk_score) {
+                 float* __restrict__ topk_score, int router_mode) {
   __shared__ float s_logit[kGateWarps][kGateTokens][kMaxGateExperts];
   extern __shared__ __align__(16) float s_gw[];
   const int warp = threadIdx.x >> 5;
@@ -149,6 +158,16 @@ gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restric
     if (logits_out != nullptr) {
       for (int e = lane; e < E; e += 32) logits_out[t * E + e] = lg[e];
     }
+    if (router_mode == kRouterNormalised) {
+      // F.normalize(logits, dim=1): divide by max(||logits||_2, 1e-12)
+      float sq = 0.f;
+      for (int e = lane; e < E; e += 32) sq = fmaf(lg[e], lg[e], sq);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-12f);
+      for (int e = lane; e < E; e += 32) lg[e] *= inv;
+      __syncwarp();
+    }
     // softmax over E
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
@@ -193,9 +212,10 @@ gate_topk_kernel(const XT* __restrict__ x, long long ldx, const float* __restric
       }
       __syncwarp();
     }
-    // F.normalize(p=1, eps=1e-12) over the k kept scores
+    // F.normalize(p=1, eps=1e-12) over the k kept scores (the normalised-logit router keeps the
+    // softmax probabilities as they are)
     const float denom = fmaxf(norm, 1e-12f);
-    if (lane == 0) {
+    if (lane == 0 && router_mode == kRouterSoftmaxRenorm) {
       for (int s = 0; s < k; ++s) topk_score[t * k + s] = topk_score[t * k + s] / denom;
     }
   }
@@ -235,7 +255,7 @@ __global__ void __launch_bounds__(kMmaGateWarps * 32, 2)
 gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const float* __restrict__ gw,
                      const float* __restrict__ gb, long long L, int d, int E, int k,
                      float* __restrict__ logits_out, long long* __restrict__ topk_idx,
-                     float* __restrict__ topk_score, int* __restrict__ group_counts) {
+                     float* __restrict__ topk_score, int* __restrict__ group_counts, int router_mode) {
   constexpr int EP = 8 * NT;
   extern __shared__ __align__(16) uint8_t smem_gate[];
   const int row_bytes = d * 2 + kMmaGatePadBytes;
@@ -383,6 +403,18 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const f
     if (t < L) {
       float* lg = s_part + threadIdx.x * (EP + 1);
       float* sel = s_part + (kMmaGateTokens + threadIdx.x) * (EP + 1);   // quarter 1's row: the chosen scores
+      if (router_mode == kRouterNormalised) {
+        // same order of operations as gate_topk_kernel: one value per lane, butterfly sum
+        float sqv[32];
+#pragma unroll
+        for (int l = 0; l < 32; ++l) sqv[l] = l < E ? lg[l] * lg[l] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+          for (int l = 0; l < o; ++l) sqv[l] += sqv[l + o];
+        const float inv = 1.0f / fmaxf(sqrtf(sqv[0]), 1e-12f);
+        for (int e = 0; e < E; ++e) lg[e] *= inv;
+      }
       float mx = -INFINITY;
       for (int e = 0; e < E; ++e) mx = fmaxf(mx, lg[e]);
       for (int e = 0; e < E; ++e) lg[e] = expf(lg[e] - mx);
@@ -414,7 +446,7 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const f
         lg[best_e] = -1.f;
         if (best_e < E) picked |= 1u << best_e;
       }
-      const float denom = fmaxf(norm, 1e-12f);
+      const float denom = router_mode == kRouterSoftmaxRenorm ? fmaxf(norm, 1e-12f) : 1.0f;
       for (int s = 0; s < k; ++s) topk_score[t * k + s] = sel[s] / denom;
     }
     if (group_counts != nullptr) {
@@ -805,7 +837,8 @@ using namespace fmoe;
 namespace {
 int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                    const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E, int k,
-                   float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, void* stream);
+                   float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, int router_mode,
+                   void* stream);
 
 // Conditions under which the tensor-core gate kernel runs (and with it the per-group counts).
 bool gate_mma_path(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* logits_in, int d, int E,
@@ -825,7 +858,15 @@ extern "C" int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const flo
                               const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E,
                               int k, float* logits_out, int64_t* topk_idx, float* topk_score, void* stream) {
   return gate_topk_impl(x, x_dtype, ldx, gate_w, gate_b, logits_in, ld_logits, logits_split, L, d, E, k, logits_out,
-                        topk_idx, topk_score, nullptr, stream);
+                        topk_idx, topk_score, nullptr, kRouterSoftmaxRenorm, stream);
+}
+
+extern "C" int fmoe_gate_topk_normalized(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
+                                         const float* gate_b, const float* logits_in, int64_t ld_logits, int64_t L,
+                                         int d, int E, int k, float* logits_out, int64_t* topk_idx, float* topk_score,
+                                         void* stream) {
+  return gate_topk_impl(x, x_dtype, ldx, gate_w, gate_b, logits_in, ld_logits, 0, L, d, E, k, logits_out, topk_idx,
+                        topk_score, nullptr, kRouterNormalised, stream);
 }
 
 extern "C" size_t fmoe_route_group_counts_bytes(int64_t L, int E) {
@@ -852,13 +893,14 @@ extern "C" int fmoe_gate_topk_counts(const void* x, int x_dtype, int64_t ldx, co
                 "small batch (L=%lld, d=%d, E=%d); use fmoe_gate_topk + fmoe_route_metadata", (long long)L, d, E);
   }
   return gate_topk_impl(x, x_dtype, ldx, gate_w, gate_b, nullptr, 0, 0, L, d, E, k, logits_out, topk_idx, topk_score,
-                        group_counts, stream);
+                        group_counts, kRouterSoftmaxRenorm, stream);
 }
 
 namespace {
 int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                    const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E,
-                   int k, float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, void* stream) {
+                   int k, float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, int router_mode,
+                   void* stream) {
   FMOE_REQUIRE(L >= 0 && E >= 1 && E <= kMaxGateExperts, "gate_topk: E=%d outside [1, %d]", E, kMaxGateExperts);
   FMOE_REQUIRE(k >= 1 && k <= E, "gate_topk: k=%d must be in [1, E=%d]", k, E);
   if (L == 0) return FMOE_OK;   // an empty batch is valid input (its tensors have NULL data pointers)
@@ -894,7 +936,7 @@ int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
     }                                                                                                              \
     kern<<<blocks, kMmaGateWarps * 32, smem, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, gate_w, gate_b, L, d, \
                                                    E, k, logits_out, reinterpret_cast<long long*>(topk_idx),      \
-                                                   topk_score, group_counts);                                      \
+                                                   topk_score, group_counts, router_mode);                         \
   } while (0)
       if (nt == 1) FMOE_GATE_MMA(1); else if (nt == 2) FMOE_GATE_MMA(2); else FMOE_GATE_MMA(4);
 #undef FMOE_GATE_MMA
@@ -926,7 +968,7 @@ int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
     }                                                                                                               \
     kern<<<grid, kGateWarps * 32, WS ? w_bytes : 0, st>>>(static_cast<const XT*>(x), ldx, gate_w, gate_b, logits_in, \
                                                           ld_logits, logits_split, L, d, E, k, vec_ok, logits_out,  \
-                                                          idx, topk_score);                                         \
+                                                          idx, topk_score, router_mode);                            \
   } while (0)
 #define FMOE_GATE_T(XT)                                      \
   do {                                                       \

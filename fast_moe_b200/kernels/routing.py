@@ -186,3 +186,80 @@ def route_tokens_fused(
             _lib.ptr(zbuf), _lib.dtype_code(zbuf.dtype) if zbuf is not None else 0, zbuf.stride(0) if zbuf is not None else 0,
             zbuf.shape[1] if zbuf is not None else 0, st))
     return idx, score, RoutingMetadata(gate_index, token_index, offsets, reverse, lengths, max_len), x_sorted, zbuf
+
+
+def gate_topk_normalized(
+    x: Optional[torch.Tensor],
+    gate_weight: Optional[torch.Tensor],
+    k: int,
+    logits: Optional[torch.Tensor] = None,
+    return_logits: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Router of the sparsely-gated layer (kernels/pytorch/mrn.py:236-252 of the reference):
+    logits = x @ gate_weight^T divided by their L2 norm per token, softmax over all experts, the k
+    largest probabilities in descending order (ties to the lower expert id), NOT renormalised.
+    gate_weight is [E, d] (the reference keeps [d, E]); ``logits`` may be given instead of x.
+    Returns (topk_idx [L, k] int64, gates [L, k] f32, un-normalised logits if requested)."""
+    lib = _lib.load()
+    if logits is not None:
+        dev = _lib.require_cuda(logits)
+        lg = logits.to(torch.float32).contiguous()
+        L, E = lg.shape
+        xx = gw = None
+        d, x_dt, ldx, ld_lg = 0, _lib.F32, 0, E
+    else:
+        assert x is not None and gate_weight is not None
+        dev = _lib.require_cuda(x, gate_weight)
+        xx = x if x.stride(1) == 1 else x.contiguous()
+        gw = gate_weight.detach().to(torch.float32).contiguous()
+        L, d = xx.shape
+        E = gw.shape[0]
+        assert gw.shape[1] == d
+        x_dt, ldx, lg, ld_lg = _lib.dtype_code(xx.dtype), xx.stride(0), None, 0
+    idx = torch.empty((L, k), dtype=torch.int64, device=dev)
+    score = torch.empty((L, k), dtype=torch.float32, device=dev)
+    lout = torch.empty((L, E), dtype=torch.float32, device=dev) if return_logits else None
+    with torch.cuda.device(dev):
+        _lib.check(lib.fmoe_gate_topk_normalized(_lib.ptr(xx), x_dt, ldx, _lib.ptr(gw), None, _lib.ptr(lg), ld_lg, L, d, E, k,
+                                                 _lib.ptr(lout), idx.data_ptr(), score.data_ptr(), _lib.stream_ptr(dev)))
+    return idx, score, lout
+
+
+def token_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
+               group_norm: bool = False, num_groups: int = 1) -> torch.Tensor:
+    """Layer norm of the rows of x [L, d], or (``group_norm``) F.group_norm of x viewed as
+    [L, num_groups, d / num_groups] with one weight / bias per group; fp32 statistics, result in
+    the dtype of x (kernels/pytorch/mrn.py:301-318 of the reference)."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, weight, bias)
+    assert x.ndim == 2
+    xx = x if x.stride(1) == 1 else x.contiguous()
+    L, d = xx.shape
+    groups = num_groups if group_norm else 1
+    w = None if weight is None else weight.detach().to(torch.float32).contiguous()
+    b = None if bias is None else bias.detach().to(torch.float32).contiguous()
+    want = groups if group_norm else d
+    assert (w is None or w.numel() == want) and (b is None or b.numel() == want), "norm weight / bias size"
+    out = torch.empty((L, d), dtype=xx.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.fmoe_token_norm(xx.data_ptr(), _lib.dtype_code(xx.dtype), L, d, xx.stride(0) if L else d, groups,
+                                       _lib.ptr(w), _lib.ptr(b), 1 if group_norm else 0, float(eps), out.data_ptr(), d,
+                                       _lib.stream_ptr(dev)))
+    return out
+
+
+def sg_load_loss(meta: RoutingMetadata, score: torch.Tensor, num_experts: int, token_dtype: torch.dtype,
+                 loss_coef: float, train: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(loss scalar f32, load fractions [E] f32) of the sparsely-gated layer
+    (kernels/pytorch/mrn.py:253-287): loss = coef * (cv2(importance) + cv2(load)) when training,
+    0 otherwise; load fraction = rows of expert e / all rows."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(score, meta.offsets)
+    load = torch.empty(num_experts, dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    sc = score.contiguous()
+    with torch.cuda.device(dev):
+        _lib.check(lib.fmoe_sg_load_loss(meta.offsets.data_ptr(), meta.gate_index.data_ptr(), sc.data_ptr(), num_experts,
+                                         1 if token_dtype == torch.bfloat16 else 0, float(loss_coef), 1 if train else 0,
+                                         load.data_ptr(), loss.data_ptr(), _lib.stream_ptr(dev)))
+    return loss, load

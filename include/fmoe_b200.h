@@ -90,6 +90,35 @@ int fmoe_gate_topk(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
                    const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E, int k,
                    float* logits_out, int64_t* topk_idx, float* topk_score, void* stream);
 
+/* The router of the sparsely-gated ("MRN" / SGMoE) layer, OrigSGMoEImpl._orig_noisy_gating without
+ * noise (kernels/pytorch/mrn.py:236-252; the same steps as _compute_top_logits,
+ * utils/utils.py:139-164): logits = x @ Wg^T (+ bias), divided by max(||logits||_2, 1e-12) per token
+ * (F.normalize), softmax over ALL experts, the k largest probabilities taken in descending order
+ * (ties to the lower expert id: a stable descending sort) and kept as they are - no
+ * renormalisation. Arguments as fmoe_gate_topk; gate_w is [E, d] (the reference stores [d, E]:
+ * pass its transpose); logits_in, when given, are the un-normalised logits. */
+int fmoe_gate_topk_normalized(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
+                              const float* logits_in, int64_t ld_logits, int64_t L, int d, int E, int k,
+                              float* logits_out, int64_t* topk_idx, float* topk_score, void* stream);
+
+/* Token normalisation in front of that router and of the experts (kernels/pytorch/mrn.py:301-318):
+ * layer norm over the d features (num_groups = 1, weight / bias [d], per_group_affine = 0), or
+ * F.group_norm of x viewed as [L, num_groups, d / num_groups] with one weight / bias per group
+ * (per_group_affine = 1). fp32 statistics (biased variance), result in the token dtype.
+ * weight / bias are f32 and may be NULL. */
+int fmoe_token_norm(const void* x, int dtype, int64_t L, int d, int64_t ldx, int num_groups, const float* weight,
+                    const float* bias, int per_group_affine, float eps, void* out, int64_t ldo, void* stream);
+
+/* Load fractions and training loss of the sparsely-gated layer (kernels/pytorch/mrn.py:186-189,
+ * :253-287): importance[e] = sum of the gate values routed to expert e (in the order of the
+ * expert-sorted rows; with round_bf16 the gates and the sum are rounded to bf16 as bf16 tokens make
+ * the reference do), load[e] = rows of expert e; load_frac [E] = load / sum(load);
+ * loss [1] = loss_coef * (cv2(importance) + cv2(load)), cv2 = unbiased variance / (mean^2 + 1e-6),
+ * or 0 when want_loss == 0 (evaluation). offsets [E+1], gate_index [rows] as fmoe_route_metadata
+ * produced them; topk_score [L, k] f32. */
+int fmoe_sg_load_loss(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
+                      int round_bf16, float loss_coef, int want_loss, float* load_frac, float* loss, void* stream);
+
 /* Replaces FastMoELayer._compute_routing_metadata (modules/fast_moe_module.py:107-144) and the
  * fbgemm op asynchronous_complete_cumsum it calls (:131): a stable counting sort of the L*k
  * (token, slot) pairs by expert id.

@@ -264,7 +264,59 @@ def op3d_cases(ref):
         save(f"ops3d_{ci}", d)
 
 
-GROUPS = {"layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases}
+def mrn_cases(ref):
+    """The sparsely-gated layer of kernels/pytorch/mrn.py (OrigSGMoEImpl.forward): token norm,
+    L2-normalised logits, softmax over all experts, top-k without renormalisation, MLP experts,
+    shared linear map, load fractions and the training loss. Shapes follow
+    kernels/tests/mrn_test.py:660-862 (d = model_d = 64, E in {4, 8}, k in {1, 2}) plus a group-norm
+    case, a k = E case and one with noisy gating (the noise the reference draws is recorded)."""
+    import importlib
+
+    mrn = importlib.import_module("fast_moe.kernels.pytorch.mrn")
+    cases = [
+        # (L, d, m, o, E, k, group_norm, groups, train, noisy, seed)
+        (50, 64, 64, 64, 4, 1, False, 1, False, False, 0),
+        (477, 64, 64, 64, 8, 2, False, 1, True, False, 1),
+        (60, 32, 48, 32, 8, 2, True, 2, True, False, 2),
+        (40, 32, 32, 32, 4, 2, False, 1, True, True, 3),
+        (33, 16, 24, 16, 8, 8, False, 1, True, False, 4),
+    ]
+    for ci, (L, d, m, o, E, k, gn, groups, train, noisy, seed) in enumerate(cases):
+        torch.manual_seed(seed)
+        cfg = mrn.SGConfig(model_d=m, num_experts=E, num_activated_experts=k, enable_noisy_gating=noisy)
+        layer = mrn.OrigSGMoEImpl(d, o, cfg)
+        with torch.no_grad():
+            layer._experts_hidden_bias.normal_(0, 0.1)
+            layer._experts_bias.normal_(0, 0.1)
+            if noisy:
+                layer._w_gate.normal_(0, 0.3)
+                layer._w_noise.normal_(0, 0.3)
+        layer.train(train)
+        x = torch.randn(L, d)
+        ns = groups if gn else d
+        nw = torch.randn(ns) * 0.2 + 1
+        nb = torch.randn(ns) * 0.1
+        torch.manual_seed(100 + seed)
+        noise = torch.randn(L, E) if (noisy and train) else None
+        torch.manual_seed(100 + seed)          # the layer's randn_like draws the recorded noise
+        with torch.no_grad():
+            out = layer(x, None, 0, gn, groups, d // groups, nw, nb, 1e-5)
+            x_norm = (torch.nn.functional.group_norm(x.view(-1, groups, d // groups), groups, nw, nb, 1e-5).view(L, d)
+                      if gn else torch.nn.functional.layer_norm(x, (d,), nw, nb, 1e-5))
+            gates, _ = layer._orig_noisy_gating(x_norm, train) if not noisy else (None, None)
+        rec = dict(k=k, group_norm=int(gn), num_groups=groups, train=int(train), loss_coef=cfg.loss_coef, norm_eps=1e-5,
+                   x=x, norm_weight=nw, norm_bias=nb, x_norm=x_norm, w_gate=layer._w_gate, w_hidden=layer._experts_hidden_w,
+                   b_hidden=layer._experts_hidden_bias, w_out=layer._experts_w, b_out=layer._experts_bias,
+                   output_weight=layer._output_weight, y=out.x, loss=out.loss.reshape(-1), load=out.load)
+        if gates is not None:
+            rec["gates"] = gates
+        if noisy:
+            rec.update(w_noise=layer._w_noise, noise=noise)
+        save(f"mrn_{ci}", rec)
+
+
+GROUPS = {"layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases,
+          "mrn": mrn_cases}
 
 
 def main():

@@ -1,0 +1,143 @@
+"""The sparsely-gated ("MRN" / SGMoE) layer on the GPU against fixtures recorded from the reference's
+OrigSGMoEImpl (kernels/pytorch/mrn.py, run unmodified on CPU by tests/golden/make_golden.py) and
+against the CPU oracle (oracle/mrn_oracle.py) at the shapes of the reference's own test
+(kernels/tests/mrn_test.py:660-862: d = model_d = 64, E in {4, 8}, k in {1, 2}, bf16, rtol = atol =
+1e-2). float32 tokens run in fp32 accuracy and are held to 1e-4."""
+import pytest
+import torch
+
+import fast_moe_b200 as fm
+from fast_moe_b200 import _lib
+from oracle import mrn_oracle as M
+from tests import golden_io as G
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def cu(t):
+    return None if t is None else t.to(DEV)
+
+
+def _layer_from_golden(g, dtype=torch.float32):
+    L, d = g["x"].shape
+    E, m, _ = g["w_hidden"].shape
+    o = g["w_out"].shape[1]
+    cfg = fm.SGConfig(model_d=m, num_experts=E, num_activated_experts=g["k"], loss_coef=g["loss_coef"],
+                      enable_noisy_gating="w_noise" in g)
+    layer = fm.SGMoELayer(d, o, cfg)
+    with torch.no_grad():
+        layer._experts_hidden_w.copy_(g["w_hidden"]); layer._experts_hidden_bias.copy_(g["b_hidden"])
+        layer._experts_w.copy_(g["w_out"]); layer._experts_bias.copy_(g["b_out"])
+        layer._w_gate.copy_(g["w_gate"]); layer._output_weight.copy_(g["output_weight"])
+    return layer.to(DEV)
+
+
+def _safe_tokens(g, min_gap=1e-6):
+    """Tokens whose k-th and (k+1)-th gate probabilities are not a near tie."""
+    x_norm = g["x_norm"]
+    logits = torch.nn.functional.normalize(x_norm @ g["w_gate"], dim=1)
+    p = torch.softmax(logits, dim=1).sort(dim=1, descending=True).values
+    k = g["k"]
+    if k >= p.shape[1]:
+        return torch.ones(p.shape[0], dtype=torch.bool)
+    return (p[:, k - 1] - p[:, k]) > min_gap
+
+
+@pytest.mark.parametrize("name", G.names("mrn_"))
+def test_token_norm_and_router_against_golden(name):
+    g = G.load(name)
+    d = g["x"].shape[1]
+    groups = g["num_groups"]
+    gn = bool(g["group_norm"])
+    x_norm = fm.token_norm(cu(g["x"]), cu(g["norm_weight"]), cu(g["norm_bias"]), g["norm_eps"], group_norm=gn,
+                           num_groups=groups)
+    torch.testing.assert_close(x_norm.cpu(), g["x_norm"], atol=2e-6, rtol=1e-5)
+    if "gates" not in g:
+        return
+    k = g["k"]
+    idx, score, logits = fm.gate_topk_normalized(cu(g["x_norm"]), cu(g["w_gate"].t().contiguous()), k, return_logits=True)
+    torch.testing.assert_close(logits.cpu(), g["x_norm"] @ g["w_gate"], atol=1e-5, rtol=1e-5)
+    safe = _safe_tokens(g)
+    dense = torch.zeros_like(g["gates"]).scatter_(1, idx.cpu(), score.cpu())
+    assert torch.equal((dense > 0)[safe], (g["gates"] > 0)[safe])
+    torch.testing.assert_close(dense[safe], g["gates"][safe], atol=1e-6, rtol=1e-5)
+    # slots in descending probability, ties to the lower expert id; precomputed logits route the same
+    assert bool((score[:, :-1] >= score[:, 1:]).all())
+    idx2, score2, _ = fm.gate_topk_normalized(None, None, k, logits=logits)
+    assert torch.equal(idx2, idx) and torch.equal(score2, score)
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("name", G.names("mrn_"))
+def test_sg_moe_layer_against_golden(name):
+    g = G.load(name)
+    if "w_noise" in g:
+        # noisy gating is a training-time path that is not built: the layer says so
+        layer = _layer_from_golden(g)
+        layer.train(True)
+        with pytest.raises(NotImplementedError):
+            layer(cu(g["x"]), None, 0, False, 1, g["x"].shape[1], cu(g["norm_weight"]), cu(g["norm_bias"]), g["norm_eps"])
+        return
+    d = g["x"].shape[1]
+    groups = g["num_groups"]
+    gn = bool(g["group_norm"])
+    args = (None, 0, gn, groups, d // groups, cu(g["norm_weight"]), cu(g["norm_bias"]), g["norm_eps"])
+    layer = _layer_from_golden(g)
+    layer.train(bool(g["train"]))
+    safe = _safe_tokens(g)
+    out = layer(cu(g["x"]), *args)
+    assert isinstance(out, fm.MRNOutput) and out.x.dtype == torch.float32
+    torch.testing.assert_close(out.x.cpu()[safe], g["y"][safe], atol=1e-4, rtol=1e-4)
+    if bool(safe.all()):
+        torch.testing.assert_close(out.load.cpu(), g["load"], atol=1e-7, rtol=1e-6)
+        torch.testing.assert_close(out.loss.cpu().reshape(-1), g["loss"], atol=1e-6, rtol=1e-4)
+    # TF32 allowed: same call on the tf32 kernels, at the bf16-class bound
+    fm.set_fp32_matmul("tf32")
+    try:
+        out_tf32 = layer(cu(g["x"]), *args)
+        torch.testing.assert_close(out_tf32.x.cpu()[safe], g["y"][safe], atol=2e-2, rtol=2e-2)
+    finally:
+        fm.set_fp32_matmul(None)
+    # bf16 tokens: the reference test's own bound against the fp32 reference on the rounded inputs
+    xb = g["x"].bfloat16()
+    ref, ref_loss, ref_load = M.sg_moe_forward(
+        xb.float(), g["norm_weight"], g["norm_bias"], g["norm_eps"], g["w_gate"], g["w_hidden"].bfloat16().float(),
+        g["b_hidden"].bfloat16().float(), g["w_out"].bfloat16().float(), g["b_out"].bfloat16().float(),
+        g["output_weight"].bfloat16().float(), g["k"], train=bool(g["train"]), loss_coef=g["loss_coef"], group_norm=gn,
+        num_groups=groups, linear_dim=d // groups)
+    outb = layer(cu(xb), *args)
+    assert outb.x.dtype == torch.bfloat16
+    err = (outb.x.float().cpu() - ref).abs()
+    bad = (err > 2e-2 + 2e-2 * ref.abs()).any(dim=1).float().mean().item()
+    # the experts see bf16(x_norm): a token whose gate probabilities nearly tie may route differently
+    assert bad < 0.05, f"{bad:.2%} of tokens outside tolerance, max err {err.max().item():.3e}"
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("B,max_seq_len,E,k", [(16, 32, 4, 1), (32, 64, 8, 2), (16, 128, 8, 2)])
+def test_sg_moe_layer_at_the_reference_test_shapes(B, max_seq_len, E, k):
+    """kernels/tests/mrn_test.py:660-862: jagged batch of B sequences, input_d = model_d = 64, bf16,
+    rtol = atol = 1e-2, training mode without noisy gating; checked against the CPU oracle."""
+    d = 64
+    g = torch.Generator().manual_seed(B + E + k)
+    lengths = torch.randint(1, max_seq_len + 1, (B,), generator=g)
+    L = int(lengths.sum())
+    torch.manual_seed(0)
+    layer = fm.SGMoELayer(d, d, fm.SGConfig(model_d=d, num_experts=E, num_activated_experts=k)).to(DEV)
+    layer.train(True)
+    x = torch.randn(L, d, generator=g).bfloat16()
+    nw, nb = torch.ones(d), torch.zeros(d)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)])
+    out = layer(cu(x), cu(offsets), max_seq_len, False, 1, d, cu(nw), cu(nb), 1e-5)
+    f = lambda p: p.detach().float().cpu()
+    rb = lambda p: p.detach().to(torch.bfloat16).float().cpu()
+    ref, ref_loss, ref_load = M.sg_moe_forward(
+        x.float(), nw, nb, 1e-5, f(layer._w_gate), rb(layer._experts_hidden_w), rb(layer._experts_hidden_bias),
+        rb(layer._experts_w), rb(layer._experts_bias), rb(layer._output_weight), k, train=True, loss_coef=layer.loss_coef)
+    err = (out.x.float().cpu() - ref).abs()
+    bad = (err > 1e-2 + 1e-2 * ref.abs()).any(dim=1).float().mean().item()
+    assert bad < 0.03, f"{bad:.2%} of tokens outside rtol/atol 1e-2, max err {err.max().item():.3e}"
+    torch.testing.assert_close(out.load.cpu(), ref_load, atol=2e-2, rtol=0)
+    torch.testing.assert_close(out.loss.cpu(), ref_loss, atol=1e-3, rtol=5e-2)
+    assert _lib.device_status(torch.device(DEV)) == 0

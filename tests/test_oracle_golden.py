@@ -154,3 +154,30 @@ def test_fp8_up_projection(name):
     # and the quantised product stays near the unquantised one (reference bound 4e-1 / 1e-1,
     # kernels/tests/moe_fp8_test.py:302-335)
     torch.testing.assert_close(out.float(), g["out_unquantised"], atol=4e-1, rtol=1e-1)
+
+
+# ------------------------------------------------------------------------------- MRN / SGMoE
+@pytest.mark.parametrize("name", G.names("mrn_"))
+def test_sg_moe_oracle_against_golden(name):
+    """oracle/mrn_oracle.py against the recorded outputs of the reference's OrigSGMoEImpl
+    (kernels/pytorch/mrn.py): output, loss and load fractions, and the dense gate matrix."""
+    from oracle import mrn_oracle as M
+
+    g = G.load(name)
+    d = g["x"].shape[1]
+    groups = g["num_groups"]
+    y, loss, load = M.sg_moe_forward(
+        g["x"], g["norm_weight"], g["norm_bias"], g["norm_eps"], g["w_gate"], g["w_hidden"], g["b_hidden"], g["w_out"],
+        g["b_out"], g["output_weight"], g["k"], train=bool(g["train"]), loss_coef=g["loss_coef"],
+        group_norm=bool(g["group_norm"]), num_groups=groups, linear_dim=d // groups, w_noise=g.get("w_noise"),
+        noise=g.get("noise"))
+    torch.testing.assert_close(y, g["y"], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(loss.reshape(-1), g["loss"], atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(load, g["load"], atol=0, rtol=0)
+    x_norm = M.normalise_tokens(g["x"], bool(g["group_norm"]), groups, d // groups, g["norm_weight"], g["norm_bias"],
+                                g["norm_eps"])
+    torch.testing.assert_close(x_norm, g["x_norm"], atol=1e-6, rtol=1e-6)
+    if "gates" in g:
+        gates, idx, topk, _ = M.gating(x_norm, g["w_gate"], g["k"], bool(g["train"]))
+        torch.testing.assert_close(gates, g["gates"], atol=1e-7, rtol=1e-6)
+        assert torch.equal((gates > 0), (g["gates"] > 0))
