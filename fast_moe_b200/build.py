@@ -20,7 +20,8 @@ LIB_PATH = LIB_DIR / "libfmoe_b200.so"
 # (source, object stem, extra flags). The grouped GEMM, by far the longest compile, is built as
 # four objects in parallel: host code and one set of kernel instantiations per operand size.
 UNITS = [("api.cu", "api", []), ("routing.cu", "routing", []), ("combine.cu", "combine", []), ("quant.cu", "quant", []),
-         ("expert_parallel.cu", "expert_parallel", []), ("sg_moe.cu", "sg_moe", [])]
+         ("expert_parallel.cu", "expert_parallel", []), ("sg_moe.cu", "sg_moe", []),
+         ("backward.cu", "backward", [])]
 UNITS += [("grouped_gemm.cu", f"grouped_gemm_p{part}", [f"-DFMOE_GEMM_PART={part}"]) for part in range(4)]
 SOURCES = sorted({u[0] for u in UNITS})
 HEADERS = [CSRC / "common.cuh", CSRC / "ptx.cuh", PKG_DIR.parent / "include" / "fmoe_b200.h"]

@@ -1,0 +1,404 @@
+// Backward-pass helpers around the grouped GEMM. The reference implements the backward of its
+// operators as Triton kernels of their own (kernels/triton/triton_moe.py:62-106 SwiGLU,
+// :290-516 d_jagged / d_weight of the up projection, :922-983 combine, :1576-1976 jagged x jagged
+// products, :3474-3559 SiLU + down projection); here every matrix product of the backward pass is
+// the forward's grouped GEMM run on differently laid out operands, and this file holds the
+// HBM-bound passes that produce those layouts and the elementwise derivatives:
+//   d_x of a projection   rows of d_out times W[e]^T: the grouped GEMM on the transposed weight
+//                         (batched_transpose_kernel), then the k rows of a token are summed by
+//                         the combine kernel;
+//   d_W of a projection   dW[e] = X_e^T dOut_e, a product whose reduction runs over the rows of an
+//                         expert: both operands are transposed into [features, padded rows]
+//                         (jagged_transpose_pad_kernel; each expert's row range padded with zeros
+//                         to whole K steps) and the grouped GEMM runs in its reduction-over-rows mode;
+//   d_bias                column sums per expert (jagged_colsum_kernel);
+//   combine backward      d_rows[p] = d_out[token(p)] * gate[p] (gather_scale_rows_kernel) and
+//                         d_gate[p] = <d_out[token(p)], rows[p]> (row_dot_kernel);
+//   activations           SiLU' and the SwiGLU derivative (elementwise).
+#include "common.cuh"
+
+namespace fmoe {
+
+extern long long g_misc_launches;
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// kseg[0] = 0, kseg[e + 1] = kseg[e] + max(unit, len_e rounded up to unit): every expert owns at
+// least one (all-zero) K step, so its weight-gradient tile is always written.
+__global__ void pad_offsets_kernel(const long long* __restrict__ offsets, int E, int unit, long long* __restrict__ kseg) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    long long run = 0;
+    kseg[0] = 0;
+    for (int e = 0; e < E; ++e) {
+      long long len = offsets[e + 1] - offsets[e];
+      if (len < 0) len = 0;
+      long long padded = (len + unit - 1) / unit * unit;
+      if (padded < unit) padded = unit;
+      run += padded;
+      kseg[e + 1] = run;
+    }
+  }
+}
+
+// out[c, kseg[e] + j] = in[offsets[e] + j, c] for j < len_e, 0 for the padding. 32 x 32 tiles
+// through shared memory; a tile of 32 padded positions never straddles two experts (unit is a
+// multiple of 32). `index` (optional) names the source row of every sorted row: in[index[r] / div].
+template <typename T>
+__global__ void __launch_bounds__(256)
+jagged_transpose_pad_kernel(const T* __restrict__ in, long long ld_in, long long in_rows, const long long* __restrict__ index,
+                            int index_div, const long long* __restrict__ offsets, const long long* __restrict__ kseg, int E,
+                            int cols, T* __restrict__ out, long long ld_out, int* status) {
+  __shared__ T tile[32][33];
+  const long long q0 = static_cast<long long>(blockIdx.x) * 32;      // padded position
+  if (q0 >= kseg[E]) return;
+  int lo = 0, hi = E;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (kseg[mid] <= q0) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const long long len = offsets[e + 1] - offsets[e];
+  const long long j0 = q0 - kseg[e];
+  const int c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;             // 32 x 8
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int jr = ty + 8 * i;
+    const long long j = j0 + jr;
+    T v = T(0.f);
+    if (j < len && c0 + tx < cols) {
+      long long r = offsets[e] + j;
+      if (index != nullptr) {
+        r = index[r] / index_div;
+        if (r < 0 || r >= in_rows) {
+          atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+          r = -1;
+        }
+      }
+      if (r >= 0) v = in[r * ld_in + c0 + tx];
+    }
+    tile[jr][tx] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int cr = ty + 8 * i;
+    if (c0 + cr < cols) out[static_cast<long long>(c0 + cr) * ld_out + q0 + tx] = tile[tx][cr];
+  }
+}
+
+// out[b, c, r] = in[b, r, c]: plain batched transpose (weights [E, N, K] -> [E, K, N]).
+template <typename T>
+__global__ void __launch_bounds__(256)
+batched_transpose_kernel(const T* __restrict__ in, long long in_sb, long long ld_in, int rows, int cols, T* __restrict__ out,
+                         long long out_sb, long long ld_out) {
+  __shared__ T tile[32][33];
+  const T* src = in + static_cast<long long>(blockIdx.z) * in_sb;
+  T* dst = out + static_cast<long long>(blockIdx.z) * out_sb;
+  const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + ty + 8 * i;
+    tile[ty + 8 * i][tx] = (r < rows && c0 + tx < cols) ? src[static_cast<long long>(r) * ld_in + c0 + tx] : T(0.f);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty + 8 * i;
+    if (c < cols && r0 + tx < rows) dst[static_cast<long long>(c) * ld_out + r0 + tx] = tile[tx][ty + 8 * i];
+  }
+}
+
+// out[e, n] = sum over the rows of expert e of x[r, n], fp32 accumulation in row order.
+template <typename T, typename OT>
+__global__ void __launch_bounds__(256)
+jagged_colsum_kernel(const T* __restrict__ x, long long ldx, const long long* __restrict__ offsets, int N, OT* __restrict__ out) {
+  const int e = blockIdx.y;
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float acc = 0.f;
+  for (long long r = offsets[e]; r < offsets[e + 1]; ++r) acc += ldf<T>(x + r * ldx + n);
+  stf(out + static_cast<long long>(e) * N + n, acc);
+}
+
+// out[p, :] = src[index[p] / div, :] * weight[weight_index[p]]; the product is rounded to the
+// output type (what Tensor.mul gives). One warp per row.
+template <typename T, typename WT>
+__global__ void __launch_bounds__(256)
+gather_scale_rows_kernel(const T* __restrict__ src, long long src_rows, long long lds, const long long* __restrict__ index,
+                         int div, const WT* __restrict__ weight, const long long* __restrict__ weight_index,
+                         long long weight_count, long long rows, int cols, T* __restrict__ out, long long ldo, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long p = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
+    long long s = index[p];
+    if (div != 1) s /= div;
+    const long long wi = weight_index ? weight_index[p] : p;
+    if (s < 0 || s >= src_rows || (weight && (wi < 0 || wi >= weight_count))) {
+      if (lane == 0) atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+      for (int c = lane; c < cols; c += 32) stf(out + p * ldo + c, 0.f);
+      continue;
+    }
+    const float w = weight ? ldf<WT>(weight + wi) : 1.f;
+    for (int c = lane; c < cols; c += 32) stf(out + p * ldo + c, ldf<T>(src + s * lds + c) * w);
+  }
+}
+
+// out[p] = sum_c a[p, c] * b[index[p] / div, c] in fp32. One warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_dot_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ b, long long b_rows, long long ldb,
+               const long long* __restrict__ index, int div, long long rows, int cols, float* __restrict__ out, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long p = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
+    long long s = index ? index[p] : p;
+    if (div != 1) s /= div;
+    if (s < 0 || s >= b_rows) {
+      if (lane == 0) {
+        atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+        out[p] = 0.f;
+      }
+      continue;
+    }
+    float acc = 0.f;
+    for (int c = lane; c < cols; c += 32) acc = fmaf(ldf<T>(a + p * lda + c), ldf<T>(b + s * ldb + c), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[p] = acc;
+  }
+}
+
+// mode 0: d_x = d_y * silu'(x), silu'(x) = s (1 + x (1 - s)), s = sigmoid(x)
+// mode 1 (SwiGLU, out = silu(alpha) * beta): d_alpha = d_out * beta * silu'(alpha), d_beta = d_out * silu(alpha)
+template <typename T>
+__global__ void __launch_bounds__(256)
+activation_backward_kernel(int mode, const T* __restrict__ d_out, long long ldd, const T* __restrict__ alpha, long long lda,
+                           const T* __restrict__ beta, long long ldb, long long rows, int cols, T* __restrict__ d_alpha,
+                           long long ldda, T* __restrict__ d_beta, long long lddb) {
+  const long long total = rows * cols;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols;
+    const int c = static_cast<int>(i - r * cols);
+    const float g = ldf<T>(d_out + r * ldd + c);
+    const float a = ldf<T>(alpha + r * lda + c);
+    const float sg = 1.0f / (1.0f + expf(-a));
+    const float dsilu = sg * (1.0f + a * (1.0f - sg));
+    if (mode == 0) {
+      stf(d_alpha + r * ldda + c, g * dsilu);
+    } else {
+      const float bt = ldf<T>(beta + r * ldb + c);
+      stf(d_alpha + r * ldda + c, g * bt * dsilu);
+      stf(d_beta + r * lddb + c, g * a * sg);
+    }
+  }
+}
+
+int grid_for(long long work, int per_block) {
+  long long b = (work + per_block - 1) / per_block;
+  if (b > 148 * 32) b = 148 * 32;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_jagged_pad_offsets(const int64_t* offsets, int E, int dtype, int64_t* kseg, void* stream) {
+  const int es = dtype_size(dtype);
+  FMOE_REQUIRE(es != 0 && E >= 1 && offsets && kseg, "jagged_pad_offsets: bad arguments");
+  pad_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const long long*>(offsets), E, 128 / es,
+                                                                       reinterpret_cast<long long*>(kseg));
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_jagged_transpose_pad(const void* in, int dtype, int64_t in_rows, int64_t ld_in, const int64_t* index,
+                                         int index_div, const int64_t* offsets, const int64_t* kseg, int E, int64_t rows,
+                                         int cols, void* out, int64_t ld_out, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "jagged_transpose_pad: dtype must be bf16 or f32");
+  FMOE_REQUIRE(E >= 1 && rows >= 0 && cols >= 1 && offsets && kseg && out, "jagged_transpose_pad: bad arguments");
+  FMOE_REQUIRE(index == nullptr || index_div >= 1, "jagged_transpose_pad: index_div must be >= 1");
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  const int unit = 128 / dtype_size(dtype);
+  // upper bound of the padded length: every expert adds less than one unit, empty ones exactly one
+  const long long padded_max = rows + static_cast<long long>(E) * unit;
+  FMOE_REQUIRE(ld_out >= padded_max, "jagged_transpose_pad: ld_out=%lld is below rows + E * %d = %lld", (long long)ld_out,
+               unit, padded_max);
+  dim3 grid(static_cast<unsigned>((padded_max + 31) / 32), static_cast<unsigned>((cols + 31) / 32), 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FMOE_BF16) {
+    jagged_transpose_pad_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(in), ld_in, in_rows, reinterpret_cast<const long long*>(index), index_div,
+        reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(kseg), E, cols,
+        static_cast<__nv_bfloat16*>(out), ld_out, status);
+  } else {
+    jagged_transpose_pad_kernel<float><<<grid, 256, 0, st>>>(
+        static_cast<const float*>(in), ld_in, in_rows, reinterpret_cast<const long long*>(index), index_div,
+        reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(kseg), E, cols,
+        static_cast<float*>(out), ld_out, status);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_batched_transpose(const void* in, int dtype, int batch, int64_t in_sb, int64_t ld_in, int rows, int cols,
+                                      void* out, int64_t out_sb, int64_t ld_out, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "batched_transpose: dtype must be bf16 or f32");
+  FMOE_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, "batched_transpose: negative size");
+  if (batch == 0 || rows == 0 || cols == 0) return FMOE_OK;
+  FMOE_REQUIRE(in && out && batch <= 65535, "batched_transpose: bad arguments");
+  dim3 grid((rows + 31) / 32, (cols + 31) / 32, batch);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FMOE_BF16) {
+    batched_transpose_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), in_sb, ld_in, rows, cols,
+                                                                   static_cast<__nv_bfloat16*>(out), out_sb, ld_out);
+  } else {
+    batched_transpose_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(in), in_sb, ld_in, rows, cols,
+                                                           static_cast<float*>(out), out_sb, ld_out);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_jagged_jagged_bmm(const int64_t* group_offsets, const int64_t* kseg, int64_t padded_rows,
+                                      const void* a_t, int64_t lda, const void* b_t, int64_t ldb, int dtype, int E, int M,
+                                      int N, void* out, int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "jagged_jagged_bmm: dtype must be bf16 or f32");
+  FMOE_REQUIRE(group_offsets && kseg && M >= 1 && N >= 1 && padded_rows >= 1, "jagged_jagged_bmm: bad arguments");
+  GemmDesc g = {};
+  g.dtype = dtype;
+  g.E = E; g.N = N;
+  g.K = static_cast<int>(padded_rows);
+  g.offsets = group_offsets;
+  g.total_rows = static_cast<int64_t>(E) * M;
+  g.a = a_t; g.a_rows = M; g.lda = lda;
+  g.b0 = b_t; g.b_se = 0; g.b_sn = ldb;
+  g.kseg = kseg;
+  g.epilogue = FMOE_EPI_NONE;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  FMOE_REQUIRE(padded_rows < (1ll << 31), "jagged_jagged_bmm: more than 2^31 padded rows");
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fmoe_jagged_colsum(const void* x, int dtype, int64_t ldx, const int64_t* offsets, int E, int N, void* out,
+                                  int out_dtype, void* stream) {
+  FMOE_REQUIRE((dtype == FMOE_BF16 || dtype == FMOE_F32) && (out_dtype == FMOE_BF16 || out_dtype == FMOE_F32),
+               "jagged_colsum: dtypes must be bf16 or f32");
+  FMOE_REQUIRE(E >= 1 && E <= 65535 && N >= 1 && offsets && out, "jagged_colsum: bad arguments");
+  dim3 grid((N + 255) / 256, E, 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long* off = reinterpret_cast<const long long*>(offsets);
+#define FMOE_COLSUM(T, OT) jagged_colsum_kernel<T, OT><<<grid, 256, 0, st>>>(static_cast<const T*>(x), ldx, off, N, static_cast<OT*>(out))
+  if (dtype == FMOE_BF16 && out_dtype == FMOE_BF16) FMOE_COLSUM(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == FMOE_BF16) FMOE_COLSUM(__nv_bfloat16, float);
+  else if (out_dtype == FMOE_F32) FMOE_COLSUM(float, float);
+  else FMOE_COLSUM(float, __nv_bfloat16);
+#undef FMOE_COLSUM
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_gather_scale_rows(const void* src, int dtype, int64_t src_rows, int64_t lds, const int64_t* index,
+                                      int index_div, const void* weight, int w_dtype, const int64_t* weight_index,
+                                      int64_t weight_count, int64_t rows, int cols, void* out, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "gather_scale_rows: dtype must be bf16 or f32");
+  FMOE_REQUIRE(weight == nullptr || w_dtype == FMOE_BF16 || w_dtype == FMOE_F32, "gather_scale_rows: weight must be bf16 or f32");
+  FMOE_REQUIRE(rows >= 0 && cols >= 1 && index_div >= 1, "gather_scale_rows: bad sizes");
+  if (rows == 0) return FMOE_OK;
+  FMOE_REQUIRE(src && index && out, "gather_scale_rows: NULL pointer argument");
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows * 32, 256);
+  const long long* idx = reinterpret_cast<const long long*>(index);
+  const long long* widx = reinterpret_cast<const long long*>(weight_index);
+#define FMOE_GS(T, WT)                                                                                                  \
+  gather_scale_rows_kernel<T, WT><<<grid, 256, 0, st>>>(static_cast<const T*>(src), src_rows, lds, idx, index_div,      \
+                                                        static_cast<const WT*>(weight), widx, weight_count, rows, cols, \
+                                                        static_cast<T*>(out), ldo, status)
+  if (dtype == FMOE_BF16 && w_dtype == FMOE_F32) FMOE_GS(__nv_bfloat16, float);
+  else if (dtype == FMOE_BF16) FMOE_GS(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dtype == FMOE_BF16) FMOE_GS(float, __nv_bfloat16);
+  else FMOE_GS(float, float);
+#undef FMOE_GS
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_row_dot(const void* a, int64_t lda, const void* b, int64_t b_rows, int64_t ldb, int dtype,
+                            const int64_t* index, int index_div, int64_t rows, int cols, float* out, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "row_dot: dtype must be bf16 or f32");
+  FMOE_REQUIRE(rows >= 0 && cols >= 1 && index_div >= 1, "row_dot: bad sizes");
+  if (rows == 0) return FMOE_OK;
+  FMOE_REQUIRE(a && b && out, "row_dot: NULL pointer argument");
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows * 32, 256);
+  const long long* idx = reinterpret_cast<const long long*>(index);
+  if (dtype == FMOE_BF16) {
+    row_dot_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a), lda,
+                                                         static_cast<const __nv_bfloat16*>(b), b_rows, ldb, idx, index_div, rows,
+                                                         cols, out, status);
+  } else {
+    row_dot_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(a), lda, static_cast<const float*>(b), b_rows, ldb,
+                                                 idx, index_div, rows, cols, out, status);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_activation_backward(int mode, const void* d_out, int64_t ldd, const void* alpha, int64_t lda,
+                                        const void* beta, int64_t ldb, int dtype, int64_t rows, int cols, void* d_alpha,
+                                        int64_t ldda, void* d_beta, int64_t lddb, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "activation_backward: dtype must be bf16 or f32");
+  FMOE_REQUIRE(mode == 0 || mode == 1, "activation_backward: mode must be 0 (SiLU) or 1 (SwiGLU)");
+  FMOE_REQUIRE(rows >= 0 && cols >= 1, "activation_backward: bad sizes");
+  if (rows == 0) return FMOE_OK;
+  FMOE_REQUIRE(d_out && alpha && d_alpha && (mode == 0 || (beta && d_beta)), "activation_backward: NULL pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows * cols, 256);
+  if (dtype == FMOE_BF16) {
+    using T = __nv_bfloat16;
+    activation_backward_kernel<T><<<grid, 256, 0, st>>>(mode, static_cast<const T*>(d_out), ldd, static_cast<const T*>(alpha), lda,
+                                                        static_cast<const T*>(beta), ldb, rows, cols, static_cast<T*>(d_alpha),
+                                                        ldda, static_cast<T*>(d_beta), lddb);
+  } else {
+    using T = float;
+    activation_backward_kernel<T><<<grid, 256, 0, st>>>(mode, static_cast<const T*>(d_out), ldd, static_cast<const T*>(alpha), lda,
+                                                        static_cast<const T*>(beta), ldb, rows, cols, static_cast<T*>(d_alpha),
+                                                        ldda, static_cast<T*>(d_beta), lddb);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}

@@ -79,6 +79,11 @@ struct GemmDesc {
   const int64_t* out_peers;
   int n_peers;
   int64_t peer_rows;
+  // Reduction over the rows of each group (weight gradients): `a` is [a_rows, K] and b0 [N, K]
+  // with K = the padded total row count of all groups, kseg [E+1] (device, elements, multiples
+  // of one K step of 128 bytes, every group at least one step) the start of each group's range;
+  // offsets must be the uniform [0, a_rows, 2 a_rows, ...] and the result is [E * a_rows, N].
+  const int64_t* kseg;
   // total_rows may be a capacity rather than a row count; rows_hint (> 0) then tells the tile-shape
   // heuristic how many rows to expect
   int64_t rows_hint;

@@ -94,6 +94,11 @@ struct GemmParams {
   const long long* gate_index;
   int gate_div;
   int vec_ok;        // output rows are 16-byte aligned: vector stores allowed
+  // Reduction over an expert's ROWS instead of over a fixed K (the weight-gradient product
+  // dW[e] = A_e^T B_e): both operands are stored transposed, [features, padded rows], and kseg[e]
+  // (elements, multiples of one K step) is where expert e's padded row range starts. Every
+  // expert then owns the same number of output rows; its tiles differ in the length of the K loop.
+  const long long* kseg;
   int* status;
 };
 
@@ -105,7 +110,7 @@ struct SmemPlan {
   static constexpr int kTileBytes = kStages * kStageBytes;
   static constexpr int kStagingBytes = kEpilogueWarps * 2048;    // 32 rows x 64 bytes per epilogue warp
   static constexpr int kBarBytes = 256;
-  static constexpr int kPmBytes = 2 * ((kMaxExperts + 1) * 4 + 12);   // tile prefix + row offsets
+  static constexpr int kPmBytes = 3 * ((kMaxExperts + 1) * 4 + 12);   // tile prefix + row offsets + reduction offsets
   static constexpr int kTotal = 1024 + kTileBytes + kStagingBytes + kBarBytes + kPmBytes;
 };
 
@@ -286,6 +291,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 200);
   int* pm = reinterpret_cast<int*>(bar_ptr + Plan::kBarBytes);
   int* soff = pm + kMaxExperts + 2;   // offsets[] as 32-bit rows, read by every role at tile changes
+  int* skb = soff + kMaxExperts + 2;  // kseg[] (reduction-over-rows mode): start of each expert's K range
+  const bool kseg_mode = p.kseg != nullptr;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -318,6 +325,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     pm[e + 1] = static_cast<int>((len + kTileRows - 1) / kTileRows);
     soff[e] = static_cast<int>(o0);
     if (e == p.E - 1) soff[p.E] = static_cast<int>(o1 < o0 ? o0 : o1);
+    if (kseg_mode) {
+      skb[e] = static_cast<int>(p.kseg[e]);
+      if (e == p.E - 1) skb[p.E] = static_cast<int>(p.kseg[p.E]);
+    }
   }
   __syncthreads();
   if (warp == 0) {
@@ -359,9 +370,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int t = unit; t < total_tiles && ok; t += num_units) {
         int e, mb, nb;
         walk.decode(t, e, mb, nb);
-        const int row0 = soff[e] + mb * kTileRows + static_cast<int>(rank) * kBM;
+        // reduction-over-rows mode: A rows are the expert's output rows (the same for every
+        // expert), the K range is the expert's, and B is a single matrix
+        const int row0 = (kseg_mode ? 0 : soff[e]) + mb * kTileRows + static_cast<int>(rank) * kBM;
         const int n0 = nb * kTileN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int k_begin = kseg_mode ? skb[e] : 0;
+        const int nkb = kseg_mode ? (skb[e + 1] - skb[e]) / kKElems : num_kb;
+        if (kseg_mode) e = 0;
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       FMOE_DEV_WAIT_PRODUCER)) {
             ok = false;
@@ -369,7 +385,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
-          const int k0 = kb * kKElems;
+          const int k0 = k_begin + kb * kKElems;
           if constexpr (!kPair) {
             const uint32_t bar = full_bar(stage);
             ptx::mbar_arrive_expect_tx(bar, kStageTx);
@@ -398,11 +414,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // =========================================================== MMA issuer (one thread, leader CTA)
     if (lane == 0 && rank == 0) {
+      TileWalker walk(pm, p.n_tiles, p.E);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       for (int t = unit; t < total_tiles && ok; t += num_units, ++it) {
+        int nkb = num_kb;
+        if (kseg_mode) {
+          int e, mb, nb;
+          walk.decode(t, e, mb, nb);
+          nkb = (skb[e + 1] - skb[e]) / kKElems;
+        }
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
         if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
@@ -410,7 +433,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kMmaN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, FMOE_DEV_WAIT_MMA)) {
             ok = false;
             break;
@@ -425,7 +448,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ptx::umma_ss<kKind, CTAS>(d_tmem, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit<CTAS>(empty_bar(stage));      // stage reusable once these MMAs have read it
-          if (kb == num_kb - 1) ptx::umma_commit<CTAS>(tfull_bar(acc));
+          if (kb == nkb - 1) ptx::umma_commit<CTAS>(tfull_bar(acc));
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -977,6 +1000,9 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
     return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: gathered rows need K to be a multiple of 16 bytes (K=%d x %d B); pad K",
                 d.K, esize);
   }
+  FMOE_REQUIRE(d.kseg == nullptr || (d.index == nullptr && d.gate_index == nullptr && d.out_index == nullptr &&
+                                     d.epilogue == FMOE_EPI_NONE && d.a_scale == nullptr),
+               "grouped_gemm: the reduction-over-rows mode takes plain contiguous operands only");
   FMOE_REQUIRE(d.out_peers == nullptr || (d.out_index != nullptr && d.gate_index == nullptr && d.n_peers >= 1),
                "grouped_gemm: peer stores need a route table and exclude the fused combine");
   if (d.gate_index != nullptr && (d.index != nullptr || d.epilogue != FMOE_EPI_NONE)) {
@@ -1019,7 +1045,9 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
     if (rc != FMOE_OK) return rc;
   }
   {
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.N), static_cast<cuuint64_t>(d.E)};
+    // reduction-over-rows mode: one B matrix [N, K] shared by all groups
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.N),
+                          static_cast<cuuint64_t>(d.kseg ? 1 : d.E)};
     cuuint64_t str[2] = {static_cast<cuuint64_t>(d.b_sn) * esize, static_cast<cuuint64_t>(d.b_se) * esize};
     cuuint32_t box[3] = {static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(box_n), 1u};
     int rc = make_tmap(&tmB0, d.dtype, 3, d.b0, dims, str, box, "weights");
@@ -1065,6 +1093,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.gate_div = d.gate_div > 0 ? d.gate_div : 1;
   const int osize = dtype_size(d.out_dtype);
   // peer buffers are 16-byte aligned by contract (their addresses live on the device)
+  p.kseg = reinterpret_cast<const long long*>(d.kseg);
   p.vec_ok = ((d.ldo * osize) % 16 == 0) && (d.out_peers != nullptr || (reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
   p.status = status;
 

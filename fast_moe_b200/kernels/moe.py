@@ -36,6 +36,12 @@ class SiluJaggedBmmCombineOption:
     d_weight_split_k_kernel_tma: bool = False
 
 
+def _ag():
+    from . import autograd
+
+    return autograd
+
+
 def _elem_align(dt: torch.dtype) -> int:
     """Elements per 16 bytes: TMA needs 16-byte aligned bases and row strides."""
     return 16 // torch.empty((), dtype=dt).element_size()
@@ -189,6 +195,8 @@ def index_select_jagged_bmm(
     assert index is None or (index.ndim == 2 and (_rows_checked or index.shape[0] == jagged.shape[0]))
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype, f"{weight.dtype=} {jagged.dtype=}"
+    if index is not None and _epilogue == _lib.EPI_NONE and _out_dtype is None and _ag().needs_grad(jagged, weight, bias):
+        return _ag().IndexSelectJaggedBmmFn.apply(offsets, index, jagged, weight, bias)
     if _out_dtype is None and _wants_fp32_split(jagged, weight):
         return index_select_jagged_bmm(max_seq_len, offsets, index, split_f32_rows(jagged, 0), split_f32_weight(weight),
                                        bias, _epilogue=_epilogue, _rows_checked=_rows_checked,
@@ -268,6 +276,8 @@ def index_select_jagged_bmm_swiglu(
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype and weight_p.dtype == jagged.dtype
     assert weight.shape == weight_p.shape
+    if index is not None and _out_dtype is None and _ag().needs_grad(jagged, weight, bias, weight_p, bias_p):
+        return _ag().IndexSelectJaggedBmmSwigluFn.apply(offsets, index, jagged, weight, bias, weight_p, bias_p)
     if _out_dtype is None and _wants_fp32_split(jagged, weight, weight_p):
         return index_select_jagged_bmm_swiglu(max_seq_len, offsets, index, split_f32_rows(jagged, 0),
                                               split_f32_weight(weight), bias, split_f32_weight(weight_p), bias_p,
@@ -355,6 +365,8 @@ def mul_merge_k_add(
     assert index.ndim == 1 and reverse_index.ndim == 2
     assert N == L * K and N == value.shape[0]
     _check_float(value, "value")
+    if _ag().needs_grad(value, weight):
+        return _ag().MulMergeKAddFn.apply(index, reverse_index, value, weight, weight_index)
     dev = _lib.require_cuda(reverse_index, value, weight, weight_index)
     lib = _lib.load()
     w = None
@@ -410,6 +422,7 @@ def silu_jagged_bmm(
     out_row_index: Optional[torch.Tensor] = None,
     *,
     _out_dtype: Optional[torch.dtype] = None,
+    _act_scratch: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """[silu](jagged) @ weight[e] + bias[e] per expert segment; weight is logical [E, K, N]
     (the GEMM half of silu_jagged_bmm_combine, kernels/pytorch/moe.py:255-275).
@@ -417,7 +430,7 @@ def silu_jagged_bmm(
     of the result land at out[out_row_index[r]]."""
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype
-    if _out_dtype is None and _wants_fp32_split(jagged, weight):
+    if _out_dtype is None and _act_scratch is None and _wants_fp32_split(jagged, weight):
         # SiLU is applied while the activations are expanded
         return silu_jagged_bmm(offsets, split_f32_rows(jagged, 0, apply_silu=has_silu), split_f32_weight(weight), bias,
                                has_silu=False, out_row_index=out_row_index, _out_dtype=torch.float32)
@@ -433,7 +446,11 @@ def silu_jagged_bmm(
     b = _prep_bias(bias, od)
     off = _index_i64(offsets)
     out = torch.empty((rows, N), dtype=od, device=dev)
-    scratch = torch.empty((rows, kp), dtype=jagged.dtype, device=dev) if has_silu else None
+    scratch = None
+    if has_silu:
+        # receives silu(jagged); a caller that wants to keep it (the backward pass) passes the buffer
+        ok = _act_scratch is not None and kp == K and tuple(_act_scratch.shape) == (rows, K) and _act_scratch.is_contiguous()
+        scratch = _act_scratch if ok else torch.empty((rows, kp), dtype=jagged.dtype, device=dev)
     oidx = None if out_row_index is None else _index_i64(out_row_index.reshape(-1))
     assert oidx is None or oidx.numel() == rows
     dt = _lib.dtype_code(jagged.dtype)
@@ -519,6 +536,12 @@ def silu_jagged_bmm_combine(
         raise NotImplementedError("TRITON_CC is not supported for silu_jagged_bmm_combine")
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype
+    if out is None and _ag().needs_grad(jagged, weight, bias, gating_scores):
+        g_in = gating_scores
+        if g_in is not None and round_scores:
+            g_in = g_in.to(jagged.dtype)
+        return _ag().SiluJaggedBmmCombineFn.apply(offsets, jagged, weight, bias, index, reverse_index, g_in, gates_index,
+                                                  has_silu)
     if _wants_fp32_split(jagged, weight) and out is None:
         # fp32 accuracy: the GEMM on the expanded operands (f32 result rows), then the
         # deterministic fp32 merge; the operand types of the merge are those of the reference

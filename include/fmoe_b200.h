@@ -356,6 +356,53 @@ int fmoe_ep_down_projection(const int64_t* offsets_local, int64_t capacity, int6
                             int64_t back_rows, int64_t ld_back, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Backward pass of the expert products. The reference implements each operator's backward as
+ * Triton kernels of its own; here every matrix product of the backward pass is the grouped GEMM
+ * above on differently laid out operands, and these entry points provide the layouts and the
+ * elementwise derivatives. The Python mirror (fast_moe_b200/kernels/autograd.py) assembles them
+ * into torch.autograd.Functions with the reference operators' signatures.
+ *
+ * d_jagged (kernels/triton/triton_moe.py:290-381 _jagged_bmm_index_add, :3474-3559): rows of d_out
+ *   times weight[e]^T is fmoe_silu_jagged_bmm / fmoe_index_select_jagged_bmm on the transposed
+ *   weight; fmoe_batched_transpose produces it (out[b, c, r] = in[b, r, c]; strides in elements),
+ *   and fmoe_mul_merge_k_add sums the k rows of every token.
+ * d_weight (:389-516, :1576-1976 _jagged_jagged_bmm*): dW[e] = A_e^T B_e, a product whose reduction
+ *   runs over the rows of expert e. fmoe_jagged_pad_offsets turns offsets [E+1] into kseg [E+1], each
+ *   expert's row count rounded up to whole K steps of 128 bytes (at least one);
+ *   fmoe_jagged_transpose_pad writes out[c, kseg[e] + j] = in[src(offsets[e] + j), c] (zeros in
+ *   the padding; src(r) = index[r] / index_div when index is given, else r; ld_out >= rows + E * 128 /
+ *   element size); fmoe_jagged_jagged_bmm multiplies the two transposed operands a_t [M, padded],
+ *   b_t [N, padded] in the grouped GEMM's reduction-over-rows mode: out[e * M + m, n] = sum over
+ *   expert e's padded range of a_t[m, r] * b_t[n, r]. group_offsets is the uniform [0, M, 2M, ...].
+ * d_bias (:1997-2140 _jagged_reduce_sum): fmoe_jagged_colsum, out[e, n] = sum of x[r, n] over the
+ *   rows of expert e (fp32 accumulation).
+ * combine backward (:922-983 _mul_merge_k_add_bwd): fmoe_gather_scale_rows,
+ *   out[p, :] = src[index[p] / index_div, :] * weight[weight_index[p]] (weight NULL: plain gather),
+ *   and fmoe_row_dot, out[p] = <a[p, :], b[index[p] / index_div, :]> in fp32 (index NULL: b[p]).
+ * activations (:62-106 _fused_swiglu_backward_kernel; triton_general_ops.py:325-344 SiLU backward):
+ *   fmoe_activation_backward mode 0: d_alpha = d_out * silu'(alpha); mode 1 (out = silu(alpha) *
+ *   beta): d_alpha = d_out * beta * silu'(alpha), d_beta = d_out * silu(alpha). */
+int fmoe_batched_transpose(const void* in, int dtype, int batch, int64_t in_sb, int64_t ld_in, int rows, int cols,
+                           void* out, int64_t out_sb, int64_t ld_out, void* stream);
+int fmoe_jagged_pad_offsets(const int64_t* offsets, int E, int dtype, int64_t* kseg, void* stream);
+int fmoe_jagged_transpose_pad(const void* in, int dtype, int64_t in_rows, int64_t ld_in, const int64_t* index,
+                              int index_div, const int64_t* offsets, const int64_t* kseg, int E, int64_t rows, int cols,
+                              void* out, int64_t ld_out, void* stream);
+int fmoe_jagged_jagged_bmm(const int64_t* group_offsets, const int64_t* kseg, int64_t padded_rows, const void* a_t,
+                           int64_t lda, const void* b_t, int64_t ldb, int dtype, int E, int M, int N, void* out,
+                           int out_dtype, int64_t ldo, void* stream);
+int fmoe_jagged_colsum(const void* x, int dtype, int64_t ldx, const int64_t* offsets, int E, int N, void* out,
+                       int out_dtype, void* stream);
+int fmoe_gather_scale_rows(const void* src, int dtype, int64_t src_rows, int64_t lds, const int64_t* index,
+                           int index_div, const void* weight, int w_dtype, const int64_t* weight_index,
+                           int64_t weight_count, int64_t rows, int cols, void* out, int64_t ldo, void* stream);
+int fmoe_row_dot(const void* a, int64_t lda, const void* b, int64_t b_rows, int64_t ldb, int dtype,
+                 const int64_t* index, int index_div, int64_t rows, int cols, float* out, void* stream);
+int fmoe_activation_backward(int mode, const void* d_out, int64_t ldd, const void* alpha, int64_t lda, const void* beta,
+                             int64_t ldb, int dtype, int64_t rows, int cols, void* d_alpha, int64_t ldda, void* d_beta,
+                             int64_t lddb, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * FP8 rowwise quantisation.
  * pytorch_rowwise_quant_fp8 + calculate_scale (kernels/pytorch/quant_fp8.py:13-34), and with
  * apply_silu != 0 pytorch_silu_jagged_fp8 (kernels/pytorch/moe_fp8.py:17-33):

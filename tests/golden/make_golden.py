@@ -315,7 +315,71 @@ def mrn_cases(ref):
         save(f"mrn_{ci}", rec)
 
 
-GROUPS = {"layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases,
+def grad_cases(ref):
+    """Gradients of the operators: torch autograd through the reference's PYTORCH functions on CPU
+    in fp32 (what its own tests use as the reference for the Triton backward,
+    kernels/tests/moe_test.py:35-129, :299-400, :729-949, :951-1133), with the same generators:
+    U(-1, 1) data, dout = randn * 0.01."""
+    cases = [
+        # (L, E, k, D_in, D_hidden, D_out, bias, has_silu, seed)
+        (100, 4, 2, 32, 64, 32, True, True, 40),
+        (200, 8, 4, 32, 48, 40, True, False, 41),
+        (37, 16, 2, 12, 32, 24, False, True, 42),       # K = 12 (padding), empty experts likely
+        (130, 4, 2, 64, 128, 64, True, True, 43),
+    ]
+    for ci, (L, E, k, d, h, o, use_bias, has_silu, seed) in enumerate(cases):
+        torch.manual_seed(seed)
+        idx, gi, ti, off, rev = routing_case(ref, L, E, k, seed)
+        msl = int((off[1:] - off[:-1]).max())
+        u = lambda *shape: torch.empty(*shape).uniform_(-1, 1)
+        x = u(L, d).requires_grad_()
+        w1 = u(E, d, h).requires_grad_()
+        w1p = u(E, d, h).requires_grad_()
+        b1 = u(E, h).requires_grad_() if use_bias else None
+        b1p = u(E, h).requires_grad_() if use_bias else None
+        w2 = u(E, h, o).requires_grad_()
+        b2 = u(E, o).requires_grad_() if use_bias else None
+        gates = torch.rand(L, k).requires_grad_()
+        rec = dict(k=k, E=E, has_silu=int(has_silu), topk_idx=idx, gate_index=gi, token_index=ti, offsets=off, reverse_index=rev,
+                   x=x, w1=w1, w1p=w1p, w2=w2, gates=gates)
+        if use_bias:
+            rec.update(b1=b1, b1p=b1p, b2=b2)
+
+        def grads(out, dout, named):
+            ts = [t for _, t in named if t is not None]
+            gs = torch.autograd.grad(out, ts, dout, allow_unused=False)
+            return {n: g for (n, t), g in zip([(n, t) for n, t in named if t is not None], gs)}
+
+        # up projection
+        up = ref.moe.index_select_jagged_bmm(msl, off, gi.view(-1, k), x, w1, b1)
+        d_up = torch.randn_like(up) * 0.01
+        for n, g in grads(up, d_up, [("x", x), ("w1", w1), ("b1", b1)]).items():
+            rec["up_d_" + n] = g
+        rec.update(up_out=up, up_dout=d_up)
+        # SwiGLU up projection
+        sw = ref.moe.index_select_jagged_bmm_swiglu(msl, off, gi.view(-1, k), x, w1, b1, w1p, b1p)
+        d_sw = torch.randn_like(sw) * 0.01
+        for n, g in grads(sw, d_sw, [("x", x), ("w1", w1), ("b1", b1), ("w1p", w1p), ("b1p", b1p)]).items():
+            rec["sw_d_" + n] = g
+        rec.update(sw_out=sw, sw_dout=d_sw)
+        # down projection + combine on a fresh hidden tensor
+        hid = u(L * k, h).requires_grad_()
+        y = ref.moe.silu_jagged_bmm_combine(msl, off, hid, w2, b2, ti, rev, gates, gi, has_silu=has_silu)
+        d_y = torch.randn_like(y) * 0.01
+        for n, g in grads(y, d_y, [("hid", hid), ("w2", w2), ("b2", b2), ("gates", gates)]).items():
+            rec["down_d_" + n] = g
+        rec.update(hid=hid, down_out=y, down_dout=d_y)
+        # combine alone
+        val = u(L * k, o).requires_grad_()
+        z = ref.moe.mul_merge_k_add(ti, rev, val, weight=gates, weight_index=gi)
+        d_z = torch.randn_like(z) * 0.01
+        for n, g in grads(z, d_z, [("val", val), ("gates", gates)]).items():
+            rec["comb_d_" + n] = g
+        rec.update(val=val, comb_out=z, comb_dout=d_z)
+        save(f"grad_{ci}", rec)
+
+
+GROUPS = {"grad": grad_cases, "layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases,
           "mrn": mrn_cases}
 
 

@@ -1,0 +1,120 @@
+"""Backward pass of the operators on the GPU against gradients recorded from the reference:
+torch autograd through its PYTORCH functions on CPU in fp32 (tests/golden/make_golden.py, group
+"grad"), the same reference and the same generators (U(-1, 1) data, dout = randn * 0.01) its own
+backward tests use (kernels/tests/moe_test.py:35-129, :299-400, :951-1133).
+
+Bars: float32 operands run the forward in fp32 accuracy and the backward products d_x likewise;
+the weight-gradient product uses tf32 tensor-core math, so float32 gradients are held to rtol 1e-2
+of the tensor's largest magnitude; bfloat16 to the reference's own bf16 bound for gradients
+(rtol 1e-2 with atol scaled by the tensor's magnitude, kernels/tests/moe_test.py:60-66)."""
+import pytest
+import torch
+
+import fast_moe_b200 as fm
+from fast_moe_b200 import _lib
+from fast_moe_b200.kernels import autograd as AG
+from tests import golden_io as G
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def leaf(t, dt):
+    return None if t is None else t.to(dt).to(DEV).requires_grad_()
+
+
+def close(got, want, dt, what):
+    want = want.float()
+    scale = max(float(want.abs().max()), 1e-6)
+    tol = 1e-2 if dt == torch.float32 else 2.5e-2
+    err = float((got.detach().float().cpu() - want).abs().max())
+    assert err <= tol * scale, f"{what}: max err {err:.3e} vs {tol:.0e} x {scale:.3e}"
+
+
+@pytest.mark.parametrize("name", G.names("grad_"))
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kmajor", [False, True])
+def test_operator_gradients_against_reference_autograd(name, dt, kmajor):
+    g = G.load(name)
+    k, E = g["k"], g["E"]
+    off, gi = g["offsets"].to(DEV), g["gate_index"].to(DEV)
+    ti, rev = g["token_index"].to(DEV), g["reverse_index"].to(DEV)
+    index = gi.view(-1, k)
+
+    def weight_leaf(w):
+        # both weight layouts of the reference's tests: plain [E, K, N], and stored [E, N, K]
+        w = w.to(dt).to(DEV)
+        if kmajor:
+            w = w.permute(0, 2, 1).contiguous().permute(0, 2, 1)
+        return w.detach().requires_grad_()
+
+    # ---- up projection
+    x, w1, b1 = leaf(g["x"], dt), weight_leaf(g["w1"]), leaf(g.get("b1"), dt)
+    out = fm.index_select_jagged_bmm(0, off, index, x, w1, b1)
+    assert out.requires_grad
+    close(out, g["up_out"], dt, "up forward")
+    out.backward(g["up_dout"].to(dt).to(DEV))
+    close(x.grad, g["up_d_x"], dt, "up d_x")
+    close(w1.grad, g["up_d_w1"], dt, "up d_w")
+    if b1 is not None:
+        close(b1.grad, g["up_d_b1"], dt, "up d_bias")
+    # ---- SwiGLU up projection
+    x, w1, w1p = leaf(g["x"], dt), weight_leaf(g["w1"]), weight_leaf(g["w1p"])
+    b1, b1p = leaf(g.get("b1"), dt), leaf(g.get("b1p"), dt)
+    out = fm.index_select_jagged_bmm_swiglu(0, off, index, x, w1, b1, w1p, b1p)
+    close(out, g["sw_out"], dt, "swiglu forward")
+    out.backward(g["sw_dout"].to(dt).to(DEV))
+    close(x.grad, g["sw_d_x"], dt, "swiglu d_x")
+    close(w1.grad, g["sw_d_w1"], dt, "swiglu d_w")
+    close(w1p.grad, g["sw_d_w1p"], dt, "swiglu d_wp")
+    if b1 is not None:
+        close(b1.grad, g["sw_d_b1"], dt, "swiglu d_bias")
+        close(b1p.grad, g["sw_d_b1p"], dt, "swiglu d_bias_p")
+    # ---- down projection + combine
+    hid, w2, b2, gates = leaf(g["hid"], dt), weight_leaf(g["w2"]), leaf(g.get("b2"), dt), leaf(g["gates"], dt)
+    y = fm.silu_jagged_bmm_combine(0, off, hid, w2, b2, ti, rev, gates, gi, has_silu=bool(g["has_silu"]))
+    close(y, g["down_out"], dt, "down forward")
+    y.backward(g["down_dout"].to(dt).to(DEV))
+    close(hid.grad, g["down_d_hid"], dt, "down d_jagged")
+    close(w2.grad, g["down_d_w2"], dt, "down d_w")
+    close(gates.grad, g["down_d_gates"], dt, "down d_gates")
+    if b2 is not None:
+        close(b2.grad, g["down_d_b2"], dt, "down d_bias")
+    # ---- combine alone
+    val, gates = leaf(g["val"], dt), leaf(g["gates"], dt)
+    z = fm.mul_merge_k_add(ti, rev, val, weight=gates, weight_index=gi)
+    close(z, g["comb_out"], dt, "combine forward")
+    z.backward(g["comb_dout"].to(dt).to(DEV))
+    close(val.grad, g["comb_d_val"], dt, "combine d_value")
+    close(gates.grad, g["comb_d_gates"], dt, "combine d_weight")
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+def test_weight_gradient_product_with_empty_and_ragged_experts():
+    """dW[e] = X_e^T dOut_e through the transposed, padded operands and the grouped GEMM's
+    reduction-over-rows mode, against per-expert matmuls: experts with 0, 1, 63, 64, 65 and 1000
+    rows (K steps are 64 bf16 rows), output dims that are not tile multiples."""
+    lens = [0, 1, 63, 64, 65, 0, 1000, 7]
+    E, N, K = len(lens), 200, 72
+    off = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    rows = int(off[-1])
+    gen = torch.Generator().manual_seed(3)
+    d_out = torch.randn(rows, N, generator=gen).bfloat16()
+    x = torch.randn(rows, K, generator=gen).bfloat16()
+    got = AG.grad_weight(off.to(DEV), d_out.to(DEV), x.to(DEV), E, torch.float32)
+    assert got.shape == (E, K, N)
+    for e in range(E):
+        a, b = int(off[e]), int(off[e + 1])
+        want = x[a:b].float().t() @ d_out[a:b].float()
+        torch.testing.assert_close(got[e].cpu(), want, rtol=1e-3, atol=1e-3 * max(1.0, float(want.abs().max())))
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+def test_no_grad_calls_take_the_forward_only_path():
+    g = G.load(G.names("grad_")[0])
+    k = g["k"]
+    x = g["x"].bfloat16().to(DEV).requires_grad_()
+    w = g["w1"].bfloat16().to(DEV).requires_grad_()
+    with torch.no_grad():
+        out = fm.index_select_jagged_bmm(0, g["offsets"].to(DEV), g["gate_index"].to(DEV).view(-1, k), x, w, None)
+    assert not out.requires_grad
