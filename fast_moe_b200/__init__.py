@@ -17,7 +17,7 @@ from .kernels.moe import (
 )
 from .kernels.routing import RoutingMetadata, gate_topk, gate_topk_normalized, route_metadata, token_norm
 from .kernels.utils import KernelType
-from .modules.fast_moe_module import (CapturedForward, FastMoELayer, GatingNetwork, StreamingForward,
+from .modules.fast_moe_module import (CapturedForward, FastMoELayer, GatingNetwork, HostPipeline, StreamingForward,
                                       SwiGLUFastMoELayer)
 from .modules.sg_moe import MRNOutput, SGConfig, SGMoELayer
 
@@ -27,6 +27,7 @@ __all__ = [
     "SwiGLUFastMoELayer",
     "CapturedForward",
     "StreamingForward",
+    "HostPipeline",
     "KernelType",
     "IndexSelectJaggedBmmOption",
     "SiluJaggedBmmCombineOption",

@@ -100,6 +100,8 @@ SIGNATURES = {
     "fmoe_ep_up_projection": (c_int, [P, I64, I64, P, c_int, I64, P, P, I64, I64, c_int, c_int, c_int, P, I64, P]),
     "fmoe_ep_down_projection": (c_int, [P, I64, I64, P, c_int, I64, P, I64, I64, c_int, c_int, c_int, P, P, c_int, I64,
                                         I64, P]),
+    "fmoe_router_backward": (c_int, [P, P, P, I64, c_int, c_int, P, P]),
+    "fmoe_gate_linear_backward": (c_int, [P, P, c_int, I64, P, I64, c_int, c_int, P, I64, P, P, P]),
     "fmoe_batched_transpose": (c_int, [P, c_int, c_int, I64, I64, c_int, c_int, P, I64, I64, P]),
     "fmoe_jagged_pad_offsets": (c_int, [P, c_int, c_int, P, P]),
     "fmoe_jagged_transpose_pad": (c_int, [P, c_int, I64, I64, P, c_int, P, P, c_int, I64, c_int, P, I64, P]),

@@ -210,6 +210,81 @@ activation_backward_kernel(int mode, const T* __restrict__ d_out, long long ldd,
   }
 }
 
+// Router backward. The forward keeps the k largest softmax probabilities of a token and
+// renormalises them to sum 1 (modules/fast_moe_module.py:93-105): y_j = p_j / sum_sel p, which is
+// the softmax over the k selected logits alone. So d_logit_j = y_j (dy_j - sum_i y_i dy_i) for the
+// selected experts and 0 for the others. One thread per token (k is small).
+__global__ void __launch_bounds__(256)
+router_backward_kernel(const long long* __restrict__ topk_idx, const float* __restrict__ y, const float* __restrict__ dy,
+                       long long L, int E, int k, float* __restrict__ d_logits, int* status) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= L) return;
+  float* row = d_logits + t * E;
+  for (int e = 0; e < E; ++e) row[e] = 0.f;
+  float dot = 0.f;
+  for (int s = 0; s < k; ++s) dot = fmaf(y[t * k + s], dy[t * k + s], dot);
+  for (int s = 0; s < k; ++s) {
+    const long long e = topk_idx[t * k + s];
+    if (e < 0 || e >= E) {
+      atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+      continue;
+    }
+    row[e] = y[t * k + s] * (dy[t * k + s] - dot);
+  }
+}
+
+// d_x[t, c] = sum_e d_logits[t, e] * W[e, c]: one block per token, threads over the columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_dx_kernel(const float* __restrict__ d_logits, const float* __restrict__ w, long long L, int d, int E, T* __restrict__ dx,
+               long long lddx) {
+  extern __shared__ float s_dl[];
+  const long long t = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_dl[e] = d_logits[t * E + e];
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int e = 0; e < E; ++e) acc = fmaf(s_dl[e], w[static_cast<long long>(e) * d + c], acc);
+    stf(dx + t * lddx + c, acc);
+  }
+}
+
+// d_W[e, c] += sum over a chunk of tokens of d_logits[t, e] * x[t, c]; d_b[e] += sum of d_logits[t, e].
+// A block owns 256 columns and one chunk of tokens, keeps 32 experts' partial sums per thread in
+// registers and adds them to the fp32 result (cleared beforehand) with atomics.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_dw_kernel(const float* __restrict__ d_logits, const T* __restrict__ x, long long ldx, long long L, int d, int E,
+               int tokens_per_chunk, float* __restrict__ dw, float* __restrict__ db) {
+  __shared__ float s_dl[32];
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long t0 = static_cast<long long>(blockIdx.y) * tokens_per_chunk;
+  const long long t1 = min(L, t0 + tokens_per_chunk);
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    const int ne = min(32, E - e0);
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    float bsum = 0.f;                      // thread i < ne of column block 0 also sums expert e0 + i's bias gradient
+    for (long long t = t0; t < t1; ++t) {
+      __syncthreads();
+      if (threadIdx.x < ne) s_dl[threadIdx.x] = d_logits[t * E + e0 + threadIdx.x];
+      __syncthreads();
+      const float xv = c < d ? ldf<T>(x + t * ldx + c) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ne) acc[i] = fmaf(s_dl[i], xv, acc[i]);
+      if (blockIdx.x == 0 && threadIdx.x < ne) bsum += s_dl[threadIdx.x];
+    }
+    if (c < d) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ne) atomicAdd(dw + static_cast<long long>(e0 + i) * d + c, acc[i]);
+    }
+    if (db != nullptr && blockIdx.x == 0 && threadIdx.x < ne) atomicAdd(db + e0 + threadIdx.x, bsum);
+  }
+}
+
 int grid_for(long long work, int per_block) {
   long long b = (work + per_block - 1) / per_block;
   if (b > 148 * 32) b = 148 * 32;
@@ -400,5 +475,57 @@ extern "C" int fmoe_activation_backward(int mode, const void* d_out, int64_t ldd
   }
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_router_backward(const int64_t* topk_idx, const float* topk_score, const float* d_score, int64_t L, int E,
+                                    int k, float* d_logits, void* stream) {
+  FMOE_REQUIRE(L >= 0 && E >= 1 && k >= 1 && k <= E, "router_backward: L=%lld E=%d k=%d", (long long)L, E, k);
+  if (L == 0) return FMOE_OK;
+  FMOE_REQUIRE(topk_idx && topk_score && d_score && d_logits, "router_backward: NULL pointer argument");
+  int err = 0;
+  int* status = device_status_ptr(&err);
+  if (!status) return err;
+  router_backward_kernel<<<static_cast<unsigned>((L + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(topk_idx), topk_score, d_score, L, E, k, d_logits, status);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_gate_linear_backward(const float* d_logits, const void* x, int x_dtype, int64_t ldx,
+                                         const float* gate_w, int64_t L, int d, int E, void* d_x, int64_t lddx,
+                                         float* d_gate_w, float* d_gate_b, void* stream) {
+  FMOE_REQUIRE(x_dtype == FMOE_BF16 || x_dtype == FMOE_F32, "gate_linear_backward: x must be bf16 or f32");
+  FMOE_REQUIRE(L >= 0 && d >= 1 && E >= 1, "gate_linear_backward: bad sizes");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d_gate_w) FMOE_CUDA_OK(cudaMemsetAsync(d_gate_w, 0, static_cast<size_t>(E) * d * sizeof(float), st));
+  if (d_gate_b) FMOE_CUDA_OK(cudaMemsetAsync(d_gate_b, 0, static_cast<size_t>(E) * sizeof(float), st));
+  if (L == 0) return FMOE_OK;
+  FMOE_REQUIRE(d_logits && x && gate_w, "gate_linear_backward: NULL pointer argument");
+  if (d_x != nullptr) {
+    const size_t smem = static_cast<size_t>(E) * sizeof(float);
+    if (x_dtype == FMOE_BF16) {
+      gate_dx_kernel<__nv_bfloat16><<<static_cast<unsigned>(L), 256, smem, st>>>(d_logits, gate_w, L, d, E,
+                                                                               static_cast<__nv_bfloat16*>(d_x), lddx);
+    } else {
+      gate_dx_kernel<float><<<static_cast<unsigned>(L), 256, smem, st>>>(d_logits, gate_w, L, d, E, static_cast<float*>(d_x), lddx);
+    }
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+  }
+  if (d_gate_w != nullptr) {
+    const int chunk = 256;
+    dim3 grid((d + 255) / 256, static_cast<unsigned>((L + chunk - 1) / chunk), 1);
+    if (x_dtype == FMOE_BF16) {
+      gate_dw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(d_logits, static_cast<const __nv_bfloat16*>(x), ldx, L, d, E, chunk,
+                                                           d_gate_w, d_gate_b);
+    } else {
+      gate_dw_kernel<float><<<grid, 256, 0, st>>>(d_logits, static_cast<const float*>(x), ldx, L, d, E, chunk, d_gate_w,
+                                                   d_gate_b);
+    }
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+  }
   return FMOE_OK;
 }

@@ -335,5 +335,49 @@ class SiluJaggedBmmCombineFn(torch.autograd.Function):
         return None, d_jagged, d_weight, d_bias, None, None, d_gates, None, None
 
 
+class RouterFn(torch.autograd.Function):
+    """gate Linear -> softmax -> top-k -> renormalised scores (fmoe_gate_topk) with the backward the
+    reference gets from autograd through its eager routing code (modules/fast_moe_module.py:21-27,
+    :93-135). Returns (topk_idx [L, k] int64, not differentiable; scores [L, k] f32)."""
+
+    @staticmethod
+    def forward(ctx, x, gate_weight, gate_bias, k):
+        from .routing import gate_topk
+
+        with torch.no_grad():
+            idx, score, _ = gate_topk(x, gate_weight, gate_bias, k)
+        ctx.save_for_backward(x, gate_weight, idx, score)
+        ctx.has_bias = gate_bias is not None
+        ctx.mark_non_differentiable(idx)
+        return idx, score
+
+    @staticmethod
+    def backward(ctx, _d_idx, d_score):
+        x, gate_weight, idx, score = ctx.saved_tensors
+        lib = _lib.load()
+        dev = x.device
+        L, d = x.shape
+        E = gate_weight.shape[0]
+        k = idx.shape[1]
+        with torch.no_grad():
+            dy = d_score.to(torch.float32).contiguous()
+            d_logits = torch.empty((L, E), dtype=torch.float32, device=dev)
+            gw = gate_weight.detach().to(torch.float32).contiguous()
+            xx = x if x.stride(1) == 1 else x.contiguous()
+            d_x = torch.empty_like(xx) if ctx.needs_input_grad[0] else None
+            d_w = torch.empty((E, d), dtype=torch.float32, device=dev) if ctx.needs_input_grad[1] else None
+            d_b = torch.empty(E, dtype=torch.float32, device=dev) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+            with torch.cuda.device(dev):
+                st = _lib.stream_ptr(dev)
+                _lib.check(lib.fmoe_router_backward(idx.data_ptr(), score.data_ptr(), dy.data_ptr(), L, E, k,
+                                                    d_logits.data_ptr(), st))
+                _lib.check(lib.fmoe_gate_linear_backward(d_logits.data_ptr(), xx.data_ptr(), _lib.dtype_code(xx.dtype),
+                                                         xx.stride(0) if L else d, gw.data_ptr(), L, d, E, _lib.ptr(d_x),
+                                                         d, _lib.ptr(d_w), _lib.ptr(d_b), st))
+            if d_w is not None and d_w.dtype != gate_weight.dtype:
+                d_w = d_w.to(gate_weight.dtype)
+        return d_x, d_w, d_b, None
+
+
 def needs_grad(*tensors) -> bool:
     return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)

@@ -81,6 +81,15 @@ class _SplitCache:
         return t
 
 
+def _training_graph(x: torch.Tensor, module: nn.Module) -> bool:
+    """True when this forward has to record an autograd graph: the layer was switched to
+    ``autograd = True`` (the default, False, keeps every call on the fused inference path without
+    the caller having to wrap it in ``torch.no_grad()``), autograd is recording, and x or a
+    parameter requires a gradient."""
+    return (getattr(module, "autograd", False) and torch.is_grad_enabled()
+            and (x.requires_grad or any(p.requires_grad for p in module.parameters())))
+
+
 def _fp32_exact(dt: torch.dtype) -> bool:
     return dt == torch.float32 and not ops.fp32_uses_tf32()
 
@@ -147,6 +156,10 @@ def route_tokens(x_flat: torch.Tensor, gate: nn.Linear, k: int, num_experts: int
 
 class _MoEBase(nn.Module):
     num_experts: int
+    # False: forward only (the fused inference path, whatever torch's grad mode says). True: when
+    # autograd is recording and x or a parameter requires a gradient, the forward runs as autograd
+    # Functions (router, projections, combine) and backward() works as it does on the reference.
+    autograd = False
     # Fold the gate-weighted combine into the down-projection GEMM (atomic adds into the token
     # rows). "auto": only when k <= 2, where two commutative additions keep the result
     # bit-reproducible; True / False force it on / off.
@@ -199,8 +212,36 @@ class FastMoELayer(_MoEBase):
         self._cast = _CastCache()
         self._split = _SplitCache()
 
-    @torch.no_grad()
     def forward(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
+        """Forward pass. When a gradient is needed (x or any parameter requires one and autograd
+        is recording) the operators run as autograd Functions - the reference's own composition:
+        index_select_jagged_bmm, then silu_jagged_bmm_combine(has_silu=True)
+        (modules/fast_moe_module.py:146-186) - otherwise as the fused inference path."""
+        if _training_graph(x, self):
+            return self._forward_with_grad(x, num_experts_per_tok)
+        with torch.no_grad():
+            return self._forward_inference(x, num_experts_per_tok)
+
+    def _forward_with_grad(self, x: torch.Tensor, k: int) -> torch.Tensor:
+        from ..kernels.autograd import RouterFn
+
+        shape = x.shape
+        _lib.require_cuda(x)
+        x_flat = x.reshape(-1, self.input_dim)
+        dt = x.dtype
+        idx, score = RouterFn.apply(x_flat, self.gate.gate.weight, self.gate.gate.bias, k)
+        meta = route_metadata(idx, self.num_experts)
+        with record_function("## expert_forward##"):
+            cast = lambda p: p if p.dtype == dt else p.to(dt)
+            hidden = ops.index_select_jagged_bmm(0, meta.offsets, meta.gate_index.view(-1, k), x_flat,
+                                                 cast(self._experts_hidden_w).permute(0, 2, 1), cast(self._experts_hidden_bias))
+            y = ops.silu_jagged_bmm_combine(0, meta.offsets, hidden, cast(self._experts_w).permute(0, 2, 1),
+                                            cast(self._experts_bias), meta.token_index, meta.reverse_index,
+                                            gating_scores=score, gates_index=meta.gate_index, has_silu=True,
+                                            round_scores=True)
+        return y.view(*shape[:-1], self.output_dim)
+
+    def _forward_inference(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
         shape = x.shape
         k = num_experts_per_tok
         x_flat = x.reshape(-1, self.input_dim)
@@ -290,8 +331,33 @@ class SwiGLUFastMoELayer(_MoEBase):
             for name in ("w_gate", "w_up", "w_down")
         }
 
-    @torch.no_grad()
     def forward(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
+        """Forward pass; with a gradient needed (and no FP8) the operators run as autograd
+        Functions: index_select_jagged_bmm_swiglu, then silu_jagged_bmm_combine(has_silu=False)."""
+        if not self.fp8 and _training_graph(x, self):
+            return self._forward_with_grad(x, num_experts_per_tok)
+        with torch.no_grad():
+            return self._forward_inference(x, num_experts_per_tok)
+
+    def _forward_with_grad(self, x: torch.Tensor, k: int) -> torch.Tensor:
+        from ..kernels.autograd import RouterFn
+
+        shape = x.shape
+        _lib.require_cuda(x)
+        x_flat = x.reshape(-1, self.input_dim)
+        dt = x.dtype
+        idx, score = RouterFn.apply(x_flat, self.gate.gate.weight, self.gate.gate.bias, k)
+        meta = route_metadata(idx, self.num_experts)
+        cast = lambda p: p if p.dtype == dt else p.to(dt)
+        hidden = ops.index_select_jagged_bmm_swiglu(0, meta.offsets, meta.gate_index.view(-1, k), x_flat,
+                                                    cast(self.w_gate).permute(0, 2, 1), None,
+                                                    cast(self.w_up).permute(0, 2, 1), None)
+        y = ops.silu_jagged_bmm_combine(0, meta.offsets, hidden, cast(self.w_down).permute(0, 2, 1), None,
+                                        meta.token_index, meta.reverse_index, gating_scores=score,
+                                        gates_index=meta.gate_index, has_silu=False, round_scores=True)
+        return y.view(*shape[:-1], self.output_dim)
+
+    def _forward_inference(self, x: torch.Tensor, num_experts_per_tok: int) -> torch.Tensor:
         shape = x.shape
         k = num_experts_per_tok
         x_flat = x.reshape(-1, self.input_dim)
@@ -493,3 +559,68 @@ class StreamingForward:
         avg = lambda a, b: sum(a[s].elapsed_time(b[s]) for s in used) / len(used)
         return dict(h2d=avg(self.in_start, self.in_ready), forward=avg(self.run_start, self.run_done),
                     d2h=avg(self.out_start, self.out_done))
+
+
+class HostPipeline:
+    """Host-to-host forward with ONE launch per batch: every slot owns a pinned input buffer, a
+    pinned output buffer, a stream and a CUDA graph that holds the slot's host-to-device copy, the
+    forward and the device-to-host copy. ``launch(s)`` replays slot s's graph on its stream;
+    consecutive batches go to different slots, so the copies of one batch overlap the forward of
+    another (copy engines and SMs work side by side) while the host issues a single call per batch
+    - at small batch sizes the per-batch host work of ``StreamingForward`` (stream switches, event
+    records and waits) is otherwise the slowest part of the pipeline.
+
+    The caller writes a batch into ``host_in[s]`` (pinned: fill it in place), calls ``launch(s)``,
+    and reads ``host_out[s]`` after ``wait(s)``. Shapes, dtype and ``k`` are fixed at construction;
+    the layer must not synchronise with the host inside its forward."""
+
+    def __init__(self, layer: nn.Module, example: torch.Tensor, num_experts_per_tok: int, slots: int = 3,
+                 out_shape: Optional[Tuple[int, ...]] = None) -> None:
+        if not example.is_cuda:
+            raise RuntimeError("HostPipeline needs a CUDA example tensor (shape and dtype of one batch)")
+        if _lib._stage_timer is not None:
+            raise RuntimeError("stage timing records events and cannot be captured; disable it first")
+        dev = example.device
+        self.device = dev
+        self.k = num_experts_per_tok
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(slots)]
+        self.host_in = [torch.empty(example.shape, dtype=example.dtype).pin_memory() for _ in range(slots)]
+        self.x = [torch.empty_like(example) for _ in range(slots)]
+        self.graphs, self.y, self.host_out = [], [], []
+        cur = torch.cuda.current_stream(dev)
+        for s in range(slots):
+            st = self.streams[s]
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                self.x[s].copy_(example)
+                for _ in range(2):
+                    y = layer(self.x[s], self.k)
+                st.synchronize()
+                self.host_out.append(torch.empty(y.shape, dtype=y.dtype).pin_memory())
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    self.x[s].copy_(self.host_in[s], non_blocking=True)
+                    y = layer(self.x[s], self.k)
+                    self.host_out[s].copy_(y, non_blocking=True)
+                self.graphs.append(g)
+                self.y.append(y)
+        for st in self.streams:
+            st.synchronize()
+
+    def launch(self, slot: int) -> None:
+        """Queue slot's batch: host_in[slot] -> device -> forward -> host_out[slot]."""
+        with torch.cuda.stream(self.streams[slot]):
+            self.graphs[slot].replay()
+
+    def wait(self, slot: int) -> None:
+        self.streams[slot].synchronize()
+
+    def drain(self) -> None:
+        """Make the current stream wait for every batch queued so far (no host block)."""
+        cur = torch.cuda.current_stream(self.device)
+        for st in self.streams:
+            cur.wait_stream(st)
+
+    def synchronize(self) -> None:
+        for st in self.streams:
+            st.synchronize()

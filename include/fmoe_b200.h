@@ -382,6 +382,18 @@ int fmoe_ep_down_projection(const int64_t* offsets_local, int64_t capacity, int6
  * activations (:62-106 _fused_swiglu_backward_kernel; triton_general_ops.py:325-344 SiLU backward):
  *   fmoe_activation_backward mode 0: d_alpha = d_out * silu'(alpha); mode 1 (out = silu(alpha) *
  *   beta): d_alpha = d_out * beta * silu'(alpha), d_beta = d_out * silu(alpha). */
+/* Router backward (the reference differentiates its eager routing code with autograd,
+ * modules/fast_moe_module.py:93-135). The renormalised top-k scores are the softmax over the k
+ * selected logits, so d_logits[t, e_j] = y_j (dy_j - sum_i y_i dy_i) and 0 for unselected experts:
+ * fmoe_router_backward (topk_idx [L, k], topk_score = y, d_score = dy, all as fmoe_gate_topk wrote
+ * them; d_logits [L, E] f32). fmoe_gate_linear_backward then gives the gradients of the gate's
+ * Linear: d_x [L, d] (dtype of x, may be NULL) = d_logits @ gate_w, d_gate_w [E, d] f32 = d_logits^T @ x,
+ * d_gate_b [E] f32 = column sums (both cleared first; either may be NULL). */
+int fmoe_router_backward(const int64_t* topk_idx, const float* topk_score, const float* d_score, int64_t L, int E, int k,
+                         float* d_logits, void* stream);
+int fmoe_gate_linear_backward(const float* d_logits, const void* x, int x_dtype, int64_t ldx, const float* gate_w,
+                              int64_t L, int d, int E, void* d_x, int64_t lddx, float* d_gate_w, float* d_gate_b,
+                              void* stream);
 int fmoe_batched_transpose(const void* in, int dtype, int batch, int64_t in_sb, int64_t ld_in, int rows, int cols,
                            void* out, int64_t out_sb, int64_t ld_out, void* stream);
 int fmoe_jagged_pad_offsets(const int64_t* offsets, int E, int dtype, int64_t* kseg, void* stream);

@@ -379,7 +379,29 @@ def grad_cases(ref):
         save(f"grad_{ci}", rec)
 
 
-GROUPS = {"grad": grad_cases, "layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases,
+def layer_grad_cases(ref):
+    """Gradients through the whole reference layer (FastMoELayer, PYTORCH kernels, fp32, CPU):
+    x, the gate Linear and the four expert parameters, for d(sum(y * dout))."""
+    KT = ref.utils.KernelType
+    for ci, (B, T, d, h, o, E, k, seed) in enumerate([(2, 24, 32, 64, 32, 4, 2, 50), (3, 17, 48, 40, 24, 8, 2, 51)]):
+        torch.manual_seed(seed)
+        layer = ref.layer.FastMoELayer(d, h, o, E, KT.PYTORCH, torch.float32)
+        with torch.no_grad():
+            layer._experts_hidden_bias.normal_(0, 0.1)
+            layer._experts_bias.normal_(0, 0.1)
+        x = torch.randn(B, T, d).requires_grad_()
+        y = layer(x, k)
+        dout = torch.randn_like(y) * 0.01
+        y.backward(dout)
+        sd = {n: p.detach().clone() for n, p in layer.state_dict().items()}
+        rec = dict(k=k, x=x.detach(), y=y.detach(), dout=dout, d_x=x.grad)
+        for n, p in layer.named_parameters():
+            rec["p::" + n] = p.detach()
+            rec["g::" + n] = p.grad
+        save(f"lgrad_{ci}", rec)
+
+
+GROUPS = {"lgrad": layer_grad_cases, "grad": grad_cases, "layer": layer_cases, "ops": op_cases, "combine": combine_cases, "fp8": fp8_cases, "ops3d": op3d_cases,
           "mrn": mrn_cases}
 
 

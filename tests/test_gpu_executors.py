@@ -57,3 +57,23 @@ def test_streaming_forward_refuses_cpu_example():
     layer = _layer()
     with pytest.raises(RuntimeError, match="CUDA"):
         fm.StreamingForward(layer, torch.zeros(1, 4, 128, dtype=torch.bfloat16), 2)
+
+
+@pytest.mark.parametrize("slots", [1, 3])
+def test_host_pipeline_matches_eager_for_every_batch(slots):
+    """One graph launch per batch (copy-in, forward and copy-out of a slot captured together):
+    every batch's result equals the eager forward, across several rounds through the slots."""
+    layer = _layer()
+    xs = _batches(7, 257, 128)
+    want = [layer(x.to(DEV), 2).cpu() for x in xs]
+    pipe = fm.HostPipeline(layer, xs[0].to(DEV), 2, slots=slots)
+    for i, x in enumerate(xs):
+        s = i % slots
+        pipe.wait(s)                      # the slot's previous batch has been read out
+        if i >= slots:
+            assert torch.equal(pipe.host_out[s], want[i - slots]), f"batch {i - slots}"
+        pipe.host_in[s].copy_(x)
+        pipe.launch(s)
+    pipe.synchronize()
+    for i in range(max(0, len(xs) - slots), len(xs)):
+        assert torch.equal(pipe.host_out[i % slots], want[i]), f"batch {i}"
