@@ -68,6 +68,10 @@ SIGNATURES = {
         c_int,
         [P, P, c_int, I64, P, c_int, I64, I64, P, I64, I64, I64, P, I64, c_int, c_int, c_int, c_int, P, c_int, I64, P],
     ),
+    "fmoe_index_select_jagged_bmm_mul": (
+        c_int,
+        [P, P, c_int, I64, P, c_int, I64, I64, P, I64, I64, I64, P, I64, c_int, c_int, c_int, P, I64, P, c_int, I64, P],
+    ),
     "fmoe_index_select_jagged_bmm_swiglu": (
         c_int,
         [P, P, c_int, I64, P, c_int, I64, I64, P, P, I64, I64, I64, P, P, I64, c_int, c_int, c_int, P, c_int, I64, P],
@@ -82,6 +86,7 @@ SIGNATURES = {
         [P, I64, P, c_int, I64, P, P, P, I64, I64, I64, I64, P, I64, c_int, c_int, c_int, c_int, P, P, P, P, c_int,
          I64, P],
     ),
+    "fmoe_expand_3d_index": (c_int, [P, P, c_int, c_int, I64, P, P]),
     "fmoe_split_f32_bf16x3": (c_int, [P, I64, c_int, I64, c_int, c_int, c_int, P, I64, P]),
     "fmoe_gather_rows": (c_int, [P, c_int, I64, I64, P, c_int, I64, c_int, P, I64, P]),
     "fmoe_mul_merge_k_add": (c_int, [P, P, c_int, I64, P, c_int, P, I64, c_int, c_int, P, c_int, I64, P]),

@@ -133,6 +133,33 @@ extern "C" int fmoe_index_select_jagged_bmm(const int64_t* offsets, const int64_
   return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int fmoe_index_select_jagged_bmm_mul(const int64_t* offsets, const int64_t* index, int index_div,
+                                                int64_t total_rows, const void* jagged, int dtype, int64_t L,
+                                                int64_t ldj, const void* weight, int64_t w_se, int64_t w_sk,
+                                                int64_t w_sn, const void* bias, int64_t bias_se, int E, int K, int N,
+                                                const void* multiplier, int64_t ld_mul, void* out, int out_dtype,
+                                                int64_t ldo, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "index_select_jagged_bmm_mul: dtype must be bf16 or f32");
+  FMOE_REQUIRE(index == nullptr || index_div >= 1, "index_select_jagged_bmm_mul: index_div must be >= 1");
+  FMOE_REQUIRE(total_rows == 0 || (multiplier != nullptr && ld_mul >= N), "index_select_jagged_bmm_mul: bad multiplier");
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = dtype;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = jagged; g.a_rows = L; g.lda = ldj;
+  g.index = index; g.index_div = index_div;
+  g.b0 = weight;
+  int rc = set_weight(g, "index_select_jagged_bmm_mul", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.bias0 = bias; g.bias_se = bias_se;
+  g.epilogue = FMOE_EPI_NONE;
+  g.mul_in = multiplier; g.ld_mul = ld_mul;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int fmoe_index_select_jagged_bmm_swiglu(const int64_t* offsets, const int64_t* index, int index_div,
                                                    int64_t total_rows, const void* jagged, int dtype, int64_t L,
                                                    int64_t ldj, const void* weight, const void* weight_p,

@@ -273,6 +273,23 @@ split_bf16x3_kernel(const float* __restrict__ in, long long ldi, long long rows,
   }
 }
 
+// Row index of index_select_jagged_bmm_3D: sorted row p of expert e reads slice e of its token,
+// i.e. row token * E + e of the [L * E, K] view: out[p] = (index[p] / A) * E + e(p), where e(p) is
+// the expert whose segment [offsets[e], offsets[e+1]) holds p.
+__global__ void __launch_bounds__(256)
+expand_3d_index_kernel(const long long* __restrict__ offsets, const long long* __restrict__ index, int A, int E,
+                       long long rows, long long* __restrict__ out) {
+  for (long long p = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; p < rows;
+       p += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (offsets[mid] <= p) lo = mid; else hi = mid;
+    }
+    out[p] = (index[p] / A) * E + lo;
+  }
+}
+
 // dst[r, :] = src[index[r] / div, :] in 16-byte pieces (or bytes when rows are not 16-byte
 // aligned). One warp-sized group of threads walks a row, so reads and writes are coalesced.
 template <typename V>
@@ -470,6 +487,21 @@ extern "C" int fmoe_split_f32_bf16x3(const float* in, int64_t rows, int cols, in
   if (blocks > 148 * 32) blocks = 148 * 32;
   split_bf16x3_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       in, ldi, rows, cols, cols_padded, pattern, apply_silu, static_cast<__nv_bfloat16*>(out), ldo);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_expand_3d_index(const int64_t* offsets, const int64_t* index, int A, int E, int64_t rows,
+                                    int64_t* out, void* stream) {
+  FMOE_REQUIRE(A >= 1 && E >= 1 && rows >= 0, "expand_3d_index: A=%d E=%d rows=%lld", A, E, (long long)rows);
+  if (rows == 0) return FMOE_OK;
+  FMOE_REQUIRE(offsets && index && out, "expand_3d_index: NULL pointer argument");
+  long long blocks = (rows + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  expand_3d_index_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(index), A, E, rows,
+      reinterpret_cast<long long*>(out));
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
   return FMOE_OK;

@@ -79,6 +79,10 @@ struct GemmDesc {
   const int64_t* out_peers;
   int n_peers;
   int64_t peer_rows;
+  // out = epilogue(...) * mul_in, elementwise: mul_in [total_rows, N] in the output type, row stride
+  // ld_mul elements (the second factor of the two-input gated product); null = none
+  const void* mul_in;
+  int64_t ld_mul;
   // Reduction over the rows of each group (weight gradients): `a` is [a_rows, K] and b0 [N, K]
   // with K = the padded total row count of all groups, kseg [E+1] (device, elements, multiples
   // of one K step of 128 bytes, every group at least one step) the start of each group's range;

@@ -99,6 +99,9 @@ struct GemmParams {
   // (elements, multiples of one K step) is where expert e's padded row range starts. Every
   // expert then owns the same number of output rows; its tiles differ in the length of the K loop.
   const long long* kseg;
+  // elementwise multiplier applied last: out[r, n] = (...)[r, n] * mul_in[r * ld_mul + n] (output type)
+  const void* mul_in;
+  long long ld_mul;
   int* status;
 };
 
@@ -647,6 +650,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           }
+          if (p.mul_in != nullptr && row_ok) {
+            // second factor of a gated product: this row's 32 values of the multiplier tensor
+            const OutT* mrow = reinterpret_cast<const OutT*>(p.mul_in) + row * p.ld_mul + col0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < ncols) v[i] *= load_as_float<OutT>(mrow, i);
+          }
           if (combine) {
             // what the reference does in the activation type: round the GEMM row, multiply by the
             // gate weight, round again (Tensor.mul), then accumulate
@@ -1000,6 +1010,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
     return fail(FMOE_ERR_UNSUPPORTED, "grouped_gemm: gathered rows need K to be a multiple of 16 bytes (K=%d x %d B); pad K",
                 d.K, esize);
   }
+  FMOE_REQUIRE(d.mul_in == nullptr || (d.gate_index == nullptr && d.out_index == nullptr && d.epilogue != FMOE_EPI_SWIGLU),
+               "grouped_gemm: the elementwise multiplier goes with the plain and SiLU epilogues only");
   FMOE_REQUIRE(d.kseg == nullptr || (d.index == nullptr && d.gate_index == nullptr && d.out_index == nullptr &&
                                      d.epilogue == FMOE_EPI_NONE && d.a_scale == nullptr),
                "grouped_gemm: the reduction-over-rows mode takes plain contiguous operands only");
@@ -1094,6 +1106,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   const int osize = dtype_size(d.out_dtype);
   // peer buffers are 16-byte aligned by contract (their addresses live on the device)
   p.kseg = reinterpret_cast<const long long*>(d.kseg);
+  p.mul_in = d.mul_in;
+  p.ld_mul = d.ld_mul;
   p.vec_ok = ((d.ldo * osize) % 16 == 0) && (d.out_peers != nullptr || (reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
   p.status = status;
 

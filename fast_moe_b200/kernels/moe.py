@@ -183,6 +183,7 @@ def index_select_jagged_bmm(
     _epilogue: int = _lib.EPI_NONE,
     _rows_checked: bool = False,
     _out_dtype: Optional[torch.dtype] = None,
+    _multiplier: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """out[r] = jagged[index.view(-1)[r] // A] @ weight[e] + bias[e] for the rows r of expert e.
 
@@ -195,12 +196,13 @@ def index_select_jagged_bmm(
     assert index is None or (index.ndim == 2 and (_rows_checked or index.shape[0] == jagged.shape[0]))
     _check_float(jagged, "jagged")
     assert weight.dtype == jagged.dtype, f"{weight.dtype=} {jagged.dtype=}"
-    if index is not None and _epilogue == _lib.EPI_NONE and _out_dtype is None and _ag().needs_grad(jagged, weight, bias):
+    if (index is not None and _epilogue == _lib.EPI_NONE and _out_dtype is None and _multiplier is None
+            and _ag().needs_grad(jagged, weight, bias)):
         return _ag().IndexSelectJaggedBmmFn.apply(offsets, index, jagged, weight, bias)
     if _out_dtype is None and _wants_fp32_split(jagged, weight):
         return index_select_jagged_bmm(max_seq_len, offsets, index, split_f32_rows(jagged, 0), split_f32_weight(weight),
                                        bias, _epilogue=_epilogue, _rows_checked=_rows_checked,
-                                       _out_dtype=torch.float32)
+                                       _out_dtype=torch.float32, _multiplier=_multiplier)
     od = _out_dtype or jagged.dtype
     dev = _lib.require_cuda(offsets, index, jagged, weight, bias)
     lib = _lib.load()
@@ -219,6 +221,18 @@ def index_select_jagged_bmm(
         a, idx, div, L = gather_rows(a, idx, div), None, 1, rows
     out = torch.empty((rows, N), dtype=od, device=dev)
     dt = _lib.dtype_code(jagged.dtype)
+    if _multiplier is not None:
+        m = _multiplier if (_multiplier.dtype == od and _multiplier.stride(1) == 1) else _multiplier.to(od).contiguous()
+        assert tuple(m.shape) == (rows, N) and _epilogue == _lib.EPI_NONE
+        with torch.cuda.device(dev):
+            _lib.check(
+                lib.fmoe_index_select_jagged_bmm_mul(
+                    off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
+                    w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, m.data_ptr(), m.stride(0), out.data_ptr(),
+                    _lib.dtype_code(od), out.stride(0), _lib.stream_ptr(dev),
+                )
+            )
+        return out
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_index_select_jagged_bmm(
@@ -249,9 +263,12 @@ def index_select_jagged_bmm_3D(
     assert weight.shape[0] == E and weight.shape[1] == K
     rows = index.numel()
     off = _index_i64(offsets)
-    tok = _index_i64(index).reshape(-1) // index.shape[1]
-    expert = torch.searchsorted(off[1:].contiguous(), torch.arange(rows, device=tok.device), right=True)
-    flat_index = (tok * E + expert.clamp_(max=E - 1)).view(-1, 1)
+    idx = _index_i64(index)
+    flat_index = torch.empty((rows, 1), dtype=torch.int64, device=idx.device)
+    lib = _lib.load()
+    with torch.cuda.device(idx.device):
+        _lib.check(lib.fmoe_expand_3d_index(off.data_ptr(), idx.data_ptr(), index.shape[1], E, rows, flat_index.data_ptr(),
+                                            _lib.stream_ptr(idx.device)))
     x2d = jagged.reshape(L * E, K)
     return index_select_jagged_bmm(max_seq_len, off, flat_index, x2d, weight, bias, _rows_checked=True)
 
@@ -332,7 +349,8 @@ def index_select_jagged_gating_bmm(
 ) -> torch.Tensor:
     """silu(A_g @ Wa + ba) * (B_g @ Wb + bb) (kernels/moe.py:192-233). With ``jagged_a is
     jagged_b`` this is the SwiGLU operator and runs as one kernel; two distinct inputs run as two
-    grouped GEMMs (the first with the SiLU epilogue) and one multiply."""
+    grouped GEMMs: the first with the SiLU epilogue, the second multiplying its result by the
+    first's in its epilogue."""
     assert (
         index.ndim == 2
         and index.shape[0] == jagged_a.shape[0] == jagged_b.shape[0]
@@ -341,9 +359,14 @@ def index_select_jagged_gating_bmm(
     )
     if jagged_a is jagged_b:
         return index_select_jagged_bmm_swiglu(max_seq_len, offsets, index, jagged_a, weight_a, bias_a, weight_b, bias_b)
+    if _ag().needs_grad(jagged_a, jagged_b, weight_a, weight_b, bias_a, bias_b):
+        # with gradients: two differentiable products and the elementwise SwiGLU on top of them
+        alpha = index_select_jagged_bmm(max_seq_len, offsets, index, jagged_a, weight_a, bias_a)
+        beta = index_select_jagged_bmm(max_seq_len, offsets, index, jagged_b, weight_b, bias_b)
+        return torch.nn.functional.silu(alpha) * beta
     alpha_silu = index_select_jagged_bmm(max_seq_len, offsets, index, jagged_a, weight_a, bias_a, _epilogue=_lib.EPI_SILU)
-    beta = index_select_jagged_bmm(max_seq_len, offsets, index, jagged_b, weight_b, bias_b)
-    return alpha_silu.mul_(beta)
+    # the second product multiplies its result by silu(first product) in its epilogue
+    return index_select_jagged_bmm(max_seq_len, offsets, index, jagged_b, weight_b, bias_b, _multiplier=alpha_silu)
 
 
 def mul_merge_k_add(

@@ -203,6 +203,17 @@ int fmoe_index_select_jagged_bmm(const int64_t* offsets, const int64_t* index, i
                                  int E, int K, int N, int epilogue, void* out, int out_dtype, int64_t ldo,
                                  void* stream);
 
+/* Second product of index_select_jagged_gating_bmm (kernels/moe.py:192-233 ->
+ * kernels/pytorch/moe.py:149-221: silu(A_g Wa + ba) * (B_g Wb + bb) on two different inputs):
+ * fmoe_index_select_jagged_bmm whose result is multiplied elementwise, in the epilogue, by
+ * `multiplier` [total_rows, N] (out_dtype, row stride ld_mul) - the SiLU'd first product, computed
+ * by fmoe_index_select_jagged_bmm with FMOE_EPI_SILU. No separate multiply pass. */
+int fmoe_index_select_jagged_bmm_mul(const int64_t* offsets, const int64_t* index, int index_div, int64_t total_rows,
+                                     const void* jagged, int dtype, int64_t L, int64_t ldj, const void* weight,
+                                     int64_t w_se, int64_t w_sk, int64_t w_sn, const void* bias, int64_t bias_se, int E,
+                                     int K, int N, const void* multiplier, int64_t ld_mul, void* out, int out_dtype,
+                                     int64_t ldo, void* stream);
+
 /* index_select_jagged_bmm_swiglu (kernels/moe.py:156-189 -> kernels/pytorch/moe.py:87-146):
  *   out[r, :] = silu(x_r @ weight[e] + bias[e]) * (x_r @ weight_p[e] + bias_p[e])
  * weight and weight_p share shape and strides. */
@@ -291,6 +302,13 @@ int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_t total_row
                                        int g_dtype, const int64_t* gates_index, int64_t L, int k, int E, int K, int N,
                                        int has_silu, void* act_scratch, void* out, int out_dtype, int64_t ldo,
                                        int flags, void* stream);
+
+/* Row index of index_select_jagged_bmm_3D (kernels/moe.py:118-153 -> kernels/pytorch/moe.py:224-252):
+ * the rows of expert e read slice e of their token in a [L, E, K] input. out[p] = (index[p] / A) * E
+ * + e(p), e(p) the expert whose segment of `offsets` holds sorted row p; fmoe_index_select_jagged_bmm
+ * on the [L * E, K] view with this index (index_div = 1) is the operator. */
+int fmoe_expand_3d_index(const int64_t* offsets, const int64_t* index, int A, int E, int64_t rows, int64_t* out,
+                         void* stream);
 
 /* fp32 operands without TF32. The tensor-core path for FMOE_F32 operands rounds them to tf32
  * (10 mantissa bits); the reference's kernels do that only when
