@@ -779,9 +779,15 @@ def main():
     _lib.set_stage_timer(None)
     clocks = sampler.window(t_wall0, t_wall1) if rank == 0 else None
     stage_ms = {n: (tot / cnt) for n, (tot, cnt) in timer.totals_ms().items()}
-    up_alone_ms = down_alone_ms = None
+    up_alone_ms = down_alone_ms = route_alone_ms = None
     if world == 1:
         up_alone_ms, down_alone_ms = gemm_alone_ms(layer, x_dev, k, bool(c.get("fp8")))
+        if hasattr(layer, "_route_with_passes") and not c.get("fp8"):
+            # the routing chain alone, as the layer runs it (gate + top-k, counting sort, and - in the
+            # fused small-batch form - the row gather and the clearing of the combine buffer)
+            with torch.no_grad():
+                xf = x_dev.reshape(-1, c["d"])
+                route_alone_ms = graph_kernel_ms(lambda: layer._route_with_passes(xf, k, 2 * c["h"], c["o"], k <= 2), device)
     status = _lib.device_status(device)
 
     sustained = None
@@ -907,6 +913,10 @@ def main():
             if down_alone_ms:
                 dtf = 2 * A * c["h"] * c["o"] / (down_alone_ms * 1e-3) / 1e12
                 roofline["down_gemm"] = dict(ms=down_alone_ms, tflops=dtf, frac=dtf / peak_tf)
+            if route_alone_ms:
+                roofline["routing_chain"] = dict(
+                    ms=route_alone_ms, includes="gate + top-k, counting sort, row gather into expert order, clearing of "
+                    "the combine buffer; 10 repetitions in a CUDA graph, warm")
         line = dict(
             metric="moe_layer_fwd_tokens_per_s", value=tokens_total / (ms_step * 1e-3), unit="tokens/s",
             n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,

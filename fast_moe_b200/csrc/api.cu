@@ -2,6 +2,7 @@
 // map the reference's operator arguments onto the grouped GEMM / combine / SiLU launchers.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -30,6 +31,15 @@ int fail(int code, const char* fmt, ...) {
 
 int cuda_fail(cudaError_t e, const char* what) {
   return fail(FMOE_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+}
+
+bool programmatic_launch_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FMOE_PDL");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
 }
 
 int current_device_slot(int* dev_out) {

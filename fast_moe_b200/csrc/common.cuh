@@ -35,6 +35,10 @@ int* device_status_ptr(int* err);
 constexpr int kMaxDevices = 64;
 int current_device_slot(int* dev_out);
 
+// FMOE_PDL=1 (read once): kernels of the layer's chain are launched with programmatic stream
+// serialization, so a kernel's set-up overlaps the tail of the kernel before it.
+bool programmatic_launch_enabled();
+
 static inline int dtype_size(int dt) {
   switch (dt) {
     case FMOE_F32: return 4;

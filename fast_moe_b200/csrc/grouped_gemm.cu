@@ -321,6 +321,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     ptx::prefetch_tmap(&tmB0);
     if (DUAL) ptx::prefetch_tmap(&tmB1);
   }
+  // Everything above touched only this CTA's shared memory. From here on the kernel reads what
+  // earlier kernels of the stream wrote (offsets, operands): with a programmatic dependent launch
+  // this is where it waits for them; the next kernel in the stream may be scheduled from now on.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
     const long long o0 = p.offsets[e], o1 = p.offsets[e + 1];
     long long len = o1 - o0;
@@ -910,13 +915,22 @@ int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap&
   cfg.blockDim = dim3(GATHER ? kGatherKernelThreads : kBaseThreads, 1, 1);
   cfg.dynamicSmemBytes = Plan::kTotal;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CTAS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (CTAS > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = CTAS;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (programmatic_launch_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = CTAS > 1 ? 1 : 0;
+  cfg.numAttrs = na;
   FMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB0, tmB1, p));
   ++g_launches;
   return FMOE_OK;

@@ -257,6 +257,7 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const f
                      float* __restrict__ logits_out, long long* __restrict__ topk_idx,
                      float* __restrict__ topk_score, int* __restrict__ group_counts, int router_mode) {
   constexpr int EP = 8 * NT;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel's set-up may start
   extern __shared__ __align__(16) uint8_t smem_gate[];
   const int row_bytes = d * 2 + kMmaGatePadBytes;
   uint8_t* s_w = smem_gate;                                            // [3 terms][EP][row_bytes]
@@ -682,7 +683,7 @@ route_place_scan_kernel(const long long* __restrict__ topk_idx, long long L, int
 // gather kernel and a memset.
 constexpr int kGroupTokens = 16;
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 route_place_gather_kernel(const long long* __restrict__ topk_idx, long long L, int E, int k, int ng,
                           const int* __restrict__ group_counts, long long* __restrict__ lengths,
                           long long* __restrict__ offsets, long long* __restrict__ max_len,
@@ -703,6 +704,9 @@ route_place_gather_kernel(const long long* __restrict__ topk_idx, long long L, i
     s_off[e] = 0;
   }
   for (int i = threadIdx.x; i < kGroupTokens * k; i += blockDim.x) s_dst[i] = -1;
+  // programmatic dependent launch: the gate kernel's outputs are read from here on
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __syncthreads();
   const long long t0 = static_cast<long long>(blockIdx.x) * kGroupTokens;
   if (threadIdx.x < kGroupTokens && t0 + threadIdx.x < L) {
@@ -795,10 +799,10 @@ route_place_gather_kernel(const long long* __restrict__ topk_idx, long long L, i
   }
   if (x_sorted == nullptr && zero_rows == nullptr) return;
   __syncthreads();
-  // memory passes: warp w serves tokens w and w + 8 of the group
+  // memory passes: one warp per token of the group
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  for (int tt = warp; tt < kGroupTokens; tt += 8) {
+  for (int tt = warp; tt < kGroupTokens; tt += static_cast<int>(blockDim.x >> 5)) {
     const long long t = t0 + tt;
     if (t >= L) break;
     if (x_sorted != nullptr) {
@@ -1102,13 +1106,26 @@ extern "C" int fmoe_route_metadata_gather(const int64_t* topk_idx, int64_t L, in
   if (!status) return err;
   const size_t smem = (static_cast<size_t>(3 * E + 1) + static_cast<size_t>(kGroupTokens) * k) * sizeof(int);
   const int64_t blocks = (L + kGroupTokens - 1) / kGroupTokens;
-  route_place_gather_kernel<<<static_cast<unsigned>(blocks), 256, smem, st>>>(
-      reinterpret_cast<const long long*>(topk_idx), L, E, k, static_cast<int>(ng), group_counts,
-      reinterpret_cast<long long*>(lengths), reinterpret_cast<long long*>(offsets), reinterpret_cast<long long*>(max_len),
-      reinterpret_cast<long long*>(gate_index), reinterpret_cast<long long*>(token_index),
-      reinterpret_cast<long long*>(reverse_index), static_cast<const uint8_t*>(x), ldx * xs, row_bytes,
-      static_cast<uint8_t*>(x_sorted), ld_sorted * xs, static_cast<uint8_t*>(zero_rows), ld_zero * zs, zero_row_bytes,
-      status);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    cfg.blockDim = dim3(512, 1, 1);     // 16 warps: one per token in the copy phase
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic_launch_enabled() ? 1 : 0;
+    FMOE_CUDA_OK(cudaLaunchKernelEx(
+        &cfg, route_place_gather_kernel, reinterpret_cast<const long long*>(topk_idx), static_cast<long long>(L), E, k,
+        static_cast<int>(ng), group_counts, reinterpret_cast<long long*>(lengths), reinterpret_cast<long long*>(offsets),
+        reinterpret_cast<long long*>(max_len), reinterpret_cast<long long*>(gate_index),
+        reinterpret_cast<long long*>(token_index), reinterpret_cast<long long*>(reverse_index),
+        static_cast<const uint8_t*>(x), static_cast<long long>(ldx * xs), row_bytes, static_cast<uint8_t*>(x_sorted),
+        static_cast<long long>(ld_sorted * xs), static_cast<uint8_t*>(zero_rows), static_cast<long long>(ld_zero * zs),
+        zero_row_bytes, status));
+  }
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
   return FMOE_OK;

@@ -379,6 +379,8 @@ class ExpertParallelSwiGLUMoE(nn.Module):
         if not self._own_process_group:
             raise RuntimeError("a logical rank of a single-process job has no forward(): drive ep_route / "
                                "ep_dispatch / ep_experts / ep_combine of all ranks phase by phase")
+        if x_flat.dtype != self.dtype:
+            raise TypeError(f"tokens are {x_flat.dtype} but the layer (weights and exchange buffers) is {self.dtype}")
         if self.exchange == "nccl":
             return self._forward_nccl(x_flat, k).view(*shape[:-1], self.output_dim)
         self._ensure_peer_buffers(x_flat.shape[0], k)
