@@ -55,12 +55,14 @@ SIGNATURES = {
     "fmoe_gate_topk": (c_int, [P, c_int, I64, P, P, P, I64, c_int, I64, c_int, c_int, c_int, P, P, P, P]),
     "fmoe_gate_topk_counts_supported": (c_int, [P, c_int, I64, P, I64, c_int, c_int]),
     "fmoe_route_group_counts_bytes": (c_size_t, [I64, c_int]),
-    "fmoe_gate_topk_counts": (c_int, [P, c_int, I64, P, P, I64, c_int, c_int, c_int, P, P, P, P, P]),
+    "fmoe_gate_topk_counts": (c_int, [P, c_int, I64, P, P, I64, c_int, c_int, c_int, P, P, P, P, P, c_int, I64, c_int, P]),
     "fmoe_route_metadata_gather": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P, P, c_int, I64, c_int, P, I64, P,
                                            c_int, I64, c_int, P]),
     "fmoe_gate_topk_normalized": (c_int, [P, c_int, I64, P, P, P, I64, I64, c_int, c_int, c_int, P, P, P, P]),
     "fmoe_token_norm": (c_int, [P, c_int, I64, c_int, I64, c_int, P, P, c_int, c_float, P, I64, P]),
-    "fmoe_sg_load_loss": (c_int, [P, P, P, c_int, c_int, c_float, c_int, P, P, P]),
+    "fmoe_sg_load_loss": (c_int, [P, P, P, c_int, c_int, c_float, c_int, P, c_int, P, P, P]),
+    "fmoe_sg_noisy_logits": (c_int, [P, I64, P, I64, c_int, c_float, P, P, P]),
+    "fmoe_sg_noisy_load": (c_int, [P, I64, P, P, I64, c_int, c_int, P, c_int, P]),
     "fmoe_route_workspace_bytes": (c_size_t, [I64, c_int, c_int]),
     "fmoe_route_metadata": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P, c_size_t, P]),
     "fmoe_route_metadata_static": (c_int, [P, I64, c_int, c_int, P, P, P, P, P, P, P]),

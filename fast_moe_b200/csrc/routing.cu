@@ -255,7 +255,8 @@ __global__ void __launch_bounds__(kMmaGateWarps * 32, 2)
 gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const float* __restrict__ gw,
                      const float* __restrict__ gb, long long L, int d, int E, int k,
                      float* __restrict__ logits_out, long long* __restrict__ topk_idx,
-                     float* __restrict__ topk_score, int* __restrict__ group_counts, int router_mode) {
+                     float* __restrict__ topk_score, int* __restrict__ group_counts, int router_mode,
+                     uint8_t* __restrict__ zero_rows, long long ldz_bytes, int zero_row_bytes) {
   constexpr int EP = 8 * NT;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel's set-up may start
   extern __shared__ __align__(16) uint8_t smem_gate[];
@@ -294,6 +295,19 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const f
   };
   // the first tile's rows go out first (HBM latency); the weight staging runs underneath them
   load_rows(blockIdx.x, 0);
+  // Optional side job: clear one row per token of a caller's buffer (the accumulator a fused
+  // combine adds into). Stores only, issued while the loads above are in flight.
+  if (zero_rows != nullptr) {
+    const int vec = zero_row_bytes >> 4;
+    for (long long tile_id = blockIdx.x; tile_id < num_tiles; tile_id += gridDim.x) {
+      for (int r = warp; r < kMmaGateTokens; r += kMmaGateWarps) {
+        const long long t = tile_id * kMmaGateTokens + r;
+        if (t >= L) break;
+        uint4* z = reinterpret_cast<uint4*>(zero_rows + t * ldz_bytes);
+        for (int c = lane; c < vec; c += 32) z[c] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
 
   // gate weights -> three bf16 terms in shared memory (zero rows for the padding experts),
   // four weights per thread and step, four steps in flight
@@ -842,7 +856,7 @@ namespace {
 int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                    const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E, int k,
                    float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, int router_mode,
-                   void* stream);
+                   void* stream, void* zero_rows = nullptr, long long ldz_bytes = 0, int zero_row_bytes = 0);
 
 // Conditions under which the tensor-core gate kernel runs (and with it the per-group counts).
 bool gate_mma_path(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* logits_in, int d, int E,
@@ -889,22 +903,33 @@ extern "C" int fmoe_gate_topk_counts_supported(const void* x, int x_dtype, int64
 
 extern "C" int fmoe_gate_topk_counts(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
                                      const float* gate_b, int64_t L, int d, int E, int k, float* logits_out,
-                                     int64_t* topk_idx, float* topk_score, int* group_counts, void* stream) {
+                                     int64_t* topk_idx, float* topk_score, int* group_counts, void* zero_rows,
+                                     int zero_dtype, int64_t ld_zero, int zero_cols, void* stream) {
   FMOE_REQUIRE(group_counts != nullptr, "gate_topk_counts: group_counts is NULL");
+  long long ldz_bytes = 0;
+  int zero_row_bytes = 0;
+  if (zero_rows != nullptr) {
+    const int zs = zero_dtype == FMOE_BF16 ? 2 : (zero_dtype == FMOE_F32 ? 4 : 0);
+    FMOE_REQUIRE(zs != 0 && zero_cols >= 1, "gate_topk_counts: zero fill needs a dtype (bf16 / f32) and a column count");
+    zero_row_bytes = zero_cols * zs;
+    ldz_bytes = static_cast<long long>(ld_zero) * zs;
+    FMOE_REQUIRE(zero_row_bytes % 16 == 0 && ldz_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(zero_rows) & 15) == 0,
+                 "gate_topk_counts: rows to clear must be 16-byte aligned and a multiple of 16 bytes long");
+  }
   if (!fmoe_gate_topk_counts_supported(x, x_dtype, ldx, gate_w, L, d, E)) {
     return fail(FMOE_ERR_UNSUPPORTED,
                 "gate_topk_counts: needs bf16 tokens with 16-byte aligned rows, E <= 32, d a multiple of 8 and a "
                 "small batch (L=%lld, d=%d, E=%d); use fmoe_gate_topk + fmoe_route_metadata", (long long)L, d, E);
   }
   return gate_topk_impl(x, x_dtype, ldx, gate_w, gate_b, nullptr, 0, 0, L, d, E, k, logits_out, topk_idx, topk_score,
-                        group_counts, kRouterSoftmaxRenorm, stream);
+                        group_counts, kRouterSoftmaxRenorm, stream, zero_rows, ldz_bytes, zero_row_bytes);
 }
 
 namespace {
 int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                    const float* logits_in, int64_t ld_logits, int logits_split, int64_t L, int d, int E,
                    int k, float* logits_out, int64_t* topk_idx, float* topk_score, int* group_counts, int router_mode,
-                   void* stream) {
+                   void* stream, void* zero_rows, long long ldz_bytes, int zero_row_bytes) {
   FMOE_REQUIRE(L >= 0 && E >= 1 && E <= kMaxGateExperts, "gate_topk: E=%d outside [1, %d]", E, kMaxGateExperts);
   FMOE_REQUIRE(k >= 1 && k <= E, "gate_topk: k=%d must be in [1, E=%d]", k, E);
   if (L == 0) return FMOE_OK;   // an empty batch is valid input (its tensors have NULL data pointers)
@@ -940,7 +965,8 @@ int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
     }                                                                                                              \
     kern<<<blocks, kMmaGateWarps * 32, smem, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, gate_w, gate_b, L, d, \
                                                    E, k, logits_out, reinterpret_cast<long long*>(topk_idx),      \
-                                                   topk_score, group_counts, router_mode);                         \
+                                                   topk_score, group_counts, router_mode,                          \
+                                                   static_cast<uint8_t*>(zero_rows), ldz_bytes, zero_row_bytes);   \
   } while (0)
       if (nt == 1) FMOE_GATE_MMA(1); else if (nt == 2) FMOE_GATE_MMA(2); else FMOE_GATE_MMA(4);
 #undef FMOE_GATE_MMA
@@ -949,7 +975,7 @@ int gate_topk_impl(const void* x, int x_dtype, int64_t ldx, const float* gate_w,
       return FMOE_OK;
     }
   }
-  if (group_counts != nullptr) {
+  if (group_counts != nullptr || zero_rows != nullptr) {
     return fail(FMOE_ERR_UNSUPPORTED, "gate_topk_counts: the per-group counts come from the tensor-core gate kernel only");
   }
   // Gate weights in shared memory when they fit beside the logits scratch (and a few blocks per SM)

@@ -1,7 +1,8 @@
 // Kernels of the sparsely-gated ("MRN" / SGMoE) layer that the FastMoELayer path does not have:
-// the token normalisation in front of the router and the experts, and the load / loss summary.
+// the token normalisation in front of the router and the experts, the training-time noise on the
+// router logits with its smooth load estimate, and the load / loss summary.
 // They stand in, forward only, for the eager PyTorch of OrigSGMoEImpl
-// (kernels/pytorch/mrn.py:186-189, :253-277, :301-333 of the reference). Both are HBM-bound or
+// (kernels/pytorch/mrn.py:186-189, :191-219, :221-277, :301-333 of the reference). Both are HBM-bound or
 // tiny; the router itself is the gate kernel in its normalised-logit mode (routing.cu) and the
 // experts are the grouped GEMMs.
 #include "common.cuh"
@@ -61,16 +62,119 @@ token_norm_kernel(const T* __restrict__ x, long long ldx, long long L, int group
   }
 }
 
+// Noisy gating while training (OrigSGMoEImpl._orig_noisy_gating, kernels/pytorch/mrn.py:229-237):
+// logits2 holds, per token, the clean logits x @ w_gate in columns [0, E) and x @ w_noise in
+// columns [E, 2E). stddev = softplus(x @ w_noise) + eps, noisy = clean + noise * stddev.
+__global__ void __launch_bounds__(256)
+noisy_logits_kernel(const float* __restrict__ logits2, long long ld, const float* __restrict__ noise, long long L, int E,
+                    float eps, float* __restrict__ noisy, float* __restrict__ stddev) {
+  const long long total = L * E;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / E;
+    const int e = static_cast<int>(i - t * E);
+    const float clean = logits2[t * ld + e];
+    const float raw = logits2[t * ld + E + e];
+    const float sp = raw > 20.f ? raw : log1pf(expf(raw));        // F.softplus (beta 1, threshold 20)
+    const float sd = sp + eps;
+    stddev[i] = sd;
+    noisy[i] = __fadd_rn(clean, __fmul_rn(noise[i], sd));       // separate multiply and add, as the eager reference
+  }
+}
+
+// Smooth load of the noisy router (OrigSGMoEImpl._prob_in_top_k, kernels/pytorch/mrn.py:191-219):
+// for every token, the probability of each expert landing in the top k under a fresh noise draw,
+//   Phi((clean - threshold) / stddev), threshold = the (k+1)-th largest L2-normalised noisy logit
+// when the expert's noisy logit (compared un-normalised, as the reference does) exceeds it, else the
+// k-th largest; summed over the tokens. One warp per token, lane l holds experts l, l + 32, ...;
+// block b writes its sums to partials[b][E]. The sums run in a fixed order (tokens of a warp in
+// sequence, then the warps of a block in sequence), so a result repeats bit for bit.
+template <int VPL>
+__global__ void __launch_bounds__(256)
+noisy_load_kernel(const float* __restrict__ logits2, long long ld, const float* __restrict__ noisy,
+                  const float* __restrict__ stddev, long long L, int E, int k, float* __restrict__ partials) {
+  extern __shared__ float s_acc[];                 // [8 warps][E]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  float acc[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) acc[j] = 0.f;
+  for (long long t = static_cast<long long>(blockIdx.x) * 8 + warp; t < L; t += static_cast<long long>(gridDim.x) * 8) {
+    float v[VPL], nv[VPL];
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      v[j] = e < E ? noisy[t * E + e] : 0.f;
+      sq = fmaf(v[j], v[j], sq);
+    }
+    const float nrm = fmaxf(sqrtf(warp_sum(sq)), 1e-12f);      // F.normalize: v / max(||v||, eps)
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) nv[j] = (lane + 32 * j) < E ? v[j] / nrm : -INFINITY;
+    // the k-th and (k+1)-th largest normalised values: k + 1 rounds of arg-max with removal
+    unsigned removed = 0u;
+    float thr_out = 0.f, thr_in = 0.f;
+    for (int r = 0; r <= k; ++r) {
+      float best = -INFINITY;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E && !((removed >> j) & 1u) && (nv[j] > best || (nv[j] == best && e < best_e))) {
+          best = nv[j];
+          best_e = e;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) {
+          best = ob;
+          best_e = oe;
+        }
+      }
+      if (best_e != 0x7fffffff && (best_e & 31) == lane) removed |= 1u << (best_e >> 5);
+      if (r == k - 1) thr_out = best;
+      if (r == k) thr_in = best;
+    }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) {
+        const float clean = logits2[t * ld + e];
+        const float thr = v[j] > thr_in ? thr_in : thr_out;
+        const float z = (clean - thr) / stddev[t * E + e];
+        acc[j] += 0.5f * (1.f + erff(z / 1.41421356237309515f));      // Normal(0, 1).cdf
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int e = lane + 32 * j;
+    if (e < E) s_acc[warp * E + e] = acc[j];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += s_acc[w * E + e];
+    partials[static_cast<long long>(blockIdx.x) * E + e] = s;
+  }
+}
+
 // Importance (sum of the gate values routed to each expert), load (rows per expert), the load
 // fractions and loss = coef * (cv2(importance) + cv2(load)), cv2(v) = var(v) / (mean(v)^2 + 1e-6)
-// with the unbiased variance, 0 for a single expert. One block; warp w sums the experts w, w + 8, ...
+// with the unbiased variance, 0 for a single expert. With noisy gating the loss uses the smooth
+// load (per-block sums of noisy_load_kernel) instead of the row counts. One block; warp w sums the experts w, w + 8, ...
 // in the fixed order of the expert-sorted rows, so the result is reproducible.
 __global__ void __launch_bounds__(256)
 sg_load_loss_kernel(const long long* __restrict__ offsets, const long long* __restrict__ gate_index,
                     const float* __restrict__ score, int E, int round_bf16, float loss_coef, int want_loss,
-                    float* __restrict__ load_frac, float* __restrict__ loss) {
-  extern __shared__ float s_imp[];                 // [E] importance, then [E] load
+                    const float* __restrict__ load_partials, int n_partials, float* __restrict__ load_frac,
+                    float* __restrict__ loss) {
+  extern __shared__ float s_imp[];                 // [E] importance, [E] rows per expert, [E] the load the loss uses
   float* s_load = s_imp + E;
+  float* s_cvload = s_load + E;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int e = warp; e < E; e += 8) {
@@ -85,6 +189,12 @@ sg_load_loss_kernel(const long long* __restrict__ offsets, const long long* __re
     if (lane == 0) {
       s_imp[e] = round_bf16 ? __bfloat162float(__float2bfloat16_rn(acc)) : acc;   // Tensor.sum returns the token dtype
       s_load[e] = static_cast<float>(p1 - p0);
+      float smooth = static_cast<float>(p1 - p0);
+      if (load_partials) {                         // noisy gating: the smooth load, block sums in order
+        smooth = 0.f;
+        for (int b = 0; b < n_partials; ++b) smooth += load_partials[static_cast<long long>(b) * E + e];
+      }
+      s_cvload[e] = smooth;
     }
   }
   __syncthreads();
@@ -92,7 +202,7 @@ sg_load_loss_kernel(const long long* __restrict__ offsets, const long long* __re
     const float total = static_cast<float>(offsets[E]);
     float cv[2] = {0.f, 0.f};
     for (int which = 0; which < 2; ++which) {
-      const float* v = which == 0 ? s_imp : s_load;
+      const float* v = which == 0 ? s_imp : s_cvload;
       if (E > 1) {
         float mean = 0.f;
         for (int e = 0; e < E; ++e) mean += v[e];
@@ -141,14 +251,51 @@ extern "C" int fmoe_token_norm(const void* x, int dtype, int64_t L, int d, int64
   return FMOE_OK;
 }
 
+extern "C" int fmoe_sg_noisy_logits(const float* logits2, int64_t ld_logits, const float* noise, int64_t L, int E,
+                                    float noise_eps, float* noisy, float* stddev, void* stream) {
+  FMOE_REQUIRE(E >= 1 && L >= 0 && ld_logits >= 2ll * E, "sg_noisy_logits: logits must hold 2 * E = %d columns per token", 2 * E);
+  if (L == 0) return FMOE_OK;
+  FMOE_REQUIRE(logits2 && noise && noisy && stddev, "sg_noisy_logits: NULL pointer argument");
+  long long blocks = (L * E + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  noisy_logits_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits2, ld_logits, noise, L, E, noise_eps, noisy, stddev);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_sg_noisy_load(const float* logits2, int64_t ld_logits, const float* noisy, const float* stddev,
+                                  int64_t L, int E, int k, float* partials, int n_partials, void* stream) {
+  FMOE_REQUIRE(E >= 2 && E <= 256, "sg_noisy_load: E=%d outside [2, 256]", E);
+  FMOE_REQUIRE(k >= 1 && k < E, "sg_noisy_load: k=%d must be in [1, E) (with k = E every expert is picked)", k);
+  FMOE_REQUIRE(n_partials >= 1 && n_partials <= 1024, "sg_noisy_load: n_partials=%d outside [1, 1024]", n_partials);
+  FMOE_REQUIRE(L >= 0 && ld_logits >= E, "sg_noisy_load: bad L or row stride");
+  FMOE_REQUIRE(partials && (L == 0 || (logits2 && noisy && stddev)), "sg_noisy_load: NULL pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = 8 * static_cast<size_t>(E) * sizeof(float);
+  const int vpl = (E + 31) / 32;
+#define FMOE_NOISY_LOAD(V) \
+  noisy_load_kernel<V><<<n_partials, 256, smem, st>>>(logits2, ld_logits, noisy, stddev, L, E, k, partials)
+  if (vpl <= 1) FMOE_NOISY_LOAD(1);
+  else if (vpl <= 2) FMOE_NOISY_LOAD(2);
+  else if (vpl <= 4) FMOE_NOISY_LOAD(4);
+  else FMOE_NOISY_LOAD(8);
+#undef FMOE_NOISY_LOAD
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
 extern "C" int fmoe_sg_load_loss(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
-                                 int round_bf16, float loss_coef, int want_loss, float* load_frac, float* loss,
-                                 void* stream) {
+                                 int round_bf16, float loss_coef, int want_loss, const float* load_partials,
+                                 int n_partials, float* load_frac, float* loss, void* stream) {
+  FMOE_REQUIRE(load_partials == nullptr || n_partials >= 1, "sg_load_loss: load_partials given with n_partials=%d", n_partials);
   FMOE_REQUIRE(E >= 1 && E <= 4096, "sg_load_loss: E=%d outside [1, 4096]", E);
   FMOE_REQUIRE(offsets && gate_index && topk_score, "sg_load_loss: NULL pointer argument");
-  sg_load_loss_kernel<<<1, 256, 2 * static_cast<size_t>(E) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+  sg_load_loss_kernel<<<1, 256, 3 * static_cast<size_t>(E) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(gate_index), topk_score, E, round_bf16,
-      loss_coef, want_loss, load_frac, loss);
+      loss_coef, want_loss, load_partials, n_partials, load_frac, loss);
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
   return FMOE_OK;

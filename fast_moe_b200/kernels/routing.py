@@ -177,14 +177,17 @@ def route_tokens_fused(
     zbuf = torch.empty((L, zero_rows[0]), dtype=zero_rows[1], device=dev) if zero_rows is not None else None
     with torch.cuda.device(dev):
         st = _lib.stream_ptr(dev)
+        # the clear rides in the gate kernel: plain stores under its load latency
+        in_gate = zbuf is not None
+        zargs = (zbuf.data_ptr(), _lib.dtype_code(zbuf.dtype), zbuf.stride(0), zbuf.shape[1]) if zbuf is not None else (None, 0, 0, 0)
+        none = (None, 0, 0, 0)
         _lib.check(lib.fmoe_gate_topk_counts(x.data_ptr(), _lib.BF16, x.stride(0), gw.data_ptr(), _lib.ptr(gb), L, d, E, k,
-                                             None, idx.data_ptr(), score.data_ptr(), counts.data_ptr(), st))
+                                             None, idx.data_ptr(), score.data_ptr(), counts.data_ptr(),
+                                             *(zargs if in_gate else none), st))
         _lib.check(lib.fmoe_route_metadata_gather(
             idx.data_ptr(), L, E, k, counts.data_ptr(), lengths.data_ptr(), offsets.data_ptr(), gate_index.data_ptr(),
             token_index.data_ptr(), reverse.data_ptr(), max_len.data_ptr(),
-            x.data_ptr(), _lib.BF16, x.stride(0), d, _lib.ptr(x_sorted), d,
-            _lib.ptr(zbuf), _lib.dtype_code(zbuf.dtype) if zbuf is not None else 0, zbuf.stride(0) if zbuf is not None else 0,
-            zbuf.shape[1] if zbuf is not None else 0, st))
+            x.data_ptr(), _lib.BF16, x.stride(0), d, _lib.ptr(x_sorted), d, *(none if in_gate else zargs), st))
     return idx, score, RoutingMetadata(gate_index, token_index, offsets, reverse, lengths, max_len), x_sorted, zbuf
 
 
@@ -249,17 +252,58 @@ def token_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
 
 
 def sg_load_loss(meta: RoutingMetadata, score: torch.Tensor, num_experts: int, token_dtype: torch.dtype,
-                 loss_coef: float, train: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+                 loss_coef: float, train: bool, smooth_load: Optional[torch.Tensor] = None
+                 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """(loss scalar f32, load fractions [E] f32) of the sparsely-gated layer
     (kernels/pytorch/mrn.py:253-287): loss = coef * (cv2(importance) + cv2(load)) when training,
-    0 otherwise; load fraction = rows of expert e / all rows."""
+    0 otherwise; load fraction = rows of expert e / all rows. ``smooth_load`` [blocks, E]: the
+    per-block sums of `noisy_gate`'s load estimate, which then replace the row counts in the loss."""
     lib = _lib.load()
-    dev = _lib.require_cuda(score, meta.offsets)
+    dev = _lib.require_cuda(score, meta.offsets, smooth_load)
     load = torch.empty(num_experts, dtype=torch.float32, device=dev)
     loss = torch.empty((), dtype=torch.float32, device=dev)
     sc = score.contiguous()
+    n_part = 0
+    if smooth_load is not None:
+        assert smooth_load.dtype == torch.float32 and smooth_load.is_contiguous() and smooth_load.shape[1] == num_experts
+        n_part = smooth_load.shape[0]
     with torch.cuda.device(dev):
         _lib.check(lib.fmoe_sg_load_loss(meta.offsets.data_ptr(), meta.gate_index.data_ptr(), sc.data_ptr(), num_experts,
                                          1 if token_dtype == torch.bfloat16 else 0, float(loss_coef), 1 if train else 0,
-                                         load.data_ptr(), loss.data_ptr(), _lib.stream_ptr(dev)))
+                                         _lib.ptr(smooth_load), n_part, load.data_ptr(), loss.data_ptr(),
+                                         _lib.stream_ptr(dev)))
     return loss, load
+
+
+def noisy_gate(x: torch.Tensor, gate_noise_weight: torch.Tensor, k: int, noise: torch.Tensor, noise_eps: float = 1e-2
+               ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Training-time router of the sparsely-gated layer with noisy gating
+    (OrigSGMoEImpl._orig_noisy_gating and _prob_in_top_k, kernels/pytorch/mrn.py:191-252):
+    x [L, d]; gate_noise_weight [2E, d] f32 = w_gate^T stacked on w_noise^T; noise [L, E] f32 (a
+    standard-normal draw). Returns (topk_idx [L, k], gates [L, k] f32, per-block sums [blocks, E]
+    of the smooth load for `sg_load_loss`, or None when k == E and every expert is picked)."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, gate_noise_weight, noise)
+    E2 = gate_noise_weight.shape[0]
+    assert E2 % 2 == 0
+    E = E2 // 2
+    L = x.shape[0]
+    assert noise.shape == (L, E) and noise.dtype == torch.float32
+    if E2 > 256:
+        raise ValueError(f"noisy gating supports up to 128 experts, got {E}")
+    _, _, logits2 = gate_topk_normalized(x, gate_noise_weight, 1, return_logits=True)
+    noisy = torch.empty((L, E), dtype=torch.float32, device=dev)
+    stddev = torch.empty((L, E), dtype=torch.float32, device=dev)
+    nz = noise.contiguous()
+    with torch.cuda.device(dev):
+        _lib.check(lib.fmoe_sg_noisy_logits(logits2.data_ptr(), E2, nz.data_ptr(), L, E, float(noise_eps), noisy.data_ptr(),
+                                            stddev.data_ptr(), _lib.stream_ptr(dev)))
+    idx, score, _ = gate_topk_normalized(None, None, k, logits=noisy)
+    partials = None
+    if k < E:
+        blocks = max(1, min(148, (L + 7) // 8))
+        partials = torch.empty((blocks, E), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.fmoe_sg_noisy_load(logits2.data_ptr(), E2, noisy.data_ptr(), stddev.data_ptr(), L, E, k,
+                                              partials.data_ptr(), blocks, _lib.stream_ptr(dev)))
+    return idx, score, partials

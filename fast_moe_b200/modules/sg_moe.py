@@ -8,10 +8,9 @@ forward signature of the reference's OrigSGMoEImpl (kernels/pytorch/mrn.py:93-33
 
 The experts, the combine and the dense map are the grouped GEMMs of the FastMoELayer path; the
 router is the gate kernel in its normalised-logit mode; normalisation and the load / loss summary
-are small kernels of their own. Forward only. Noisy gating draws fresh noise per training step
-and only changes which experts are picked while training; it is not built: a layer configured
-with it routes on the clean logits in evaluation mode (as the reference does) and raises in
-training mode.
+are small kernels of their own. Forward only. With noisy gating a layer in training mode adds
+softplus-scaled standard-normal noise to the logits before routing and uses the smooth load
+estimate in its loss; in evaluation mode it routes on the clean logits (as the reference does).
 """
 from __future__ import annotations
 
@@ -23,7 +22,7 @@ import torch.nn as nn
 
 from .. import _lib
 from ..kernels import moe as ops
-from ..kernels.routing import gate_topk_normalized, route_metadata, sg_load_loss, token_norm
+from ..kernels.routing import gate_topk_normalized, noisy_gate, route_metadata, sg_load_loss, token_norm
 from .fast_moe_module import _CastCache, _SplitCache, _fp32_exact, _xavier_stack
 
 
@@ -78,6 +77,8 @@ class SGMoELayer(nn.Module):
         self._cast = _CastCache()
         self._split = _SplitCache()
         self._gate_t = None          # (version, data_ptr, [E, d] f32 copy of _w_gate)
+        self._gate_noise_t = None    # (versions, data_ptrs, [2E, d] f32: _w_gate^T stacked on _w_noise^T)
+        self._noise = None           # standard-normal draw for the next noisy forward (set_noise)
         self._out_t = {}             # dtype -> (version, data_ptr, [1, o, d] copy of _output_weight)
         self._ident = {}
 
@@ -88,6 +89,20 @@ class SGMoELayer(nn.Module):
         if hit is None or hit[0] != p._version or hit[1] != p.data_ptr():
             self._gate_t = hit = (p._version, p.data_ptr(), p.detach().to(torch.float32).t().contiguous())
         return hit[2]
+
+    def _gate_noise_rows(self) -> torch.Tensor:
+        g, n = self._w_gate, self._w_noise
+        key = (g._version, n._version, g.data_ptr(), n.data_ptr())
+        hit = self._gate_noise_t
+        if hit is None or hit[0] != key:
+            both = torch.cat([g.detach().to(torch.float32).t(), n.detach().to(torch.float32).t()], dim=0).contiguous()
+            self._gate_noise_t = hit = (key, both)
+        return hit[1]
+
+    def set_noise(self, noise: Optional[torch.Tensor]) -> None:
+        """Noise [L, num_experts] (f32, standard normal) for the next noisy-gating forward instead of
+        a fresh torch.randn draw: reproducible runs and tests. Used once."""
+        self._noise = noise
 
     def _shared_weight(self, dtype: torch.dtype) -> torch.Tensor:
         """_output_weight [d, o] as a one-expert weight with the reduction dimension contiguous:
@@ -114,17 +129,21 @@ class SGMoELayer(nn.Module):
         """x [L, input_size] (jagged batch, already flattened; ``x_offsets`` / ``max_seq_len`` are
         accepted and unused, as in the reference) -> MRNOutput(y [L, output_size], loss, load)."""
         dev = _lib.require_cuda(x)
-        if self.training and self.enable_noisy_gating:
-            raise NotImplementedError("noisy gating (training-time noise on the router logits) is not built; "
-                                      "evaluate the layer, or train with enable_noisy_gating=False")
         assert x.ndim == 2 and x.shape[1] == self.input_size
         if group_norm:
             assert num_groups * linear_dim == self.input_size
         L, k, E, dt = x.shape[0], self.k, self.num_experts, x.dtype
         with _lib.stage("norm"):
             x_norm = token_norm(x, norm_weight, norm_bias, norm_eps, group_norm=group_norm, num_groups=num_groups)
+        smooth_load = None
         with _lib.stage("route"):
-            idx, score, _ = gate_topk_normalized(x_norm, self._gate_weight_rows(), k)
+            if self.training and self.enable_noisy_gating:
+                noise, self._noise = self._noise, None
+                if noise is None:
+                    noise = torch.randn((L, E), dtype=torch.float32, device=dev)
+                idx, score, smooth_load = noisy_gate(x_norm, self._gate_noise_rows(), k, noise.to(dev, torch.float32))
+            else:
+                idx, score, _ = gate_topk_normalized(x_norm, self._gate_weight_rows(), k)
             meta = route_metadata(idx, E)
         index = meta.gate_index.view(-1, k)
         b1 = self._cast.get("b1", self._experts_hidden_bias, dt)
@@ -160,5 +179,5 @@ class SGMoELayer(nn.Module):
                 y = ops.silu_jagged_bmm_combine(0, off1, x, self._shared_weight(dt), None, ar, ar2, gating_scores=ones,
                                                 gates_index=ar, has_silu=False, fused=True, out=moe) if L else moe
         with _lib.stage("loss"):
-            loss, load = sg_load_loss(meta, score, E, dt, self.loss_coef, self.training)
+            loss, load = sg_load_loss(meta, score, E, dt, self.loss_coef, self.training, smooth_load)
         return MRNOutput(y, loss, load)

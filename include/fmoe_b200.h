@@ -115,9 +115,29 @@ int fmoe_token_norm(const void* x, int dtype, int64_t L, int d, int64_t ldx, int
  * the reference do), load[e] = rows of expert e; load_frac [E] = load / sum(load);
  * loss [1] = loss_coef * (cv2(importance) + cv2(load)), cv2 = unbiased variance / (mean^2 + 1e-6),
  * or 0 when want_loss == 0 (evaluation). offsets [E+1], gate_index [rows] as fmoe_route_metadata
- * produced them; topk_score [L, k] f32. */
+ * produced them; topk_score [L, k] f32. With noisy gating the loss uses the smooth load instead of
+ * the row counts: load_partials [n_partials, E] as fmoe_sg_noisy_load wrote them (NULL otherwise);
+ * load_frac stays the row fractions, as in the reference. */
 int fmoe_sg_load_loss(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
-                      int round_bf16, float loss_coef, int want_loss, float* load_frac, float* loss, void* stream);
+                      int round_bf16, float loss_coef, int want_loss, const float* load_partials, int n_partials,
+                      float* load_frac, float* loss, void* stream);
+
+/* Training-time noise on the router logits of the sparsely-gated layer
+ * (OrigSGMoEImpl._orig_noisy_gating, kernels/pytorch/mrn.py:229-237). logits2 [L, >= 2E] f32 holds
+ * x @ w_gate in columns [0, E) and x @ w_noise in columns [E, 2E) (one gate product on the two
+ * weights stacked); noise [L, E] f32 is the caller's standard-normal draw.
+ *   stddev = softplus(x @ w_noise) + noise_eps,  noisy = clean + noise * stddev   (both [L, E] f32)
+ * The noisy logits then go through fmoe_gate_topk_normalized (logits_in). */
+int fmoe_sg_noisy_logits(const float* logits2, int64_t ld_logits, const float* noise, int64_t L, int E,
+                         float noise_eps, float* noisy, float* stddev, void* stream);
+
+/* Smooth load of the noisy router (OrigSGMoEImpl._prob_in_top_k, kernels/pytorch/mrn.py:191-219):
+ * per token and expert Phi((clean - threshold) / stddev), the threshold being the (k+1)-th largest
+ * L2-normalised noisy logit where the expert's noisy logit exceeds it and the k-th largest elsewhere,
+ * summed over the tokens. partials [n_partials, E] f32 receives one row of sums per block
+ * (n_partials blocks, 1..1024; fmoe_sg_load_loss adds them up in order). 1 <= k < E <= 256. */
+int fmoe_sg_noisy_load(const float* logits2, int64_t ld_logits, const float* noisy, const float* stddev, int64_t L,
+                       int E, int k, float* partials, int n_partials, void* stream);
 
 /* Replaces FastMoELayer._compute_routing_metadata (modules/fast_moe_module.py:107-144) and the
  * fbgemm op asynchronous_complete_cumsum it calls (:131): a stable counting sort of the L*k
@@ -147,7 +167,9 @@ int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, int k, int64_
  *     tokens with 16-byte aligned rows, E <= 32, d a multiple of 8, ceil(L/32) * 2 * E <= 32768).
  *   fmoe_gate_topk_counts: fmoe_gate_topk (x given, no precomputed logits) that also writes, for
  *     every group of 16 tokens, the rows per expert: group_counts, fmoe_route_group_counts_bytes(L, E)
- *     bytes.
+ *     bytes. It optionally clears rows 0..L-1 of zero_rows ([L, zero_cols] bf16 / f32, 16-byte
+ *     aligned rows): the buffer a fused combine accumulates into; the stores ride under the
+ *     kernel's load latency. zero_rows may be NULL.
  *   fmoe_route_metadata_gather: fmoe_route_metadata from those counts (one launch, no workspace),
  *     which optionally also (a) writes x_sorted[p, :] = x[token_index[p], :] for every sorted row p
  *     - the row gather of the up projection, x read once - and (b) clears rows 0..L-1 of zero_rows
@@ -157,7 +179,8 @@ int fmoe_gate_topk_counts_supported(const void* x, int x_dtype, int64_t ldx, con
 size_t fmoe_route_group_counts_bytes(int64_t L, int E);
 int fmoe_gate_topk_counts(const void* x, int x_dtype, int64_t ldx, const float* gate_w, const float* gate_b,
                           int64_t L, int d, int E, int k, float* logits_out, int64_t* topk_idx, float* topk_score,
-                          int* group_counts, void* stream);
+                          int* group_counts, void* zero_rows, int zero_dtype, int64_t ld_zero, int zero_cols,
+                          void* stream);
 int fmoe_route_metadata_gather(const int64_t* topk_idx, int64_t L, int E, int k, const int* group_counts,
                                int64_t* lengths, int64_t* offsets, int64_t* gate_index, int64_t* token_index,
                                int64_t* reverse_index, int64_t* max_len, const void* x, int x_dtype, int64_t ldx,

@@ -30,13 +30,18 @@ def _layer_from_golden(g, dtype=torch.float32):
         layer._experts_hidden_w.copy_(g["w_hidden"]); layer._experts_hidden_bias.copy_(g["b_hidden"])
         layer._experts_w.copy_(g["w_out"]); layer._experts_bias.copy_(g["b_out"])
         layer._w_gate.copy_(g["w_gate"]); layer._output_weight.copy_(g["output_weight"])
+        if "w_noise" in g:
+            layer._w_noise.copy_(g["w_noise"])
     return layer.to(DEV)
 
 
 def _safe_tokens(g, min_gap=1e-6):
     """Tokens whose k-th and (k+1)-th gate probabilities are not a near tie."""
     x_norm = g["x_norm"]
-    logits = torch.nn.functional.normalize(x_norm @ g["w_gate"], dim=1)
+    raw = x_norm @ g["w_gate"]
+    if "w_noise" in g and g["train"]:
+        raw = raw + g["noise"] * (torch.nn.functional.softplus(x_norm @ g["w_noise"]) + 1e-2)
+    logits = torch.nn.functional.normalize(raw, dim=1)
     p = torch.softmax(logits, dim=1).sort(dim=1, descending=True).values
     k = g["k"]
     if k >= p.shape[1]:
@@ -69,15 +74,82 @@ def test_token_norm_and_router_against_golden(name):
     assert _lib.device_status(torch.device(DEV)) == 0
 
 
+def _check_noisy_layer(g):
+    """Noisy gating while training (kernels/pytorch/mrn.py:191-237): with the noise the reference
+    drew, the layer reproduces its output, its load fractions and its loss (which uses the smooth
+    load estimate); the same noise twice gives the same bits; a fresh draw and evaluation mode run."""
+    d = g["x"].shape[1]
+    args = (None, 0, False, 1, d, cu(g["norm_weight"]), cu(g["norm_bias"]), g["norm_eps"])
+    layer = _layer_from_golden(g)
+    layer.train(True)
+    safe = _safe_tokens(g)
+    layer.set_noise(cu(g["noise"]))
+    out = layer(cu(g["x"]), *args)
+    torch.testing.assert_close(out.x.cpu()[safe], g["y"][safe], atol=1e-4, rtol=1e-4)
+    if bool(safe.all()):
+        torch.testing.assert_close(out.load.cpu(), g["load"], atol=1e-7, rtol=1e-6)
+        torch.testing.assert_close(out.loss.cpu().reshape(-1), g["loss"], atol=1e-6, rtol=1e-4)
+    layer.set_noise(cu(g["noise"]))
+    again = layer(cu(g["x"]), *args)
+    assert torch.equal(again.x, out.x) and torch.equal(again.loss, out.loss)
+    fresh = layer(cu(g["x"]), *args)                      # the layer's own draw
+    assert torch.isfinite(fresh.x).all() and torch.isfinite(fresh.loss)
+    # evaluation: clean logits, no loss
+    layer.train(False)
+    ev = layer(cu(g["x"]), *args)
+    ref, _, ref_load = M.sg_moe_forward(g["x"], g["norm_weight"], g["norm_bias"], g["norm_eps"], g["w_gate"], g["w_hidden"],
+                                        g["b_hidden"], g["w_out"], g["b_out"], g["output_weight"], g["k"], train=False)
+    logits = torch.nn.functional.normalize(g["x_norm"] @ g["w_gate"], dim=1)
+    p = torch.softmax(logits, dim=1).sort(dim=1, descending=True).values
+    clean_safe = (p[:, g["k"] - 1] - p[:, g["k"]]) > 1e-6
+    torch.testing.assert_close(ev.x.cpu()[clean_safe], ref[clean_safe], atol=1e-4, rtol=1e-4)
+    assert float(ev.loss) == 0.0
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("L,d,E,k", [(1000, 64, 64, 4), (333, 48, 8, 2), (64, 32, 128, 7), (5, 16, 4, 3), (40, 32, 4, 4)])
+def test_noisy_router_against_oracle(L, d, E, k):
+    """noisy_gate against the CPU restatement of _orig_noisy_gating / _prob_in_top_k on the same
+    noise: picks and gate values on tokens without a near tie, the smooth load per expert and the
+    loss built on it (fp32 sums in a different order: 1e-5 relative)."""
+    from fast_moe_b200.kernels.routing import noisy_gate, route_metadata, sg_load_loss
+
+    torch.manual_seed(L + E)
+    x = torch.randn(L, d)
+    wg = torch.randn(d, E) * 0.3
+    wn = torch.randn(d, E) * 0.3
+    noise = torch.randn(L, E)
+    gates, idx_ref, topk_ref, loss_ref = M.gating(x, wg, k, True, wn, noise)
+    both = torch.cat([wg.t(), wn.t()], dim=0).contiguous()
+    idx, score, partials = noisy_gate(cu(x), cu(both), k, cu(noise))
+    raw = x @ wg + noise * (torch.nn.functional.softplus(x @ wn) + 1e-2)
+    p = torch.softmax(torch.nn.functional.normalize(raw, dim=1), dim=1).sort(dim=1, descending=True).values
+    safe = (p[:, k - 1] - p[:, k]) > 1e-6 if k < E else torch.ones(L, dtype=torch.bool)
+    assert torch.equal(idx.cpu()[safe], idx_ref[safe])
+    torch.testing.assert_close(score.cpu()[safe], topk_ref[safe], atol=1e-6, rtol=1e-5)
+    meta = route_metadata(idx, E)
+    loss, load = sg_load_loss(meta, score, E, torch.float32, 1.0, True, partials)
+    if k < E:
+        assert partials is not None
+        # the oracle's smooth load, recomputed here from its definition
+        stddev = torch.nn.functional.softplus(x @ wn) + 1e-2
+        srt = torch.nn.functional.normalize(raw, dim=1).sort(dim=1, descending=True).values
+        thr_in, thr_out = srt[:, k:k + 1], srt[:, k - 1:k]
+        nrm = torch.distributions.normal.Normal(torch.tensor([0.0]), torch.tensor([1.0]), validate_args=False)
+        prob = torch.where(raw > thr_in, nrm.cdf((x @ wg - thr_in) / stddev), nrm.cdf((x @ wg - thr_out) / stddev))
+        torch.testing.assert_close(partials.sum(0).cpu(), prob.sum(0), atol=1e-4, rtol=2e-5)
+    else:
+        assert partials is None
+    if bool(safe.all()):
+        torch.testing.assert_close(loss.cpu(), loss_ref.float(), atol=1e-6, rtol=1e-4)
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
 @pytest.mark.parametrize("name", G.names("mrn_"))
 def test_sg_moe_layer_against_golden(name):
     g = G.load(name)
     if "w_noise" in g:
-        # noisy gating is a training-time path that is not built: the layer says so
-        layer = _layer_from_golden(g)
-        layer.train(True)
-        with pytest.raises(NotImplementedError):
-            layer(cu(g["x"]), None, 0, False, 1, g["x"].shape[1], cu(g["norm_weight"]), cu(g["norm_bias"]), g["norm_eps"])
+        _check_noisy_layer(g)
         return
     d = g["x"].shape[1]
     groups = g["num_groups"]
