@@ -615,6 +615,129 @@ def single_gpu_record(name, device, args, peaks, fp8_peak, sampler=None, sustain
     return rec
 
 
+def sg_flops_of(A, L, d, h, o, E):
+    """Forward FLOPs of the sparsely-gated layer: two expert products, the shared map, the gate."""
+    return 2 * A * d * h + 2 * A * h * o + 2 * L * d * o + 2 * L * d * E
+
+
+def next_rows_record(device, peaks, steps=10):
+    """Device times of the widened rows at the C2 sizes (4096 tokens, d 1024, h 4096, 8 experts,
+    top-2, bf16): a training step (forward + backward) of both layers, the sparsely-gated layer's
+    forward with and without noisy gating, and the two operators no layer uses. Parity of each is
+    held by the GPU tests against fixtures recorded from the reference; these are timings only."""
+    import fast_moe_b200 as fm
+    from fast_moe_b200 import _lib
+    from fast_moe_b200.kernels import moe as ops
+
+    c = CONFIGS["c2"]
+    L, d, h, o, E, k = c["tokens"], c["d"], c["h"], c["o"], c["E"], c["k"]
+    A = L * k
+    rec = {}
+
+    def eager_ms(fn, n=steps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / n, (time.perf_counter() - t0) / n * 1e3
+
+    # ---- backward pass: training step of the two layers
+    x = make_inputs(c, 0).to(device)
+    for name, build in (("swiglu_layer", lambda: build_layer(c, device)),
+                        ("silu_layer", lambda: fm.FastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(device))):
+        layer = build()
+        layer.autograd = True
+        xg = x.clone().requires_grad_(True)
+
+        def train_step():
+            for p_ in layer.parameters():
+                p_.grad = None
+            xg.grad = None
+            y_ = layer(xg, k)
+            y_.backward(torch.ones_like(y_))
+
+        ms_eager, ms_wall = eager_ms(train_step)
+        for p_ in layer.parameters():
+            p_.grad = None
+        graph_step = fm.CapturedTrainStep(layer, x, k)
+        ms_dev, _ = eager_ms(graph_step.replay)
+        proj = 3 if name == "swiglu_layer" else 2
+        fwd_flops = 2 * A * d * h * (proj - 1) + 2 * A * h * o
+        rec_flops = 4 * A * d * h if name == "swiglu_layer" else 0        # SwiGLU backward recomputes the up projection
+        rec["train_" + name] = dict(
+            ms_per_step=ms_dev, launch_mode="forward + backward as one CUDA graph (CapturedTrainStep), CUDA events around 10 replays",
+            ms_per_step_eager=ms_eager, ms_per_step_eager_wall=ms_wall,
+            model_tflops=3 * fwd_flops / (ms_dev * 1e-3) / 1e12,
+            executed_tflops=(3 * fwd_flops + rec_flops) / (ms_dev * 1e-3) / 1e12,
+            frac_of_bf16_burst=(3 * fwd_flops + rec_flops) / (ms_dev * 1e-3) / 1e12 / peaks["bf16_tflops"],
+            tokens_per_s=L / (ms_dev * 1e-3), device_status=_lib.device_status(device))
+        del graph_step, layer, xg
+    # ---- sparsely-gated layer forward (d -> h -> o MLP experts + shared linear map)
+    torch.manual_seed(0)
+    sg = fm.SGMoELayer(d, o, fm.SGConfig(model_d=h, num_experts=E, num_activated_experts=k)).to(device)
+    sgn = fm.SGMoELayer(d, o, fm.SGConfig(model_d=h, num_experts=E, num_activated_experts=k, enable_noisy_gating=True)).to(device)
+    with torch.no_grad():
+        sgn._w_gate.normal_(0, 0.05)
+        sgn._w_noise.normal_(0, 0.05)
+    x2 = x.reshape(L, d)
+    nw = torch.ones(d, device=device)
+    nb = torch.zeros(d, device=device)
+    sg.train(False)
+    ms_eval = graph_kernel_ms(lambda: sg(x2, None, 0, False, 1, d, nw, nb, 1e-5), device)
+    sgn.train(True)
+    ms_noisy, _ = eager_ms(lambda: sgn(x2, None, 0, False, 1, d, nw, nb, 1e-5))
+    sg_flops = sg_flops_of(A, L, d, h, o, E)
+    sg.train(True)
+    sg.autograd = True
+    xs = x2.clone().requires_grad_(True)
+
+    def sg_train_step():
+        for p_ in sg.parameters():
+            p_.grad = None
+        xs.grad = None
+        out_ = sg(xs, None, 0, False, 1, d, nw, nb, 1e-5)
+        (out_.x.float().sum() + out_.loss).backward()
+
+    ms_sg_train, ms_sg_wall = eager_ms(sg_train_step)
+    rec["train_sg_moe_layer"] = dict(ms_per_step=ms_sg_train, ms_per_step_wall=ms_sg_wall,
+                                     launch_mode="eager autograd, CUDA events around 10 steps",
+                                     model_tflops=3 * sg_flops_of(A, L, d, h, o, E) / (ms_sg_train * 1e-3) / 1e12,
+                                     tokens_per_s=L / (ms_sg_train * 1e-3))
+    sg.autograd = False
+    rec["sg_moe_forward"] = dict(ms_per_step=ms_eval, tokens_per_s=L / (ms_eval * 1e-3),
+                                 layer_tflops=sg_flops / (ms_eval * 1e-3) / 1e12, launch_mode="10 forwards in a CUDA graph",
+                                 noisy_gating_training_ms=ms_noisy, noisy_launch_mode="eager (fresh torch.randn per step)")
+    del sg, sgn
+    # ---- the two operators no layer calls
+    torch.manual_seed(1)
+    idx = torch.stack([torch.randperm(E, device=device)[:k] for _ in range(64)]).repeat(L // 64, 1)
+    meta = fm.route_metadata(idx, E)
+    index = meta.gate_index.view(-1, k)
+    xa = x2
+    xb = torch.randn_like(x2)
+    wa = (torch.randn(E, h, d, device=device) * 0.02).bfloat16().permute(0, 2, 1)
+    wb = (torch.randn(E, h, d, device=device) * 0.02).bfloat16().permute(0, 2, 1)
+    ms_gate2 = graph_kernel_ms(lambda: ops.index_select_jagged_gating_bmm(0, meta.offsets, index, xa, xb, wa, None, wb, None), device)
+    rec["gating_bmm_two_inputs"] = dict(ms=ms_gate2, tflops=4 * A * d * h / (ms_gate2 * 1e-3) / 1e12,
+                                        frac_of_bf16_burst=4 * A * d * h / (ms_gate2 * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                                        shape=f"{A} rows, K={d}, N={h}, two inputs, two weights")
+    x3 = torch.randn(L, E, 256, device=device).bfloat16()
+    w3 = (torch.randn(E, 1024, 256, device=device) * 0.02).bfloat16().permute(0, 2, 1)
+    ms_3d = graph_kernel_ms(lambda: ops.index_select_jagged_bmm_3D(0, meta.offsets, index, x3, w3, None), device)
+    rec["bmm_3D"] = dict(ms=ms_3d, tflops=2 * A * 256 * 1024 / (ms_3d * 1e-3) / 1e12,
+                         shape=f"input [{L}, {E}, 256], {A} rows, N=1024")
+    rec["parity"] = ("tests/test_gpu_backward.py, tests/test_gpu_sg_moe.py, tests/test_gpu_parity.py: gradients, layer outputs "
+                     "and operator outputs against fixtures recorded from the reference")
+    torch.cuda.empty_cache()
+    return rec
+
+
 def ep_single_gpu_record(device, args, peaks, with_e2e=True, parity=True):
     """c5 (64 experts, d=4096, h=14336, 8192 tokens) with every expert on this GPU: the per-rank
     workload of the multi-GPU runs, i.e. the denominator of their weak-scaling efficiency."""
@@ -953,6 +1076,7 @@ def main():
             if not args.no_sub_records:
                 for sub in ("c3", "c4"):
                     line[sub] = single_gpu_record(sub, device, args, peaks, fp8_peak, parity=not args.no_parity)
+                line["next_rows"] = next_rows_record(device, peaks)
             if not args.no_ep_reference:
                 line["c5_ep_1gpu"] = ep_single_gpu_record(device, args, peaks, with_e2e=True, parity=not args.no_parity)
         print(json.dumps(line), flush=True)

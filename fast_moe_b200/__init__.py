@@ -17,7 +17,7 @@ from .kernels.moe import (
 )
 from .kernels.routing import RoutingMetadata, gate_topk, gate_topk_normalized, route_metadata, token_norm
 from .kernels.utils import KernelType
-from .modules.fast_moe_module import (CapturedForward, FastMoELayer, GatingNetwork, HostPipeline, StreamingForward,
+from .modules.fast_moe_module import (CapturedForward, CapturedTrainStep, FastMoELayer, GatingNetwork, HostPipeline, StreamingForward,
                                       SwiGLUFastMoELayer)
 from .modules.sg_moe import MRNOutput, SGConfig, SGMoELayer
 
@@ -26,6 +26,7 @@ __all__ = [
     "GatingNetwork",
     "SwiGLUFastMoELayer",
     "CapturedForward",
+    "CapturedTrainStep",
     "StreamingForward",
     "HostPipeline",
     "KernelType",

@@ -61,6 +61,9 @@ SIGNATURES = {
     "fmoe_gate_topk_normalized": (c_int, [P, c_int, I64, P, P, P, I64, I64, c_int, c_int, c_int, P, P, P, P]),
     "fmoe_token_norm": (c_int, [P, c_int, I64, c_int, I64, c_int, P, P, c_int, c_float, P, I64, P]),
     "fmoe_sg_load_loss": (c_int, [P, P, P, c_int, c_int, c_float, c_int, P, c_int, P, P, P]),
+    "fmoe_token_norm_backward": (c_int, [P, P, c_int, I64, c_int, I64, I64, c_int, P, c_int, c_float, P, I64, P, P, c_int, P, P, P]),
+    "fmoe_sg_router_backward": (c_int, [P, P, P, I64, c_int, c_int, P, P]),
+    "fmoe_sg_loss_backward": (c_int, [P, P, P, c_int, c_int, c_float, P, P, P]),
     "fmoe_sg_noisy_logits": (c_int, [P, I64, P, I64, c_int, c_float, P, P, P]),
     "fmoe_sg_noisy_load": (c_int, [P, I64, P, P, I64, c_int, c_int, P, c_int, P]),
     "fmoe_route_workspace_bytes": (c_size_t, [I64, c_int, c_int]),

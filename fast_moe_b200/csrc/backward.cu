@@ -102,6 +102,100 @@ jagged_transpose_pad_kernel(const T* __restrict__ in, long long ld_in, long long
   }
 }
 
+// 64 x 64 tiles of 2-byte elements with 16-byte global accesses on both sides (the 32 x 32
+// tiles above move 64-byte row pieces). Shared tile: 64 rows of 33 words; the load phase stores
+// four words per 16-byte vector, the store phase gathers eight elements of one tile column.
+constexpr int kT16Pitch = 66;    // elements per tile row (33 words: conflict-free word stores)
+
+__device__ __forceinline__ void tile16_put(__nv_bfloat16 (*tile)[kT16Pitch], int r, int v, uint4 x) {
+  uint32_t* w = reinterpret_cast<uint32_t*>(&tile[r][8 * v]);
+  w[0] = x.x; w[1] = x.y; w[2] = x.z; w[3] = x.w;
+}
+__device__ __forceinline__ uint4 tile16_column(__nv_bfloat16 (*tile)[kT16Pitch], int r0, int c) {
+  const unsigned short* t = reinterpret_cast<const unsigned short*>(&tile[0][0]);
+  unsigned short h[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) h[i] = t[(r0 + i) * kT16Pitch + c];
+  uint4 o;
+  o.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
+  o.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
+  o.z = h[4] | (static_cast<uint32_t>(h[5]) << 16);
+  o.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
+  return o;
+}
+
+// jagged_transpose_pad_kernel for bf16 with cols a multiple of 8 and 16-byte aligned rows on both
+// sides: a block owns 64 padded positions (one K step: never straddles two experts) x 64 columns.
+__global__ void __launch_bounds__(256)
+jagged_transpose_pad_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, long long in_rows,
+                                 const long long* __restrict__ index, int index_div, const long long* __restrict__ offsets,
+                                 const long long* __restrict__ kseg, int E, int cols, __nv_bfloat16* __restrict__ out,
+                                 long long ld_out, int* status) {
+  __shared__ __align__(16) __nv_bfloat16 tile[64][kT16Pitch];
+  const long long q0 = static_cast<long long>(blockIdx.x) * 64;
+  if (q0 >= kseg[E]) return;
+  int lo = 0, hi = E;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (kseg[mid] <= q0) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const long long len = offsets[e + 1] - offsets[e];
+  const long long j0 = q0 - kseg[e];
+  const int c0 = blockIdx.y * 64;
+  const int v = threadIdx.x & 7, rr = threadIdx.x >> 3;      // 8 vectors x 32 rows per pass
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int jr = rr + 32 * i;
+    const long long j = j0 + jr;
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (j < len && c0 + 8 * v < cols) {
+      long long r = offsets[e] + j;
+      if (index != nullptr) {
+        r = index[r] / index_div;
+        if (r < 0 || r >= in_rows) {
+          atomicCAS(status, 0, FMOE_DEV_BAD_INDEX);
+          r = -1;
+        }
+      }
+      if (r >= 0) x = *reinterpret_cast<const uint4*>(in + r * ld_in + c0 + 8 * v);
+    }
+    tile16_put(tile, jr, v, x);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int cr = rr + 32 * i;
+    if (c0 + cr < cols)
+      *reinterpret_cast<uint4*>(out + static_cast<long long>(c0 + cr) * ld_out + q0 + 8 * v) = tile16_column(tile, 8 * v, cr);
+  }
+}
+
+// batched_transpose_kernel for bf16 with rows and cols multiples of 8 and 16-byte aligned rows.
+__global__ void __launch_bounds__(256)
+batched_transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long in_sb, long long ld_in, int rows, int cols,
+                              __nv_bfloat16* __restrict__ out, long long out_sb, long long ld_out) {
+  __shared__ __align__(16) __nv_bfloat16 tile[64][kT16Pitch];
+  const __nv_bfloat16* src = in + static_cast<long long>(blockIdx.z) * in_sb;
+  __nv_bfloat16* dst = out + static_cast<long long>(blockIdx.z) * out_sb;
+  const int r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+  const int v = threadIdx.x & 7, rr = threadIdx.x >> 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + rr + 32 * i;
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (r < rows && c0 + 8 * v < cols) x = *reinterpret_cast<const uint4*>(src + static_cast<long long>(r) * ld_in + c0 + 8 * v);
+    tile16_put(tile, rr + 32 * i, v, x);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int c = c0 + rr + 32 * i;
+    if (c < cols && r0 + 8 * v < rows)
+      *reinterpret_cast<uint4*>(dst + static_cast<long long>(c) * ld_out + r0 + 8 * v) = tile16_column(tile, 8 * v, rr + 32 * i);
+  }
+}
+
 // out[b, c, r] = in[b, r, c]: plain batched transpose (weights [E, N, K] -> [E, K, N]).
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -125,16 +219,35 @@ batched_transpose_kernel(const T* __restrict__ in, long long in_sb, long long ld
   }
 }
 
-// out[e, n] = sum over the rows of expert e of x[r, n], fp32 accumulation in row order.
+// out[e, n] = sum over the rows of expert e of x[r, n], fp32 accumulation. A block owns 32 columns
+// of one expert: its 8 warps take the rows r0 + w, r0 + w + 8, ... (lane = column, 4 rows in flight
+// per warp), then the 8 partial sums of a column are added in warp order. The order is fixed, so
+// a result repeats bit for bit.
 template <typename T, typename OT>
 __global__ void __launch_bounds__(256)
 jagged_colsum_kernel(const T* __restrict__ x, long long ldx, const long long* __restrict__ offsets, int N, OT* __restrict__ out) {
+  __shared__ float part[8][33];
   const int e = blockIdx.y;
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
-  float acc = 0.f;
-  for (long long r = offsets[e]; r < offsets[e + 1]; ++r) acc += ldf<T>(x + r * ldx + n);
-  stf(out + static_cast<long long>(e) * N + n, acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * 32 + lane;
+  const long long r0 = offsets[e], r1 = offsets[e + 1];
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (n < N) {
+    long long r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] += ldf<T>(x + (r + 8 * u) * ldx + n);
+    }
+    for (; r < r1; r += 8) acc[0] += ldf<T>(x + r * ldx + n);
+  }
+  part[warp][lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  __syncthreads();
+  if (warp == 0 && n < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += part[w][lane];
+    stf(out + static_cast<long long>(e) * N + n, s);
+  }
 }
 
 // out[p, :] = src[index[p] / div, :] * weight[weight_index[p]]; the product is rounded to the
@@ -210,6 +323,49 @@ activation_backward_kernel(int mode, const T* __restrict__ d_out, long long ldd,
   }
 }
 
+// The same for bf16 with 8 elements (16 bytes) per thread and step: cols a multiple of 8, row
+// strides multiples of 8, 16-byte aligned bases.
+__global__ void __launch_bounds__(256)
+activation_backward_bf16x8_kernel(int mode, const __nv_bfloat16* __restrict__ d_out, long long ldd,
+                                  const __nv_bfloat16* __restrict__ alpha, long long lda,
+                                  const __nv_bfloat16* __restrict__ beta, long long ldb, long long rows, int cols,
+                                  __nv_bfloat16* __restrict__ d_alpha, long long ldda, __nv_bfloat16* __restrict__ d_beta,
+                                  long long lddb) {
+  const int vec = cols >> 3;
+  const long long total = rows * vec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec;
+    const int c = static_cast<int>(i - r * vec) << 3;
+    const uint4 gv = *reinterpret_cast<const uint4*>(d_out + r * ldd + c);
+    const uint4 av = *reinterpret_cast<const uint4*>(alpha + r * lda + c);
+    uint4 bv = make_uint4(0, 0, 0, 0);
+    if (mode != 0) bv = *reinterpret_cast<const uint4*>(beta + r * ldb + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+    uint4 oa, ob;
+    __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+    __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]);
+      const float2 a = __bfloat1622float2(a2[j]);
+      const float2 b = __bfloat1622float2(b2[j]);
+      const float sx = 1.0f / (1.0f + expf(-a.x)), sy = 1.0f / (1.0f + expf(-a.y));
+      const float dx = sx * (1.0f + a.x * (1.0f - sx)), dy = sy * (1.0f + a.y * (1.0f - sy));
+      if (mode == 0) {
+        oa2[j] = __floats2bfloat162_rn(g.x * dx, g.y * dy);
+      } else {
+        oa2[j] = __floats2bfloat162_rn(g.x * b.x * dx, g.y * b.y * dy);
+        ob2[j] = __floats2bfloat162_rn(g.x * a.x * sx, g.y * a.y * sy);
+      }
+    }
+    *reinterpret_cast<uint4*>(d_alpha + r * ldda + c) = oa;
+    if (mode != 0) *reinterpret_cast<uint4*>(d_beta + r * lddb + c) = ob;
+  }
+}
+
 // Router backward. The forward keeps the k largest softmax probabilities of a token and
 // renormalises them to sum 1 (modules/fast_moe_module.py:93-105): y_j = p_j / sum_sel p, which is
 // the softmax over the k selected logits alone. So d_logit_j = y_j (dy_j - sum_i y_i dy_i) for the
@@ -250,38 +406,45 @@ gate_dx_kernel(const float* __restrict__ d_logits, const float* __restrict__ w, 
 }
 
 // d_W[e, c] += sum over a chunk of tokens of d_logits[t, e] * x[t, c]; d_b[e] += sum of d_logits[t, e].
-// A block owns 256 columns and one chunk of tokens, keeps 32 experts' partial sums per thread in
-// registers and adds them to the fp32 result (cleared beforehand) with atomics.
+// A block owns 256 columns and one chunk of kGateDwChunk tokens: the chunk's d_logits are staged in
+// shared memory once, each thread keeps 32 experts' partial sums in registers and adds them to the
+// fp32 result (cleared beforehand) with atomics.
+constexpr int kGateDwChunk = 64;
 template <typename T>
 __global__ void __launch_bounds__(256)
 gate_dw_kernel(const float* __restrict__ d_logits, const T* __restrict__ x, long long ldx, long long L, int d, int E,
-               int tokens_per_chunk, float* __restrict__ dw, float* __restrict__ db) {
-  __shared__ float s_dl[32];
+               float* __restrict__ dw, float* __restrict__ db) {
+  __shared__ float s_dl[kGateDwChunk][33];
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const long long t0 = static_cast<long long>(blockIdx.y) * tokens_per_chunk;
-  const long long t1 = min(L, t0 + tokens_per_chunk);
+  const long long t0 = static_cast<long long>(blockIdx.y) * kGateDwChunk;
+  const int nt = static_cast<int>(min(static_cast<long long>(kGateDwChunk), L - t0));
   for (int e0 = 0; e0 < E; e0 += 32) {
     const int ne = min(32, E - e0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * ne; i += blockDim.x) {
+      const int tt = i / ne, ee = i - tt * ne;
+      s_dl[tt][ee] = d_logits[(t0 + tt) * E + e0 + ee];
+    }
+    __syncthreads();
     float acc[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    float bsum = 0.f;                      // thread i < ne of column block 0 also sums expert e0 + i's bias gradient
-    for (long long t = t0; t < t1; ++t) {
-      __syncthreads();
-      if (threadIdx.x < ne) s_dl[threadIdx.x] = d_logits[t * E + e0 + threadIdx.x];
-      __syncthreads();
-      const float xv = c < d ? ldf<T>(x + t * ldx + c) : 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < ne) acc[i] = fmaf(s_dl[i], xv, acc[i]);
-      if (blockIdx.x == 0 && threadIdx.x < ne) bsum += s_dl[threadIdx.x];
-    }
     if (c < d) {
+      for (int tt = 0; tt < nt; ++tt) {
+        const float xv = ldf<T>(x + (t0 + tt) * ldx + c);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < ne) acc[i] = fmaf(s_dl[tt][i], xv, acc[i]);
+      }
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         if (i < ne) atomicAdd(dw + static_cast<long long>(e0 + i) * d + c, acc[i]);
     }
-    if (db != nullptr && blockIdx.x == 0 && threadIdx.x < ne) atomicAdd(db + e0 + threadIdx.x, bsum);
+    if (db != nullptr && blockIdx.x == 0 && threadIdx.x < ne) {
+      float bsum = 0.f;
+      for (int tt = 0; tt < nt; ++tt) bsum += s_dl[tt][threadIdx.x];
+      atomicAdd(db + e0 + threadIdx.x, bsum);
+    }
   }
 }
 
@@ -323,7 +486,14 @@ extern "C" int fmoe_jagged_transpose_pad(const void* in, int dtype, int64_t in_r
                unit, padded_max);
   dim3 grid(static_cast<unsigned>((padded_max + 31) / 32), static_cast<unsigned>((cols + 31) / 32), 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == FMOE_BF16) {
+  const auto aligned16 = [](const void* p_) { return (reinterpret_cast<uintptr_t>(p_) & 15) == 0; };
+  if (dtype == FMOE_BF16 && cols % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && aligned16(in) && aligned16(out)) {
+    dim3 grid64(static_cast<unsigned>((padded_max + 63) / 64), static_cast<unsigned>((cols + 63) / 64), 1);
+    jagged_transpose_pad_bf16_kernel<<<grid64, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(in), ld_in, in_rows, reinterpret_cast<const long long*>(index), index_div,
+        reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(kseg), E, cols,
+        static_cast<__nv_bfloat16*>(out), ld_out, status);
+  } else if (dtype == FMOE_BF16) {
     jagged_transpose_pad_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(in), ld_in, in_rows, reinterpret_cast<const long long*>(index), index_div,
         reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(kseg), E, cols,
@@ -347,7 +517,13 @@ extern "C" int fmoe_batched_transpose(const void* in, int dtype, int batch, int6
   FMOE_REQUIRE(in && out && batch <= 65535, "batched_transpose: bad arguments");
   dim3 grid((rows + 31) / 32, (cols + 31) / 32, batch);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == FMOE_BF16) {
+  const auto aligned16 = [](const void* p_) { return (reinterpret_cast<uintptr_t>(p_) & 15) == 0; };
+  if (dtype == FMOE_BF16 && rows % 8 == 0 && cols % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && in_sb % 8 == 0 &&
+      out_sb % 8 == 0 && aligned16(in) && aligned16(out)) {
+    dim3 grid64((rows + 63) / 64, (cols + 63) / 64, batch);
+    batched_transpose_bf16_kernel<<<grid64, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), in_sb, ld_in, rows, cols,
+                                                          static_cast<__nv_bfloat16*>(out), out_sb, ld_out);
+  } else if (dtype == FMOE_BF16) {
     batched_transpose_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), in_sb, ld_in, rows, cols,
                                                                    static_cast<__nv_bfloat16*>(out), out_sb, ld_out);
   } else {
@@ -384,7 +560,7 @@ extern "C" int fmoe_jagged_colsum(const void* x, int dtype, int64_t ldx, const i
   FMOE_REQUIRE((dtype == FMOE_BF16 || dtype == FMOE_F32) && (out_dtype == FMOE_BF16 || out_dtype == FMOE_F32),
                "jagged_colsum: dtypes must be bf16 or f32");
   FMOE_REQUIRE(E >= 1 && E <= 65535 && N >= 1 && offsets && out, "jagged_colsum: bad arguments");
-  dim3 grid((N + 255) / 256, E, 1);
+  dim3 grid((N + 31) / 32, E, 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long* off = reinterpret_cast<const long long*>(offsets);
 #define FMOE_COLSUM(T, OT) jagged_colsum_kernel<T, OT><<<grid, 256, 0, st>>>(static_cast<const T*>(x), ldx, off, N, static_cast<OT*>(out))
@@ -462,7 +638,14 @@ extern "C" int fmoe_activation_backward(int mode, const void* d_out, int64_t ldd
   FMOE_REQUIRE(d_out && alpha && d_alpha && (mode == 0 || (beta && d_beta)), "activation_backward: NULL pointer argument");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = grid_for(rows * cols, 256);
-  if (dtype == FMOE_BF16) {
+  const auto vec_ok = [](const void* p_, long long ld_) { return p_ == nullptr || ((reinterpret_cast<uintptr_t>(p_) & 15) == 0 && ld_ % 8 == 0); };
+  if (dtype == FMOE_BF16 && cols % 8 == 0 && vec_ok(d_out, ldd) && vec_ok(alpha, lda) && vec_ok(beta, ldb) &&
+      vec_ok(d_alpha, ldda) && vec_ok(d_beta, lddb)) {
+    using T = __nv_bfloat16;
+    activation_backward_bf16x8_kernel<<<grid_for(rows * (cols / 8), 256), 256, 0, st>>>(
+        mode, static_cast<const T*>(d_out), ldd, static_cast<const T*>(alpha), lda, static_cast<const T*>(beta), ldb, rows, cols,
+        static_cast<T*>(d_alpha), ldda, static_cast<T*>(d_beta), lddb);
+  } else if (dtype == FMOE_BF16) {
     using T = __nv_bfloat16;
     activation_backward_kernel<T><<<grid, 256, 0, st>>>(mode, static_cast<const T*>(d_out), ldd, static_cast<const T*>(alpha), lda,
                                                         static_cast<const T*>(beta), ldb, rows, cols, static_cast<T*>(d_alpha),
@@ -515,14 +698,14 @@ extern "C" int fmoe_gate_linear_backward(const float* d_logits, const void* x, i
     ++g_misc_launches;
   }
   if (d_gate_w != nullptr) {
-    const int chunk = 256;
-    dim3 grid((d + 255) / 256, static_cast<unsigned>((L + chunk - 1) / chunk), 1);
+    FMOE_REQUIRE(L <= 65535ll * kGateDwChunk, "gate_linear_backward: L=%lld exceeds %lld tokens", (long long)L,
+                 65535ll * kGateDwChunk);
+    dim3 grid((d + 255) / 256, static_cast<unsigned>((L + kGateDwChunk - 1) / kGateDwChunk), 1);
     if (x_dtype == FMOE_BF16) {
-      gate_dw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(d_logits, static_cast<const __nv_bfloat16*>(x), ldx, L, d, E, chunk,
+      gate_dw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(d_logits, static_cast<const __nv_bfloat16*>(x), ldx, L, d, E,
                                                            d_gate_w, d_gate_b);
     } else {
-      gate_dw_kernel<float><<<grid, 256, 0, st>>>(d_logits, static_cast<const float*>(x), ldx, L, d, E, chunk, d_gate_w,
-                                                   d_gate_b);
+      gate_dw_kernel<float><<<grid, 256, 0, st>>>(d_logits, static_cast<const float*>(x), ldx, L, d, E, d_gate_w, d_gate_b);
     }
     FMOE_CUDA_OK(cudaGetLastError());
     ++g_misc_launches;

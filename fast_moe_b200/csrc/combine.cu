@@ -240,6 +240,30 @@ silu_kernel(const T* __restrict__ in, long long ldi, T* __restrict__ out, long l
   }
 }
 
+// The same for bf16 rows that allow 16-byte accesses (cols a multiple of 8, aligned rows): 8 values
+// per thread and step. Same arithmetic as silu_kernel (expf, IEEE division).
+__global__ void __launch_bounds__(256)
+silu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, long long ldi, __nv_bfloat16* __restrict__ out, long long ldo,
+                   long long rows, int cols) {
+  const int vec = cols >> 3;
+  const long long total = rows * vec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec;
+    const int c = static_cast<int>(i - r * vec) << 3;
+    const uint4 xv = *reinterpret_cast<const uint4*>(in + r * ldi + c);
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    uint4 yv;
+    __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&yv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __bfloat1622float2(x2[j]);
+      y2[j] = __floats2bfloat162_rn(x.x / (1.0f + expf(-x.x)), x.y / (1.0f + expf(-x.y)));
+    }
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = yv;
+  }
+}
+
 // fp32 -> three bf16 terms, hi + mid + lo = x to about 2^-24 relative (hi = bf16(x), mid =
 // bf16(x - hi), lo = bf16(x - hi - mid); the subtractions are exact in fp32). The six partial
 // products a_i * b_j with i + j <= 2 reproduce a * b to fp32 accuracy, and each of them is exact
@@ -389,7 +413,14 @@ int launch_silu(const void* in, int dtype, long long ldi, void* out, long long l
   if (rows <= 0 || cols <= 0) return FMOE_OK;
   long long blocks = (rows * cols + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  if (dtype == FMOE_BF16) {
+  const bool vec8 = dtype == FMOE_BF16 && cols % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 &&
+                    (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  if (vec8) {
+    long long b8 = (rows * (cols / 8) + 255) / 256;
+    if (b8 > 148 * 32) b8 = 148 * 32;
+    silu_bf16x8_kernel<<<static_cast<unsigned>(b8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), ldi,
+                                                                  static_cast<__nv_bfloat16*>(out), ldo, rows, cols);
+  } else if (dtype == FMOE_BF16) {
     silu_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(in), ldi, static_cast<__nv_bfloat16*>(out), ldo, rows, cols);
   } else if (dtype == FMOE_F32) {

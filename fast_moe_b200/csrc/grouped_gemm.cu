@@ -102,6 +102,7 @@ struct GemmParams {
   // elementwise multiplier applied last: out[r, n] = (...)[r, n] * mul_in[r * ld_mul + n] (output type)
   const void* mul_in;
   long long ld_mul;
+  int mul_vec;       // rows of mul_in are 16-byte aligned: 16-byte loads in the store phase
   int* status;
 };
 
@@ -173,15 +174,28 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int
 // With `accumulate` the 16-byte pieces are added to memory (one vector red.global.add per
 // piece) instead of stored: the fused combine, where several expert rows land on
 // one token row.
+// `mul_row` (optional, per stored row): a second factor of the same shape as the output, read here
+// in the same coalesced pattern (16 bytes per lane, a row's 64 bytes from 4 neighbouring lanes)
+// and multiplied into the staged values, which are already rounded to the output type.
 template <typename OutT>
 __device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, const float (&v)[32],
                                                 OutT* const (&st_row)[4], const bool (&st_ok)[4], int col0,
-                                                bool accumulate) {
+                                                bool accumulate, const OutT* const (&mul_row)[4], bool has_mul) {
   constexpr int kHalves = sizeof(OutT) == 2 ? 1 : 2;
+  constexpr int kPieceElemsM = 16 / sizeof(OutT);
   const uint32_t my_row = stage_w + lane * 64;
   const int wsw = (lane >> 1) & 3;
 #pragma unroll
   for (int h = 0; h < kHalves; ++h) {
+    uint4 mv[4];
+    if (has_mul) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mv[i] = make_uint4(0, 0, 0, 0);
+        if (st_ok[i])
+          mv[i] = *reinterpret_cast<const uint4*>(mul_row[i] + col0 + (kHalves == 2 ? 16 * h : 0) + (lane & 3) * kPieceElemsM);
+      }
+    }
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t w0, w1, w2, w3;
@@ -217,6 +231,23 @@ __device__ __forceinline__ void stage_and_store(uint32_t stage_w, int lane, cons
       if (st_ok[i]) {
         constexpr int kPieceElems = 16 / sizeof(OutT);
         OutT* dst = st_row[i] + col0 + (kHalves == 2 ? 16 * h : 0) + piece * kPieceElems;
+        if (has_mul) {
+          if constexpr (sizeof(OutT) == 2) {
+            const uint32_t m4[4] = {mv[i].x, mv[i].y, mv[i].z, mv[i].w};
+            uint32_t* w4[4] = {&w0, &w1, &w2, &w3};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(w4[u]),
+                                                  *reinterpret_cast<const __nv_bfloat162*>(&m4[u]));
+              *w4[u] = *reinterpret_cast<const uint32_t*>(&prod);
+            }
+          } else {
+            w0 = __float_as_uint(__uint_as_float(w0) * __uint_as_float(mv[i].x));
+            w1 = __float_as_uint(__uint_as_float(w1) * __uint_as_float(mv[i].y));
+            w2 = __float_as_uint(__uint_as_float(w2) * __uint_as_float(mv[i].z));
+            w3 = __float_as_uint(__uint_as_float(w3) * __uint_as_float(mv[i].w));
+          }
+        }
         if (!accumulate) {
           *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
         } else if constexpr (sizeof(OutT) == 2) {
@@ -532,6 +563,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // It needs those rows' destinations, which live in the lanes that own them.
       OutT* st_row[4];
       bool st_ok[4];
+      const OutT* mul_row[4] = {nullptr, nullptr, nullptr, nullptr};
+      // the multiplier of a gated product goes in with the coalesced store phase (not with a combine)
+      // (the in-kernel-gather variants run at their register cap and keep the multiplier in the math phase)
+      const bool mul_staged = !GATHER && p.mul_in != nullptr && !combine && p.mul_vec != 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int src_lane = (lane >> 2) + 8 * i;
@@ -539,8 +574,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out_row), src_lane);
         st_row[i] = reinterpret_cast<OutT*>(ptr_bits);
         st_ok[i] = __shfl_sync(0xffffffffu, store_ok ? 1 : 0, src_lane) != 0;
+        if constexpr (!GATHER) {
+          if (mul_staged) {
+            const long long mrow = __shfl_sync(0xffffffffu, row, src_lane);
+            mul_row[i] = reinterpret_cast<const OutT*>(p.mul_in) + mrow * p.ld_mul;
+          }
+        }
       }
       const int n0 = nb * kTileN;
+      // Column factors of this tile (bias, FP8 column scales): fetched before the wait for the
+      // accumulator, lane i holding column i of every 32-column chunk, so that their latency
+      // hides behind the MMAs instead of stalling every chunk.
+      float pre_b0[kChunks], pre_b1[DUAL ? kChunks : 1], pre_f0[fp8 ? kChunks : 1], pre_f1[(fp8 && DUAL) ? kChunks : 1];
+      pre_b1[0] = 0.f; pre_f0[0] = 1.f; pre_f1[0] = 1.f;
+#pragma unroll
+      for (int j = 0; j < kChunks; ++j) {
+        pre_b0[j] = 0.f;
+        if constexpr (DUAL) pre_b1[j] = 0.f;
+        if constexpr (fp8) pre_f0[j] = 1.f;
+        if constexpr (fp8 && DUAL) pre_f1[j] = 1.f;
+        const int col = n0 + c_begin + 32 * j + lane;
+        if (col < p.N) {
+          if (p.bias0 != nullptr) pre_b0[j] = load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col);
+          if constexpr (DUAL) {
+            if (p.bias1 != nullptr) pre_b1[j] = load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col);
+          }
+          if constexpr (fp8) {
+            if (p.a_scale != nullptr) {
+              const long long so = static_cast<long long>(e) * p.bscale_se + col;
+              pre_f0[j] = 1.0f / p.b0_scale[so];
+              if constexpr (DUAL) pre_f1[j] = 1.0f / p.b1_scale[so];
+            }
+          }
+        }
+      }
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, p.status, FMOE_DEV_WAIT_EPILOGUE)) {
@@ -573,11 +640,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
+        // the arithmetic of all chunks of the round first (independent special-function work back
+        // to back), then their stores
+        float vv[kPerRound][32];
+        const bool want_silu = !DUAL && p.epilogue == FMOE_EPI_SILU;
 #pragma unroll
         for (int j = 0; j < kPerRound; ++j) {
           const int col0 = n0 + c_begin + 32 * (j0 + j);
           const int ncols = min(32, p.N - col0);
-          float v[32];
+          float (&v)[32] = vv[j];
           if (DUAL && ncols == 32 && plain_math) {
             // gated tile, whole chunk inside N, no bias, no dequantisation: straight-line arithmetic
 #pragma unroll
@@ -594,15 +665,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const bool scaled = fp8 && p.a_scale != nullptr;
             const bool has_b0 = p.bias0 != nullptr;
             const bool has_b1 = DUAL && p.bias1 != nullptr;
-            float f0 = 1.f, f1 = 1.f, bb0 = 0.f, bb1 = 0.f;
             const float inv_a = 1.0f / scale_a;          // this lane's row
-            if (scaled) {                                // column factors: lane i holds column i's
-              const long long so = static_cast<long long>(e) * p.bscale_se + col0 + lane;
-              f0 = 1.0f / p.b0_scale[so];
-              if constexpr (DUAL) f1 = 1.0f / p.b1_scale[so];
-            }
-            if (has_b0) bb0 = load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col0 + lane);
-            if (has_b1) bb1 = load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col0 + lane);
+            // column factors: lane i holds column i's (fetched at the top of the tile)
+            const float f0 = pre_f0[fp8 ? j0 + j : 0], f1 = pre_f1[(fp8 && DUAL) ? j0 + j : 0];
+            const float bb0 = pre_b0[j0 + j], bb1 = pre_b1[DUAL ? j0 + j : 0];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float g = __uint_as_float(r0[j][i]);
@@ -624,8 +690,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if constexpr (DUAL) {
                 v[i] = silu_f(g) * u;
               } else {
-                v[i] = (p.epilogue == FMOE_EPI_SILU) ? silu_f(g) : g;
+                v[i] = g;
               }
+            }
+            if (want_silu) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
             }
           } else {
 #pragma unroll
@@ -655,12 +725,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           }
-          if (p.mul_in != nullptr && row_ok) {
-            // second factor of a gated product: this row's 32 values of the multiplier tensor
+        }
+#pragma unroll
+        for (int j = 0; j < kPerRound; ++j) {
+          const int col0 = n0 + c_begin + 32 * (j0 + j);
+          const int ncols = min(32, p.N - col0);
+          float (&v)[32] = vv[j];
+          const bool staged = ncols == 32 && p.vec_ok;
+          if (p.mul_in != nullptr && row_ok && !(staged && mul_staged)) {
+            // second factor of a gated product on the paths without the staged store: this row's
+            // values of the multiplier tensor, the product of the two rounded operands as there
             const OutT* mrow = reinterpret_cast<const OutT*>(p.mul_in) + row * p.ld_mul + col0;
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < ncols) v[i] *= load_as_float<OutT>(mrow, i);
+            for (int i = 0; i < 32; ++i) {
+              if (i < ncols) {
+                float y = v[i];
+                if constexpr (sizeof(OutT) == 2) y = __bfloat162float(__float2bfloat16_rn(y));
+                v[i] = y * load_as_float<OutT>(mrow, i);
+              }
+            }
           }
           if (combine) {
             // what the reference does in the activation type: round the GEMM row, multiply by the
@@ -672,8 +755,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               v[i] = y * gate_scale;
             }
           }
-          if (ncols == 32 && p.vec_ok) {
-            stage_and_store<OutT>(stage_w, lane, v, st_row, st_ok, col0, combine);
+          if (staged) {
+            stage_and_store<OutT>(stage_w, lane, v, st_row, st_ok, col0, combine, mul_row, mul_staged);
           } else if (store_ok && ncols > 0) {
             if (combine) {
 #pragma unroll
@@ -1122,6 +1205,7 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.kseg = reinterpret_cast<const long long*>(d.kseg);
   p.mul_in = d.mul_in;
   p.ld_mul = d.ld_mul;
+  p.mul_vec = d.mul_in != nullptr && ((d.ld_mul * osize) % 16 == 0) && (reinterpret_cast<uintptr_t>(d.mul_in) & 15) == 0;
   p.vec_ok = ((d.ldo * osize) % 16 == 0) && (d.out_peers != nullptr || (reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
   p.status = status;
 

@@ -220,6 +220,211 @@ sg_load_loss_kernel(const long long* __restrict__ offsets, const long long* __re
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward of the layer's own pieces (the reference gets them from torch autograd through its eager
+// code, kernels/pytorch/mrn.py:221-333; its test compares them, kernels/tests/mrn_test.py:816-860).
+
+// Token norm: one warp per (token, group). With xh = (x - mean) * rstd and g = d_out * w,
+//   d_x = rstd * (g - mean(g) - xh * mean(g * xh)).
+// Also leaves (mean, rstd) per segment in `stats` for the parameter-gradient pass.
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_norm_backward_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ dy, long long lddy, long long L,
+                           int groups, int n, const float* __restrict__ w, int per_group_affine, float eps,
+                           T* __restrict__ dx, long long lddx, float* __restrict__ stats) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long total = L * groups;
+  for (long long seg = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; seg < total; seg += warps) {
+    const long long t = seg / groups;
+    const int g = static_cast<int>(seg - t * groups);
+    const T* row = x + t * ldx + static_cast<long long>(g) * n;
+    const T* drow = dy + t * lddy + static_cast<long long>(g) * n;
+    float s = 0.f;
+    for (int c = lane; c < n; c += 32) s += ld_as_float<T>(row + c);
+    const float mean = warp_sum(s) / n;
+    float v = 0.f;
+    for (int c = lane; c < n; c += 32) {
+      const float dlt = ld_as_float<T>(row + c) - mean;
+      v = fmaf(dlt, dlt, v);
+    }
+    const float rstd = rsqrtf(warp_sum(v) / n + eps);
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < n; c += 32) {
+      const int a = per_group_affine ? g : static_cast<int>(static_cast<long long>(g) * n + c);
+      const float gg = ld_as_float<T>(drow + c) * (w ? w[a] : 1.f);
+      const float xh = (ld_as_float<T>(row + c) - mean) * rstd;
+      s1 += gg;
+      s2 = fmaf(gg, xh, s2);
+    }
+    s1 = warp_sum(s1) / n;
+    s2 = warp_sum(s2) / n;
+    T* orow = dx + t * lddx + static_cast<long long>(g) * n;
+    for (int c = lane; c < n; c += 32) {
+      const int a = per_group_affine ? g : static_cast<int>(static_cast<long long>(g) * n + c);
+      const float gg = ld_as_float<T>(drow + c) * (w ? w[a] : 1.f);
+      const float xh = (ld_as_float<T>(row + c) - mean) * rstd;
+      st_from_float(orow + c, rstd * (gg - s1 - xh * s2));
+    }
+    if (lane == 0 && stats) {
+      stats[2 * seg] = mean;
+      stats[2 * seg + 1] = rstd;
+    }
+  }
+}
+
+// Parameter gradients of the norm, first stage: thread c of chunk q sums, over the chunk's tokens,
+// d_out[t, c] * xh[t, c] (weight) and d_out[t, c] (bias) -> partial[q][0 / 1][c]. Fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_param_partial_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ dy, long long lddy, long long L, int d,
+                          int groups, int n, const float* __restrict__ stats, int chunks, float* __restrict__ partial) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int q = blockIdx.y;
+  if (c >= d) return;
+  const long long per = (L + chunks - 1) / chunks;
+  const long long t0 = q * per, t1 = min(L, t0 + per);
+  const int g = c / n;
+  float aw = 0.f, ab = 0.f;
+  for (long long t = t0; t < t1; ++t) {
+    const float mean = stats[2 * (t * groups + g)], rstd = stats[2 * (t * groups + g) + 1];
+    const float go = ld_as_float<T>(dy + t * lddy + c);
+    aw = fmaf(go, (ld_as_float<T>(x + t * ldx + c) - mean) * rstd, aw);
+    ab += go;
+  }
+  partial[(static_cast<long long>(q) * 2 + 0) * d + c] = aw;
+  partial[(static_cast<long long>(q) * 2 + 1) * d + c] = ab;
+}
+
+// Second stage: parameter a (a feature, or a whole group when the affine is per group) sums its
+// partials over chunks and, per group, over the group's features. One warp per parameter.
+__global__ void __launch_bounds__(256)
+norm_param_reduce_kernel(const float* __restrict__ partial, int chunks, int d, int n_params, int span,
+                         float* __restrict__ d_weight, float* __restrict__ d_bias) {
+  const int lane = threadIdx.x & 31;
+  const int a = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (a >= n_params) return;
+  float sw = 0.f, sb = 0.f;
+  const int total = chunks * span;
+  for (int i = lane; i < total; i += 32) {
+    const int q = i / span;
+    const int c = a * span + (i - q * span);
+    sw += partial[(static_cast<long long>(q) * 2 + 0) * d + c];
+    sb += partial[(static_cast<long long>(q) * 2 + 1) * d + c];
+  }
+  sw = warp_sum(sw);
+  sb = warp_sum(sb);
+  if (lane == 0) {
+    if (d_weight) d_weight[a] = sw;
+    if (d_bias) d_bias[a] = sb;
+  }
+}
+
+// Router backward: scores = softmax(l / max(||l||, eps)) at the k chosen experts, not renormalised.
+// One warp per token, lane j holds experts j, j + 32, ...
+template <int VPL>
+__global__ void __launch_bounds__(256)
+sg_router_backward_kernel(const float* __restrict__ logits, const long long* __restrict__ idx,
+                          const float* __restrict__ d_score, long long L, int E, int k, float* __restrict__ d_logits) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < L; t += warps) {
+    float l[VPL], nv[VPL], p[VPL], dp[VPL];
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      l[j] = e < E ? logits[t * E + e] : 0.f;
+      sq = fmaf(l[j], l[j], sq);
+    }
+    const float nrm = fmaxf(sqrtf(warp_sum(sq)), 1e-12f);
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      nv[j] = l[j] / nrm;
+      if (lane + 32 * j < E) mx = fmaxf(mx, nv[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float z = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      p[j] = (lane + 32 * j) < E ? expf(nv[j] - mx) : 0.f;
+      z += p[j];
+    }
+    z = warp_sum(z);
+    float sdot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      p[j] /= z;
+      dp[j] = 0.f;
+      for (int s = 0; s < k; ++s)
+        if (idx[t * k + s] == e) dp[j] += d_score[t * k + s];
+      sdot = fmaf(p[j], dp[j], sdot);
+    }
+    sdot = warp_sum(sdot);
+    float ndot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      dp[j] = p[j] * (dp[j] - sdot);            // d_n
+      ndot = fmaf(nv[j], dp[j], ndot);
+    }
+    ndot = warp_sum(ndot);
+    const bool clamped = nrm <= 1e-12f;         // F.normalize divides by the constant eps then
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) d_logits[t * E + e] = (clamped ? dp[j] : (dp[j] - nv[j] * ndot)) / nrm;
+    }
+  }
+}
+
+// d loss / d scores: loss = coef * (cv2(importance) + cv2(load)); only the importance (sum of the
+// gate values per expert) depends on the scores. One block: importance as the forward sums it, its
+// cv2 derivative per expert, then every chosen (token, slot) receives its expert's value.
+__global__ void __launch_bounds__(256)
+sg_loss_backward_kernel(const long long* __restrict__ offsets, const long long* __restrict__ gate_index,
+                        const float* __restrict__ score, int E, int round_bf16, float loss_coef,
+                        const float* __restrict__ d_loss, float* __restrict__ d_score) {
+  extern __shared__ float s_imp[];                 // [E] importance, then its gradient
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int e = warp; e < E; e += 8) {
+    float acc = 0.f;
+    for (long long p = offsets[e] + lane; p < offsets[e + 1]; p += 32) {
+      float g = score[gate_index[p]];
+      if (round_bf16) g = __bfloat162float(__float2bfloat16_rn(g));
+      acc += g;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) s_imp[e] = round_bf16 ? __bfloat162float(__float2bfloat16_rn(acc)) : acc;
+  }
+  __syncthreads();
+  __shared__ float s_mean, s_var;
+  if (threadIdx.x == 0) {
+    float mean = 0.f;
+    for (int e = 0; e < E; ++e) mean += s_imp[e];
+    mean /= E;
+    float var = 0.f;
+    for (int e = 0; e < E; ++e) var += (s_imp[e] - mean) * (s_imp[e] - mean);
+    s_mean = mean;
+    s_var = E > 1 ? var / (E - 1) : 0.f;
+  }
+  __syncthreads();
+  const float scale = loss_coef * (d_loss ? *d_loss : 1.f);
+  const float den = s_mean * s_mean + 1e-6f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const float g = E > 1 ? (2.f * (s_imp[e] - s_mean) / ((E - 1) * den) - s_var * 2.f * s_mean / (E * den * den)) : 0.f;
+    s_imp[e] = g * scale;
+  }
+  __syncthreads();
+  for (int e = 0; e < E; ++e) {
+    const float g = s_imp[e];
+    for (long long p = offsets[e] + threadIdx.x; p < offsets[e + 1]; p += blockDim.x) d_score[gate_index[p]] = g;
+  }
+}
+
 }  // namespace
 }  // namespace fmoe
 
@@ -296,6 +501,91 @@ extern "C" int fmoe_sg_load_loss(const int64_t* offsets, const int64_t* gate_ind
   sg_load_loss_kernel<<<1, 256, 3 * static_cast<size_t>(E) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(gate_index), topk_score, E, round_bf16,
       loss_coef, want_loss, load_partials, n_partials, load_frac, loss);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_token_norm_backward(const void* x, const void* d_out, int dtype, int64_t L, int d, int64_t ldx,
+                                        int64_t ld_dout, int num_groups, const float* weight, int per_group_affine,
+                                        float eps, void* d_x, int64_t ld_dx, float* stats, float* partial, int chunks,
+                                        float* d_weight, float* d_bias, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "token_norm_backward: dtype must be bf16 or f32");
+  FMOE_REQUIRE(L >= 0 && d >= 1 && num_groups >= 1 && d % num_groups == 0, "token_norm_backward: d=%d must split into %d groups",
+               d, num_groups);
+  const bool params = d_weight != nullptr || d_bias != nullptr;
+  FMOE_REQUIRE(!params || (stats && partial && chunks >= 1 && chunks <= 1024),
+               "token_norm_backward: parameter gradients need the stats and partial scratch and 1..1024 chunks");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n = d / num_groups;
+  const int n_params = per_group_affine ? num_groups : d;
+  if (L == 0) {
+    if (d_weight) FMOE_CUDA_OK(cudaMemsetAsync(d_weight, 0, n_params * sizeof(float), st));
+    if (d_bias) FMOE_CUDA_OK(cudaMemsetAsync(d_bias, 0, n_params * sizeof(float), st));
+    return FMOE_OK;
+  }
+  FMOE_REQUIRE(x && d_out && d_x, "token_norm_backward: NULL pointer argument");
+  const long long segs = L * num_groups;
+  long long blocks = (segs * 32 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dim3 pgrid((d + 255) / 256, chunks > 0 ? chunks : 1);
+  if (dtype == FMOE_BF16) {
+    using T = __nv_bfloat16;
+    token_norm_backward_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const T*>(x), ldx, static_cast<const T*>(d_out), ld_dout, L, num_groups, n, weight, per_group_affine, eps,
+        static_cast<T*>(d_x), ld_dx, stats);
+    if (params)
+      norm_param_partial_kernel<T><<<pgrid, 256, 0, st>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(d_out), ld_dout,
+                                                          L, d, num_groups, n, stats, chunks, partial);
+  } else {
+    token_norm_backward_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const float*>(x), ldx, static_cast<const float*>(d_out), ld_dout, L, num_groups, n, weight,
+        per_group_affine, eps, static_cast<float*>(d_x), ld_dx, stats);
+    if (params)
+      norm_param_partial_kernel<float><<<pgrid, 256, 0, st>>>(static_cast<const float*>(x), ldx,
+                                                              static_cast<const float*>(d_out), ld_dout, L, d, num_groups, n,
+                                                              stats, chunks, partial);
+  }
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  if (params) {
+    ++g_misc_launches;                                   // the partial-sum launch above
+    norm_param_reduce_kernel<<<(n_params * 32 + 255) / 256, 256, 0, st>>>(partial, chunks, d, n_params,
+                                                                         per_group_affine ? n : 1, d_weight, d_bias);
+    FMOE_CUDA_OK(cudaGetLastError());
+    ++g_misc_launches;
+  }
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_sg_router_backward(const float* logits, const int64_t* topk_idx, const float* d_score, int64_t L, int E,
+                                       int k, float* d_logits, void* stream) {
+  FMOE_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= E && L >= 0, "sg_router_backward: E=%d (<= 256), k=%d out of range", E, k);
+  if (L == 0) return FMOE_OK;
+  FMOE_REQUIRE(logits && topk_idx && d_score && d_logits, "sg_router_backward: NULL pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long blocks = (L * 32 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long long* idx = reinterpret_cast<const long long*>(topk_idx);
+  const int vpl = (E + 31) / 32;
+#define FMOE_SG_RB(V) sg_router_backward_kernel<V><<<static_cast<unsigned>(blocks), 256, 0, st>>>(logits, idx, d_score, L, E, k, d_logits)
+  if (vpl <= 1) FMOE_SG_RB(1);
+  else if (vpl <= 2) FMOE_SG_RB(2);
+  else if (vpl <= 4) FMOE_SG_RB(4);
+  else FMOE_SG_RB(8);
+#undef FMOE_SG_RB
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_sg_loss_backward(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
+                                     int round_bf16, float loss_coef, const float* d_loss, float* d_score, void* stream) {
+  FMOE_REQUIRE(E >= 1 && E <= 4096, "sg_loss_backward: E=%d outside [1, 4096]", E);
+  FMOE_REQUIRE(offsets && gate_index && topk_score && d_score, "sg_loss_backward: NULL pointer argument");
+  sg_loss_backward_kernel<<<1, 256, static_cast<size_t>(E) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(gate_index), topk_score, E, round_bf16,
+      loss_coef, d_loss, d_score);
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
   return FMOE_OK;

@@ -53,6 +53,26 @@ def transposed_weight(weight: torch.Tensor) -> torch.Tensor:
     return out.permute(0, 2, 1)
 
 
+def transposed_weights_side_by_side(weight: torch.Tensor, weight_p: torch.Tensor) -> torch.Tensor:
+    """The operand of d_x = [d_alpha | d_beta] @ [W ; Wp]^T as one product over 2N: logical
+    [E, 2N, K] with storage [E, K, 2N] (2N contiguous). Each weight is transposed straight into its
+    half of that storage; a weight that already has N contiguous is copied."""
+    E, K, N = weight.shape
+    dev = weight.device
+    store = torch.empty((E, K, 2 * N), dtype=weight.dtype, device=dev)
+    lib = _lib.load()
+    for col0, w in ((0, weight), (N, weight_p)):
+        half = store[:, :, col0:col0 + N]
+        wt = w.permute(0, 2, 1)                       # [E, N, K]
+        if w.stride(2) == 1 or wt.stride(2) != 1:
+            half.copy_(w)                             # N already contiguous, or an arbitrary layout: plain copy
+            continue
+        with torch.cuda.device(dev):
+            _lib.check(lib.fmoe_batched_transpose(wt.data_ptr(), _lib.dtype_code(wt.dtype), E, wt.stride(0), wt.stride(1), N, K,
+                                                  half.data_ptr(), K * 2 * N, 2 * N, _lib.stream_ptr(dev)))
+    return store.permute(0, 2, 1)
+
+
 def _padded_reduction(offsets: torch.Tensor, E: int, dtype: torch.dtype, rows: int) -> Tuple[torch.Tensor, int]:
     lib = _lib.load()
     dev = offsets.device
@@ -80,10 +100,11 @@ def _transpose_pad(src: torch.Tensor, offsets: torch.Tensor, kseg: torch.Tensor,
 
 
 def grad_weight(offsets: torch.Tensor, d_out: torch.Tensor, x: torch.Tensor, E: int, out_dtype: torch.dtype,
-                index: Optional[torch.Tensor] = None, index_div: int = 1) -> torch.Tensor:
+                index: Optional[torch.Tensor] = None, index_div: int = 1, shared: Optional[dict] = None) -> torch.Tensor:
     """dW logical [E, K, N] with dW[e] = X_e^T dOut_e: d_out [rows, N] and x (rows named by
     ``index // index_div`` when given, else row r itself) [*, K], expert-sorted by ``offsets``.
-    Computed in the storage layout [E, N, K] and returned as its permuted view."""
+    Computed in the storage layout [E, N, K] and returned as its permuted view. ``shared``: a dict
+    two calls with the same offsets / x / index pass to transpose x once."""
     lib = _lib.load()
     dev = d_out.device
     rows, N = d_out.shape
@@ -92,9 +113,14 @@ def grad_weight(offsets: torch.Tensor, d_out: torch.Tensor, x: torch.Tensor, E: 
     assert x.dtype == dt
     if rows == 0:
         return torch.zeros((E, N, K), dtype=out_dtype, device=dev).permute(0, 2, 1)
-    kseg, padded = _padded_reduction(offsets, E, dt, rows)
+    if shared is not None and "b_t" in shared:
+        kseg, padded, b_t = shared["kseg"], shared["padded"], shared["b_t"]
+    else:
+        kseg, padded = _padded_reduction(offsets, E, dt, rows)
+        b_t = _transpose_pad(x, offsets, kseg, padded, E, rows, index, index_div)
+        if shared is not None:
+            shared.update(kseg=kseg, padded=padded, b_t=b_t)
     a_t = _transpose_pad(d_out, offsets, kseg, padded, E, rows)
-    b_t = _transpose_pad(x, offsets, kseg, padded, E, rows, index, index_div)
     group_off = torch.arange(E + 1, dtype=torch.int64, device=dev) * N
     out = torch.empty((E * N, K), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
@@ -243,16 +269,19 @@ class IndexSelectJaggedBmmSwigluFn(torch.autograd.Function):
             if ctx.needs_input_grad[2]:
                 # d_rows = [d_alpha | d_beta] @ [W ; Wp]^T as one product over 2N
                 # (the two transposed weights side by side: storage [E, K, 2N], 2N contiguous)
-                w_cat = torch.cat([transposed_weight(weight).permute(0, 2, 1), transposed_weight(weight_p).permute(0, 2, 1)],
-                                  dim=2).permute(0, 2, 1)                                        # logical [E, 2N, K]
+                w_cat = transposed_weights_side_by_side(weight, weight_p)                        # logical [E, 2N, K]
                 d_rows = ops.silu_jagged_bmm(offsets, d_ab, w_cat, None, has_silu=False)
                 tok = index.reshape(-1) // A
                 d_jagged = ops.mul_merge_k_add(tok, _inverse_rows(index), d_rows)
             flat = index.reshape(-1).contiguous()
+            # two products, each written in its parameter's own storage layout (a gradient that
+            # is a slice of a larger buffer would be copied by autograd); the token rows are
+            # transposed once for both
+            once: dict = {}
             if ctx.needs_input_grad[3]:
-                d_w = grad_weight(offsets, d_alpha, jagged, E, weight.dtype, index=flat, index_div=A)
+                d_w = grad_weight(offsets, d_alpha, jagged, E, weight.dtype, index=flat, index_div=A, shared=once)
             if ctx.needs_input_grad[5]:
-                d_wp = grad_weight(offsets, d_beta, jagged, E, weight_p.dtype, index=flat, index_div=A)
+                d_wp = grad_weight(offsets, d_beta, jagged, E, weight_p.dtype, index=flat, index_div=A, shared=once)
             if bias is not None and ctx.needs_input_grad[4]:
                 d_b = grad_bias(offsets, d_alpha, E, bias.dtype)
             if bias_p is not None and ctx.needs_input_grad[6]:
@@ -377,6 +406,134 @@ class RouterFn(torch.autograd.Function):
             if d_w is not None and d_w.dtype != gate_weight.dtype:
                 d_w = d_w.to(gate_weight.dtype)
         return d_x, d_w, d_b, None
+
+
+class TokenNormFn(torch.autograd.Function):
+    """fmoe_token_norm (layer norm, or group norm with one weight / bias per group;
+    kernels/pytorch/mrn.py:301-318) with its backward: d_x and the gradients of weight and bias."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, group_norm, num_groups):
+        from .routing import token_norm
+
+        with torch.no_grad():
+            out = token_norm(x, weight, bias, eps, group_norm=group_norm, num_groups=num_groups)
+        ctx.save_for_backward(x, weight)
+        ctx.cfg = (float(eps), bool(group_norm), int(num_groups) if group_norm else 1, bias is not None,
+                   None if bias is None else bias.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        x, weight = ctx.saved_tensors
+        eps, group_norm, groups, has_bias, bias_dtype = ctx.cfg
+        lib = _lib.load()
+        dev = x.device
+        L, d = x.shape
+        with torch.no_grad():
+            xx = x if x.stride(1) == 1 else x.contiguous()
+            g = _contig_rows(d_out.to(xx.dtype) if d_out.dtype != xx.dtype else d_out)
+            w32 = None if weight is None else weight.detach().to(torch.float32).contiguous()
+            n_params = groups if group_norm else d
+            want_w = weight is not None and ctx.needs_input_grad[1]
+            want_b = has_bias and ctx.needs_input_grad[2]
+            d_x = torch.empty((L, d), dtype=xx.dtype, device=dev)
+            chunks = max(1, min(64, (L + 63) // 64))
+            stats = torch.empty(max(1, L * groups * 2), dtype=torch.float32, device=dev)
+            partial = torch.empty(chunks * 2 * d, dtype=torch.float32, device=dev) if (want_w or want_b) else None
+            d_w = torch.empty(n_params, dtype=torch.float32, device=dev) if want_w else None
+            d_b = torch.empty(n_params, dtype=torch.float32, device=dev) if want_b else None
+            with torch.cuda.device(dev):
+                _lib.check(lib.fmoe_token_norm_backward(
+                    xx.data_ptr(), g.data_ptr(), _lib.dtype_code(xx.dtype), L, d, xx.stride(0) if L else d,
+                    g.stride(0) if L else d, groups, _lib.ptr(w32), 1 if group_norm else 0, eps, d_x.data_ptr(), d,
+                    stats.data_ptr(), _lib.ptr(partial), chunks, _lib.ptr(d_w), _lib.ptr(d_b), _lib.stream_ptr(dev)))
+            if d_w is not None and d_w.dtype != weight.dtype:
+                d_w = d_w.to(weight.dtype)
+            if d_b is not None and d_b.dtype != bias_dtype:
+                d_b = d_b.to(bias_dtype)
+        return (d_x if ctx.needs_input_grad[0] else None), d_w, d_b, None, None, None
+
+
+class SGRouterFn(torch.autograd.Function):
+    """Router of the sparsely-gated layer (fmoe_gate_topk_normalized; kernels/pytorch/mrn.py:236-252)
+    with the backward the reference gets from autograd: softmax over all experts of the
+    L2-normalised logits, then the gate product. ``gate_weight`` is the parameter as the reference
+    stores it, [d, E]. Returns (topk_idx, not differentiable; gates [L, k] f32)."""
+
+    @staticmethod
+    def forward(ctx, x, gate_weight, k):
+        from .routing import gate_topk_normalized
+
+        with torch.no_grad():
+            rows = gate_weight.detach().to(torch.float32).t().contiguous()        # [E, d]
+            idx, score, logits = gate_topk_normalized(x, rows, k, return_logits=True)
+        ctx.save_for_backward(x, rows, idx, logits)
+        ctx.w_dtype = gate_weight.dtype
+        ctx.mark_non_differentiable(idx)
+        return idx, score
+
+    @staticmethod
+    def backward(ctx, _d_idx, d_score):
+        x, rows, idx, logits = ctx.saved_tensors
+        lib = _lib.load()
+        dev = x.device
+        L, d = x.shape
+        E = rows.shape[0]
+        k = idx.shape[1]
+        with torch.no_grad():
+            dy = d_score.to(torch.float32).contiguous()
+            d_logits = torch.empty((L, E), dtype=torch.float32, device=dev)
+            xx = x if x.stride(1) == 1 else x.contiguous()
+            d_x = torch.empty_like(xx) if ctx.needs_input_grad[0] else None
+            d_w = torch.empty((E, d), dtype=torch.float32, device=dev) if ctx.needs_input_grad[1] else None
+            with torch.cuda.device(dev):
+                st = _lib.stream_ptr(dev)
+                _lib.check(lib.fmoe_sg_router_backward(logits.data_ptr(), idx.data_ptr(), dy.data_ptr(), L, E, k,
+                                                       d_logits.data_ptr(), st))
+                _lib.check(lib.fmoe_gate_linear_backward(d_logits.data_ptr(), xx.data_ptr(), _lib.dtype_code(xx.dtype),
+                                                         xx.stride(0) if L else d, rows.data_ptr(), L, d, E, _lib.ptr(d_x),
+                                                         d, _lib.ptr(d_w), None, st))
+            if d_w is not None:
+                d_w = d_w.t().to(ctx.w_dtype)          # back to the parameter's [d, E]
+        return d_x, d_w, None
+
+
+class SGLossFn(torch.autograd.Function):
+    """Training loss and load fractions of the sparsely-gated layer (fmoe_sg_load_loss;
+    kernels/pytorch/mrn.py:186-189, :253-277). The loss differentiates with respect to the gates
+    through the importance; the load is a count. Returns (loss, load fractions)."""
+
+    @staticmethod
+    def forward(ctx, score, offsets, gate_index, num_experts, round_bf16, loss_coef):
+        lib = _lib.load()
+        dev = score.device
+        load = torch.empty(num_experts, dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        sc = score.detach().contiguous()
+        with torch.cuda.device(dev):
+            _lib.check(lib.fmoe_sg_load_loss(offsets.data_ptr(), gate_index.data_ptr(), sc.data_ptr(), num_experts,
+                                             1 if round_bf16 else 0, float(loss_coef), 1, None, 0, load.data_ptr(),
+                                             loss.data_ptr(), _lib.stream_ptr(dev)))
+        ctx.save_for_backward(sc, offsets, gate_index)
+        ctx.cfg = (int(num_experts), bool(round_bf16), float(loss_coef))
+        ctx.mark_non_differentiable(load)
+        return loss, load
+
+    @staticmethod
+    def backward(ctx, d_loss, _d_load):
+        sc, offsets, gate_index = ctx.saved_tensors
+        E, round_bf16, coef = ctx.cfg
+        lib = _lib.load()
+        dev = sc.device
+        with torch.no_grad():
+            d_score = torch.zeros_like(sc)
+            dl = d_loss.to(torch.float32).contiguous()
+            with torch.cuda.device(dev):
+                _lib.check(lib.fmoe_sg_loss_backward(offsets.data_ptr(), gate_index.data_ptr(), sc.data_ptr(), E,
+                                                     1 if round_bf16 else 0, coef, dl.data_ptr(), d_score.data_ptr(),
+                                                     _lib.stream_ptr(dev)))
+        return d_score, None, None, None, None, None
 
 
 def needs_grad(*tensors) -> bool:

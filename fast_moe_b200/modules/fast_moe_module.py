@@ -463,6 +463,65 @@ class CapturedForward:
         return self.y
 
 
+class CapturedTrainStep:
+    """Forward and backward of a layer (``layer.autograd = True``) recorded as one CUDA graph.
+
+    A training step of a layer at small token counts is some fifty launches and as many Python
+    calls of autograd bookkeeping; replayed as a graph it costs one launch. ``step(x, d_out)``
+    copies the tokens and the output gradient into static buffers, replays, and leaves
+    ``self.y`` (the output), ``self.d_x`` and every parameter's ``.grad`` (static tensors,
+    overwritten by the next step; an optimizer reads them in place). The backward seeds from
+    ``d_out``; ``forward_fn(layer, x)`` may replace the default call ``layer(x, k)`` and must
+    return the tensor to differentiate. Shapes, dtype and routing width are fixed at capture time;
+    the routing itself is data dependent and runs inside the graph."""
+
+    def __init__(self, layer: nn.Module, example: torch.Tensor, num_experts_per_tok: int, warmup: int = 3,
+                 forward_fn=None) -> None:
+        if not example.is_cuda:
+            raise RuntimeError("CapturedTrainStep needs a CUDA tensor")
+        if not getattr(layer, "autograd", False):
+            raise RuntimeError("CapturedTrainStep needs layer.autograd = True")
+        if _lib._stage_timer is not None:
+            raise RuntimeError("stage timing records events and cannot be captured; disable it first")
+        self.layer = layer
+        k = num_experts_per_tok
+        self._fwd = forward_fn if forward_fn is not None else (lambda m, t: m(t, k))
+        dev = example.device
+        self.x = example.detach().clone().requires_grad_(True)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            y = self._fwd(layer, self.x)
+            self.d_out = torch.zeros_like(y)
+            y.backward(self.d_out)
+            for _ in range(max(0, warmup - 1)):
+                self._clear_grads()
+                self._fwd(layer, self.x).backward(self.d_out)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self._clear_grads()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.y = self._fwd(layer, self.x)
+            self.y.backward(self.d_out)
+        self.d_x = self.x.grad
+
+    def _clear_grads(self) -> None:
+        self.x.grad = None
+        for p in self.layer.parameters():
+            p.grad = None
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.y
+
+    def step(self, x: torch.Tensor, d_out: torch.Tensor) -> torch.Tensor:
+        with torch.no_grad():
+            self.x.copy_(x, non_blocking=True)
+            self.d_out.copy_(d_out, non_blocking=True)
+        self.graph.replay()
+        return self.y
+
+
 class StreamingForward:
     """Host-to-host forward over a stream of batches: tokens come from pinned host memory and the
     result goes back to pinned host memory, with the three legs of consecutive batches overlapped.

@@ -8,7 +8,9 @@ forward signature of the reference's OrigSGMoEImpl (kernels/pytorch/mrn.py:93-33
 
 The experts, the combine and the dense map are the grouped GEMMs of the FastMoELayer path; the
 router is the gate kernel in its normalised-logit mode; normalisation and the load / loss summary
-are small kernels of their own. Forward only. With noisy gating a layer in training mode adds
+are small kernels of their own. ``layer.autograd = True`` switches the forward to a chain of
+differentiable operators (backward of the norm, the router, the experts, the shared map and the
+loss); the default is the fused inference path under any grad mode. With noisy gating a layer in training mode adds
 softplus-scaled standard-normal noise to the logits before routing and uses the smooth load
 estimate in its loss; in evaluation mode it routes on the clean logits (as the reference does).
 """
@@ -79,6 +81,7 @@ class SGMoELayer(nn.Module):
         self._gate_t = None          # (version, data_ptr, [E, d] f32 copy of _w_gate)
         self._gate_noise_t = None    # (versions, data_ptrs, [2E, d] f32: _w_gate^T stacked on _w_noise^T)
         self._noise = None           # standard-normal draw for the next noisy forward (set_noise)
+        self.autograd = False        # True: forward through the differentiable operators (training)
         self._out_t = {}             # dtype -> (version, data_ptr, [1, o, d] copy of _output_weight)
         self._ident = {}
 
@@ -122,12 +125,51 @@ class SGMoELayer(nn.Module):
         return self._ident[key]
 
     # ------------------------------------------------------------------ forward
-    @torch.no_grad()
     def forward(self, x: torch.Tensor, x_offsets: Optional[torch.Tensor], max_seq_len: int, group_norm: bool,
                 num_groups: int, linear_dim: int, norm_weight: Optional[torch.Tensor],
                 norm_bias: Optional[torch.Tensor], norm_eps: float) -> MRNOutput:
         """x [L, input_size] (jagged batch, already flattened; ``x_offsets`` / ``max_seq_len`` are
-        accepted and unused, as in the reference) -> MRNOutput(y [L, output_size], loss, load)."""
+        accepted and unused, as in the reference) -> MRNOutput(y [L, output_size], loss, load).
+        With ``self.autograd = True`` (and torch's grad mode on) the call records a backward for x,
+        the norm's weight / bias and every parameter; otherwise it is the fused inference path."""
+        if self.autograd and torch.is_grad_enabled():
+            return self._forward_with_grad(x, group_norm, num_groups, linear_dim, norm_weight, norm_bias, norm_eps)
+        with torch.no_grad():
+            return self._forward_inference(x, group_norm, num_groups, linear_dim, norm_weight, norm_bias, norm_eps)
+
+    def _forward_with_grad(self, x, group_norm, num_groups, linear_dim, norm_weight, norm_bias, norm_eps) -> MRNOutput:
+        """The same layer as a chain of differentiable operators: token norm, router, the two
+        expert products with SiLU between them and the gate-weighted combine, the dense map of the
+        un-normalised tokens, and the loss. Noisy gating has no backward."""
+        from ..kernels.autograd import SGLossFn, SGRouterFn, TokenNormFn
+
+        dev = _lib.require_cuda(x)
+        if self.training and self.enable_noisy_gating:
+            raise NotImplementedError("noisy gating has no backward pass; train with enable_noisy_gating=False or "
+                                      "leave autograd off")
+        assert x.ndim == 2 and x.shape[1] == self.input_size
+        L, k, E, dt = x.shape[0], self.k, self.num_experts, x.dtype
+        cast = lambda p: p if p.dtype == dt else p.to(dt)
+        x_norm = TokenNormFn.apply(x, norm_weight, norm_bias, norm_eps, bool(group_norm), num_groups)
+        idx, score = SGRouterFn.apply(x_norm, self._w_gate, k)
+        meta = route_metadata(idx, E)
+        hidden = ops.index_select_jagged_bmm(0, meta.offsets, meta.gate_index.view(-1, k), x_norm,
+                                             cast(self._experts_hidden_w).permute(0, 2, 1), cast(self._experts_hidden_bias))
+        moe = ops.silu_jagged_bmm_combine(0, meta.offsets, hidden, cast(self._experts_w).permute(0, 2, 1),
+                                          cast(self._experts_bias), meta.token_index, meta.reverse_index,
+                                          gating_scores=score, gates_index=meta.gate_index, has_silu=True, round_scores=True)
+        off1, ar, ar2, _ = self._identity_routing(L, dt, dev)
+        shared = ops.index_select_jagged_bmm(0, off1, ar2, x, cast(self._output_weight).unsqueeze(0), None)
+        y = moe + shared
+        if self.training:
+            loss, load = SGLossFn.apply(score, meta.offsets, meta.gate_index, E, dt == torch.bfloat16, self.loss_coef)
+        else:
+            loss, load = sg_load_loss(meta, score.detach(), E, dt, self.loss_coef, False)
+        return MRNOutput(y, loss, load)
+
+    def _forward_inference(self, x: torch.Tensor, group_norm: bool, num_groups: int, linear_dim: int,
+                           norm_weight: Optional[torch.Tensor], norm_bias: Optional[torch.Tensor],
+                           norm_eps: float) -> MRNOutput:
         dev = _lib.require_cuda(x)
         assert x.ndim == 2 and x.shape[1] == self.input_size
         if group_norm:

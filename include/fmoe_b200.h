@@ -131,6 +131,27 @@ int fmoe_sg_load_loss(const int64_t* offsets, const int64_t* gate_index, const f
 int fmoe_sg_noisy_logits(const float* logits2, int64_t ld_logits, const float* noise, int64_t L, int E,
                          float noise_eps, float* noisy, float* stddev, void* stream);
 
+/* Backward of the sparsely-gated layer's own pieces. The reference obtains them from torch autograd
+ * through its eager code (kernels/pytorch/mrn.py:221-333) and its test compares the gradients of x,
+ * every parameter and the norm's weight / bias (kernels/tests/mrn_test.py:816-860).
+ *   fmoe_token_norm_backward: d_x of fmoe_token_norm and, when d_weight / d_bias are given, the
+ *     gradients of its weight / bias ([d] per feature, or [num_groups] with per_group_affine) as
+ *     fixed-order sums over the tokens. Scratch: stats [L * num_groups * 2] f32,
+ *     partial [chunks * 2 * d] f32 (1 <= chunks <= 1024).
+ *   fmoe_sg_router_backward: d_logits [L, E] of fmoe_gate_topk_normalized from the gradient of its
+ *     k scores (softmax over all experts, then the L2 normalisation of the logits); logits are the
+ *     un-normalised ones it returned.
+ *   fmoe_sg_loss_backward: d_score [L, k] of fmoe_sg_load_loss's loss (through the importance only;
+ *     the load is a count), scaled by *d_loss (1 when NULL). */
+int fmoe_token_norm_backward(const void* x, const void* d_out, int dtype, int64_t L, int d, int64_t ldx, int64_t ld_dout,
+                             int num_groups, const float* weight, int per_group_affine, float eps, void* d_x,
+                             int64_t ld_dx, float* stats, float* partial, int chunks, float* d_weight, float* d_bias,
+                             void* stream);
+int fmoe_sg_router_backward(const float* logits, const int64_t* topk_idx, const float* d_score, int64_t L, int E, int k,
+                            float* d_logits, void* stream);
+int fmoe_sg_loss_backward(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
+                          int round_bf16, float loss_coef, const float* d_loss, float* d_score, void* stream);
+
 /* Smooth load of the noisy router (OrigSGMoEImpl._prob_in_top_k, kernels/pytorch/mrn.py:191-219):
  * per token and expert Phi((clean - threshold) / stddev), the threshold being the (k+1)-th largest
  * L2-normalised noisy logit where the expert's noisy logit exceeds it and the k-th largest elsewhere,

@@ -214,3 +214,42 @@ def test_swiglu_layer_gradients_against_oracle_autograd():
     close(layer.w_up.grad, wu.grad, torch.float32, "d w_up")
     close(layer.w_down.grad, wd.grad, torch.float32, "d w_down")
     assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_captured_train_step_matches_eager(swiglu):
+    """Forward + backward replayed as one CUDA graph: output, d_x and every parameter gradient equal
+    the eager autograd run bit for bit where no atomics are involved (the gate weight gradient is
+    summed with atomics: 1e-5), also after new tokens are copied in."""
+    torch.manual_seed(3)
+    d, h, o, E, k, L = 64, 128, 64, 8, 2, 256
+    cls = fm.SwiGLUFastMoELayer if swiglu else fm.FastMoELayer
+    layer = cls(d, h, o, E, dtype=torch.bfloat16).to(DEV)
+    layer.autograd = True
+    x0 = torch.randn(1, L, d, device=DEV).bfloat16()
+    step = fm.CapturedTrainStep(layer, x0, k)
+    for seed in (4, 5):
+        torch.manual_seed(seed)
+        x = torch.randn(1, L, d, device=DEV).bfloat16()
+        dout = (torch.randn(1, L, o, device=DEV) * 0.01).bfloat16()
+        y = step.step(x, dout).clone()
+        got = {n: p.grad.clone() for n, p in layer.named_parameters()}
+        got_dx = step.d_x.clone()
+        # eager reference on fresh leaves
+        for p in layer.parameters():
+            p.grad = None
+        xe = x.clone().requires_grad_()
+        ye = layer(xe, k)
+        ye.backward(dout)
+        assert torch.equal(y, ye)
+        assert torch.equal(got_dx, xe.grad)
+        for n, p in layer.named_parameters():
+            if n.startswith("gate."):
+                torch.testing.assert_close(got[n], p.grad, atol=1e-5, rtol=1e-4)
+            else:
+                assert torch.equal(got[n], p.grad), n
+        # hand the static gradient tensors back to the graph
+        for n, p in layer.named_parameters():
+            p.grad = None
+        step = fm.CapturedTrainStep(layer, x0, k)
+    assert _lib.device_status(torch.device(DEV)) == 0

@@ -213,3 +213,106 @@ def test_sg_moe_layer_at_the_reference_test_shapes(B, max_seq_len, E, k):
     torch.testing.assert_close(out.load.cpu(), ref_load, atol=2e-2, rtol=0)
     torch.testing.assert_close(out.loss.cpu(), ref_loss, atol=1e-3, rtol=5e-2)
     assert _lib.device_status(torch.device(DEV)) == 0
+
+
+def _close(got, want, dt, what, bf16_tol=2.5e-2):
+    want = want.float()
+    scale = max(float(want.abs().max()), 1e-6)
+    tol = 1e-2 if dt == torch.float32 else bf16_tol
+    err = float((got.detach().float().cpu() - want).abs().max())
+    assert err <= tol * scale, f"{what}: max err {err:.3e} vs {tol:.0e} x {scale:.3e}"
+
+
+@pytest.mark.parametrize("name", G.names("mgrad_"))
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_sg_moe_layer_gradients_against_reference(name, dt):
+    """``autograd = True``: backward of sum(y * dout) + loss gives the gradients the reference's
+    OrigSGMoEImpl gives on CPU in fp32 for x, the norm's weight and bias and every parameter
+    (what kernels/tests/mrn_test.py:816-860 compares), the loss's own path into the router
+    included. Bars as for the FastMoELayer gradients: 1e-2 of a tensor's largest magnitude in fp32
+    (tf32 weight-gradient products), the reference's bf16 bound otherwise."""
+    g = G.load(name)
+    d = g["x"].shape[1]
+    E, m, _ = g["p::_experts_hidden_w"].shape
+    o = g["p::_experts_w"].shape[1]
+    groups, gn = g["num_groups"], bool(g["group_norm"])
+    cfg = fm.SGConfig(model_d=m, num_experts=E, num_activated_experts=g["k"], loss_coef=g["loss_coef"])
+    layer = fm.SGMoELayer(d, o, cfg)
+    with torch.no_grad():
+        for n, p in layer.named_parameters():
+            p.copy_(g["p::" + n])
+    layer.to(DEV)
+    layer.train(True)
+    layer.autograd = True
+    x = g["x"].to(dt).to(DEV).requires_grad_()
+    nw = g["norm_weight"].to(DEV).requires_grad_()
+    nb = g["norm_bias"].to(DEV).requires_grad_()
+    out = layer(x, None, 0, gn, groups, d // groups, nw, nb, g["norm_eps"])
+    assert out.x.requires_grad and out.loss.requires_grad and not out.load.requires_grad
+    _close(out.x, g["y"], dt, "forward")
+    _close(out.loss.reshape(-1), g["loss"], dt, "loss")
+    ((out.x.float() * g["dout"].to(DEV)).sum() + out.loss).backward()
+    _close(x.grad, g["d_x"], dt, "d_x")
+    _close(nw.grad, g["d_norm_weight"], dt, "d norm weight")
+    _close(nb.grad, g["d_norm_bias"], dt, "d norm bias")
+    for n, p in layer.named_parameters():
+        assert p.grad is not None, n
+        _close(p.grad, g["g::" + n], dt, "d " + n, bf16_tol=6e-2 if n == "_w_gate" else 2.5e-2)
+    # switched off (the default) nothing is recorded
+    layer.autograd = False
+    assert not layer(x, None, 0, gn, groups, d // groups, nw, nb, g["norm_eps"]).x.requires_grad
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+def test_sg_moe_pieces_against_torch_autograd():
+    """The layer's own backward kernels one at a time against torch autograd on the CPU: token norm
+    (layer and group form, with parameter gradients), the normalised-logit router, the loss."""
+    from fast_moe_b200.kernels.autograd import SGLossFn, SGRouterFn, TokenNormFn
+    import torch.nn.functional as F
+
+    torch.manual_seed(5)
+    L, d, E, k = 300, 96, 16, 3
+    # ---- token norm
+    for gn, groups in ((False, 1), (True, 4)):
+        x = torch.randn(L, d)
+        ns = groups if gn else d
+        w = torch.randn(ns) * 0.3 + 1
+        b = torch.randn(ns) * 0.1
+        dy = torch.randn(L, d)
+        xc, wc, bc = x.clone().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+        ref = (F.group_norm(xc.view(-1, groups, d // groups), groups, wc, bc, 1e-5).view(L, d) if gn
+               else F.layer_norm(xc, (d,), wc, bc, 1e-5))
+        ref.backward(dy)
+        xg, wg, bg = cu(x).requires_grad_(), cu(w).requires_grad_(), cu(b).requires_grad_()
+        out = TokenNormFn.apply(xg, wg, bg, 1e-5, gn, groups)
+        out.backward(cu(dy))
+        torch.testing.assert_close(out.detach().cpu(), ref.detach(), atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(xg.grad.cpu(), xc.grad, atol=2e-5, rtol=1e-4)
+        torch.testing.assert_close(wg.grad.cpu(), wc.grad, atol=1e-4, rtol=1e-4)
+        torch.testing.assert_close(bg.grad.cpu(), bc.grad, atol=1e-4, rtol=1e-4)
+    # ---- router: softmax over all experts of the L2-normalised logits, k largest kept
+    x = torch.randn(L, d)
+    wgt = torch.randn(d, E) * 0.2
+    dsc = torch.randn(L, k)
+    xg, wg = cu(x).requires_grad_(), cu(wgt).requires_grad_()
+    idx, score = SGRouterFn.apply(xg, wg, k)
+    score.backward(cu(dsc))
+    xc, wc = x.clone().requires_grad_(), wgt.clone().requires_grad_()
+    p = torch.softmax(F.normalize(xc @ wc, dim=1), dim=1)
+    sel = p.gather(1, idx.cpu())
+    torch.testing.assert_close(score.detach().cpu(), sel.detach(), atol=1e-6, rtol=1e-5)
+    sel.backward(dsc)
+    torch.testing.assert_close(xg.grad.cpu(), xc.grad, atol=1e-5, rtol=1e-3)
+    torch.testing.assert_close(wg.grad.cpu(), wc.grad, atol=1e-4, rtol=1e-3)
+    # ---- loss through the importance
+    meta = fm.route_metadata(idx, E)
+    sg = score.detach().clone().requires_grad_()
+    loss, load = SGLossFn.apply(sg, meta.offsets, meta.gate_index, E, False, 0.7)
+    (loss * 3.0).backward()
+    sc = score.detach().cpu().clone().requires_grad_()
+    gates = torch.zeros(L, E).scatter(1, idx.cpu(), sc)
+    ref_loss = 0.7 * (M.cv_squared(gates.sum(0)) + M.cv_squared((gates > 0).sum(0)))
+    (ref_loss * 3.0).backward()
+    torch.testing.assert_close(loss.detach().cpu(), ref_loss.detach(), atol=1e-6, rtol=1e-4)
+    torch.testing.assert_close(sg.grad.cpu(), sc.grad, atol=1e-6, rtol=1e-3)
+    assert _lib.device_status(torch.device(DEV)) == 0
