@@ -704,11 +704,20 @@ def next_rows_record(device, peaks, steps=10):
         out_ = sg(xs, None, 0, False, 1, d, nw, nb, 1e-5)
         (out_.x.float().sum() + out_.loss).backward()
 
-    ms_sg_train, ms_sg_wall = eager_ms(sg_train_step)
-    rec["train_sg_moe_layer"] = dict(ms_per_step=ms_sg_train, ms_per_step_wall=ms_sg_wall,
-                                     launch_mode="eager autograd, CUDA events around 10 steps",
+    ms_sg_eager, ms_sg_wall = eager_ms(sg_train_step)
+    for p_ in sg.parameters():
+        p_.grad = None
+    sg_graph = fm.CapturedTrainStep(sg, x2, k, forward_fn=lambda m_, t_: m_(t_, None, 0, False, 1, d, nw, nb, 1e-5).x)
+    ms_sg_train, _ = eager_ms(sg_graph.replay)
+    rec["train_sg_moe_layer"] = dict(ms_per_step=ms_sg_train,
+                                     launch_mode="forward + backward of the output as one CUDA graph (CapturedTrainStep)",
+                                     ms_per_step_eager=ms_sg_eager, ms_per_step_eager_wall=ms_sg_wall,
+                                     eager_includes="the loss's backward as well",
                                      model_tflops=3 * sg_flops_of(A, L, d, h, o, E) / (ms_sg_train * 1e-3) / 1e12,
                                      tokens_per_s=L / (ms_sg_train * 1e-3))
+    del sg_graph
+    for p_ in sg.parameters():
+        p_.grad = None
     sg.autograd = False
     rec["sg_moe_forward"] = dict(ms_per_step=ms_eval, tokens_per_s=L / (ms_eval * 1e-3),
                                  layer_tflops=sg_flops / (ms_eval * 1e-3) / 1e12, launch_mode="10 forwards in a CUDA graph",

@@ -550,7 +550,7 @@ def test_fused_combine_epilogue_against_two_kernel_form(name):
 @pytest.mark.parametrize("name", G.names("ops_"))
 def test_fused_combine_flags_round_scores_and_accumulate(name):
     """round_scores=True with f32 scores equals casting the scores to the activation type first
-    (what the reference layer does, modules/fast_moe_module.py:215), in both forms; out= adds the
+    (the reference's gate runs in the layer's dtype, modules/fast_moe_module.py:21-27, so its scores arrive in that type), in both forms; out= adds the
     combined rows to what the buffer already holds (a residual) and returns that buffer."""
     g = G.load(name)
     k = g["k"]
