@@ -74,7 +74,23 @@ def _stale(target: Path, deps) -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles the CUDA sources when they are newer than the library. Returns the .so path."""
+    """Compiles the CUDA sources when they are newer than the library. Returns the .so path.
+    Several processes may call this at once (one per GPU under torchrun): a file lock lets one of
+    them build while the others wait and then find the library current."""
+    import fcntl
+
+    LIB_DIR.mkdir(exist_ok=True)
+    with open(LIB_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and library_is_current():
+                return LIB_PATH
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     obj_dir = LIB_DIR / "obj"
     obj_dir.mkdir(exist_ok=True)

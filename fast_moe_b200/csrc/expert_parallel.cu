@@ -81,7 +81,12 @@ ep_dispatch_kernel(const uint8_t* __restrict__ x, long long x_rows, long long ld
                    long long ld_recv_bytes, long long capacity, int rank, int vec_ok, int* status) {
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long p = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; p < rows; p += warps) {
+  // Rows are sorted by owner and blocks start in index order: every rank begins a different
+  // fraction of the way through its rows, so that the ranks do not all write to the same owner
+  // at the same time (its NVLink ingress would be the one busy port).
+  const long long shift = rows * rank / (E / El);
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < rows; i += warps) {
+    const long long p = (i + shift) % rows;
     // expert of row p: the last e with offsets[e] <= p
     int lo = 0, hi = E;
     while (hi - lo > 1) {
