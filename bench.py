@@ -265,6 +265,30 @@ def routing_sweep(c, device):
         a = torch.randn(R, C, generator=g).to(torch.bfloat16).to(device)
         add("rowwise_quant_fp8", shape, lambda: ops_fp8.rowwise_quant_fp8(a), R * C * 3 + 4 * R)
         del a
+    # the backward pass's layout and elementwise passes at the C2 shapes
+    from fast_moe_b200.kernels import autograd as AG
+
+    L, E, k, d_, h_ = 4096, 8, 2, 1024, 4096
+    idx = torch.rand(L, E, generator=g).topk(k, dim=1).indices.to(device)
+    meta = fm.route_metadata(idx, E)
+    A = L * k
+    hid = torch.randn(A, h_, generator=g).to(torch.bfloat16).to(device)
+    hid2 = torch.randn(A, h_, generator=g).to(torch.bfloat16).to(device)
+    dh = torch.randn(A, h_, generator=g).to(torch.bfloat16).to(device)
+    wst = (torch.randn(E, h_, d_, generator=g) * 0.02).to(torch.bfloat16).to(device)       # storage [E, N, K]
+    kseg, padded = AG._padded_reduction(meta.offsets, E, torch.bfloat16, A)
+    add("jagged_transpose_pad", f"c2 hidden {A} x {h_}", lambda: AG._transpose_pad(hid, meta.offsets, kseg, padded, E, A),
+        2 * A * h_ * 2)
+    add("batched_transpose (weight)", f"c2 {E} x {h_} x {d_}", lambda: AG.transposed_weight(wst.permute(0, 2, 1)), 2 * E * h_ * d_ * 2)
+    da, db = torch.empty_like(hid), torch.empty_like(hid)
+    add("activation_backward (SwiGLU)", f"c2 {A} x {h_}", lambda: AG.activation_backward(1, dh, hid, hid2, da, db), 5 * A * h_ * 2)
+    add("jagged_colsum (d_bias)", f"c2 {A} x {h_}", lambda: AG.grad_bias(meta.offsets, dh, E, torch.bfloat16), A * h_ * 2)
+    sc = torch.rand(L, k, generator=g).to(device)
+    dy = torch.randn(L, d_, generator=g).to(torch.bfloat16).to(device)
+    rows2 = torch.randn(A, d_, generator=g).to(torch.bfloat16).to(device)
+    add("gather_scale_rows", f"c2 {A} x {d_}", lambda: AG.gather_scale_rows(dy, meta.token_index, 1, sc, meta.gate_index),
+        (L + A) * d_ * 2)
+    add("row_dot", f"c2 {A} x {d_}", lambda: AG.row_dot(rows2, dy, meta.token_index), (L + A) * d_ * 2)
     print(json.dumps(dict(routing_sweep=rows_out, d=c["d"], E=c["E"], k=c["k"], hbm_kernels=hbm,
                           hbm_peak_gbs=peak)), flush=True)
 
