@@ -79,10 +79,18 @@ namespace {
 
 // Fills the weight part of a GemmDesc; rejects layouts the tensor-core path cannot read.
 int set_weight(GemmDesc& g, const char* op, int64_t w_se, int64_t w_sk, int64_t w_sn) {
+  g.b_sk = 1;
   if (g.K > 1 && w_sk != 1) {
-    return fail(FMOE_ERR_UNSUPPORTED,
-                "%s: weight must have K contiguous (stride_k == 1, got %lld); pass the [E, N, K]-stored view",
-                op, (long long)w_sk);
+    // N contiguous instead (a plain [E, K, N] tensor): read in place as an MN-major operand where
+    // the tensor cores allow it
+    const bool mn_ok = w_sn == 1 && g.dtype == FMOE_BF16 && g.N % 64 == 0 && (w_sk * 2) % 16 == 0;
+    if (!mn_ok) {
+      return fail(FMOE_ERR_UNSUPPORTED,
+                  "%s: weight must have K contiguous (stride_k == 1, got %lld), or - bf16 with N a multiple of 64 - N "
+                  "contiguous with 16-byte aligned rows; pass the [E, N, K]-stored view",
+                  op, (long long)w_sk);
+    }
+    g.b_sk = w_sk;
   }
   g.b_se = w_se;
   g.b_sn = w_sn;
@@ -267,6 +275,30 @@ extern "C" int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, 
   g.epilogue = FMOE_EPI_NONE;
   g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
   return launch_grouped_gemm(g, st);
+}
+
+extern "C" int fmoe_jagged_bmm_two_weights(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype,
+                                           int64_t ldj, const void* weight0, const void* weight1, int k_split,
+                                           int64_t w_se, int64_t w_sk, int64_t w_sn, int E, int K, int N, void* out,
+                                           int out_dtype, int64_t ldo, void* stream) {
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "jagged_bmm_two_weights: dtype must be bf16 or f32");
+  FMOE_REQUIRE(weight0 && weight1 && k_split > 0 && k_split < K, "jagged_bmm_two_weights: need two weights and 0 < k_split < K");
+  GemmDesc g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = dtype;
+  g.E = E; g.N = N; g.K = K;
+  g.offsets = offsets;
+  g.total_rows = total_rows;
+  g.a = jagged; g.a_rows = total_rows; g.lda = ldj;
+  g.index_div = 1;
+  g.b0 = weight0;
+  g.b1 = weight1;
+  g.b_ksplit = k_split;
+  int rc = set_weight(g, "jagged_bmm_two_weights", w_se, w_sk, w_sn);
+  if (rc != FMOE_OK) return rc;
+  g.epilogue = FMOE_EPI_NONE;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fmoe_silu_jagged_bmm_combine(const int64_t* offsets, int64_t total_rows, const void* jagged,

@@ -61,10 +61,17 @@ struct GemmDesc {
   int64_t lda;               // elements
   const int64_t* index;      // device [total_rows] or null; source row = index[r] / index_div
   int index_div;
-  // B operands, logical [E, K, N], element (e,k,n) at b + e*b_se + n*b_sn + k (K contiguous)
+  // B operands, logical [E, K, N], element (e,k,n) at b + e*b_se + n*b_sn + k*b_sk. Either K is
+  // contiguous (b_sk 0 or 1: the weights' storage layout) or N is (b_sn == 1, b_sk = row stride:
+  // a plain [E, K, N] tensor, read as an MN-major tensor-core operand; bf16 only, N % 64 == 0)
   const void* b0;
   const void* b1;            // second operand of the gated (SwiGLU) form, else null
   int64_t b_se, b_sn;        // elements
+  int64_t b_sk;              // elements; 0 or 1: K contiguous
+  // b_ksplit > 0 (plain epilogues only): the reduction runs over two weights, A[:, :b_ksplit] @ b0[e]
+  // + A[:, b_ksplit:] @ b1[e], b0 logical [E, b_ksplit, N] and b1 [E, K - b_ksplit, N] with the same
+  // strides; b_ksplit a multiple of one K step (128 bytes)
+  int b_ksplit;
   // bias [E, N] in the output type (nullable)
   const void* bias0;
   const void* bias1;

@@ -102,6 +102,8 @@ struct GemmParams {
   // elementwise multiplier applied last: out[r, n] = (...)[r, n] * mul_in[r * ld_mul + n] (output type)
   const void* mul_in;
   long long ld_mul;
+  int b_ksplit;      // > 0: K steps from here on read the second weight (tmB1) at k - b_ksplit
+  int b_mn;          // B tiles are MN-major (N contiguous in memory): 4-D tensor map, MN-major descriptors
   int mul_vec;       // rows of mul_in are 16-byte aligned: 16-byte loads in the store phase
   int* status;
 };
@@ -425,12 +427,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const int k0 = k_begin + kb * kKElems;
+          // two weights along the reduction (plain tiles only): the second one takes over at b_ksplit
+          const bool second = !DUAL && p.b_ksplit > 0 && k0 >= p.b_ksplit;
+          const CUtensorMap* tb = second ? &tmB1 : &tmB0;
+          const int kw = second ? k0 - p.b_ksplit : k0;
           if constexpr (!kPair) {
             const uint32_t bar = full_bar(stage);
             ptx::mbar_arrive_expect_tx(bar, kStageTx);
             if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
-            ptx::tma_load_3d(b_dst, &tmB0, bar, k0, n0, e);
-            if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+            if (p.b_mn) {
+              // N contiguous in memory: box = 64 columns x one K step x (atoms of 64 columns)
+              ptx::tma_load_4d(b_dst, tb, bar, 0, kw, n0 >> 6, e);
+              if constexpr (DUAL) ptx::tma_load_4d(b_dst + kTileN * kRowBytes, &tmB1, bar, 0, k0, n0 >> 6, e);
+            } else {
+              ptx::tma_load_3d(b_dst, tb, bar, kw, n0, e);
+              if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+            }
           } else {
             // Both CTAs report their bytes to the leader's barrier; only the leader arms it.
             const uint32_t bar = ptx::mapa(full_bar(stage), 0);
@@ -438,9 +450,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if constexpr (!GATHER) ptx::tma_load_2d_pair(a_dst, &tmA, bar, k0, row0);
             if constexpr (DUAL) {
               // leader stages the gate weights, its peer the up weights: 128 rows each
-              ptx::tma_load_3d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, k0, n0, e);
+              if (p.b_mn) {
+                ptx::tma_load_4d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, 0, k0, n0 >> 6, e);
+              } else {
+                ptx::tma_load_3d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, k0, n0, e);
+              }
             } else {
-              ptx::tma_load_3d_pair(b_dst, &tmB0, bar, k0, n0 + static_cast<int>(rank) * (kMmaN / 2), e);
+              const int nh = n0 + static_cast<int>(rank) * (kMmaN / 2);
+              if (p.b_mn) {
+                ptx::tma_load_4d_pair(b_dst, tb, bar, 0, kw, nh >> 6, e);
+              } else {
+                ptx::tma_load_3d_pair(b_dst, tb, bar, kw, nh, e);
+              }
             }
           }
           if (++stage == kStages) {
@@ -481,10 +502,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::tc_fence_after();
           const uint32_t a_src = tiles_addr + stage * Plan::kStageBytes;
           const uint64_t da = ptx::umma_desc_k_sw128(a_src);
-          const uint64_t db = ptx::umma_desc_k_sw128(a_src + kABytes);
+          if (!p.b_mn) {
+            const uint64_t db = ptx::umma_desc_k_sw128(a_src + kABytes);
 #pragma unroll
-          for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
-            ptx::umma_ss<kKind, CTAS>(d_tmem, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
+              ptx::umma_ss<kKind, CTAS>(d_tmem, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            }
+          } else {
+            // MN-major B: a K step of one MMA is kUmmaKBytes / ESIZE rows of 128 bytes
+            constexpr uint32_t kAtomBytes = (kRowBytes / ESIZE) * kRowBytes;          // 64 K rows x 128 B (bf16)
+            constexpr uint32_t kStep = (kUmmaKBytes / ESIZE) * kRowBytes;             // bytes per MMA along K
+            const uint64_t db = ptx::umma_desc_mn_sw128(a_src + kABytes, kAtomBytes);
+#pragma unroll
+            for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
+              ptx::umma_ss<kKind, CTAS>(d_tmem, da + 2u * k, db + static_cast<uint64_t>((kStep >> 4) * k),
+                                        kIdesc | ptx::kUmmaIdescBMnMajor, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           ptx::umma_commit<CTAS>(empty_bar(stage));      // stage reusable once these MMAs have read it
           if (kb == nkb - 1) ptx::umma_commit<CTAS>(tfull_bar(acc));
@@ -955,7 +988,7 @@ int make_tmap(CUtensorMap* m, int dt, int rank, const void* base, const cuuint64
   int err = 0;
   EncodeTiledFn fn = encode_fn(&err);
   if (!fn) return err;
-  cuuint32_t estr[3] = {1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(m, tmap_dtype(dt), rank, const_cast<void*>(base), dims, strides_bytes, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1096,7 +1129,20 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   FMOE_REQUIRE(d.dtype != FMOE_F32 || d.out_dtype == FMOE_F32, "grouped_gemm: f32 operands need an f32 output");
   FMOE_REQUIRE(d.epilogue != FMOE_EPI_SWIGLU || d.b1 != nullptr, "grouped_gemm: SwiGLU needs a second weight");
   FMOE_REQUIRE(d.index == nullptr || d.index_div >= 1, "grouped_gemm: index_div must be >= 1");
-  if ((d.lda * esize) % 16 != 0 || (d.b_sn * esize) % 16 != 0 || (d.b_se * esize) % 16 != 0 ||
+  const bool b_mn = d.b_sk > 1;
+  if (b_mn) {
+    FMOE_REQUIRE(esize == 2 && d.b_sn == 1 && d.N % 64 == 0 && d.kseg == nullptr,
+                 "grouped_gemm: an N-contiguous weight needs bf16 operands and N a multiple of 64 (N=%d)", d.N);
+  }
+  const int ksplit = d.b_ksplit;
+  if (ksplit > 0) {
+    FMOE_REQUIRE(d.b1 != nullptr && d.epilogue != FMOE_EPI_SWIGLU && d.kseg == nullptr && ksplit < d.K &&
+                     (static_cast<long long>(ksplit) * esize) % kRowBytes == 0,
+                 "grouped_gemm: a reduction over two weights needs a second weight, a plain epilogue and a split at a "
+                 "multiple of %d elements inside K (split %d, K %d)", kRowBytes / esize, ksplit, d.K);
+  }
+  const long long b_row_stride = b_mn ? d.b_sk : d.b_sn;     // stride of the non-contiguous matrix dimension
+  if ((d.lda * esize) % 16 != 0 || (b_row_stride * esize) % 16 != 0 || (d.b_se * esize) % 16 != 0 ||
       (reinterpret_cast<uintptr_t>(d.a) & 15) || (reinterpret_cast<uintptr_t>(d.b0) & 15) ||
       (d.b1 && (reinterpret_cast<uintptr_t>(d.b1) & 15))) {
     return fail(FMOE_ERR_UNSUPPORTED,
@@ -1153,15 +1199,32 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
     int rc = make_tmap(&tmA, d.dtype, 2, d.a, dims, str, box, "activations");
     if (rc != FMOE_OK) return rc;
   }
-  {
+  if (b_mn) {
+    // N contiguous: dimensions (64 columns of an atom, K, atoms, expert); one load brings
+    // box_n / 64 atoms of [one K step x 64 columns], each atom laid out as 128-byte rows
+    cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(ksplit > 0 ? ksplit : d.K), static_cast<cuuint64_t>(d.N / 64),
+                          static_cast<cuuint64_t>(d.E)};
+    cuuint64_t str[3] = {static_cast<cuuint64_t>(d.b_sk) * esize, 64ull * esize, static_cast<cuuint64_t>(d.b_se) * esize};
+    cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(box_n / 64), 1u};
+    int rc = make_tmap(&tmB0, d.dtype, 4, d.b0, dims, str, box, "weights (N contiguous)");
+    if (rc != FMOE_OK) return rc;
+    if (dual || ksplit > 0) {
+      if (ksplit > 0) dims[1] = static_cast<cuuint64_t>(d.K - ksplit);
+      rc = make_tmap(&tmB1, d.dtype, 4, d.b1, dims, str, box, "second weights (N contiguous)");
+      if (rc != FMOE_OK) return rc;
+    } else {
+      tmB1 = tmB0;
+    }
+  } else {
     // reduction-over-rows mode: one B matrix [N, K] shared by all groups
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.K), static_cast<cuuint64_t>(d.N),
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(ksplit > 0 ? ksplit : d.K), static_cast<cuuint64_t>(d.N),
                           static_cast<cuuint64_t>(d.kseg ? 1 : d.E)};
     cuuint64_t str[2] = {static_cast<cuuint64_t>(d.b_sn) * esize, static_cast<cuuint64_t>(d.b_se) * esize};
     cuuint32_t box[3] = {static_cast<cuuint32_t>(k_elems), static_cast<cuuint32_t>(box_n), 1u};
     int rc = make_tmap(&tmB0, d.dtype, 3, d.b0, dims, str, box, "weights");
     if (rc != FMOE_OK) return rc;
-    if (dual) {
+    if (dual || ksplit > 0) {
+      if (ksplit > 0) dims[0] = static_cast<cuuint64_t>(d.K - ksplit);
       rc = make_tmap(&tmB1, d.dtype, 3, d.b1, dims, str, box, "second weights");
       if (rc != FMOE_OK) return rc;
     } else {
@@ -1205,6 +1268,8 @@ int launch_grouped_gemm(const GemmDesc& d, cudaStream_t stream) {
   p.kseg = reinterpret_cast<const long long*>(d.kseg);
   p.mul_in = d.mul_in;
   p.ld_mul = d.ld_mul;
+  p.b_mn = b_mn ? 1 : 0;
+  p.b_ksplit = ksplit;
   p.mul_vec = d.mul_in != nullptr && ((d.ld_mul * osize) % 16 == 0) && (reinterpret_cast<uintptr_t>(d.mul_in) & 15) == 0;
   p.vec_ok = ((d.ldo * osize) % 16 == 0) && (d.out_peers != nullptr || (reinterpret_cast<uintptr_t>(d.out) & 15) == 0);
   p.status = status;

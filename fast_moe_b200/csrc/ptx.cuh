@@ -180,6 +180,22 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                                 int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 // ---------------------------------------------------------------- cp.async (per-thread 16-byte copies)
 // Copies src_bytes (0 or 16) bytes from global memory and zero-fills the rest of the 16.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
@@ -259,6 +275,20 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t saddr) {
   d |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
   return d;
 }
+
+// The same for an MN-major operand tile: rows of 128 bytes hold 64 consecutive M (or N) indices of
+// one K index (one swizzle atom along MN), 8 K indices per 1024-byte group (stride offset), and the
+// next 64 MN indices start `atom_bytes` further on (leading offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr, uint32_t atom_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((atom_bytes >> 4) & 0x3FFFu) << 16;   // leading byte offset: next MN atom
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride between 8-K groups
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+constexpr uint32_t kUmmaIdescBMnMajor = 1u << 16;   // instruction descriptor bit: B is MN-major
 
 // Instruction descriptor: D=f32, A/B format code `ab_fmt` (kind::f16: 0 f16, 1 bf16;
 // kind::tf32: 2; kind::f8f6f4: 0 e4m3), both operands K-major, shape M x N.

@@ -39,7 +39,14 @@ def transposed_weight(weight: torch.Tensor) -> torch.Tensor:
     the operand of d_x = d_out @ W[e]^T. A plain contiguous [E, K, N] weight already is that
     (a view); a weight stored [E, N, K] (the layers' layout) is transposed once."""
     E, K, N = weight.shape
-    if weight.stride(2) == 1 and weight.stride(1) % (16 // weight.element_size()) == 0:
+    a = 16 // weight.element_size()
+    if weight.stride(2) == 1 and weight.stride(1) % a == 0:
+        return weight.permute(0, 2, 1)
+    ops = _ops()
+    if (ops.MN_MAJOR_WEIGHTS and weight.dtype == torch.bfloat16 and weight.stride(1) == 1 and K % 64 == 0 and N > 1
+            and weight.stride(2) % a == 0 and weight.stride(0) % a == 0 and weight.data_ptr() % 16 == 0):
+        # stored [E, N, K] (the layers' layout): as the operand of d_out @ W^T its output dimension K
+        # is the contiguous one, which the grouped GEMM reads in place (MN-major operand)
         return weight.permute(0, 2, 1)
     lib = _lib.load()
     dev = weight.device
@@ -269,8 +276,12 @@ class IndexSelectJaggedBmmSwigluFn(torch.autograd.Function):
             if ctx.needs_input_grad[2]:
                 # d_rows = [d_alpha | d_beta] @ [W ; Wp]^T as one product over 2N
                 # (the two transposed weights side by side: storage [E, K, 2N], 2N contiguous)
-                w_cat = transposed_weights_side_by_side(weight, weight_p)                        # logical [E, 2N, K]
-                d_rows = ops.silu_jagged_bmm(offsets, d_ab, w_cat, None, has_silu=False)
+                # (one grouped product whose reduction walks both transposed weights where they lie;
+                #  else the two are laid side by side first: storage [E, K, 2N], 2N contiguous)
+                d_rows = ops.jagged_bmm_two_weights(offsets, d_ab, weight.permute(0, 2, 1), weight_p.permute(0, 2, 1))
+                if d_rows is None:
+                    w_cat = transposed_weights_side_by_side(weight, weight_p)                    # logical [E, 2N, K]
+                    d_rows = ops.silu_jagged_bmm(offsets, d_ab, w_cat, None, has_silu=False)
                 tok = index.reshape(-1) // A
                 d_jagged = ops.mul_merge_k_add(tok, _inverse_rows(index), d_rows)
             flat = index.reshape(-1).contiguous()

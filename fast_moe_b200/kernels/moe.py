@@ -64,11 +64,18 @@ def prep_activation(jagged: torch.Tensor, k_pad: int) -> torch.Tensor:
     return jagged
 
 
-def prep_weight(weight: torch.Tensor, k_pad: int) -> Tuple[torch.Tensor, int, int]:
-    """weight is logical [E, K, N]. Returns (storage [E, N, k_pad] with K contiguous, expert
-    stride, row stride) in elements. The permuted view FastMoELayer passes
-    (modules/fast_moe_module.py:167,177) is used in place; a plain contiguous [E, K, N] tensor is
-    transposed once (a copy)."""
+# A plain [E, K, N] weight (N contiguous) is read in place as an MN-major tensor-core operand
+# where the hardware path exists (bf16, N a multiple of 64); False forces the transposed copy.
+MN_MAJOR_WEIGHTS = True
+
+
+def prep_weight(weight: torch.Tensor, k_pad: int) -> Tuple[torch.Tensor, int, int, int]:
+    """weight is logical [E, K, N]. Returns (tensor whose data pointer the kernel takes, expert
+    stride, K stride, N stride) in elements. The permuted view FastMoELayer passes
+    (modules/fast_moe_module.py:167,177; storage [E, N, K], K contiguous) is used in place with
+    strides (se, 1, sn). A plain contiguous [E, K, N] tensor - what the reference's operators are
+    documented with (kernels/moe.py:39-68) - is used in place too when it is bf16 with N a
+    multiple of 64 (strides (se, sk, 1)); otherwise it is transposed once (a copy)."""
     E, K, N = weight.shape
     a = _elem_align(weight.dtype)
     wt = weight.permute(0, 2, 1)  # [E, N, K]
@@ -79,11 +86,15 @@ def prep_weight(weight: torch.Tensor, k_pad: int) -> Tuple[torch.Tensor, int, in
         and wt.data_ptr() % 16 == 0
         and k_pad == K
     )
-    if not ok:
-        wt = wt.contiguous()
-        if k_pad != K:
-            wt = torch.nn.functional.pad(wt, (0, k_pad - K))
-    return wt, wt.stride(0), wt.stride(1)
+    if ok:
+        return wt, wt.stride(0), 1, wt.stride(1)
+    if (MN_MAJOR_WEIGHTS and weight.dtype == torch.bfloat16 and weight.stride(2) == 1 and N % 64 == 0 and k_pad == K
+            and K > 1 and weight.stride(1) % a == 0 and weight.stride(0) % a == 0 and weight.data_ptr() % 16 == 0):
+        return weight, weight.stride(0), weight.stride(1), 1
+    wt = wt.contiguous()
+    if k_pad != K:
+        wt = torch.nn.functional.pad(wt, (0, k_pad - K))
+    return wt, wt.stride(0), 1, wt.stride(1)
 
 
 def _pad_k(K: int, dt: torch.dtype) -> int:
@@ -212,7 +223,7 @@ def index_select_jagged_bmm(
     rows = index.numel() if index is not None else L
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
-    w, w_se, w_sn = prep_weight(weight, kp)
+    w, w_se, w_sk, w_sn = prep_weight(weight, kp)
     b = _prep_bias(bias, od)
     off = _index_i64(offsets)
     idx = None if index is None else _index_i64(index)
@@ -228,7 +239,7 @@ def index_select_jagged_bmm(
             _lib.check(
                 lib.fmoe_index_select_jagged_bmm_mul(
                     off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
-                    w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, m.data_ptr(), m.stride(0), out.data_ptr(),
+                    w.data_ptr(), w_se, w_sk, w_sn, _lib.ptr(b), N, E, kp, N, m.data_ptr(), m.stride(0), out.data_ptr(),
                     _lib.dtype_code(od), out.stride(0), _lib.stream_ptr(dev),
                 )
             )
@@ -237,7 +248,7 @@ def index_select_jagged_bmm(
         _lib.check(
             lib.fmoe_index_select_jagged_bmm(
                 off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
-                w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), N, E, kp, N, _epilogue, out.data_ptr(), _lib.dtype_code(od),
+                w.data_ptr(), w_se, w_sk, w_sn, _lib.ptr(b), N, E, kp, N, _epilogue, out.data_ptr(), _lib.dtype_code(od),
                 out.stride(0), _lib.stream_ptr(dev),
             )
         )
@@ -308,13 +319,16 @@ def index_select_jagged_bmm_swiglu(
     rows = index.numel() if index is not None else L
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
-    w, w_se, w_sn = prep_weight(weight, kp)
-    wp, wp_se, wp_sn = prep_weight(weight_p, kp)
-    if (wp_se, wp_sn) != (w_se, w_sn):
-        # the kernel walks both weights with one set of strides
-        w = w.contiguous()
-        wp = wp.contiguous()
-        w_se, w_sn = w.stride(0), w.stride(1)
+    w, w_se, w_sk, w_sn = prep_weight(weight, kp)
+    wp, wp_se, wp_sk, wp_sn = prep_weight(weight_p, kp)
+    if (wp_se, wp_sk, wp_sn) != (w_se, w_sk, w_sn):
+        # the kernel walks both weights with one set of strides: both as [E, N, K] copies
+        w = weight.permute(0, 2, 1).contiguous()
+        wp = weight_p.permute(0, 2, 1).contiguous()
+        if kp != K:
+            w = torch.nn.functional.pad(w, (0, kp - K))
+            wp = torch.nn.functional.pad(wp, (0, kp - K))
+        w_se, w_sk, w_sn = w.stride(0), 1, w.stride(1)
     b = _prep_bias(bias, od)
     bp = _prep_bias(bias_p, od)
     off = _index_i64(offsets)
@@ -328,7 +342,7 @@ def index_select_jagged_bmm_swiglu(
         _lib.check(
             lib.fmoe_index_select_jagged_bmm_swiglu(
                 off.data_ptr(), _lib.ptr(idx), div, rows, a.data_ptr(), dt, L, a.stride(0),
-                w.data_ptr(), wp.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), _lib.ptr(bp), N, E, kp, N,
+                w.data_ptr(), wp.data_ptr(), w_se, w_sk, w_sn, _lib.ptr(b), _lib.ptr(bp), N, E, kp, N,
                 out.data_ptr(), _lib.dtype_code(od), out.stride(0), _lib.stream_ptr(dev),
             )
         )
@@ -465,7 +479,7 @@ def silu_jagged_bmm(
     assert Kw == K
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
-    w, w_se, w_sn = prep_weight(weight, kp)
+    w, w_se, w_sk, w_sn = prep_weight(weight, kp)
     b = _prep_bias(bias, od)
     off = _index_i64(offsets)
     out = torch.empty((rows, N), dtype=od, device=dev)
@@ -480,12 +494,41 @@ def silu_jagged_bmm(
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_silu_jagged_bmm(
-                off.data_ptr(), rows, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
+                off.data_ptr(), rows, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, w_sk, w_sn, 0,
                 _lib.ptr(b), N, E, kp, N, 1 if has_silu else 0, _lib.ptr(scratch), None, _lib.ptr(oidx), out.data_ptr(),
                 _lib.dtype_code(od), out.stride(0),
                 _lib.stream_ptr(dev),
             )
         )
+    return out
+
+
+def jagged_bmm_two_weights(offsets: torch.Tensor, jagged: torch.Tensor, weight0: torch.Tensor, weight1: torch.Tensor
+                           ) -> Optional[torch.Tensor]:
+    """rows[:, :K0] @ weight0[e] + rows[:, K0:] @ weight1[e] as one grouped product whose reduction
+    walks the two weights (logical [E, K0, N] and [E, K1, N]). Returns None when the two weights
+    cannot be read in place with one set of strides (the caller then concatenates)."""
+    dev = _lib.require_cuda(offsets, jagged, weight0, weight1)
+    lib = _lib.load()
+    rows, K = jagged.shape
+    E, K0, N = weight0.shape
+    K1 = weight1.shape[1]
+    if K0 + K1 != K or weight1.shape[0] != E or weight1.shape[2] != N or weight0.dtype != jagged.dtype:
+        return None
+    unit = 128 // jagged.element_size()
+    if K0 % unit or _pad_k(K, jagged.dtype) != K or jagged.stride(1) != 1:
+        return None
+    w0, se0, sk0, sn0 = prep_weight(weight0, K0)
+    w1, se1, sk1, sn1 = prep_weight(weight1, K1)
+    if (se0, sk0, sn0) != (se1, sk1, sn1) or w0.data_ptr() != weight0.data_ptr() or w1.data_ptr() != weight1.data_ptr():
+        return None
+    a = prep_activation(jagged, K)
+    out = torch.empty((rows, N), dtype=jagged.dtype, device=dev)
+    off = _index_i64(offsets)
+    with torch.cuda.device(dev):
+        _lib.check(lib.fmoe_jagged_bmm_two_weights(off.data_ptr(), rows, a.data_ptr(), _lib.dtype_code(jagged.dtype), a.stride(0),
+                                                   w0.data_ptr(), w1.data_ptr(), K0, se0, sk0, sn0, E, K, N, out.data_ptr(),
+                                                   _lib.dtype_code(out.dtype), out.stride(0), _lib.stream_ptr(dev)))
     return out
 
 
@@ -500,7 +543,7 @@ def silu_jagged_bmm_raw(offsets: torch.Tensor, jagged: torch.Tensor, weight: tor
     assert Kw == K and weight.dtype == jagged.dtype
     kp = _pad_k(K, jagged.dtype)
     a = prep_activation(jagged, kp)
-    w, w_se, w_sn = prep_weight(weight, kp)
+    w, w_se, w_sk, w_sn = prep_weight(weight, kp)
     od = out_dtype or jagged.dtype
     out = torch.empty((rows, N), dtype=od, device=dev)
     off = _index_i64(offsets)
@@ -508,7 +551,7 @@ def silu_jagged_bmm_raw(offsets: torch.Tensor, jagged: torch.Tensor, weight: tor
         _lib.check(
             lib.fmoe_silu_jagged_bmm(
                 off.data_ptr(), rows, a.data_ptr(), _lib.dtype_code(jagged.dtype), a.stride(0), None, w.data_ptr(),
-                None, w_se, 1, w_sn, 0, None, 0, E, kp, N, 0, None, None, None, out.data_ptr(), _lib.dtype_code(od),
+                None, w_se, w_sk, w_sn, 0, None, 0, E, kp, N, 0, None, None, None, out.data_ptr(), _lib.dtype_code(od),
                 out.stride(0), _lib.stream_ptr(dev),
             )
         )
@@ -577,7 +620,7 @@ def silu_jagged_bmm_combine(
     lib = _lib.load()
     kp = _pad_k(D_in, jagged.dtype)
     a = prep_activation(jagged, kp)
-    w, w_se, w_sn = prep_weight(weight, kp)
+    w, w_se, w_sk, w_sn = prep_weight(weight, kp)
     b = _prep_bias(bias, jagged.dtype)
     off = _index_i64(offsets)
     rev = _index_i64(reverse_index)
@@ -610,7 +653,7 @@ def silu_jagged_bmm_combine(
         with torch.cuda.device(dev):
             _lib.check(
                 lib.fmoe_silu_jagged_bmm_combine_fused(
-                    off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, 1, w_sn, 0,
+                    off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), None, w.data_ptr(), None, w_se, w_sk, w_sn, 0,
                     _lib.ptr(b), D_out, g.data_ptr(), _lib.dtype_code(g.dtype), gidx.data_ptr(), L, K, E, kp, D_out,
                     1 if has_silu else 0, _lib.ptr(act_scratch), out.data_ptr(), _lib.dtype_code(out_dtype),
                     out.stride(0), flags, _lib.stream_ptr(dev),
@@ -621,7 +664,7 @@ def silu_jagged_bmm_combine(
     with torch.cuda.device(dev):
         _lib.check(
             lib.fmoe_silu_jagged_bmm_combine(
-                off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), w.data_ptr(), w_se, 1, w_sn, _lib.ptr(b), D_out,
+                off.data_ptr(), N, a.data_ptr(), dt, a.stride(0), w.data_ptr(), w_se, w_sk, w_sn, _lib.ptr(b), D_out,
                 rev.data_ptr(), _lib.ptr(g), _lib.dtype_code(g.dtype) if g is not None else 0, _lib.ptr(gidx), L, K,
                 E, kp, D_out, 1 if has_silu else 0, _lib.ptr(act_scratch), bmm_scratch.data_ptr(), out.data_ptr(),
                 _lib.dtype_code(out_dtype), out.stride(0), _lib.stream_ptr(dev),

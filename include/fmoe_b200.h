@@ -456,6 +456,14 @@ int fmoe_router_backward(const int64_t* topk_idx, const float* topk_score, const
 int fmoe_gate_linear_backward(const float* d_logits, const void* x, int x_dtype, int64_t ldx, const float* gate_w,
                               int64_t L, int d, int E, void* d_x, int64_t lddx, float* d_gate_w, float* d_gate_b,
                               void* stream);
+/* out[r, :] = jagged[r, :k_split] @ weight0[e] + jagged[r, k_split:] @ weight1[e] for the rows r of expert
+ * e: one grouped product whose reduction walks two weights (logical [E, k_split, N] and
+ * [E, K - k_split, N], same strides). The backward of the gated up projection uses it for
+ * d_x = d_alpha @ W^T + d_beta @ Wp^T (kernels/triton/triton_moe.py:2378-2511) without building the
+ * concatenated weight; k_split a multiple of 128 bytes of K. */
+int fmoe_jagged_bmm_two_weights(const int64_t* offsets, int64_t total_rows, const void* jagged, int dtype, int64_t ldj,
+                                const void* weight0, const void* weight1, int k_split, int64_t w_se, int64_t w_sk,
+                                int64_t w_sn, int E, int K, int N, void* out, int out_dtype, int64_t ldo, void* stream);
 int fmoe_batched_transpose(const void* in, int dtype, int batch, int64_t in_sb, int64_t ld_in, int rows, int cols,
                            void* out, int64_t out_sb, int64_t ld_out, void* stream);
 int fmoe_jagged_pad_offsets(const int64_t* offsets, int E, int dtype, int64_t* kseg, void* stream);

@@ -50,10 +50,15 @@ def test_argument_validation_returns_status_not_crash():
     # missing workspace
     rc = lib.fmoe_route_metadata(None, 16, 4, 2, None, ctypes.c_void_p(16), None, None, None, None, None, 0, None)
     assert rc == _lib.FMOE_ERR_BAD_ARG
-    # weight whose K is not contiguous is refused, never silently transposed
+    # a weight with neither K nor N contiguous is refused, never silently transposed (so is an
+    # N-contiguous one outside bf16 with N a multiple of 64)
     rc = lib.fmoe_index_select_jagged_bmm(ctypes.c_void_p(16), ctypes.c_void_p(16), 2, 8, ctypes.c_void_p(16),
-                                          _lib.BF16, 4, 64, ctypes.c_void_p(16), 64 * 64, 64, 1, None, 0, 2, 64, 64,
+                                          _lib.BF16, 4, 64, ctypes.c_void_p(16), 64 * 128, 128, 2, None, 0, 2, 64, 64,
                                           0, ctypes.c_void_p(16), _lib.BF16, 64, None)
+    assert rc == _lib.FMOE_ERR_UNSUPPORTED
+    rc = lib.fmoe_index_select_jagged_bmm(ctypes.c_void_p(16), ctypes.c_void_p(16), 2, 8, ctypes.c_void_p(16),
+                                          _lib.F32, 4, 64, ctypes.c_void_p(16), 64 * 64, 64, 1, None, 0, 2, 64, 64,
+                                          0, ctypes.c_void_p(16), _lib.F32, 64, None)
     assert rc == _lib.FMOE_ERR_UNSUPPORTED
     assert b"contiguous" in lib.fmoe_last_error()
     with pytest.raises(_lib.FmoeError):

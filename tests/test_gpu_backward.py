@@ -253,3 +253,36 @@ def test_captured_train_step_matches_eager(swiglu):
             p.grad = None
         step = fm.CapturedTrainStep(layer, x0, k)
     assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("stored_kmajor", [True, False])
+@pytest.mark.parametrize("rows_per_expert", [96, 1500])
+def test_reduction_over_two_weights_matches_concatenation(stored_kmajor, rows_per_expert):
+    """jagged_bmm_two_weights (d_x of the gated up projection: d_alpha @ W^T + d_beta @ Wp^T as one
+    product) gives the bits of the product with the two transposed weights laid side by side, for
+    weights stored [E, N, K] (read as MN-major operands) and plain [E, K, N] ones."""
+    from fast_moe_b200.kernels import moe as ops
+
+    torch.manual_seed(rows_per_expert)
+    E, K, N = 4, 128, 192          # the up projection's K (tokens) and N (hidden); d_ab is [rows, 2N]
+    lens = torch.tensor([rows_per_expert, 0, rows_per_expert + 37, 5])
+    off = torch.cat([torch.zeros(1, dtype=torch.int64), lens.cumsum(0)]).to(DEV)
+    rows = int(lens.sum())
+    d_ab = torch.randn(rows, 2 * N, device=DEV).bfloat16()
+
+    def make():
+        w = (torch.randn(E, K, N, device=DEV) * 0.1).bfloat16()
+        return w.permute(0, 2, 1).contiguous().permute(0, 2, 1) if stored_kmajor else w
+
+    w, wp = make(), make()
+    got = ops.jagged_bmm_two_weights(off, d_ab, w.permute(0, 2, 1), wp.permute(0, 2, 1))
+    assert got is not None
+    w_cat = AG.transposed_weights_side_by_side(w, wp)
+    want = ops.silu_jagged_bmm(off, d_ab, w_cat, None, has_silu=False)
+    assert torch.equal(got, want)
+    ref = torch.zeros(rows, K)
+    for e in range(E):
+        a, b = int(off[e]), int(off[e + 1])
+        ref[a:b] = d_ab[a:b, :N].float().cpu() @ w[e].float().cpu().t() + d_ab[a:b, N:].float().cpu() @ wp[e].float().cpu().t()
+    close(got, ref, torch.bfloat16, "two-weight product")
+    assert _lib.device_status(torch.device(DEV)) == 0

@@ -703,3 +703,45 @@ def test_gather_rows_all_kernel_forms(src_rows, rows, cols, dt, div):
     keep[3] = False
     assert torch.equal(got[keep], want[keep])
     clean_status()
+
+
+@pytest.mark.parametrize("L,E,k,K,N", [(512, 4, 2, 128, 256), (4096, 2, 2, 200, 192), (300, 8, 3, 64, 64),
+                                       (8192, 4, 1, 1024, 1024)])
+def test_plain_weight_layout_is_read_in_place(L, E, k, K, N):
+    """A plain contiguous [E, K, N] bf16 weight (N contiguous; N a multiple of 64) is read in place
+    as an MN-major tensor-core operand: same bits as the transposed-copy path, for the plain, SiLU,
+    gated and combine operators, lone CTAs and CTA pairs, ragged K and N tiles."""
+    from fast_moe_b200.kernels import moe as ops
+
+    torch.manual_seed(L + K)
+    dev = torch.device(DEV)
+    idx = torch.rand(L, E, device=dev).topk(k, dim=1).indices
+    meta = fm.route_metadata(idx, E)
+    index = meta.gate_index.view(-1, k)
+    x = torch.randn(L, K, device=dev).bfloat16()
+    w = (torch.randn(E, K, N, device=dev) * 0.1).bfloat16()
+    wp = (torch.randn(E, K, N, device=dev) * 0.1).bfloat16()
+    b = (torch.randn(E, N, device=dev) * 0.1).bfloat16()
+    hid = torch.randn(L * k, K, device=dev).bfloat16()
+    score = torch.rand(L, k, device=dev)
+
+    def run():
+        return (
+            fm.index_select_jagged_bmm(0, meta.offsets, index, x, w, b),
+            fm.index_select_jagged_bmm_swiglu(0, meta.offsets, index, x, w, None, wp, None),
+            ops.silu_jagged_bmm(meta.offsets, hid, w, b, has_silu=True),
+            fm.silu_jagged_bmm_combine(0, meta.offsets, hid, w, None, meta.token_index, meta.reverse_index,
+                                       gating_scores=score, gates_index=meta.gate_index, has_silu=False),
+        )
+
+    assert ops.prep_weight(w, K)[2] == N and ops.prep_weight(w, K)[3] == 1       # taken in place, N contiguous
+    got = run()
+    ops.MN_MAJOR_WEIGHTS = False
+    try:
+        assert ops.prep_weight(w, K)[2] == 1
+        want = run()
+    finally:
+        ops.MN_MAJOR_WEIGHTS = True
+    for g_, w_ in zip(got, want):
+        assert torch.equal(g_, w_)
+    assert _lib.device_status(dev) == 0
