@@ -406,44 +406,55 @@ gate_dx_kernel(const float* __restrict__ d_logits, const float* __restrict__ w, 
 }
 
 // d_W[e, c] += sum over a chunk of tokens of d_logits[t, e] * x[t, c]; d_b[e] += sum of d_logits[t, e].
-// A block owns 256 columns and one chunk of kGateDwChunk tokens: the chunk's d_logits are staged in
-// shared memory once, each thread keeps 32 experts' partial sums in registers and adds them to the
-// fp32 result (cleared beforehand) with atomics.
-constexpr int kGateDwChunk = 64;
+// A block owns 64 columns (two per lane) and a chunk of kGateDwChunk tokens; its 8 warps take the
+// tokens t0 + w, t0 + w + 8, ..., keep up to 32 experts' partial sums per lane in registers, fold
+// them into one shared [experts][64] table and add that to the fp32 result (cleared beforehand) with
+// one global atomic per entry and block.
+constexpr int kGateDwChunk = 256;
 template <typename T>
 __global__ void __launch_bounds__(256)
 gate_dw_kernel(const float* __restrict__ d_logits, const T* __restrict__ x, long long ldx, long long L, int d, int E,
                float* __restrict__ dw, float* __restrict__ db) {
-  __shared__ float s_dl[kGateDwChunk][33];
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ float s_acc[32][64];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 64 + 2 * lane;
   const long long t0 = static_cast<long long>(blockIdx.y) * kGateDwChunk;
-  const int nt = static_cast<int>(min(static_cast<long long>(kGateDwChunk), L - t0));
+  const long long t1 = min(L, t0 + kGateDwChunk);
   for (int e0 = 0; e0 < E; e0 += 32) {
     const int ne = min(32, E - e0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nt * ne; i += blockDim.x) {
-      const int tt = i / ne, ee = i - tt * ne;
-      s_dl[tt][ee] = d_logits[(t0 + tt) * E + e0 + ee];
-    }
+    for (int i = threadIdx.x; i < 32 * 64; i += blockDim.x) (&s_acc[0][0])[i] = 0.f;
     __syncthreads();
-    float acc[32];
+    float a0[32], a1[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    if (c < d) {
-      for (int tt = 0; tt < nt; ++tt) {
-        const float xv = ldf<T>(x + (t0 + tt) * ldx + c);
+    for (int i = 0; i < 32; ++i) a0[i] = a1[i] = 0.f;
+    float bsum = 0.f;                    // lane i of the first column block also sums expert e0 + i's bias gradient
+    for (long long t = t0 + warp; t < t1; t += 8) {
+      const float x0 = c < d ? ldf<T>(x + t * ldx + c) : 0.f;
+      const float x1 = c + 1 < d ? ldf<T>(x + t * ldx + c + 1) : 0.f;
+      const float dl = lane < ne ? d_logits[t * E + e0 + lane] : 0.f;
+      bsum += dl;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < ne) acc[i] = fmaf(s_dl[tt][i], xv, acc[i]);
+      for (int i = 0; i < 32; ++i) {
+        if (i < ne) {
+          const float g = __shfl_sync(0xffffffffu, dl, i);
+          a0[i] = fmaf(g, x0, a0[i]);
+          a1[i] = fmaf(g, x1, a1[i]);
+        }
       }
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < ne) atomicAdd(dw + static_cast<long long>(e0 + i) * d + c, acc[i]);
     }
-    if (db != nullptr && blockIdx.x == 0 && threadIdx.x < ne) {
-      float bsum = 0.f;
-      for (int tt = 0; tt < nt; ++tt) bsum += s_dl[tt][threadIdx.x];
-      atomicAdd(db + e0 + threadIdx.x, bsum);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i < ne) {
+        atomicAdd(&s_acc[i][2 * lane], a0[i]);
+        atomicAdd(&s_acc[i][2 * lane + 1], a1[i]);
+      }
+    }
+    if (db != nullptr && blockIdx.x == 0 && lane < ne) atomicAdd(db + e0 + lane, bsum);
+    __syncthreads();
+    for (int i = threadIdx.x; i < ne * 64; i += blockDim.x) {
+      const int ee = i >> 6, cc = blockIdx.x * 64 + (i & 63);
+      if (cc < d) atomicAdd(dw + static_cast<long long>(e0 + ee) * d + cc, s_acc[ee][i & 63]);
     }
   }
 }
@@ -700,7 +711,7 @@ extern "C" int fmoe_gate_linear_backward(const float* d_logits, const void* x, i
   if (d_gate_w != nullptr) {
     FMOE_REQUIRE(L <= 65535ll * kGateDwChunk, "gate_linear_backward: L=%lld exceeds %lld tokens", (long long)L,
                  65535ll * kGateDwChunk);
-    dim3 grid((d + 255) / 256, static_cast<unsigned>((L + kGateDwChunk - 1) / kGateDwChunk), 1);
+    dim3 grid((d + 63) / 64, static_cast<unsigned>((L + kGateDwChunk - 1) / kGateDwChunk), 1);
     if (x_dtype == FMOE_BF16) {
       gate_dw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(d_logits, static_cast<const __nv_bfloat16*>(x), ldx, L, d, E,
                                                            d_gate_w, d_gate_b);
