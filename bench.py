@@ -275,11 +275,9 @@ def routing_sweep(c, device):
     hid = torch.randn(A, h_, generator=g).to(torch.bfloat16).to(device)
     hid2 = torch.randn(A, h_, generator=g).to(torch.bfloat16).to(device)
     dh = torch.randn(A, h_, generator=g).to(torch.bfloat16).to(device)
-    wst = (torch.randn(E, h_, d_, generator=g) * 0.02).to(torch.bfloat16).to(device)       # storage [E, N, K]
     kseg, padded = AG._padded_reduction(meta.offsets, E, torch.bfloat16, A)
     add("jagged_transpose_pad", f"c2 hidden {A} x {h_}", lambda: AG._transpose_pad(hid, meta.offsets, kseg, padded, E, A),
         2 * A * h_ * 2)
-    add("batched_transpose (weight)", f"c2 {E} x {h_} x {d_}", lambda: AG.transposed_weight(wst.permute(0, 2, 1)), 2 * E * h_ * d_ * 2)
     da, db = torch.empty_like(hid), torch.empty_like(hid)
     add("activation_backward (SwiGLU)", f"c2 {A} x {h_}", lambda: AG.activation_backward(1, dh, hid, hid2, da, db), 5 * A * h_ * 2)
     add("jagged_colsum (d_bias)", f"c2 {A} x {h_}", lambda: AG.grad_bias(meta.offsets, dh, E, torch.bfloat16), A * h_ * 2)
