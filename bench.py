@@ -699,6 +699,13 @@ def next_rows_record(device, peaks, steps=10):
             executed_tflops=(3 * fwd_flops + rec_flops) / (ms_dev * 1e-3) / 1e12,
             frac_of_bf16_burst=(3 * fwd_flops + rec_flops) / (ms_dev * 1e-3) / 1e12 / peaks["bf16_tflops"],
             tokens_per_s=L / (ms_dev * 1e-3), device_status=_lib.device_status(device))
+        if name == "silu_layer":
+            # the reference's primary layer class (FastMoELayer: SiLU experts with biases), forward only
+            layer.autograd = False
+            ms_fwd = graph_kernel_ms(lambda: layer(x, k), device)
+            rec["silu_layer_forward"] = dict(ms_per_step=ms_fwd, tokens_per_s=L / (ms_fwd * 1e-3),
+                                             layer_tflops=(fwd_flops + 2 * L * d * E) / (ms_fwd * 1e-3) / 1e12,
+                                             launch_mode="10 forwards in a CUDA graph")
         del graph_step, layer, xg
     # ---- sparsely-gated layer forward (d -> h -> o MLP experts + shared linear map)
     torch.manual_seed(0)
