@@ -637,6 +637,16 @@ def single_gpu_record(name, device, args, peaks, fp8_peak, sampler=None, sustain
     return rec
 
 
+def _guarded(fn):
+    """A secondary record must not take the line down with it: its failure is reported in its place."""
+    try:
+        return fn()
+    except Exception as exc:      # noqa: BLE001 - reported, not swallowed
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        return dict(error=f"{type(exc).__name__}: {exc}"[:500])
+
+
 def sg_flops_of(A, L, d, h, o, E):
     """Forward FLOPs of the sparsely-gated layer: two expert products, the shared map, the gate."""
     return 2 * A * d * h + 2 * A * h * o + 2 * L * d * o + 2 * L * d * E
@@ -1113,10 +1123,11 @@ def main():
             line["fp8_dense_peak_tflops"] = fp8_peak
             if not args.no_sub_records:
                 for sub in ("c3", "c4"):
-                    line[sub] = single_gpu_record(sub, device, args, peaks, fp8_peak, parity=not args.no_parity)
-                line["next_rows"] = next_rows_record(device, peaks)
+                    line[sub] = _guarded(lambda: single_gpu_record(sub, device, args, peaks, fp8_peak, parity=not args.no_parity))
+                line["next_rows"] = _guarded(lambda: next_rows_record(device, peaks))
             if not args.no_ep_reference:
-                line["c5_ep_1gpu"] = ep_single_gpu_record(device, args, peaks, with_e2e=True, parity=not args.no_parity)
+                line["c5_ep_1gpu"] = _guarded(lambda: ep_single_gpu_record(device, args, peaks, with_e2e=True,
+                                                                           parity=not args.no_parity))
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
