@@ -450,7 +450,9 @@ int fmoe_ep_down_projection(const int64_t* offsets_local, int64_t capacity, int6
  * fmoe_router_backward (topk_idx [L, k], topk_score = y, d_score = dy, all as fmoe_gate_topk wrote
  * them; d_logits [L, E] f32). fmoe_gate_linear_backward then gives the gradients of the gate's
  * Linear: d_x [L, d] (dtype of x, may be NULL) = d_logits @ gate_w, d_gate_w [E, d] f32 = d_logits^T @ x,
- * d_gate_b [E] f32 = column sums (both cleared first; either may be NULL). */
+ * d_gate_b [E] f32 = column sums (both cleared first; either may be NULL). The two parameter
+ * gradients are accumulated with fp32 atomics over chunks of 256 tokens: their last bits can
+ * differ from run to run. */
 int fmoe_router_backward(const int64_t* topk_idx, const float* topk_score, const float* d_score, int64_t L, int E, int k,
                          float* d_logits, void* stream);
 int fmoe_gate_linear_backward(const float* d_logits, const void* x, int x_dtype, int64_t ldx, const float* gate_w,
