@@ -247,7 +247,7 @@ extern "C" int fmoe_silu_jagged_bmm(const int64_t* offsets, int64_t total_rows, 
   FMOE_REQUIRE(fp8 || dtype == FMOE_BF16 || dtype == FMOE_F32, "silu_jagged_bmm: bad dtype %d", dtype);
   FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm: FP8 operands need their scales");
   FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm: has_silu is not available on FP8 input (quantise silu(x) instead)");
-  FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm: has_silu needs act_scratch");
+  FMOE_REQUIRE(!has_silu || act_scratch != nullptr || total_rows == 0, "silu_jagged_bmm: has_silu needs act_scratch");
   FMOE_REQUIRE(!(has_silu && jagged_index), "silu_jagged_bmm: has_silu and jagged_index cannot be combined");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const void* a = jagged;
@@ -335,7 +335,8 @@ extern "C" int fmoe_silu_jagged_bmm_combine_fused(const int64_t* offsets, int64_
                "silu_jagged_bmm_combine_fused: unknown flags 0x%x", flags);
   FMOE_REQUIRE(!fp8 || (jagged_scale && weight_scale), "silu_jagged_bmm_combine_fused: FP8 operands need their scales");
   FMOE_REQUIRE(!(fp8 && has_silu), "silu_jagged_bmm_combine_fused: has_silu is not available on FP8 input");
-  FMOE_REQUIRE(!has_silu || act_scratch != nullptr, "silu_jagged_bmm_combine_fused: has_silu needs act_scratch");
+  FMOE_REQUIRE(!has_silu || act_scratch != nullptr || total_rows == 0,
+               "silu_jagged_bmm_combine_fused: has_silu needs act_scratch");
   FMOE_REQUIRE(L == 0 || (gating_scores && gates_index),
                "silu_jagged_bmm_combine_fused: gating_scores and gates_index are required");
   FMOE_REQUIRE(g_dtype == FMOE_BF16 || g_dtype == FMOE_F32, "silu_jagged_bmm_combine_fused: gate weights must be bf16 or f32");

@@ -522,11 +522,16 @@ class SGLossFn(torch.autograd.Function):
         load = torch.empty(num_experts, dtype=torch.float32, device=dev)
         loss = torch.empty((), dtype=torch.float32, device=dev)
         sc = score.detach().contiguous()
+        ctx.empty = sc.numel() == 0
+        if ctx.empty:        # an empty batch: its tensors have no storage; nothing is read through these
+            sc = torch.zeros(1, dtype=torch.float32, device=dev)
+            gate_index = torch.zeros(1, dtype=torch.int64, device=dev)
         with torch.cuda.device(dev):
             _lib.check(lib.fmoe_sg_load_loss(offsets.data_ptr(), gate_index.data_ptr(), sc.data_ptr(), num_experts,
                                              1 if round_bf16 else 0, float(loss_coef), 1, None, 0, load.data_ptr(),
                                              loss.data_ptr(), _lib.stream_ptr(dev)))
         ctx.save_for_backward(sc, offsets, gate_index)
+        ctx.score_shape = tuple(score.shape)
         ctx.cfg = (int(num_experts), bool(round_bf16), float(loss_coef))
         ctx.mark_non_differentiable(load)
         return loss, load
@@ -537,6 +542,8 @@ class SGLossFn(torch.autograd.Function):
         E, round_bf16, coef = ctx.cfg
         lib = _lib.load()
         dev = sc.device
+        if ctx.empty:
+            return torch.zeros((0, 0), dtype=torch.float32, device=dev).reshape(ctx.score_shape), None, None, None, None, None
         with torch.no_grad():
             d_score = torch.zeros_like(sc)
             dl = d_loss.to(torch.float32).contiguous()

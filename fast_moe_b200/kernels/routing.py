@@ -263,12 +263,16 @@ def sg_load_loss(meta: RoutingMetadata, score: torch.Tensor, num_experts: int, t
     load = torch.empty(num_experts, dtype=torch.float32, device=dev)
     loss = torch.empty((), dtype=torch.float32, device=dev)
     sc = score.contiguous()
+    gidx = meta.gate_index
+    if sc.numel() == 0:      # an empty batch: its tensors have no storage; nothing is read through these
+        sc = torch.zeros(1, dtype=torch.float32, device=dev)
+        gidx = torch.zeros(1, dtype=torch.int64, device=dev)
     n_part = 0
     if smooth_load is not None:
         assert smooth_load.dtype == torch.float32 and smooth_load.is_contiguous() and smooth_load.shape[1] == num_experts
         n_part = smooth_load.shape[0]
     with torch.cuda.device(dev):
-        _lib.check(lib.fmoe_sg_load_loss(meta.offsets.data_ptr(), meta.gate_index.data_ptr(), sc.data_ptr(), num_experts,
+        _lib.check(lib.fmoe_sg_load_loss(meta.offsets.data_ptr(), gidx.data_ptr(), sc.data_ptr(), num_experts,
                                          1 if token_dtype == torch.bfloat16 else 0, float(loss_coef), 1 if train else 0,
                                          _lib.ptr(smooth_load), n_part, load.data_ptr(), loss.data_ptr(),
                                          _lib.stream_ptr(dev)))

@@ -156,3 +156,54 @@ def test_quantized_weights_are_persistent_until_requantized():
     assert layer._q["w_gate"][0] is not q1
     assert not torch.equal(layer(x, 2), y1)
     assert _lib.device_status(torch.device(DEV)) == 0
+
+
+def test_training_and_sparsely_gated_paths_accept_an_empty_batch():
+    """Zero tokens through the differentiable paths and the sparsely-gated layer (inference, noisy
+    gating, training with backward): shapes come back right, gradients are zeros, no status."""
+    d, h, o, E, k = 64, 128, 64, 4, 2
+    layer = fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(DEV)
+    layer.autograd = True
+    x = torch.empty((1, 0, d), dtype=torch.bfloat16, device=DEV, requires_grad=True)
+    y = layer(x, k)
+    assert y.shape == (1, 0, o)
+    y.sum().backward()
+    assert x.grad.shape == x.shape
+    for p in layer.parameters():
+        assert p.grad is not None and float(p.grad.abs().sum()) == 0.0
+    nw, nb = torch.ones(d, device=DEV), torch.zeros(d, device=DEV)
+    x2 = torch.empty((0, d), dtype=torch.bfloat16, device=DEV)
+    for noisy in (False, True):
+        sg = fm.SGMoELayer(d, o, fm.SGConfig(model_d=h, num_experts=E, num_activated_experts=k, enable_noisy_gating=noisy)).to(DEV)
+        for train in (False, True):
+            sg.train(train)
+            out = sg(x2, None, 0, False, 1, d, nw, nb, 1e-5)
+            assert out.x.shape == (0, o) and torch.isfinite(out.loss)
+    sg = fm.SGMoELayer(d, o, fm.SGConfig(model_d=h, num_experts=E, num_activated_experts=k)).to(DEV)
+    sg.train(True)
+    sg.autograd = True
+    xg = x2.clone().requires_grad_()
+    out = sg(xg, None, 0, False, 1, d, nw, nb, 1e-5)
+    (out.x.float().sum() + out.loss).backward()
+    assert xg.grad.shape == (0, d)
+    assert _lib.device_status(torch.device(DEV)) == 0
+
+
+def test_two_weight_product_and_in_place_weights_at_the_small_end():
+    """One expert, N = 64 (a single 64-column atom), a handful of rows; and zero rows."""
+    E, K, N = 1, 64, 64
+    off = torch.tensor([0, 5], dtype=torch.int64, device=DEV)
+    x = torch.randn(5, K, device=DEV).bfloat16()
+    w = (torch.randn(E, K, N, device=DEV) * 0.1).bfloat16()          # plain layout: N contiguous
+    assert moe.prep_weight(w, K)[3] == 1
+    got = moe.silu_jagged_bmm(off, x, w, None, has_silu=False)
+    torch.testing.assert_close(got.float(), x.float() @ w[0].float(), atol=2e-2, rtol=2e-2)
+    a = torch.randn(5, 2 * K, device=DEV).bfloat16()
+    w1 = (torch.randn(E, K, N, device=DEV) * 0.1).bfloat16()
+    two = moe.jagged_bmm_two_weights(off, a, w, w1)
+    assert two is not None
+    torch.testing.assert_close(two.float(), a[:, :K].float() @ w[0].float() + a[:, K:].float() @ w1[0].float(), atol=3e-2, rtol=2e-2)
+    off0 = torch.zeros(2, dtype=torch.int64, device=DEV)
+    empty = moe.jagged_bmm_two_weights(off0, torch.empty((0, 2 * K), dtype=torch.bfloat16, device=DEV), w, w1)
+    assert empty is not None and empty.shape == (0, N)
+    assert _lib.device_status(torch.device(DEV)) == 0
