@@ -286,3 +286,43 @@ def test_reduction_over_two_weights_matches_concatenation(stored_kmajor, rows_pe
         ref[a:b] = d_ab[a:b, :N].float().cpu() @ w[e].float().cpu().t() + d_ab[a:b, N:].float().cpu() @ wp[e].float().cpu().t()
     close(got, ref, torch.bfloat16, "two-weight product")
     assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_partial_gradients_frozen_experts_or_constant_input(swiglu):
+    """Only what requires a gradient gets one: frozen expert weights stay without .grad while x and
+    the gate still receive theirs (equal to the all-trainable run), and a constant input with
+    trainable parameters works as well."""
+    torch.manual_seed(8)
+    d, h, o, E, k, L = 64, 128, 64, 4, 2, 200
+    cls = fm.SwiGLUFastMoELayer if swiglu else fm.FastMoELayer
+    layer = cls(d, h, o, E, dtype=torch.bfloat16).to(DEV)
+    layer.autograd = True
+    x = torch.randn(1, L, d, device=DEV).bfloat16()
+    dout = (torch.randn(1, L, o, device=DEV) * 0.01).bfloat16()
+    xa = x.clone().requires_grad_()
+    layer(xa, k).backward(dout)
+    full = {n: p.grad.clone() for n, p in layer.named_parameters()}
+    for n, p in layer.named_parameters():
+        p.grad = None
+        if not n.startswith("gate."):
+            p.requires_grad_(False)
+    xb = x.clone().requires_grad_()
+    layer(xb, k).backward(dout)
+    assert torch.equal(xb.grad, xa.grad)
+    for n, p in layer.named_parameters():
+        if n.startswith("gate."):
+            torch.testing.assert_close(p.grad, full[n], atol=1e-5, rtol=1e-4)
+        else:
+            assert p.grad is None, n
+    # constant input, trainable experts
+    for n, p in layer.named_parameters():
+        p.requires_grad_(True)
+        p.grad = None
+    y = layer(x, k)
+    assert y.requires_grad
+    y.backward(dout)
+    for n, p in layer.named_parameters():
+        if not n.startswith("gate."):
+            assert torch.equal(p.grad, full[n]), n
+    assert _lib.device_status(torch.device(DEV)) == 0

@@ -171,6 +171,11 @@ def test_training_and_sparsely_gated_paths_accept_an_empty_batch():
     assert x.grad.shape == x.shape
     for p in layer.parameters():
         assert p.grad is not None and float(p.grad.abs().sum()) == 0.0
+    mlp = fm.FastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(DEV)        # SiLU experts with biases
+    mlp.autograd = True
+    xm = torch.empty((1, 0, d), dtype=torch.bfloat16, device=DEV, requires_grad=True)
+    mlp(xm, k).sum().backward()
+    assert xm.grad.shape == xm.shape and all(p.grad is not None for p in mlp.parameters())
     nw, nb = torch.ones(d, device=DEV), torch.zeros(d, device=DEV)
     x2 = torch.empty((0, d), dtype=torch.bfloat16, device=DEV)
     for noisy in (False, True):
