@@ -63,7 +63,8 @@ SIGNATURES = {
     "fmoe_sg_load_loss": (c_int, [P, P, P, c_int, c_int, c_float, c_int, P, c_int, P, P, P]),
     "fmoe_token_norm_backward": (c_int, [P, P, c_int, I64, c_int, I64, I64, c_int, P, c_int, c_float, P, I64, P, P, c_int, P, P, P]),
     "fmoe_sg_router_backward": (c_int, [P, P, P, I64, c_int, c_int, P, P]),
-    "fmoe_sg_loss_backward": (c_int, [P, P, P, c_int, c_int, c_float, P, P, P]),
+    "fmoe_sg_loss_backward": (c_int, [P, P, P, c_int, c_int, c_float, P, P, P, c_int, P, P]),
+    "fmoe_sg_noisy_router_backward": (c_int, [P, I64, P, P, P, P, P, P, I64, c_int, c_int, P, I64, P]),
     "fmoe_jagged_bmm_two_weights": (c_int, [P, I64, P, c_int, I64, P, P, c_int, I64, I64, I64, c_int, c_int, c_int, P, c_int, I64, P]),
     "fmoe_sg_noisy_logits": (c_int, [P, I64, P, I64, c_int, c_float, P, P, P]),
     "fmoe_sg_noisy_load": (c_int, [P, I64, P, P, I64, c_int, c_int, P, c_int, P]),

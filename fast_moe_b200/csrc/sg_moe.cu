@@ -380,14 +380,165 @@ sg_router_backward_kernel(const float* __restrict__ logits, const long long* __r
   }
 }
 
+// Router backward with noisy gating (training): the logits that were routed on are
+//   noisy = clean + noise * stddev,  stddev = softplus(raw) + eps,  clean = x @ w_gate, raw = x @ w_noise,
+// and the loss also holds the smooth load  sum_t Phi((clean - thr) / stddev)  whose thresholds are
+// the k-th / (k+1)-th largest normalised noisy logits of the token (kernels/pytorch/mrn.py:191-252).
+// Per token: d_n from the k scores (softmax over all experts) plus the thresholds' share of the
+// load gradient, the normalisation's backward, then d_clean and d_raw. `g_load` [E] is
+// d loss / d load (NULL: the load takes no part, e.g. k == E). One warp per token.
+template <int VPL>
+__global__ void __launch_bounds__(256)
+sg_noisy_router_backward_kernel(const float* __restrict__ logits2, long long ld, const float* __restrict__ noise,
+                                const float* __restrict__ noisy, const float* __restrict__ stddev,
+                                const long long* __restrict__ idx, const float* __restrict__ d_score,
+                                const float* __restrict__ g_load, long long L, int E, int k,
+                                float* __restrict__ d_logits2, long long ldd) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < L; t += warps) {
+    float l[VPL], nv[VPL], p[VPL], dn[VPL];
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      l[j] = e < E ? noisy[t * E + e] : 0.f;
+      sq = fmaf(l[j], l[j], sq);
+    }
+    const float nrm = fmaxf(sqrtf(warp_sum(sq)), 1e-12f);
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      nv[j] = (lane + 32 * j) < E ? l[j] / nrm : -INFINITY;
+      mx = fmaxf(mx, nv[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float z = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      p[j] = (lane + 32 * j) < E ? expf(nv[j] - mx) : 0.f;
+      z += p[j];
+    }
+    z = warp_sum(z);
+    float sdot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      p[j] /= z;
+      dn[j] = 0.f;
+      for (int s = 0; s < k; ++s)
+        if (idx[t * k + s] == e) dn[j] += d_score[t * k + s];
+      sdot = fmaf(p[j], dn[j], sdot);
+    }
+    sdot = warp_sum(sdot);
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) dn[j] = p[j] * (dn[j] - sdot);
+    // ---- the smooth load's share
+    float dc[VPL], dsd[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) dc[j] = dsd[j] = 0.f;
+    if (g_load != nullptr && k < E) {
+      unsigned removed = 0u;
+      float thr_out = 0.f, thr_in = 0.f;
+      int e_out = -1, e_in = -1;
+      for (int r = 0; r <= k; ++r) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          const int e = lane + 32 * j;
+          if (e < E && !((removed >> j) & 1u) && (nv[j] > best || (nv[j] == best && e < best_e))) {
+            best = nv[j];
+            best_e = e;
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+          if (ob > best || (ob == best && oe < best_e)) {
+            best = ob;
+            best_e = oe;
+          }
+        }
+        if (best_e != 0x7fffffff && (best_e & 31) == lane) removed |= 1u << (best_e >> 5);
+        if (r == k - 1) { thr_out = best; e_out = best_e; }
+        if (r == k) { thr_in = best; e_in = best_e; }
+      }
+      float d_in = 0.f, d_out = 0.f;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E) {
+          const float clean = logits2[t * ld + e];
+          const float sd = stddev[t * E + e];
+          const bool in = l[j] > thr_in;
+          const float zz = (clean - (in ? thr_in : thr_out)) / sd;
+          const float c = g_load[e] * expf(-0.5f * zz * zz) * 0.3989422804014327f / sd;   // G * pdf(z) / stddev
+          dc[j] = c;
+          dsd[j] = -c * zz;
+          if (in) d_in -= c; else d_out -= c;
+        }
+      }
+      d_in = warp_sum(d_in);
+      d_out = warp_sum(d_out);
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int e = lane + 32 * j;
+        if (e == e_in) dn[j] += d_in;
+        if (e == e_out) dn[j] += d_out;
+      }
+    }
+    float ndot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+      if (lane + 32 * j < E) ndot = fmaf(nv[j], dn[j], ndot);
+    ndot = warp_sum(ndot);
+    const bool clamped = nrm <= 1e-12f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) {
+        const float dl = (clamped ? dn[j] : (dn[j] - nv[j] * ndot)) / nrm;      // d loss / d noisy
+        const float raw = logits2[t * ld + E + e];
+        const float sig = raw > 20.f ? 1.f : 1.f / (1.f + expf(-raw));          // softplus'
+        d_logits2[t * ldd + e] = dl + dc[j];
+        d_logits2[t * ldd + E + e] = (dl * noise[t * E + e] + dsd[j]) * sig;
+      }
+    }
+  }
+}
+
 // d loss / d scores: loss = coef * (cv2(importance) + cv2(load)); only the importance (sum of the
 // gate values per expert) depends on the scores. One block: importance as the forward sums it, its
 // cv2 derivative per expert, then every chosen (token, slot) receives its expert's value.
 __global__ void __launch_bounds__(256)
 sg_loss_backward_kernel(const long long* __restrict__ offsets, const long long* __restrict__ gate_index,
                         const float* __restrict__ score, int E, int round_bf16, float loss_coef,
-                        const float* __restrict__ d_loss, float* __restrict__ d_score) {
+                        const float* __restrict__ d_loss, float* __restrict__ d_score,
+                        const float* __restrict__ load_partials, int n_partials, float* __restrict__ d_load) {
   extern __shared__ float s_imp[];                 // [E] importance, then its gradient
+  // with noisy gating the loss's second term is cv2 of the smooth load: its derivative per expert
+  if (load_partials != nullptr && d_load != nullptr && threadIdx.x == 0) {
+    float mean = 0.f;
+    for (int e = 0; e < E; ++e) {
+      float v = 0.f;
+      for (int b = 0; b < n_partials; ++b) v += load_partials[static_cast<long long>(b) * E + e];
+      d_load[e] = v;                               // the load itself for now
+      mean += v;
+    }
+    mean /= E;
+    float var = 0.f;
+    for (int e = 0; e < E; ++e) var += (d_load[e] - mean) * (d_load[e] - mean);
+    var = E > 1 ? var / (E - 1) : 0.f;
+    const float den = mean * mean + 1e-6f;
+    const float sc = loss_coef * (d_loss ? *d_loss : 1.f);
+    for (int e = 0; e < E; ++e) {
+      const float g = E > 1 ? (2.f * (d_load[e] - mean) / ((E - 1) * den) - var * 2.f * mean / (E * den * den)) : 0.f;
+      d_load[e] = g * sc;
+    }
+  }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int e = warp; e < E; e += 8) {
@@ -580,12 +731,42 @@ extern "C" int fmoe_sg_router_backward(const float* logits, const int64_t* topk_
 }
 
 extern "C" int fmoe_sg_loss_backward(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
-                                     int round_bf16, float loss_coef, const float* d_loss, float* d_score, void* stream) {
+                                     int round_bf16, float loss_coef, const float* d_loss, float* d_score,
+                                     const float* load_partials, int n_partials, float* d_load, void* stream) {
   FMOE_REQUIRE(E >= 1 && E <= 4096, "sg_loss_backward: E=%d outside [1, 4096]", E);
   FMOE_REQUIRE(offsets && gate_index && topk_score && d_score, "sg_loss_backward: NULL pointer argument");
+  FMOE_REQUIRE((load_partials == nullptr) == (d_load == nullptr) && (load_partials == nullptr || n_partials >= 1),
+               "sg_loss_backward: load_partials and d_load go together");
   sg_loss_backward_kernel<<<1, 256, static_cast<size_t>(E) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const long long*>(offsets), reinterpret_cast<const long long*>(gate_index), topk_score, E, round_bf16,
-      loss_coef, d_loss, d_score);
+      loss_coef, d_loss, d_score, load_partials, n_partials, d_load);
+  FMOE_CUDA_OK(cudaGetLastError());
+  ++g_misc_launches;
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_sg_noisy_router_backward(const float* logits2, int64_t ld_logits, const float* noise,
+                                             const float* noisy, const float* stddev, const int64_t* topk_idx,
+                                             const float* d_score, const float* d_load, int64_t L, int E, int k,
+                                             float* d_logits2, int64_t ld_d, void* stream) {
+  FMOE_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= E && L >= 0, "sg_noisy_router_backward: E=%d (<= 256), k=%d out of range", E, k);
+  FMOE_REQUIRE(ld_logits >= 2ll * E && ld_d >= 2ll * E, "sg_noisy_router_backward: rows must hold 2 * E columns");
+  if (L == 0) return FMOE_OK;
+  FMOE_REQUIRE(logits2 && noise && noisy && stddev && topk_idx && d_score && d_logits2,
+               "sg_noisy_router_backward: NULL pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long blocks = (L * 32 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long long* idx = reinterpret_cast<const long long*>(topk_idx);
+  const int vpl = (E + 31) / 32;
+#define FMOE_SG_NRB(V)                                                                                                  \
+  sg_noisy_router_backward_kernel<V><<<static_cast<unsigned>(blocks), 256, 0, st>>>(logits2, ld_logits, noise, noisy, stddev, \
+                                                                                    idx, d_score, d_load, L, E, k, d_logits2, ld_d)
+  if (vpl <= 1) FMOE_SG_NRB(1);
+  else if (vpl <= 2) FMOE_SG_NRB(2);
+  else if (vpl <= 4) FMOE_SG_NRB(4);
+  else FMOE_SG_NRB(8);
+#undef FMOE_SG_NRB
   FMOE_CUDA_OK(cudaGetLastError());
   ++g_misc_launches;
   return FMOE_OK;

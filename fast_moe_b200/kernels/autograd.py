@@ -510,26 +510,105 @@ class SGRouterFn(torch.autograd.Function):
         return d_x, d_w, None
 
 
+class SGNoisyRouterFn(torch.autograd.Function):
+    """Router of the sparsely-gated layer with noisy gating (training): noise * (softplus(x @ w_noise)
+    + eps) on the logits, routing on the noisy logits, and the smooth load estimate
+    (kernels/pytorch/mrn.py:191-252). ``gate_weight`` / ``noise_weight`` are the parameters [d, E];
+    ``noise`` [L, E] f32 is the standard-normal draw. Returns (topk_idx, not differentiable; gates
+    [L, k] f32; per-block sums of the smooth load [blocks, E], differentiable, or an empty tensor
+    when k == E)."""
+
+    @staticmethod
+    def forward(ctx, x, gate_weight, noise_weight, k, noise, noise_eps=1e-2):
+        from .routing import gate_topk_normalized
+
+        lib = _lib.load()
+        dev = x.device
+        L = x.shape[0]
+        E = gate_weight.shape[1]
+        if 2 * E > 256:
+            raise ValueError(f"noisy gating supports up to 128 experts, got {E}")
+        with torch.no_grad():
+            both = torch.cat([gate_weight.detach().to(torch.float32).t(), noise_weight.detach().to(torch.float32).t()],
+                             dim=0).contiguous()                                     # [2E, d]
+            _, _, logits2 = gate_topk_normalized(x, both, 1, return_logits=True)
+            nz = noise.detach().to(torch.float32).contiguous()
+            noisy = torch.empty((L, E), dtype=torch.float32, device=dev)
+            stddev = torch.empty((L, E), dtype=torch.float32, device=dev)
+            with torch.cuda.device(dev):
+                _lib.check(lib.fmoe_sg_noisy_logits(logits2.data_ptr(), 2 * E, nz.data_ptr(), L, E, float(noise_eps),
+                                                    noisy.data_ptr(), stddev.data_ptr(), _lib.stream_ptr(dev)))
+            idx, score, _ = gate_topk_normalized(None, None, k, logits=noisy)
+            if k < E:
+                blocks = max(1, min(148, (L + 7) // 8))
+                partials = torch.empty((blocks, E), dtype=torch.float32, device=dev)
+                with torch.cuda.device(dev):
+                    _lib.check(lib.fmoe_sg_noisy_load(logits2.data_ptr(), 2 * E, noisy.data_ptr(), stddev.data_ptr(), L, E,
+                                                      k, partials.data_ptr(), blocks, _lib.stream_ptr(dev)))
+            else:
+                partials = torch.empty((0, E), dtype=torch.float32, device=dev)
+        ctx.save_for_backward(x, both, idx, logits2, nz, noisy, stddev)
+        ctx.dtypes = (gate_weight.dtype, noise_weight.dtype)
+        ctx.mark_non_differentiable(idx)
+        return idx, score, partials
+
+    @staticmethod
+    def backward(ctx, _d_idx, d_score, d_partials):
+        x, both, idx, logits2, nz, noisy, stddev = ctx.saved_tensors
+        lib = _lib.load()
+        dev = x.device
+        L, d = x.shape
+        E = both.shape[0] // 2
+        k = idx.shape[1]
+        with torch.no_grad():
+            dy = d_score.to(torch.float32).contiguous()
+            # every per-block row carries the same d loss / d load
+            d_load = d_partials[0].to(torch.float32).contiguous() if (d_partials is not None and d_partials.shape[0] > 0) else None
+            d_logits2 = torch.empty((L, 2 * E), dtype=torch.float32, device=dev)
+            xx = x if x.stride(1) == 1 else x.contiguous()
+            d_x = torch.empty_like(xx) if ctx.needs_input_grad[0] else None
+            want_w = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
+            d_both = torch.empty((2 * E, d), dtype=torch.float32, device=dev) if want_w else None
+            with torch.cuda.device(dev):
+                st = _lib.stream_ptr(dev)
+                _lib.check(lib.fmoe_sg_noisy_router_backward(logits2.data_ptr(), 2 * E, nz.data_ptr(), noisy.data_ptr(),
+                                                             stddev.data_ptr(), idx.data_ptr(), dy.data_ptr(), _lib.ptr(d_load),
+                                                             L, E, k, d_logits2.data_ptr(), 2 * E, st))
+                _lib.check(lib.fmoe_gate_linear_backward(d_logits2.data_ptr(), xx.data_ptr(), _lib.dtype_code(xx.dtype),
+                                                         xx.stride(0) if L else d, both.data_ptr(), L, d, 2 * E, _lib.ptr(d_x),
+                                                         d, _lib.ptr(d_both), None, st))
+            d_wg = d_wn = None
+            if d_both is not None:
+                if ctx.needs_input_grad[1]:
+                    d_wg = d_both[:E].t().to(ctx.dtypes[0])
+                if ctx.needs_input_grad[2]:
+                    d_wn = d_both[E:].t().to(ctx.dtypes[1])
+        return d_x, d_wg, d_wn, None, None, None
+
+
 class SGLossFn(torch.autograd.Function):
     """Training loss and load fractions of the sparsely-gated layer (fmoe_sg_load_loss;
     kernels/pytorch/mrn.py:186-189, :253-277). The loss differentiates with respect to the gates
     through the importance; the load is a count. Returns (loss, load fractions)."""
 
     @staticmethod
-    def forward(ctx, score, offsets, gate_index, num_experts, round_bf16, loss_coef):
+    def forward(ctx, score, offsets, gate_index, num_experts, round_bf16, loss_coef, smooth_load=None):
         lib = _lib.load()
         dev = score.device
         load = torch.empty(num_experts, dtype=torch.float32, device=dev)
         loss = torch.empty((), dtype=torch.float32, device=dev)
         sc = score.detach().contiguous()
+        part = None if smooth_load is None else smooth_load.detach().contiguous()
+        ctx.part = part
         ctx.empty = sc.numel() == 0
         if ctx.empty:        # an empty batch: its tensors have no storage; nothing is read through these
             sc = torch.zeros(1, dtype=torch.float32, device=dev)
             gate_index = torch.zeros(1, dtype=torch.int64, device=dev)
         with torch.cuda.device(dev):
             _lib.check(lib.fmoe_sg_load_loss(offsets.data_ptr(), gate_index.data_ptr(), sc.data_ptr(), num_experts,
-                                             1 if round_bf16 else 0, float(loss_coef), 1, None, 0, load.data_ptr(),
-                                             loss.data_ptr(), _lib.stream_ptr(dev)))
+                                             1 if round_bf16 else 0, float(loss_coef), 1, _lib.ptr(part),
+                                             0 if part is None else part.shape[0], load.data_ptr(), loss.data_ptr(),
+                                             _lib.stream_ptr(dev)))
         ctx.save_for_backward(sc, offsets, gate_index)
         ctx.score_shape = tuple(score.shape)
         ctx.cfg = (int(num_experts), bool(round_bf16), float(loss_coef))
@@ -542,16 +621,23 @@ class SGLossFn(torch.autograd.Function):
         E, round_bf16, coef = ctx.cfg
         lib = _lib.load()
         dev = sc.device
+        part = ctx.part
         if ctx.empty:
-            return torch.zeros((0, 0), dtype=torch.float32, device=dev).reshape(ctx.score_shape), None, None, None, None, None
+            d_part = None if part is None else torch.zeros_like(part)
+            return (torch.zeros((0, 0), dtype=torch.float32, device=dev).reshape(ctx.score_shape), None, None, None, None,
+                    None, d_part)
         with torch.no_grad():
             d_score = torch.zeros_like(sc)
             dl = d_loss.to(torch.float32).contiguous()
+            d_load = None if part is None else torch.empty(E, dtype=torch.float32, device=dev)
             with torch.cuda.device(dev):
                 _lib.check(lib.fmoe_sg_loss_backward(offsets.data_ptr(), gate_index.data_ptr(), sc.data_ptr(), E,
                                                      1 if round_bf16 else 0, coef, dl.data_ptr(), d_score.data_ptr(),
+                                                     _lib.ptr(part), 0 if part is None else part.shape[0], _lib.ptr(d_load),
                                                      _lib.stream_ptr(dev)))
-        return d_score, None, None, None, None, None
+            # load[e] is the sum of the per-block rows: every row receives d loss / d load
+            d_part = None if part is None else d_load.unsqueeze(0).expand_as(part).contiguous()
+        return d_score, None, None, None, None, None, d_part
 
 
 def needs_grad(*tensors) -> bool:

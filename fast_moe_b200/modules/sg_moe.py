@@ -140,18 +140,25 @@ class SGMoELayer(nn.Module):
     def _forward_with_grad(self, x, group_norm, num_groups, linear_dim, norm_weight, norm_bias, norm_eps) -> MRNOutput:
         """The same layer as a chain of differentiable operators: token norm, router, the two
         expert products with SiLU between them and the gate-weighted combine, the dense map of the
-        un-normalised tokens, and the loss. Noisy gating has no backward."""
-        from ..kernels.autograd import SGLossFn, SGRouterFn, TokenNormFn
+        un-normalised tokens, and the loss (with noisy gating: noise on the logits and the smooth load,
+        both differentiated with respect to the two gate matrices)."""
+        from ..kernels.autograd import SGLossFn, SGNoisyRouterFn, SGRouterFn, TokenNormFn
 
         dev = _lib.require_cuda(x)
-        if self.training and self.enable_noisy_gating:
-            raise NotImplementedError("noisy gating has no backward pass; train with enable_noisy_gating=False or "
-                                      "leave autograd off")
         assert x.ndim == 2 and x.shape[1] == self.input_size
         L, k, E, dt = x.shape[0], self.k, self.num_experts, x.dtype
         cast = lambda p: p if p.dtype == dt else p.to(dt)
         x_norm = TokenNormFn.apply(x, norm_weight, norm_bias, norm_eps, bool(group_norm), num_groups)
-        idx, score = SGRouterFn.apply(x_norm, self._w_gate, k)
+        smooth_load = None
+        if self.training and self.enable_noisy_gating:
+            noise, self._noise = self._noise, None
+            if noise is None:
+                noise = torch.randn((L, E), dtype=torch.float32, device=dev)
+            idx, score, smooth_load = SGNoisyRouterFn.apply(x_norm, self._w_gate, self._w_noise, k, noise.to(dev))
+            if smooth_load.shape[0] == 0:
+                smooth_load = None
+        else:
+            idx, score = SGRouterFn.apply(x_norm, self._w_gate, k)
         meta = route_metadata(idx, E)
         hidden = ops.index_select_jagged_bmm(0, meta.offsets, meta.gate_index.view(-1, k), x_norm,
                                              cast(self._experts_hidden_w).permute(0, 2, 1), cast(self._experts_hidden_bias))
@@ -162,7 +169,8 @@ class SGMoELayer(nn.Module):
         shared = ops.index_select_jagged_bmm(0, off1, ar2, x, cast(self._output_weight).unsqueeze(0), None)
         y = moe + shared
         if self.training:
-            loss, load = SGLossFn.apply(score, meta.offsets, meta.gate_index, E, dt == torch.bfloat16, self.loss_coef)
+            loss, load = SGLossFn.apply(score, meta.offsets, meta.gate_index, E, dt == torch.bfloat16, self.loss_coef,
+                                        smooth_load)
         else:
             loss, load = sg_load_loss(meta, score.detach(), E, dt, self.loss_coef, False)
         return MRNOutput(y, loss, load)

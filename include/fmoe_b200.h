@@ -150,7 +150,19 @@ int fmoe_token_norm_backward(const void* x, const void* d_out, int dtype, int64_
 int fmoe_sg_router_backward(const float* logits, const int64_t* topk_idx, const float* d_score, int64_t L, int E, int k,
                             float* d_logits, void* stream);
 int fmoe_sg_loss_backward(const int64_t* offsets, const int64_t* gate_index, const float* topk_score, int E,
-                          int round_bf16, float loss_coef, const float* d_loss, float* d_score, void* stream);
+                          int round_bf16, float loss_coef, const float* d_loss, float* d_score,
+                          const float* load_partials, int n_partials, float* d_load, void* stream);
+/* Noisy gating (training): fmoe_sg_loss_backward also returns d loss / d load [E] when the loss was
+ * built on the smooth load (load_partials as fmoe_sg_noisy_load wrote them; NULL otherwise), and
+ * fmoe_sg_noisy_router_backward turns the gradient of the k scores and that d_load into
+ * d_logits2 [L, 2E] = (d clean | d raw) for the stacked gate product x @ [w_gate | w_noise]
+ * (through the softmax, the L2 normalisation, the thresholds of the load estimate, noise * stddev
+ * and softplus); fmoe_gate_linear_backward on the stacked weight finishes the job. d_load NULL:
+ * the load takes no part (k == E). */
+int fmoe_sg_noisy_router_backward(const float* logits2, int64_t ld_logits, const float* noise, const float* noisy,
+                                  const float* stddev, const int64_t* topk_idx, const float* d_score,
+                                  const float* d_load, int64_t L, int E, int k, float* d_logits2, int64_t ld_d,
+                                  void* stream);
 
 /* Smooth load of the noisy router (OrigSGMoEImpl._prob_in_top_k, kernels/pytorch/mrn.py:191-219):
  * per token and expert Phi((clean - threshold) / stddev), the threshold being the (k+1)-th largest

@@ -401,6 +401,9 @@ def layer_grad_cases(ref):
         save(f"lgrad_{ci}", rec)
 
 
+NOISY_SEED = 31      # chosen like the others: no near tie of the k-th / (k+1)-th noisy gate in fp32 or bf16
+
+
 def mrn_grad_cases(ref):
     """Gradients of the sparsely-gated layer: OrigSGMoEImpl (kernels/pytorch/mrn.py) in training
     mode on CPU in fp32, backward of sum(y * dout) + loss - what kernels/tests/mrn_test.py:816-860
@@ -413,28 +416,38 @@ def mrn_grad_cases(ref):
         # (L, d, m, o, E, k, group_norm, groups, seed)
         # seeds chosen so that no token's k-th and (k+1)-th gate probabilities come closer than
         # 5e-4, with the tokens in fp32 and rounded to bf16 alike: both dtypes route identically
-        (96, 64, 64, 64, 8, 2, False, 1, 23),
-        (70, 32, 48, 24, 4, 1, False, 1, 22),
-        (64, 32, 40, 32, 8, 3, True, 2, 22),
+        (96, 64, 64, 64, 8, 2, False, 1, 23, False),
+        (70, 32, 48, 24, 4, 1, False, 1, 22, False),
+        (64, 32, 40, 32, 8, 3, True, 2, 22, False),
+        # noisy gating: the noise the reference draws is recorded; the loss then holds the smooth load
+        (80, 32, 32, 32, 8, 2, False, 1, NOISY_SEED, True),
     ]
-    for ci, (L, d, m, o, E, k, gn, groups, seed) in enumerate(cases):
+    for ci, (L, d, m, o, E, k, gn, groups, seed, noisy) in enumerate(cases):
         torch.manual_seed(seed)
-        cfg = mrn.SGConfig(model_d=m, num_experts=E, num_activated_experts=k, loss_coef=0.5)
+        cfg = mrn.SGConfig(model_d=m, num_experts=E, num_activated_experts=k, loss_coef=0.5, enable_noisy_gating=noisy)
         layer = mrn.OrigSGMoEImpl(d, o, cfg)
         with torch.no_grad():
             layer._experts_hidden_bias.normal_(0, 0.1)
             layer._experts_bias.normal_(0, 0.1)
+            if noisy:
+                layer._w_gate.normal_(0, 0.3)
+                layer._w_noise.normal_(0, 0.3)
         layer.train(True)
         x = torch.randn(L, d, requires_grad=True)
         ns = groups if gn else d
         nw = (torch.randn(ns) * 0.2 + 1).requires_grad_()
         nb = (torch.randn(ns) * 0.1).requires_grad_()
+        torch.manual_seed(200 + seed)
+        noise = torch.randn(L, E) if noisy else None
+        torch.manual_seed(200 + seed)          # the layer's randn_like draws the recorded noise
         out = layer(x, None, 0, gn, groups, d // groups, nw, nb, 1e-5)
         dout = torch.randn_like(out.x) * 0.01
         ((out.x * dout).sum() + out.loss).backward()
         rec = dict(k=k, group_norm=int(gn), num_groups=groups, loss_coef=cfg.loss_coef, norm_eps=1e-5, x=x.detach(),
                    norm_weight=nw.detach(), norm_bias=nb.detach(), y=out.x.detach(), loss=out.loss.detach().reshape(-1),
                    dout=dout, d_x=x.grad, d_norm_weight=nw.grad, d_norm_bias=nb.grad)
+        if noisy:
+            rec["noise"] = noise
         for n, p_ in layer.named_parameters():
             rec["p::" + n] = p_.detach()
             rec["g::" + n] = p_.grad
