@@ -188,7 +188,7 @@ def moe_layer_mlp(x, gate_w, gate_b, w_hidden, b_hidden, w_out, b_out, k: int) -
 
 def moe_layer_swiglu(x, gate_w, gate_b, w_gate, w_up, w_down, k: int, b_gate=None, b_up=None,
                      b_down=None) -> torch.Tensor:
-    """The SwiGLU composition BASELINE's configs describe: FastMoELayer routing, then
+    """The SwiGLU layer the benchmark configurations describe: FastMoELayer routing, then
     index_select_jagged_bmm_swiglu and silu_jagged_bmm_combine(has_silu=False).
     Weights are logical [E, K, N]: w_gate / w_up [E, d, h], w_down [E, h, o]."""
     shape = x.shape
