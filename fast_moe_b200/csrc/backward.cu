@@ -104,24 +104,31 @@ jagged_transpose_pad_kernel(const T* __restrict__ in, long long ld_in, long long
 
 // 64 x 64 tiles of 2-byte elements with 16-byte global accesses on both sides (the 32 x 32
 // tiles above move 64-byte row pieces). Shared tile: 64 rows of 33 words; the load phase stores
-// four words per 16-byte vector, the store phase gathers eight elements of one tile column.
+// four words per 16-byte vector, the store phase reads eight words of one column pair.
 constexpr int kT16Pitch = 66;    // elements per tile row (33 words: conflict-free word stores)
 
 __device__ __forceinline__ void tile16_put(__nv_bfloat16 (*tile)[kT16Pitch], int r, int v, uint4 x) {
   uint32_t* w = reinterpret_cast<uint32_t*>(&tile[r][8 * v]);
   w[0] = x.x; w[1] = x.y; w[2] = x.z; w[3] = x.w;
 }
-__device__ __forceinline__ uint4 tile16_column(__nv_bfloat16 (*tile)[kT16Pitch], int r0, int c) {
-  const unsigned short* t = reinterpret_cast<const unsigned short*>(&tile[0][0]);
-  unsigned short h[8];
+// Store phase: thread (warp w, lane l) takes the column pair cp = (w / 2) * 8 + l / 4 and the 8 tile
+// rows 8 v .. 8 v + 7 with v = (w % 2) * 4 + l % 4. It reads 8 words (two neighbouring columns of
+// one row each; the 32 lanes of a warp hit 32 different banks) and splits them into the two output
+// vectors: column 2 cp from the low halves, column 2 cp + 1 from the high halves.
+__device__ __forceinline__ void tile16_column_pair(__nv_bfloat16 (*tile)[kT16Pitch], int r0, int cp, uint4& lo, uint4& hi) {
+  const uint32_t* t = reinterpret_cast<const uint32_t*>(&tile[0][0]);
+  uint32_t w[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) h[i] = t[(r0 + i) * kT16Pitch + c];
-  uint4 o;
-  o.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
-  o.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
-  o.z = h[4] | (static_cast<uint32_t>(h[5]) << 16);
-  o.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
-  return o;
+  for (int i = 0; i < 8; ++i) w[i] = t[(r0 + i) * (kT16Pitch / 2) + cp];
+  lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+  lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+  lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+  lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+}
+__device__ __forceinline__ void tile16_store_map(int& cp, int& v) {
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  cp = (w >> 1) * 8 + (l >> 2);
+  v = (w & 1) * 4 + (l & 3);
 }
 
 // jagged_transpose_pad_kernel for bf16 with cols a multiple of 8 and 16-byte aligned rows on both
@@ -163,11 +170,14 @@ jagged_transpose_pad_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long
     tile16_put(tile, jr, v, x);
   }
   __syncthreads();
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int cr = rr + 32 * i;
-    if (c0 + cr < cols)
-      *reinterpret_cast<uint4*>(out + static_cast<long long>(c0 + cr) * ld_out + q0 + 8 * v) = tile16_column(tile, 8 * v, cr);
+  int cp, sv;
+  tile16_store_map(cp, sv);
+  uint4 even, odd;
+  tile16_column_pair(tile, 8 * sv, cp, even, odd);
+  const int cr = c0 + 2 * cp;                 // cols is a multiple of 8: the pair is inside or outside together
+  if (cr < cols) {
+    *reinterpret_cast<uint4*>(out + static_cast<long long>(cr) * ld_out + q0 + 8 * sv) = even;
+    *reinterpret_cast<uint4*>(out + static_cast<long long>(cr + 1) * ld_out + q0 + 8 * sv) = odd;
   }
 }
 
@@ -188,11 +198,14 @@ batched_transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long in
     tile16_put(tile, rr + 32 * i, v, x);
   }
   __syncthreads();
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int c = c0 + rr + 32 * i;
-    if (c < cols && r0 + 8 * v < rows)
-      *reinterpret_cast<uint4*>(dst + static_cast<long long>(c) * ld_out + r0 + 8 * v) = tile16_column(tile, 8 * v, rr + 32 * i);
+  int cp, sv;
+  tile16_store_map(cp, sv);
+  uint4 lo, hi;
+  tile16_column_pair(tile, 8 * sv, cp, lo, hi);
+  const int c = c0 + 2 * cp;
+  if (c < cols && r0 + 8 * sv < rows) {
+    *reinterpret_cast<uint4*>(dst + static_cast<long long>(c) * ld_out + r0 + 8 * sv) = lo;
+    *reinterpret_cast<uint4*>(dst + static_cast<long long>(c + 1) * ld_out + r0 + 8 * sv) = hi;
   }
 }
 
