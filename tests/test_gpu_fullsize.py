@@ -111,7 +111,7 @@ def test_c4_true_size_zipf_routing_with_empty_experts():
     assert lengths[lengths > 0].min().item() < 0.01 * L * k, "expected a long tail of lightly loaded experts"
     y = layer(x.to(DEV), k)
     assert _lib.device_status(torch.device(DEV)) == 0
-    par = B.parity_block(layer, c, x, y, B.layer_expert_weights(layer), layer.gate.gate, n_sample=64, max_experts=24)
+    par = B.parity_block(layer, c, x, y, B.layer_expert_weights(layer), layer.gate.gate, n_sample=256, max_experts=24)
     _assert_parity(par)
     # the lightly loaded experts too: tokens routed to the least loaded non-empty experts
     load = lengths.cpu()
@@ -163,7 +163,7 @@ def test_c3_true_size_fp8_layer_with_outlier_rows():
     y = layer(x.to(DEV), k)
     assert y.dtype == torch.bfloat16
     assert _lib.device_status(torch.device(DEV)) == 0
-    par = B.parity_block(layer, c, x, y, B.layer_expert_weights(layer), layer.gate.gate, n_sample=96, max_experts=3)
+    par = B.parity_block(layer, c, x, y, B.layer_expert_weights(layer), layer.gate.gate, n_sample=256, max_experts=3)
     # the outlier rows carry logits 50 times larger than the rest, and an fp32 sum of 4096 products
     # taken in another order differs by about 1e-6 of the logit's size: the scores of those rows
     # agree to 1e-4 rather than 1e-5 (the expert choice itself is compared exactly)
@@ -188,7 +188,7 @@ def test_c5_dims_on_one_gpu_all_experts_local():
     y = layer(x.to(dev), c["k"])
     assert _lib.device_status(dev) == 0
     par = B.parity_block(layer, c, x, y, lambda e: tuple(t.cpu() for t in layer.materialize_expert(e)), layer.gate,
-                         n_sample=64, max_experts=8)
+                         n_sample=256, max_experts=8)
     _assert_parity(par)
     del layer
     torch.cuda.empty_cache()
