@@ -37,6 +37,8 @@
 
 #include <atomic>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -403,77 +405,108 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (warp == 0) {
     // =========================================================== TMA producer (one thread)
+    // Two versions of the loop, chosen once: the common one (K-contiguous weights, one weight per
+    // reduction) carries none of the other modes' address arithmetic.
     if (lane == 0) {
-      TileWalker walk(pm, p.n_tiles, p.E);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = unit; t < total_tiles && ok; t += num_units) {
-        int e, mb, nb;
-        walk.decode(t, e, mb, nb);
-        // reduction-over-rows mode: A rows are the expert's output rows (the same for every
-        // expert), the K range is the expert's, and B is a single matrix
-        const int row0 = (kseg_mode ? 0 : soff[e]) + mb * kTileRows + static_cast<int>(rank) * kBM;
-        const int n0 = nb * kTileN;
-        const int k_begin = kseg_mode ? skb[e] : 0;
-        const int nkb = kseg_mode ? (skb[e + 1] - skb[e]) / kKElems : num_kb;
-        if (kseg_mode) e = 0;
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                                      FMOE_DEV_WAIT_PRODUCER)) {
-            ok = false;
-            break;
-          }
-          const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
-          const uint32_t b_dst = a_dst + kABytes;
-          const int k0 = k_begin + kb * kKElems;
-          // two weights along the reduction (plain tiles only): the second one takes over at b_ksplit
-          const bool second = !DUAL && p.b_ksplit > 0 && k0 >= p.b_ksplit;
-          const CUtensorMap* tb = second ? &tmB1 : &tmB0;
-          const int kw = second ? k0 - p.b_ksplit : k0;
-          if constexpr (!kPair) {
-            const uint32_t bar = full_bar(stage);
-            ptx::mbar_arrive_expect_tx(bar, kStageTx);
-            if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
-            if (p.b_mn) {
-              // N contiguous in memory: box = 64 columns x one K step x (atoms of 64 columns)
-              ptx::tma_load_4d(b_dst, tb, bar, 0, kw, n0 >> 6, e);
-              if constexpr (DUAL) ptx::tma_load_4d(b_dst + kTileN * kRowBytes, &tmB1, bar, 0, k0, n0 >> 6, e);
-            } else {
-              ptx::tma_load_3d(b_dst, tb, bar, kw, n0, e);
-              if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+      auto produce = [&](auto alt_tag) {
+        constexpr bool ALT = decltype(alt_tag)::value;    // N-contiguous weights and / or a second weight along K
+        TileWalker walk(pm, p.n_tiles, p.E);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = unit; t < total_tiles && ok; t += num_units) {
+          int e, mb, nb;
+          walk.decode(t, e, mb, nb);
+          // reduction-over-rows mode: A rows are the expert's output rows (the same for every
+          // expert), the K range is the expert's, and B is a single matrix
+          const int row0 = (kseg_mode ? 0 : soff[e]) + mb * kTileRows + static_cast<int>(rank) * kBM;
+          const int n0 = nb * kTileN;
+          const int k_begin = kseg_mode ? skb[e] : 0;
+          const int nkb = kseg_mode ? (skb[e + 1] - skb[e]) / kKElems : num_kb;
+          if (kseg_mode) e = 0;
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                        FMOE_DEV_WAIT_PRODUCER)) {
+              ok = false;
+              break;
             }
-          } else {
-            // Both CTAs report their bytes to the leader's barrier; only the leader arms it.
-            const uint32_t bar = ptx::mapa(full_bar(stage), 0);
-            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), kStageTx);
-            if constexpr (!GATHER) ptx::tma_load_2d_pair(a_dst, &tmA, bar, k0, row0);
-            if constexpr (DUAL) {
-              // leader stages the gate weights, its peer the up weights: 128 rows each
-              if (p.b_mn) {
-                ptx::tma_load_4d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, 0, k0, n0 >> 6, e);
+            const uint32_t a_dst = tiles_addr + stage * Plan::kStageBytes;
+            const uint32_t b_dst = a_dst + kABytes;
+            const int k0 = k_begin + kb * kKElems;
+            if constexpr (!ALT) {
+              if constexpr (!kPair) {
+                const uint32_t bar = full_bar(stage);
+                ptx::mbar_arrive_expect_tx(bar, kStageTx);
+                if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
+                ptx::tma_load_3d(b_dst, &tmB0, bar, k0, n0, e);
+                if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
               } else {
-                ptx::tma_load_3d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, k0, n0, e);
+                // Both CTAs report their bytes to the leader's barrier; only the leader arms it.
+                const uint32_t bar = ptx::mapa(full_bar(stage), 0);
+                if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), kStageTx);
+                if constexpr (!GATHER) ptx::tma_load_2d_pair(a_dst, &tmA, bar, k0, row0);
+                if constexpr (DUAL) {
+                  // leader stages the gate weights, its peer the up weights: 128 rows each
+                  ptx::tma_load_3d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, k0, n0, e);
+                } else {
+                  ptx::tma_load_3d_pair(b_dst, &tmB0, bar, k0, n0 + static_cast<int>(rank) * (kMmaN / 2), e);
+                }
               }
             } else {
-              const int nh = n0 + static_cast<int>(rank) * (kMmaN / 2);
-              if (p.b_mn) {
-                ptx::tma_load_4d_pair(b_dst, tb, bar, 0, kw, nh >> 6, e);
+              // two weights along the reduction (plain tiles only): the second one takes over at b_ksplit
+              const bool second = !DUAL && p.b_ksplit > 0 && k0 >= p.b_ksplit;
+              const CUtensorMap* tb = second ? &tmB1 : &tmB0;
+              const int kw = second ? k0 - p.b_ksplit : k0;
+              if constexpr (!kPair) {
+                const uint32_t bar = full_bar(stage);
+                ptx::mbar_arrive_expect_tx(bar, kStageTx);
+                if constexpr (!GATHER) ptx::tma_load_2d(a_dst, &tmA, bar, k0, row0);
+                if (p.b_mn) {
+                  // N contiguous in memory: box = 64 columns x one K step x (atoms of 64 columns)
+                  ptx::tma_load_4d(b_dst, tb, bar, 0, kw, n0 >> 6, e);
+                  if constexpr (DUAL) ptx::tma_load_4d(b_dst + kTileN * kRowBytes, &tmB1, bar, 0, k0, n0 >> 6, e);
+                } else {
+                  ptx::tma_load_3d(b_dst, tb, bar, kw, n0, e);
+                  if constexpr (DUAL) ptx::tma_load_3d(b_dst + kTileN * kRowBytes, &tmB1, bar, k0, n0, e);
+                }
               } else {
-                ptx::tma_load_3d_pair(b_dst, tb, bar, kw, nh, e);
+                const uint32_t bar = ptx::mapa(full_bar(stage), 0);
+                if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), kStageTx);
+                if constexpr (!GATHER) ptx::tma_load_2d_pair(a_dst, &tmA, bar, k0, row0);
+                if constexpr (DUAL) {
+                  if (p.b_mn) {
+                    ptx::tma_load_4d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, 0, k0, n0 >> 6, e);
+                  } else {
+                    ptx::tma_load_3d_pair(b_dst, rank == 0 ? &tmB0 : &tmB1, bar, k0, n0, e);
+                  }
+                } else {
+                  const int nh = n0 + static_cast<int>(rank) * (kMmaN / 2);
+                  if (p.b_mn) {
+                    ptx::tma_load_4d_pair(b_dst, tb, bar, 0, kw, nh >> 6, e);
+                  } else {
+                    ptx::tma_load_3d_pair(b_dst, tb, bar, kw, nh, e);
+                  }
+                }
               }
             }
-          }
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
+      };
+      if (p.b_mn != 0 || p.b_ksplit > 0) {
+        produce(std::true_type{});
+      } else {
+        produce(std::false_type{});
       }
     }
   } else if (warp == 1) {
     // =========================================================== MMA issuer (one thread, leader CTA)
     if (lane == 0 && rank == 0) {
+     auto issue = [&](auto bmn_tag) {
+      constexpr bool BMN = decltype(bmn_tag)::value;     // B tiles are MN-major
       TileWalker walk(pm, p.n_tiles, p.E);
       int stage = 0;
       uint32_t phase = 0;
@@ -502,7 +535,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::tc_fence_after();
           const uint32_t a_src = tiles_addr + stage * Plan::kStageBytes;
           const uint64_t da = ptx::umma_desc_k_sw128(a_src);
-          if (!p.b_mn) {
+          if constexpr (!BMN) {
             const uint64_t db = ptx::umma_desc_k_sw128(a_src + kABytes);
 #pragma unroll
             for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
@@ -527,6 +560,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       }
+     };
+     if (p.b_mn != 0) {
+       issue(std::true_type{});
+     } else {
+       issue(std::false_type{});
+     }
     }
   } else if (warp < 2 + kEpilogueWarps) {
     // =========================================================== epilogue (8 warps)
@@ -598,8 +637,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool st_ok[4];
       const OutT* mul_row[4] = {nullptr, nullptr, nullptr, nullptr};
       // the multiplier of a gated product goes in with the coalesced store phase (not with a combine)
-      // (the in-kernel-gather variants run at their register cap and keep the multiplier in the math phase)
-      const bool mul_staged = !GATHER && p.mul_in != nullptr && !combine && p.mul_vec != 0;
+      // (plain tiles only; the in-kernel-gather variants run at their register cap and keep the
+      //  multiplier in the math phase)
+      constexpr bool kMulStaged = !GATHER && !DUAL;
+      const bool mul_staged = kMulStaged && p.mul_in != nullptr && !combine && p.mul_vec != 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int src_lane = (lane >> 2) + 8 * i;
@@ -607,7 +648,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(out_row), src_lane);
         st_row[i] = reinterpret_cast<OutT*>(ptr_bits);
         st_ok[i] = __shfl_sync(0xffffffffu, store_ok ? 1 : 0, src_lane) != 0;
-        if constexpr (!GATHER) {
+        if constexpr (kMulStaged) {
           if (mul_staged) {
             const long long mrow = __shfl_sync(0xffffffffu, row, src_lane);
             mul_row[i] = reinterpret_cast<const OutT*>(p.mul_in) + mrow * p.ld_mul;
@@ -618,10 +659,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // Column factors of this tile (bias, FP8 column scales): fetched before the wait for the
       // accumulator, lane i holding column i of every 32-column chunk, so that their latency
       // hides behind the MMAs instead of stalling every chunk.
-      float pre_b0[kChunks], pre_b1[DUAL ? kChunks : 1], pre_f0[fp8 ? kChunks : 1], pre_f1[(fp8 && DUAL) ? kChunks : 1];
-      pre_b1[0] = 0.f; pre_f0[0] = 1.f; pre_f1[0] = 1.f;
+      // (Plain tiles: their epilogue has no slack at small K. The gated tiles keep fetching per chunk:
+      //  they run at the register cap and measured slower with the extra live values.)
+      constexpr bool kPrefetch = !DUAL;
+      float pre_b0[kPrefetch ? kChunks : 1], pre_b1[1], pre_f0[(kPrefetch && fp8) ? kChunks : 1], pre_f1[1];
+      pre_b0[0] = 0.f; pre_b1[0] = 0.f; pre_f0[0] = 1.f; pre_f1[0] = 1.f;
 #pragma unroll
-      for (int j = 0; j < kChunks; ++j) {
+      for (int j = 0; j < (kPrefetch ? kChunks : 0); ++j) {
         pre_b0[j] = 0.f;
         if constexpr (DUAL) pre_b1[j] = 0.f;
         if constexpr (fp8) pre_f0[j] = 1.f;
@@ -699,9 +743,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const bool has_b0 = p.bias0 != nullptr;
             const bool has_b1 = DUAL && p.bias1 != nullptr;
             const float inv_a = 1.0f / scale_a;          // this lane's row
-            // column factors: lane i holds column i's (fetched at the top of the tile)
-            const float f0 = pre_f0[fp8 ? j0 + j : 0], f1 = pre_f1[(fp8 && DUAL) ? j0 + j : 0];
-            const float bb0 = pre_b0[j0 + j], bb1 = pre_b1[DUAL ? j0 + j : 0];
+            // column factors: lane i holds column i's
+            float f0 = 1.f, f1 = 1.f, bb0 = 0.f, bb1 = 0.f;
+            if constexpr (kPrefetch) {                   // fetched at the top of the tile
+              f0 = pre_f0[fp8 ? j0 + j : 0];
+              bb0 = pre_b0[j0 + j];
+            } else {
+              if (scaled) {
+                const long long so = static_cast<long long>(e) * p.bscale_se + col0 + lane;
+                f0 = 1.0f / p.b0_scale[so];
+                if constexpr (DUAL) f1 = 1.0f / p.b1_scale[so];
+              }
+              if (has_b0) bb0 = load_as_float<OutT>(p.bias0, static_cast<long long>(e) * p.bias_se + col0 + lane);
+              if (has_b1) bb1 = load_as_float<OutT>(p.bias1, static_cast<long long>(e) * p.bias_se + col0 + lane);
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float g = __uint_as_float(r0[j][i]);
