@@ -212,3 +212,42 @@ def test_two_weight_product_and_in_place_weights_at_the_small_end():
     empty = moe.jagged_bmm_two_weights(off0, torch.empty((0, 2 * K), dtype=torch.bfloat16, device=DEV), w, w1)
     assert empty is not None and empty.shape == (0, N)
     assert _lib.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.parametrize("L,d,h,o,E,k", [
+    (1, 8, 8, 8, 1, 1),          # one token, one expert, the smallest aligned sizes
+    (17, 64, 96, 32, 4, 4),      # k == E: every expert for every token
+    (255, 72, 200, 40, 3, 2),    # sizes that are multiples of 8 only; ragged tiles everywhere
+    (257, 128, 64, 128, 32, 1),  # top-1 over many experts: most segments a handful of rows
+    (33, 16, 24, 16, 5, 3),
+])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_layers_at_degenerate_shapes_against_oracle(L, d, h, o, E, k, swiglu):
+    """Both layers at the corners of their shape space, bf16, against the CPU oracle on the same
+    inputs (rtol / atol 2e-2; tokens whose k-th / (k+1)-th gate scores nearly tie are counted)."""
+    from oracle import moe_oracle as O
+
+    torch.manual_seed(L * 7 + E)
+    f = lambda p: p.detach().float().cpu()
+    x = torch.randn(1, L, d).bfloat16()
+    if swiglu:
+        layer = fm.SwiGLUFastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(DEV)
+        y = layer(x.to(DEV), k)
+        ref = O.moe_layer_swiglu(x.float(), f(layer.gate.gate.weight), f(layer.gate.gate.bias),
+                                 f(layer.w_gate).permute(0, 2, 1), f(layer.w_up).permute(0, 2, 1),
+                                 f(layer.w_down).permute(0, 2, 1), k)
+    else:
+        layer = fm.FastMoELayer(d, h, o, E, dtype=torch.bfloat16).to(DEV)
+        with torch.no_grad():
+            layer._experts_hidden_bias.normal_(0, 0.1)
+            layer._experts_bias.normal_(0, 0.1)
+        y = layer(x.to(DEV), k)
+        ref = O.moe_layer_mlp(x.float(), f(layer.gate.gate.weight), f(layer.gate.gate.bias),
+                                  f(layer._experts_hidden_w), f(layer._experts_hidden_bias),
+                                  f(layer._experts_w), f(layer._experts_bias), k)
+    assert y.shape == (1, L, o)
+    err = (y.float().cpu() - ref).abs()
+    bad = (err > 2e-2 + 2e-2 * ref.abs()).view(L, o).any(dim=1).float().mean().item()
+    allowed = 0.0 if L < 50 else 0.02       # a near tie may route a token differently in a large batch
+    assert bad <= allowed, f"{bad:.2%} of tokens out of tolerance, max err {err.max():.3e}"
+    assert _lib.device_status(torch.device(DEV)) == 0
