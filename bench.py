@@ -883,6 +883,9 @@ def main():
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        # stdout carries the one JSON line: NCCL's own messages (its version banner, when the
+        # environment sets NCCL_DEBUG) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     from fast_moe_b200 import _lib
