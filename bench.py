@@ -879,13 +879,17 @@ def main():
         return
     peaks = load_peaks()
     dist = None
+    json_fd = None
     if world > 1:
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        # stdout carries the one JSON line: NCCL's own messages (its version banner, when the
-        # environment sets NCCL_DEBUG) go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # stdout carries the one JSON line and nothing else: whatever the libraries write to file
+        # descriptor 1 on the way (the communicator's version banner) goes to stderr, and the line
+        # itself is written to the descriptor saved here
+        sys.stdout.flush()
+        json_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=device)
 
     from fast_moe_b200 import _lib
@@ -1131,7 +1135,12 @@ def main():
             if not args.no_ep_reference:
                 line["c5_ep_1gpu"] = _guarded(lambda: ep_single_gpu_record(device, args, peaks, with_e2e=True,
                                                                            parity=not args.no_parity))
-        print(json.dumps(line), flush=True)
+        if json_fd is None:
+            print(json.dumps(line), flush=True)
+        else:
+            sys.stdout.flush()
+            with os.fdopen(json_fd, "w") as out:
+                out.write(json.dumps(line) + "\n")
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
