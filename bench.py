@@ -291,6 +291,29 @@ def routing_sweep(c, device):
                           hbm_peak_gbs=peak)), flush=True)
 
 
+def layer_sweep(c, device):
+    """The C2 layer (d, h, experts, top-k of configuration c) over a range of batch sizes: graph-replay
+    forward time, tokens/s and layer TFLOP/s per token count. Prints one JSON line."""
+    from fast_moe_b200 import CapturedForward
+
+    layer = build_layer(c, device)
+    rows = []
+    g = torch.Generator().manual_seed(11)
+    for tokens in (256, 1024, 4096, 16384, 65536, 262144):
+        x = torch.randn(1, tokens, c["d"], generator=g).to(torch.bfloat16).to(device)
+        for _ in range(3):
+            layer(x, c["k"])
+        cap = CapturedForward(layer, x, c["k"])
+        for _ in range(3):
+            cap.replay()
+        ms = time_steps(cap.replay, 20, torch.cuda.synchronize)[0] / 20
+        rows.append(dict(tokens=tokens, ms=ms, tokens_per_s=tokens / (ms * 1e-3),
+                         layer_tflops=layer_flops(c, tokens) / (ms * 1e-3) / 1e12))
+        del cap, x
+        torch.cuda.empty_cache()
+    print(json.dumps(dict(layer_sweep=rows, d=c["d"], h=c["h"], E=c["E"], k=c["k"], dtype="bf16")), flush=True)
+
+
 def gemm_alone_ms(layer, x_dev, k, fp8):
     """The two grouped GEMMs alone on this batch's routing, each timed as graph_kernel_ms does:
     (gate/up GEMM + SwiGLU epilogue on the expert-sorted rows, down GEMM + fused combine). The
@@ -855,6 +878,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows through peer-mapped buffers (default) or NCCL all-to-all")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
+    ap.add_argument("--layer-sweep", action="store_true", help="forward time of the layer over a range of batch sizes")
     ap.add_argument("--routing-sweep", action="store_true",
                     help="only time the routing operators and the HBM-bound kernels alone (one JSON line)")
     args = ap.parse_args()
@@ -873,9 +897,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if args.routing_sweep:
+    if args.routing_sweep or args.layer_sweep:
         if rank == 0:
-            routing_sweep(c, device)
+            (routing_sweep if args.routing_sweep else layer_sweep)(c, device)
         return
     peaks = load_peaks()
     dist = None
