@@ -314,6 +314,27 @@ def layer_sweep(c, device):
     print(json.dumps(dict(layer_sweep=rows, d=c["d"], h=c["h"], E=c["E"], k=c["k"], dtype="bf16")), flush=True)
 
 
+def train_step_only(c, device, steps, warmup):
+    """A training step (forward + backward, eager autograd) of the C2 SwiGLU layer and nothing else:
+    the command the launch list of the backward pass is taken from. Prints one JSON line."""
+    layer = build_layer(c, device)
+    layer.autograd = True
+    x = make_inputs(c, 0).to(device).requires_grad_(True)
+
+    def step():
+        for p_ in layer.parameters():
+            p_.grad = None
+        x.grad = None
+        y_ = layer(x, c["k"])
+        y_.backward(torch.ones_like(y_))
+
+    for _ in range(warmup):
+        step()
+    ms = time_steps(step, steps, torch.cuda.synchronize)[0] / steps
+    print(json.dumps(dict(train_step_ms_eager=ms, steps=steps, warmup=warmup, tokens=c["tokens"], d=c["d"], h=c["h"],
+                          E=c["E"], k=c["k"], dtype="bf16")), flush=True)
+
+
 def gemm_alone_ms(layer, x_dev, k, fp8):
     """The two grouped GEMMs alone on this batch's routing, each timed as graph_kernel_ms does:
     (gate/up GEMM + SwiGLU epilogue on the expert-sorted rows, down GEMM + fused combine). The
@@ -878,6 +899,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows through peer-mapped buffers (default) or NCCL all-to-all")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA-graph replay")
+    ap.add_argument("--train-step", action="store_true", help="only a training step of the layer (profiling runs)")
     ap.add_argument("--layer-sweep", action="store_true", help="forward time of the layer over a range of batch sizes")
     ap.add_argument("--routing-sweep", action="store_true",
                     help="only time the routing operators and the HBM-bound kernels alone (one JSON line)")
@@ -897,9 +919,12 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if args.routing_sweep or args.layer_sweep:
+    if args.routing_sweep or args.layer_sweep or args.train_step:
         if rank == 0:
-            (routing_sweep if args.routing_sweep else layer_sweep)(c, device)
+            if args.train_step:
+                train_step_only(c, device, args.steps, args.warmup)
+            else:
+                (routing_sweep if args.routing_sweep else layer_sweep)(c, device)
         return
     peaks = load_peaks()
     dist = None
