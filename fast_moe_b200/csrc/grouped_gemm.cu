@@ -3,7 +3,7 @@
 //
 //   out[r, n] = epilogue( sum_k A[src(r), k] * B[e(r)][k, n] )
 //
-// Replaces, forward only, the reference's per-expert loops
+// Replaces the reference's per-expert loops
 //   pytorch_index_select_jagged_bmm          kernels/pytorch/moe.py:40-84
 //   pytorch_index_select_jagged_bmm_swiglu   kernels/pytorch/moe.py:87-146
 //   pytorch_silu_jagged_bmm                  kernels/pytorch/moe.py:255-275

@@ -1,9 +1,9 @@
 // Kernels of the sparsely-gated ("MRN" / SGMoE) layer that the FastMoELayer path does not have:
 // the token normalisation in front of the router and the experts, the training-time noise on the
 // router logits with its smooth load estimate, and the load / loss summary.
-// They stand in, forward only, for the eager PyTorch of OrigSGMoEImpl
-// (kernels/pytorch/mrn.py:186-189, :191-219, :221-277, :301-333 of the reference). Both are HBM-bound or
-// tiny; the router itself is the gate kernel in its normalised-logit mode (routing.cu) and the
+// They stand in for the eager PyTorch of OrigSGMoEImpl (kernels/pytorch/mrn.py:186-189, :191-219,
+// :221-277, :301-333 of the reference) and, further down, for what autograd makes of it. All are
+// HBM-bound or tiny; the router itself is the gate kernel in its normalised-logit mode (routing.cu) and the
 // experts are the grouped GEMMs.
 #include "common.cuh"
 

@@ -1,5 +1,6 @@
 """Operators of the MoE forward path with the reference's signatures (kernels/moe.py:39-292),
-backed by libfmoe_b200 (hand-written sm_100a kernels). Forward only.
+backed by libfmoe_b200 (hand-written sm_100a kernels). An operator whose inputs require a gradient
+runs as the matching autograd Function of kernels/autograd.py; otherwise nothing is recorded.
 
 ``kernel=`` / ``triton_option=`` are accepted and ignored: there is one implementation here.
 Tensors must live on a CUDA device; outputs are freshly allocated on the same device.

@@ -5,7 +5,8 @@ layer (modules/fast_moe_module.py:45-225): gate Linear + softmax, top-k, fc1 + b
 fc2 + bias per expert, gate-weighted combine. ``SwiGLUFastMoELayer`` is the same routing around
 a SwiGLU expert (index_select_jagged_bmm_swiglu + silu_jagged_bmm_combine(has_silu=False),
 kernels/moe.py:156-189, :236-292), optionally with e4m3 operands and rowwise scales.
-Forward only; tensors must be on a CUDA device.
+Tensors must be on a CUDA device. The default is the fused inference path; ``layer.autograd = True``
+sends the bf16 / fp32 layers through the differentiable operators (kernels/autograd.py).
 """
 from __future__ import annotations
 
