@@ -688,7 +688,8 @@ route_place_scan_kernel(const long long* __restrict__ topk_idx, long long L, int
 
 // Placement for small batches, fused with the two memory passes that follow it in the layers:
 // one block per group of 16 tokens. The per-group counts come from the gate kernel, so the
-// indices are read once. Every block reads the whole table of group counts (at most 32 k entries),
+// indices are read once. Every block reads the whole table of group counts (at most 16 k entries:
+// beyond that the per-block scan costs more than the separate counting sort it replaces),
 // derives its own base and the offsets, places its rows, and then
 //   - copies each of its tokens' rows to the k expert-sorted positions it has just computed
 //     (the index_select of the up projection: x is read once, each row written k times), and
@@ -845,7 +846,7 @@ route_place_gather_kernel(const long long* __restrict__ topk_idx, long long L, i
   }
 }
 
-constexpr long long kGroupTableMaxEntries = 32 * 1024;
+constexpr long long kGroupTableMaxEntries = 16 * 1024;
 
 }  // namespace
 }  // namespace fmoe

@@ -197,7 +197,7 @@ int fmoe_route_metadata(const int64_t* topk_idx, int64_t L, int E, int k, int64_
  * (modules/fast_moe_module.py:93-144) and the index_select of the up projection
  * (kernels/pytorch/moe.py:69-73); results are bit-identical to those entry points.
  *   fmoe_gate_topk_counts_supported: 1 when fmoe_gate_topk_counts can run on these arguments (bf16
- *     tokens with 16-byte aligned rows, E <= 32, d a multiple of 8, ceil(L/32) * 2 * E <= 32768).
+ *     tokens with 16-byte aligned rows, E <= 32, d a multiple of 8, ceil(L/32) * 2 * E <= 16384).
  *   fmoe_gate_topk_counts: fmoe_gate_topk (x given, no precomputed logits) that also writes, for
  *     every group of 16 tokens, the rows per expert: group_counts, fmoe_route_group_counts_bytes(L, E)
  *     bytes. It optionally clears rows 0..L-1 of zero_rows ([L, zero_cols] bf16 / f32, 16-byte
